@@ -1,0 +1,42 @@
+"""ctypes binding of libdifb200.so. There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libdifb200.so")
+
+_lib = None
+
+
+class Difb200Error(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__("difb200 status %d: %s" % (status, text))
+        self.status = status
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "libdifb200.so is not built (%s). Run `python -m diffusion_compiler_b200.build`; "
+                "there is no CPU or PyTorch fallback." % LIB_PATH)
+        L = C.CDLL(LIB_PATH)
+        vp, u64, u32, i32, f32 = C.c_void_p, C.c_uint64, C.c_uint32, C.c_int32, C.c_float
+        L.difb200_last_error.restype = C.c_char_p
+        L.difb200_version.restype = C.c_int
+        L.difb200_poll_status.restype = C.c_int
+        L.difb200_quantize_int8_rows.restype = C.c_int
+        L.difb200_quantize_int8_rows.argtypes = [C.POINTER(vp), C.POINTER(u64), u32, u64, i32, f32, vp,
+                                                 vp, vp, vp, vp, vp]
+        L.difb200_linear_int8_scaled.restype = C.c_int
+        L.difb200_linear_int8_scaled.argtypes = [vp, vp, vp, vp, vp, u32, u64, u64, u64, vp, vp, vp]
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise Difb200Error(status, lib().difb200_last_error().decode(errors="replace"))

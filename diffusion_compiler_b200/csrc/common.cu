@@ -1,0 +1,78 @@
+// Host-side helpers shared by the difb200 entry points: error text, CUDA status mapping,
+// the per-device status words that kernels with bounded waits report through.
+#include "common.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace difb200 {
+
+namespace {
+thread_local std::string g_last_error;
+std::mutex g_mutex;
+std::unordered_map<int, DeviceStatus *> g_status_words;
+std::unordered_map<int, int> g_sm_counts;
+} // namespace
+
+void set_last_error(const std::string &text) { g_last_error = text; }
+const std::string &last_error() { return g_last_error; }
+
+int fail(int status, const std::string &text) {
+  g_last_error = text;
+  return status;
+}
+
+int check_cuda(cudaError_t code, const char *what) {
+  if (code == cudaSuccess)
+    return kOk;
+  std::string text = std::string(what) + ": " + cudaGetErrorName(code) + " (" +
+                     cudaGetErrorString(code) + ")";
+  return fail(code == cudaErrorMemoryAllocation ? kOutOfMemory : kExecutionError, text);
+}
+
+int sm_count() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess)
+    return 148;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = g_sm_counts.find(device);
+  if (it != g_sm_counts.end())
+    return it->second;
+  int count = 148;
+  cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+  g_sm_counts[device] = count;
+  return count;
+}
+
+DeviceStatus *device_status_words() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess)
+    return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = g_status_words.find(device);
+  if (it != g_status_words.end())
+    return it->second;
+  DeviceStatus *words = nullptr;
+  if (cudaMalloc(&words, sizeof(DeviceStatus)) != cudaSuccess)
+    return nullptr;
+  cudaMemset(words, 0, sizeof(DeviceStatus));
+  g_status_words[device] = words;
+  return words;
+}
+
+int poll_device_status(const char *what) {
+  DeviceStatus *words = device_status_words();
+  if (!words)
+    return fail(kInternalError, "device status words are unavailable");
+  DeviceStatus host{};
+  if (int rc = check_cuda(cudaMemcpy(&host, words, sizeof(host), cudaMemcpyDeviceToHost), what))
+    return rc;
+  if (host.flag == 0)
+    return kOk;
+  cudaMemset(words, 0, sizeof(DeviceStatus));
+  return fail(kExecutionError, std::string(what) + ": a bounded device-side wait ran out (kernel " +
+                                   std::to_string(host.kernel) + ", role " + std::to_string(host.role) +
+                                   ", detail " + std::to_string(host.detail) + ")");
+}
+
+} // namespace difb200

@@ -1,0 +1,606 @@
+// QuantizeInt8Rows for sm_100a: orthogonal block rotation fused with per-row absmax INT8
+// quantisation. Semantics follow the reference opcode bit for bit
+// (reference src/runtime/cpu_executor.cpp:124-307; generated GPU kernel
+// src/compiler/compiler.cpp:635-845). bf16 is read once from HBM, codes and scales are
+// written once; the rotation runs in registers with one shared-memory transpose per
+// 256-wide group.
+//
+// ConvRot kernel layout. A 256-wide group is the Kronecker product H4 (x) H4 (x) H4 (x) H4,
+// applied as four radix-4 stages with strides 1, 4, 16, 64 in exactly the reference's fp32
+// association order ((x0+x1)+x2)-x3 etc. The reference multiplies every stage by 0.5; a
+// multiplication by a power of two commutes with fp32 rounding, so the kernel skips it and
+// carries values scaled by 16 (64 for the six-stage 4096-wide variants), folding the factor into the
+// divisor. Results are bit-identical unless an intermediate leaves the normal fp32 range.
+//
+// Each thread owns 16 consecutive elements of two neighbouring groups and keeps them as 16
+// packed fp32x2 registers (lane 0 of the pair = first group, lane 1 = second group), so every
+// butterfly is one packed add/sub for two groups. Stages 0-1 run on the thread's own 16
+// elements; a 16x16 transpose through shared memory (XOR-swizzled, conflict-free) gives the
+// thread the 16 elements of stride 16, on which stages 2-3 run. The 4096-wide variants add a
+// second, CTA-wide transpose across 16 groups for stages 4-5.
+#include "common.cuh"
+
+#include <cstdio>
+
+namespace difb200 {
+namespace {
+
+constexpr int kMaxParts = 8;
+
+struct QuantParams {
+  const uint16_t *part[kMaxParts];
+  uint32_t width[kMaxParts];
+  uint32_t part_count;
+  uint32_t columns;
+  uint64_t rows;
+  float clip;
+  const float *clip_device;
+  int8_t *codes;
+  float *scales;
+  int8_t *rcodes;
+  float *rscales;
+};
+
+// Fixed Rademacher diagonal of the signed variants (reference cpu_executor.cpp:183-189).
+__device__ __forceinline__ uint32_t sign_bit(uint32_t column) {
+  uint32_t hash = column + 0x9e3779b9u;
+  hash = (hash ^ (hash >> 16)) * 0x7feb352du;
+  hash = (hash ^ (hash >> 15)) * 0x846ca68bu;
+  hash ^= hash >> 16;
+  return hash & 1u;
+}
+
+// One radix-4 butterfly on packed pairs, without the reference's exact factor 0.5.
+__device__ __forceinline__ void bfly(uint64_t &x0, uint64_t &x1, uint64_t &x2, uint64_t &x3) {
+  const uint64_t s = add2(x0, x1);
+  const uint64_t t = sub2(x0, x1);
+  const uint64_t n = sub2(x1, x0);
+  const uint64_t y0 = sub2(add2(s, x2), x3);
+  const uint64_t y1 = add2(sub2(s, x2), x3);
+  const uint64_t y2 = add2(add2(t, x2), x3);
+  const uint64_t y3 = add2(add2(n, x2), x3);
+  x0 = y0;
+  x1 = y1;
+  x2 = y2;
+  x3 = y3;
+}
+
+__device__ __forceinline__ float absmax2(float m, uint64_t v) {
+  float lo, hi;
+  unpack2(v, lo, hi);
+  return fmaxf(fmaxf(m, fabsf(lo)), fabsf(hi));
+}
+
+// Loads 16 consecutive bf16 of the logical (concatenated) row starting at `column`.
+// Part widths are multiples of 16 on this path, so a run never straddles two parts.
+__device__ __forceinline__ void load16(const QuantParams &p, uint64_t row, uint32_t column,
+                                       uint4 &a, uint4 &b) {
+  uint32_t c = column;
+  const uint16_t *src = nullptr;
+#pragma unroll
+  for (int i = 0; i < kMaxParts; ++i) {
+    if (i < (int)p.part_count && src == nullptr) {
+      if (c < p.width[i])
+        src = p.part[i] + row * p.width[i] + c;
+      else
+        c -= p.width[i];
+    }
+  }
+  const uint4 *v = reinterpret_cast<const uint4 *>(src);
+  a = __ldg(v);
+  b = __ldg(v + 1);
+}
+
+// Correctly rounded fp32 quotient a/b from y = RN(1/b): two Markstein refinements.
+__device__ __forceinline__ uint64_t div2_exact(uint64_t a, uint64_t y, uint64_t negb) {
+  uint64_t q = mul2(a, y);
+  uint64_t r = fma2(negb, q, a);
+  q = fma2(r, y, q);
+  r = fma2(negb, q, a);
+  return fma2(r, y, q);
+}
+// a and b are bf16 values (8 significant bits): no quotient of two such numbers lies within
+// 2^-17 (relative) of a bf16 rounding boundary unless it is an exact tie, and one refinement
+// reproduces an exactly representable quotient, so this is enough for bf16(a/b).
+__device__ __forceinline__ uint64_t div2_bf16(uint64_t a, uint64_t y, uint64_t negb) {
+  const uint64_t q = mul2(a, y);
+  const uint64_t r = fma2(negb, q, a);
+  return fma2(r, y, q);
+}
+
+__device__ __forceinline__ uint64_t round_bf16_2(uint64_t v) {
+  float lo, hi;
+  unpack2(v, lo, hi);
+  uint32_t packed;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+  return pack2(__uint_as_float(packed << 16), __uint_as_float(packed & 0xffff0000u));
+}
+
+__device__ __forceinline__ int sat_s8(float v) {
+  int r;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return r;
+}
+
+template <bool F32>
+__device__ __forceinline__ void quantize_pair(uint64_t value, uint64_t y, uint64_t negb, int &c0,
+                                              int &c1) {
+  float q0, q1;
+  if (F32) {
+    unpack2(div2_exact(value, y, negb), q0, q1);
+    c0 = max(sat_s8(q0), -127);
+    c1 = max(sat_s8(q1), -127);
+  } else {
+    unpack2(round_bf16_2(div2_bf16(round_bf16_2(value), y, negb)), q0, q1);
+    c0 = sat_s8(q0);
+    c1 = sat_s8(q1);
+  }
+}
+
+// Shared memory per warp: 4 groups x 256 fp32 (two swizzled 16x32-word transposes), reused
+// for the code bytes; plus two words per warp for the row maxima.
+constexpr int kWarpWords = 1024;
+
+template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL>
+__global__ void __launch_bounds__(512, 2)
+convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int rows_per_cta) {
+  extern __shared__ __align__(16) uint32_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = warp / warps_per_row;         // which row of this CTA's batch
+  const int wrow = warp - slot * warps_per_row;  // warp index inside the row
+  const int h = lane >> 4, a = lane & 15;
+  const uint32_t groups = p.columns >> 8;
+  const uint32_t group_a = 4u * wrow + 2u * h;   // first group of this thread's pair
+  const bool act_a = group_a < groups, act_b = group_a + 1u < groups;
+  uint32_t *wsm = smem + warp * kWarpWords;
+  float *red = reinterpret_cast<float *>(smem + (blockDim.x >> 5) * kWarpWords);
+  const int total_warps = blockDim.x >> 5;
+  const float clip = p.clip_device ? __ldg(p.clip_device) : p.clip;
+  // The values carried through the rotation are scaled by 2^stages.
+  constexpr float kCarry = H4096 ? 64.0f : 16.0f;
+
+  // Sign masks of this thread's 32 columns (bit i: element i of group A, bit 16+i: group B).
+  uint32_t signs = 0;
+  if (SIGNED) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      signs |= sign_bit(group_a * 256u + 16u * a + i) << i;
+      signs |= sign_bit((group_a + 1u) * 256u + 16u * a + i) << (16 + i);
+    }
+  }
+
+  uint32_t parity = 0;
+  for (uint64_t row0 = (uint64_t)blockIdx.x * rows_per_cta; row0 < p.rows;
+       row0 += (uint64_t)gridDim.x * rows_per_cta, parity ^= 1u) {
+    const uint64_t row = row0 + slot;
+    const bool row_ok = row < p.rows;
+    uint64_t P[16];
+    {
+      uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, b0 = a0, b1 = a0;
+      if (row_ok && act_a)
+        load16(p, row, group_a * 256u + 16u * a, a0, a1);
+      if (row_ok && act_b)
+        load16(p, row, (group_a + 1u) * 256u + 16u * a, b0, b1);
+      const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint32_t alo = wa[i] << 16, ahi = wa[i] & 0xffff0000u;
+        uint32_t blo = wb[i] << 16, bhi = wb[i] & 0xffff0000u;
+        if (SIGNED) {
+          alo ^= ((signs >> (2 * i)) & 1u) << 31;
+          ahi ^= ((signs >> (2 * i + 1)) & 1u) << 31;
+          blo ^= ((signs >> (16 + 2 * i)) & 1u) << 31;
+          bhi ^= ((signs >> (17 + 2 * i)) & 1u) << 31;
+        }
+        P[2 * i] = pack2(__uint_as_float(alo), __uint_as_float(blo));
+        P[2 * i + 1] = pack2(__uint_as_float(ahi), __uint_as_float(bhi));
+      }
+    }
+    // stage 0 (stride 1) and stage 1 (stride 4)
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      bfly(P[4 * q], P[4 * q + 1], P[4 * q + 2], P[4 * q + 3]);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      bfly(P[q], P[q + 4], P[q + 8], P[q + 12]);
+    // 16x16 transpose of pairs through shared memory. Thread a writes its row of 16 pairs
+    // as 8 chunks of 2 pairs; chunk c goes to position c ^ (a & 7).
+    {
+      uint32_t *half = wsm + h * 512;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 v;
+        float x0, x1, x2, x3;
+        unpack2(P[2 * c], x0, x1);
+        unpack2(P[2 * c + 1], x2, x3);
+        v.x = __float_as_uint(x0);
+        v.y = __float_as_uint(x1);
+        v.z = __float_as_uint(x2);
+        v.w = __float_as_uint(x3);
+        *reinterpret_cast<uint4 *>(half + 32 * a + 4 * (c ^ (a & 7))) = v;
+      }
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(
+            half + 32 * j + 4 * ((a >> 1) ^ (j & 7)) + 2 * (a & 1));
+        P[j] = pack2(__uint_as_float(v.x), __uint_as_float(v.y));
+      }
+      __syncwarp();
+    }
+    // Now P[j] = element 16*j + a of both groups. stage 2 (stride 16), stage 3 (stride 64).
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      bfly(P[4 * q], P[4 * q + 1], P[4 * q + 2], P[4 * q + 3]);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      bfly(P[q], P[q + 4], P[q + 8], P[q + 12]);
+
+    // Column of P[j] lane 0 / lane 1 (used for output addressing).
+    uint32_t col_a = group_a * 256u + a, col_b = col_a + 256u; // + 16*j
+    uint32_t col_step = 16u;
+    bool out_a = act_a, out_b = act_b;
+    if (H4096) {
+      // Second transpose across the 16 groups of every 4096-wide block (one row per CTA).
+      float *rowbuf = reinterpret_cast<float *>(smem);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float x0, x1;
+        unpack2(P[j], x0, x1);
+        if (act_a)
+          rowbuf[col_a + 16u * j] = x0;
+        if (act_b)
+          rowbuf[col_b + 16u * j] = x1;
+      }
+      __syncthreads();
+      // Thread t takes element e of block G for u = t and u = t + columns/32.
+      const uint32_t per = p.columns >> 5;
+      const uint32_t u0 = threadIdx.x, u1 = threadIdx.x + per;
+      col_a = (u0 >> 8) * 4096u + (u0 & 255u);
+      col_b = (u1 >> 8) * 4096u + (u1 & 255u);
+      col_step = 256u;
+      out_a = out_b = threadIdx.x < per;
+#pragma unroll
+      for (int g = 0; g < 16; ++g)
+        P[g] = out_a ? pack2(rowbuf[col_a + 256u * g], rowbuf[col_b + 256u * g]) : pack2(0.f, 0.f);
+      __syncthreads();
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        bfly(P[4 * q], P[4 * q + 1], P[4 * q + 2], P[4 * q + 3]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        bfly(P[q], P[q + 4], P[q + 8], P[q + 12]);
+    }
+
+    // Row maximum: thread -> warp -> row.
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      m = absmax2(m, P[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float *redp = red + parity * 2 * total_warps;
+    if (lane == 0)
+      redp[warp] = m;
+    __syncthreads();
+    m = 0.0f;
+    for (int w = 0; w < warps_per_row; ++w)
+      m = fmaxf(m, redp[slot * warps_per_row + w]);
+
+    const float maximum = m * (1.0f / kCarry);
+    const float scale = fmaxf(__fdiv_rn(__fmul_rn(maximum, clip), 127.0f), 1.0e-30f);
+    const float scale_bf16 = round_bf16(scale);
+    const float stored = (SIGNED && !F32) ? scale_bf16 : scale;
+    const float divisor = (F32 ? scale : scale_bf16) * kCarry;
+    const float recip = __frcp_rn(divisor);
+    const uint64_t y2 = pack2(recip, recip), nb2 = pack2(-divisor, -divisor);
+    if (row_ok && wrow == 0 && lane == 0)
+      p.scales[row] = stored;
+
+    // Code bytes alias the transpose area: one byte per column, with a 64-byte skew per 512
+    // columns that keeps the two half-warps on different banks. For the 256-wide variants
+    // every warp stages the 1024 columns it owns in its own area; the 4096-wide variants
+    // index the whole row (writer and owner of a column are different warps there).
+    int8_t *code_bytes = reinterpret_cast<int8_t *>(smem);
+    const uint32_t code_base = H4096 ? 0u : (uint32_t)warp * kWarpWords * 4u;
+    const uint32_t code_col0 = H4096 ? 0u : (uint32_t)wrow * 1024u;
+#define DIFB200_CODE_ADDR(col) \
+  (code_base + ((col) - code_col0) + ((((col) - code_col0) >> 9) << 6))
+    auto stage_code = [&](int j, int ca, int cb) {
+      if (out_a)
+        code_bytes[DIFB200_CODE_ADDR(col_a + col_step * j)] = (int8_t)ca;
+      if (out_b)
+        code_bytes[DIFB200_CODE_ADDR(col_b + col_step * j)] = (int8_t)cb;
+    };
+    auto flush_codes = [&](int8_t *dst) {
+      if (H4096)
+        __syncthreads();
+      else
+        __syncwarp();
+      // every lane copies 2 x 16 bytes of its warp's 1024 columns
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const uint32_t col = (uint32_t)wrow * 1024u + part * 512u + lane * 16u;
+        if (row_ok && col < p.columns) {
+          const uint4 v = *reinterpret_cast<const uint4 *>(code_bytes + DIFB200_CODE_ADDR(col));
+          *reinterpret_cast<uint4 *>(dst + row * p.columns + col) = v;
+        }
+      }
+      if (H4096)
+        __syncthreads();
+      else
+        __syncwarp();
+    };
+
+    int codes_a[RESIDUAL ? 16 : 1], codes_b[RESIDUAL ? 16 : 1];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int ca, cb;
+      quantize_pair<F32>(P[j], y2, nb2, ca, cb);
+      stage_code(j, ca, cb);
+      if (RESIDUAL) {
+        codes_a[j] = ca;
+        codes_b[j] = cb;
+      }
+    }
+    flush_codes(p.codes);
+
+    if (RESIDUAL) {
+      // Residual pair (reference cpu_executor.cpp:262-305): r = fma(-code, stored, value).
+      float rm = 0.0f;
+      float ra[16], rb[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float x0, x1;
+        unpack2(P[j], x0, x1);
+        x0 *= (1.0f / kCarry);
+        x1 *= (1.0f / kCarry);
+        if (!F32) {
+          x0 = round_bf16(x0);
+          x1 = round_bf16(x1);
+        }
+        ra[j] = __fmaf_rn(-(float)codes_a[j], stored, x0);
+        rb[j] = __fmaf_rn(-(float)codes_b[j], stored, x1);
+        rm = fmaxf(rm, fmaxf(fabsf(ra[j]), fabsf(rb[j])));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, o));
+      if (lane == 0)
+        redp[total_warps + warp] = rm;
+      __syncthreads();
+      rm = 0.0f;
+      for (int w = 0; w < warps_per_row; ++w)
+        rm = fmaxf(rm, redp[total_warps + slot * warps_per_row + w]);
+      const float rscale = fmaxf(__fdiv_rn(rm, 127.0f), 1.0e-30f);
+      const float rscale_bf16 = round_bf16(rscale);
+      if (row_ok && wrow == 0 && lane == 0)
+        p.rscales[row] = (SIGNED && !F32) ? rscale_bf16 : rscale;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (F32) {
+          codes_a[j] = max(sat_s8(__fdiv_rn(ra[j], rscale)), -127);
+          codes_b[j] = max(sat_s8(__fdiv_rn(rb[j], rscale)), -127);
+        } else {
+          codes_a[j] = sat_s8(round_bf16(__fdiv_rn(round_bf16(ra[j]), rscale_bf16)));
+          codes_b[j] = sat_s8(round_bf16(__fdiv_rn(round_bf16(rb[j]), rscale_bf16)));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        stage_code(j, codes_a[j], codes_b[j]);
+      flush_codes(p.rcodes);
+    }
+#undef DIFB200_CODE_ADDR
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Direct variant (no rotation; reference cpu_executor.cpp:232-260): one warp per row, any
+// width. Used for activations of plain W8A8 linears and for the per-token-per-head
+// quantisation of attention Q/K (rows of width 128).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float load_logical(const QuantParams &p, uint64_t row, uint32_t column) {
+  uint32_t c = column;
+  for (uint32_t i = 0; i < p.part_count; ++i) {
+    if (c < p.width[i])
+      return bf16_bits_to_f32(__ldg(p.part[i] + row * p.width[i] + c));
+    c -= p.width[i];
+  }
+  return 0.0f;
+}
+
+template <bool VEC8>
+__global__ void __launch_bounds__(256)
+direct_quant_kernel(const QuantParams p) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp_global = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const uint64_t warp_count = (uint64_t)gridDim.x * (blockDim.x >> 5);
+  const float clip = p.clip_device ? __ldg(p.clip_device) : p.clip;
+  const uint32_t K = p.columns;
+  for (uint64_t row = warp_global; row < p.rows; row += warp_count) {
+    float m = 0.0f;
+    if (VEC8) { // single part, width % 8 == 0, 16-byte aligned rows
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.part[0] + row * K);
+      for (uint32_t c = lane; c < (K >> 3); c += 32) {
+        const uint4 v = __ldg(src + c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          m = fmaxf(m, fabsf(__uint_as_float(w[i] << 16)));
+          m = fmaxf(m, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
+        }
+      }
+    } else {
+      for (uint32_t c = lane; c < K; c += 32)
+        m = fmaxf(m, fabsf(load_logical(p, row, c)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float scale = fmaxf(__fdiv_rn(__fmul_rn(m, clip), 127.0f), 1.0e-30f);
+    if (lane == 0)
+      p.scales[row] = scale;
+    const bool residual = p.rcodes != nullptr;
+    float rm = 0.0f;
+    if (VEC8) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.part[0] + row * K);
+      uint2 *dst = reinterpret_cast<uint2 *>(p.codes + row * K);
+      for (uint32_t c = lane; c < (K >> 3); c += 32) {
+        const uint4 v = __ldg(src + c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t out[2] = {0, 0};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float x0 = __uint_as_float(w[i] << 16), x1 = __uint_as_float(w[i] & 0xffff0000u);
+          const int c0 = max(sat_s8(__fdiv_rn(x0, scale)), -127);
+          const int c1 = max(sat_s8(__fdiv_rn(x1, scale)), -127);
+          out[i >> 1] |= ((uint32_t)(c0 & 0xff) << (16 * (i & 1))) |
+                         ((uint32_t)(c1 & 0xff) << (16 * (i & 1) + 8));
+          if (residual) {
+            rm = fmaxf(rm, fabsf(__fmaf_rn(-(float)c0, scale, x0)));
+            rm = fmaxf(rm, fabsf(__fmaf_rn(-(float)c1, scale, x1)));
+          }
+        }
+        dst[c] = make_uint2(out[0], out[1]);
+      }
+    } else {
+      for (uint32_t c = lane; c < K; c += 32) {
+        const float x = load_logical(p, row, c);
+        const int code = max(sat_s8(__fdiv_rn(x, scale)), -127);
+        p.codes[row * K + c] = (int8_t)code;
+        if (residual)
+          rm = fmaxf(rm, fabsf(__fmaf_rn(-(float)code, scale, x)));
+      }
+    }
+    if (residual) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, o));
+      const float rscale = fmaxf(__fdiv_rn(rm, 127.0f), 1.0e-30f);
+      if (lane == 0)
+        p.rscales[row] = rscale;
+      __syncwarp();
+      for (uint32_t c = lane; c < K; c += 32) {
+        const float x = load_logical(p, row, c);
+        const float r = __fmaf_rn(-(float)p.codes[row * K + c], scale, x);
+        p.rcodes[row * K + c] = (int8_t)max(sat_s8(__fdiv_rn(r, rscale)), -127);
+      }
+    }
+  }
+}
+
+template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL>
+int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
+  const uint32_t groups = p.columns >> 8;
+  const int warps_per_row = (int)((groups + 3u) / 4u);
+  if (warps_per_row > 16)
+    return fail(kUnsupported, "QuantizeInt8Rows: ConvRot width above 16384 is not supported");
+  int rows_per_cta = H4096 ? 1 : (8 / warps_per_row);
+  if (rows_per_cta < 1)
+    rows_per_cta = 1;
+  if ((uint64_t)rows_per_cta > p.rows)
+    rows_per_cta = (int)p.rows;
+  const int warps = warps_per_row * rows_per_cta;
+  const size_t smem = (size_t)warps * kWarpWords * 4 + (size_t)warps * 4 * sizeof(float) + 64;
+  auto kernel = convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL>;
+  if (smem > 48 * 1024) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem),
+                            "cudaFuncSetAttribute(convrot)"))
+      return rc;
+  }
+  const uint64_t batches = (p.rows + rows_per_cta - 1) / rows_per_cta;
+  const int threads = warps * 32;
+  int resident = 1;
+  if (int rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, threads, smem),
+                          "occupancy(convrot)"))
+    return rc;
+  if (resident < 1)
+    resident = 1;
+  uint64_t grid = (uint64_t)sm_count() * resident;
+  if (grid > batches)
+    grid = batches;
+  kernel<<<(unsigned)grid, threads, smem, stream>>>(p, warps_per_row, rows_per_cta);
+  return check_cuda(cudaGetLastError(), "convrot_quant_kernel launch");
+}
+
+template <bool SIGNED, bool F32, bool H4096>
+int launch_convrot(const QuantParams &p, cudaStream_t stream) {
+  return p.rcodes ? launch_convrot_impl<SIGNED, F32, H4096, true>(p, stream)
+                  : launch_convrot_impl<SIGNED, F32, H4096, false>(p, stream);
+}
+
+} // namespace
+
+int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, uint32_t part_count,
+                       uint64_t rows, int implementation, float clip, const float *clip_device,
+                       int8_t *codes, float *scales, int8_t *rcodes, float *rscales,
+                       cudaStream_t stream) {
+  if (part_count == 0 || part_count > kMaxParts)
+    return fail(kUnsupported, "QuantizeInt8Rows: 1..8 concatenated inputs are supported");
+  if (!codes || !scales || (rcodes == nullptr) != (rscales == nullptr))
+    return fail(kInvalidArgument, "QuantizeInt8Rows: missing output pointer");
+  if (!(clip > 0.0f) && !clip_device)
+    return fail(kInvalidArgument, "QuantizeInt8Rows: clip ratio must be positive");
+  QuantParams p{};
+  uint64_t columns = 0;
+  bool aligned16 = true, aligned8 = true;
+  for (uint32_t i = 0; i < part_count; ++i) {
+    if (!parts[i] || part_widths[i] == 0 || part_widths[i] > 0xffffffffull)
+      return fail(kInvalidArgument, "QuantizeInt8Rows: bad input part");
+    p.part[i] = static_cast<const uint16_t *>(parts[i]);
+    p.width[i] = (uint32_t)part_widths[i];
+    columns += part_widths[i];
+    aligned16 = aligned16 && part_widths[i] % 16 == 0 && (reinterpret_cast<uintptr_t>(parts[i]) & 15) == 0;
+    aligned8 = aligned8 && part_widths[i] % 8 == 0 && (reinterpret_cast<uintptr_t>(parts[i]) & 15) == 0;
+  }
+  if (columns > 0xffffffffull)
+    return fail(kUnsupported, "QuantizeInt8Rows: row too wide");
+  p.part_count = part_count;
+  p.columns = (uint32_t)columns;
+  p.rows = rows;
+  p.clip = clip;
+  p.clip_device = clip_device;
+  p.codes = codes;
+  p.scales = scales;
+  p.rcodes = rcodes;
+  p.rscales = rscales;
+  if (rows == 0)
+    return kOk;
+  if (implementation == 1) {
+    const int threads = 256;
+    uint64_t blocks = (rows + 7) / 8;
+    const uint64_t cap = (uint64_t)sm_count() * 16;
+    if (blocks > cap)
+      blocks = cap;
+    const bool vec = part_count == 1 && aligned8 && (reinterpret_cast<uintptr_t>(codes) & 7) == 0;
+    if (vec)
+      direct_quant_kernel<true><<<(unsigned)blocks, threads, 0, stream>>>(p);
+    else
+      direct_quant_kernel<false><<<(unsigned)blocks, threads, 0, stream>>>(p);
+    return check_cuda(cudaGetLastError(), "direct_quant_kernel launch");
+  }
+  if (implementation < 2 || implementation > 7)
+    return fail(kInvalidArgument, "QuantizeInt8Rows: unknown implementation");
+  const bool h4096 = implementation == 4 || implementation == 7;
+  if (columns % (h4096 ? 4096u : 256u) != 0)
+    return fail(kInvalidArgument, "QuantizeInt8Rows: width is not a multiple of the rotation group");
+  if (!aligned16 || (reinterpret_cast<uintptr_t>(codes) & 15) != 0 ||
+      (rcodes && (reinterpret_cast<uintptr_t>(rcodes) & 15) != 0))
+    return fail(kUnsupported,
+                "QuantizeInt8Rows: ConvRot path needs 16-byte aligned pointers and part widths "
+                "that are multiples of 16");
+  switch (implementation) {
+  case 2: return launch_convrot<false, false, false>(p, stream);
+  case 3: return launch_convrot<true, false, false>(p, stream);
+  case 4: return launch_convrot<true, false, true>(p, stream);
+  case 5: return launch_convrot<false, true, false>(p, stream);
+  case 6: return launch_convrot<true, true, false>(p, stream);
+  default: return launch_convrot<true, true, true>(p, stream);
+  }
+}
+
+} // namespace difb200

@@ -1,0 +1,354 @@
+// LinearInt8Scaled for sm_100a: Y[M,N] = bf16((float(X[M,K] . W[N,K]^T) * xs[m]) * ws[n]),
+// optionally followed by the BiasAdd and tanh-Gelu ops that the W8A8 rewrite puts after it.
+// Semantics: reference src/runtime/cpu_executor.cpp:309-335 (multiplication order row scale
+// first, then column scale), BiasAdd :1288-1296, Gelu :93-113; it replaces the reference's
+// Sm80 mma.sync CUTLASS kernel (src/runtime/cutlass_gemm.cu:185-303).
+//
+// Structure: persistent CTAs, one per SM, 128x256 output tiles. Both operands are K-major
+// INT8, brought in by TMA as 128-byte-swizzled [rows x 128 B] boxes into a 4-stage ring.
+// One thread issues tcgen05.mma kind::i8 (M128 N256 K32) into one of two 256-column INT32
+// accumulators in tensor memory, so the epilogue of tile i overlaps the MMAs of tile i+1.
+// Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2..5 = epilogue (each reads the
+// TMEM lane quarter warp_id % 4).
+#include "common.cuh"
+#include "ptx.cuh"
+
+#include <mutex>
+
+namespace difb200 {
+
+int encode_tensor_map(CUtensorMap *out, CUtensorMapDataType type, uint32_t rank, const void *base,
+                      const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box,
+                      CUtensorMapSwizzle swizzle) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                               const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                               const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query) ==
+            cudaSuccess &&
+        query == cudaDriverEntryPointSuccess)
+      encode = reinterpret_cast<EncodeFn>(fn);
+  });
+  if (!encode)
+    return fail(kInternalError, "cuTensorMapEncodeTiled is unavailable in this driver");
+  cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[5];
+  cuuint32_t gbox[5];
+  for (uint32_t i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    if (i + 1 < rank)
+      gstrides[i] = strides_bytes[i];
+  }
+  const CUresult rc = encode(out, type, rank, const_cast<void *>(base), gdims, gstrides, gbox,
+                             elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return fail(kInvalidArgument, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)rc));
+  return kOk;
+}
+
+namespace {
+
+constexpr int kBM = 128, kBN = 256, kBK = 128; // BK in bytes == INT8 elements
+constexpr int kStages = 4;
+constexpr int kUmmaK = 32;
+constexpr uint32_t kABytes = kBM * kBK, kBBytes = kBN * kBK, kStageBytes = kABytes + kBBytes;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + 256;
+
+enum : uint32_t { kEpiBias = 1u, kEpiGeluTanh = 2u };
+
+struct GemmParams {
+  const float *row_scales;
+  const float *col_scales;
+  const uint16_t *bias;
+  uint16_t *out;
+  int32_t *acc_out;
+  uint32_t M, N, K;
+  uint32_t epilogue;
+  DeviceStatus *status;
+};
+
+__device__ __forceinline__ void report_timeout(DeviceStatus *status, uint32_t role, uint32_t detail) {
+  if (atomicExch(&status->flag, 1u) == 0u) {
+    status->kernel = 2u;
+    status->role = role;
+    status->detail = detail;
+  }
+}
+
+__device__ __forceinline__ float gelu_tanh(float v) {
+  // 0.5 * v * (1 + tanh(0.79788456 * (v + 0.044715 * v^3))), evaluated without contraction
+  const float cubic = __fmul_rn(__fmul_rn(v, v), v);
+  const float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(v, __fmul_rn(0.044715f, cubic)));
+  return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(inner)));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t packed;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+  return packed;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + kStages * kStageBytes;
+  // barrier layout (8 bytes each): full[4], empty[4], tmem_full[2], tmem_empty[2]; then a word
+  // for the TMEM base address and a word for the abort flag.
+  const uint32_t full_bar = bar_base, empty_bar = bar_base + 8 * kStages;
+  const uint32_t tfull_bar = bar_base + 16 * kStages, tempty_bar = tfull_bar + 16;
+  const uint32_t tmem_slot = tempty_bar + 16;
+  volatile uint32_t *slot_ptr =
+      reinterpret_cast<volatile uint32_t *>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+  volatile uint32_t *abort_ptr = slot_ptr + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles_m = (p.M + kBM - 1) / kBM, tiles_n = (p.N + kBN - 1) / kBN;
+  const uint32_t num_tiles = tiles_m * tiles_n;
+  const uint32_t k_blocks = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar + 8 * s, 1);
+      ptx::mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(tfull_bar + 8 * b, 1);
+      ptx::mbar_init(tempty_bar + 8 * b, 4);
+    }
+    *abort_ptr = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int32_t m0 = (int32_t)((tile / tiles_n) * kBM), n0 = (int32_t)((tile % tiles_n) * kBN);
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+          if (*abort_ptr || !ptx::mbar_wait(empty_bar + 8 * stage, phase ^ 1u)) {
+            if (!*abort_ptr)
+              report_timeout(p.status, 0, kb);
+            *abort_ptr = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
+          ptx::mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
+          ptx::tma_load_2d(a_dst, &map_a, full_bar + 8 * stage, (int32_t)(kb * kBK), m0);
+          ptx::tma_load_2d(b_dst, &map_b, full_bar + 8 * stage, (int32_t)(kb * kBK), n0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, 0, 0, kBM, kBN);
+      uint32_t stage = 0, phase = 0, local = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
+        if (*abort_ptr || !ptx::mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u)) {
+          if (!*abort_ptr)
+            report_timeout(p.status, 1, 0xffffu);
+          *abort_ptr = 1;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+          if (*abort_ptr || !ptx::mbar_wait(full_bar + 8 * stage, phase)) {
+            if (!*abort_ptr)
+              report_timeout(p.status, 1, kb);
+            *abort_ptr = 1;
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * kStageBytes, b_addr = a_addr + kABytes;
+          const uint64_t a_desc = ptx::smem_desc_sw128(a_addr, 16, 1024);
+          const uint64_t b_desc = ptx::smem_desc_sw128(b_addr, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            ptx::mma_i8_ss(d_tmem, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
+                           idesc, (kb | (uint32_t)k) != 0u ? 1u : 0u);
+          ptx::mma_commit(empty_bar + 8 * stage); // frees the smem stage when these MMAs retire
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok)
+          ptx::mma_commit(tfull_bar + 8 * acc); // accumulator complete
+      }
+    }
+  } else {
+    const uint32_t quarter = (uint32_t)warp & 3u;
+    uint32_t local = 0;
+    const bool vec_ok = (p.N % 8u == 0u) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0u);
+    for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
+      const uint32_t m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * kBN;
+      if (*abort_ptr || !ptx::mbar_wait(tfull_bar + 8 * acc, acc_phase)) {
+        if (!*abort_ptr && lane == 0)
+          report_timeout(p.status, 2, tile);
+        *abort_ptr = 1;
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t row = m0 + quarter * 32u + lane;
+      const bool row_ok = row < p.M;
+      const float rs = row_ok ? __ldg(p.row_scales + row) : 0.0f;
+#pragma unroll 1
+      for (uint32_t chunk = 0; chunk < kBN / 32; ++chunk) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * kBN + chunk * 32u, r);
+        ptx::tmem_ld_wait();
+        const uint32_t n_base = n0 + chunk * 32u;
+        if (n_base >= p.N)
+          continue; // (warp-uniform) whole chunk past the N edge
+        if (p.acc_out && row_ok) {
+          for (int i = 0; i < 32; ++i)
+            if (n_base + i < p.N)
+              p.acc_out[(size_t)row * p.N + n_base + i] = (int32_t)r[i];
+        }
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const uint32_t n = n_base + i;
+          const float c0 = n < p.N ? __ldg(p.col_scales + n) : 0.0f;
+          const float c1 = n + 1 < p.N ? __ldg(p.col_scales + n + 1) : 0.0f;
+          float y0 = __fmul_rn(__fmul_rn((float)(int32_t)r[i], rs), c0);
+          float y1 = __fmul_rn(__fmul_rn((float)(int32_t)r[i + 1], rs), c1);
+          uint32_t pk = pack_bf16x2(y0, y1);
+          if (p.epilogue & kEpiBias) {
+            const float b0 = n < p.N ? bf16_bits_to_f32(__ldg(p.bias + n)) : 0.0f;
+            const float b1 = n + 1 < p.N ? bf16_bits_to_f32(__ldg(p.bias + n + 1)) : 0.0f;
+            y0 = __fadd_rn(__uint_as_float(pk << 16), b0);
+            y1 = __fadd_rn(__uint_as_float(pk & 0xffff0000u), b1);
+            pk = pack_bf16x2(y0, y1);
+          }
+          if (p.epilogue & kEpiGeluTanh) {
+            y0 = gelu_tanh(__uint_as_float(pk << 16));
+            y1 = gelu_tanh(__uint_as_float(pk & 0xffff0000u));
+            pk = pack_bf16x2(y0, y1);
+          }
+          packed[i >> 1] = pk;
+        }
+        if (row_ok) {
+          uint16_t *dst = p.out + (size_t)row * p.N + n_base;
+          if (vec_ok && n_base + 32u <= p.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              reinterpret_cast<uint4 *>(dst)[v] =
+                  make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (n_base + i < p.N)
+                dst[i] = (uint16_t)((packed[i >> 1] >> (16 * (i & 1))) & 0xffffu);
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        ptx::mbar_arrive(tempty_bar + 8 * acc);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+} // namespace
+
+int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales,
+                       const float *col_scales, const void *bias_bf16, uint32_t epilogue, uint64_t M,
+                       uint64_t N, uint64_t K, void *out_bf16, int32_t *acc_out, cudaStream_t stream) {
+  if (!x || !w || !row_scales || !col_scales || !out_bf16)
+    return fail(kInvalidArgument, "LinearInt8Scaled: null pointer");
+  if ((epilogue & kEpiBias) && !bias_bf16)
+    return fail(kInvalidArgument, "LinearInt8Scaled: bias epilogue without a bias pointer");
+  if (epilogue & ~(kEpiBias | kEpiGeluTanh))
+    return fail(kInvalidArgument, "LinearInt8Scaled: unknown epilogue flags");
+  if (M == 0 || N == 0)
+    return kOk;
+  if (K == 0 || K % 16 != 0)
+    return fail(kUnsupported, "LinearInt8Scaled: K must be a positive multiple of 16 (TMA row pitch)");
+  if (M > 0x7fffffffull || N > 0x7fffffffull || K > 0x7fffffffull)
+    return fail(kUnsupported, "LinearInt8Scaled: dimension too large");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return fail(kUnsupported, "LinearInt8Scaled: operands must be 16-byte aligned");
+  DeviceStatus *status = device_status_words();
+  if (!status)
+    return fail(kOutOfMemory, "LinearInt8Scaled: cannot allocate device status words");
+
+  CUtensorMap map_a, map_b;
+  const uint64_t dims_a[2] = {K, M}, dims_b[2] = {K, N};
+  const uint64_t strides[1] = {K};
+  const uint32_t box_a[2] = {(uint32_t)kBK, (uint32_t)kBM}, box_b[2] = {(uint32_t)kBK, (uint32_t)kBN};
+  if (int rc = encode_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, x, dims_a, strides, box_a,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = encode_tensor_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w, dims_b, strides, box_b,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+
+  static std::once_flag once;
+  static cudaError_t attr_rc = cudaSuccess;
+  std::call_once(once, [] {
+    attr_rc = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)kSmemBytes);
+  });
+  if (int rc = check_cuda(attr_rc, "cudaFuncSetAttribute(gemm_i8_kernel)"))
+    return rc;
+
+  GemmParams p{};
+  p.row_scales = row_scales;
+  p.col_scales = col_scales;
+  p.bias = static_cast<const uint16_t *>(bias_bf16);
+  p.out = static_cast<uint16_t *>(out_bf16);
+  p.acc_out = acc_out;
+  p.M = (uint32_t)M;
+  p.N = (uint32_t)N;
+  p.K = (uint32_t)K;
+  p.epilogue = epilogue;
+  p.status = status;
+  const uint64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+  uint64_t grid = (uint64_t)sm_count();
+  if (grid > tiles)
+    grid = tiles;
+  gemm_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  return check_cuda(cudaGetLastError(), "gemm_i8_kernel launch");
+}
+
+} // namespace difb200

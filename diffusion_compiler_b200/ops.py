@@ -1,0 +1,101 @@
+"""Device-resident operators on torch CUDA tensors (torch is only the memory/stream plumbing;
+every op below is one call into libdifb200.so).
+
+Names and argument meaning follow the reference opcodes (``QuantizeInt8Rows``,
+``LinearInt8Scaled``; reference ``include/dif/ir/ir.hpp:123-139``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+
+EPILOGUE_BIAS = 1
+EPILOGUE_GELU_TANH = 2
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _require(t: torch.Tensor, dtype: torch.dtype, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ValueError("%s must be a CUDA tensor (there is no CPU path)" % name)
+    if t.dtype != dtype:
+        raise ValueError("%s must be %s, got %s" % (name, dtype, t.dtype))
+    return t.contiguous()
+
+
+def quantize_int8_rows(parts: Sequence[torch.Tensor], implementation: int = 2, clip: float = 1.0,
+                       clip_tensor: Optional[torch.Tensor] = None, residual: bool = False
+                       ) -> Tuple[torch.Tensor, ...]:
+    """QuantizeInt8Rows: bf16 inputs concatenated on the last axis -> (codes i8, scales f32
+    [, residual codes, residual scales]). ``implementation`` is the Int8RowQuantization value."""
+    if isinstance(parts, torch.Tensor):
+        parts = [parts]
+    parts = [_require(p, torch.bfloat16, "input") for p in parts]
+    lead = parts[0].shape[:-1]
+    rows = 1
+    for d in lead:
+        rows *= int(d)
+    widths = [int(p.shape[-1]) for p in parts]
+    for p in parts:
+        if p.shape[:-1] != lead:
+            raise ValueError("all inputs must share their leading dimensions")
+    total = sum(widths)
+    dev = parts[0].device
+    codes = torch.empty(tuple(lead) + (total,), dtype=torch.int8, device=dev)
+    scales = torch.empty((rows,), dtype=torch.float32, device=dev)
+    rcodes = torch.empty_like(codes) if residual else None
+    rscales = torch.empty_like(scales) if residual else None
+    n = len(parts)
+    ptrs = (C.c_void_p * n)(*[p.data_ptr() for p in parts])
+    ws = (C.c_uint64 * n)(*widths)
+    if clip_tensor is not None:
+        clip_tensor = _require(clip_tensor, torch.float32, "clip_tensor")
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().difb200_quantize_int8_rows(ptrs, ws, n, rows, int(implementation), float(clip),
+                                                         _ptr(clip_tensor), _ptr(codes), _ptr(scales),
+                                                         _ptr(rcodes), _ptr(rscales), _stream()))
+    return (codes, scales, rcodes, rscales) if residual else (codes, scales)
+
+
+def linear_int8_scaled(x8: torch.Tensor, w8: torch.Tensor, row_scales: torch.Tensor,
+                       col_scales: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
+                       want_acc: bool = False, out: Optional[torch.Tensor] = None):
+    """LinearInt8Scaled (+ fused BiasAdd / tanh-Gelu): x8 [..,K] i8, w8 [N,K] i8 -> bf16 [..,N]."""
+    x8 = _require(x8, torch.int8, "x8")
+    w8 = _require(w8, torch.int8, "w8")
+    row_scales = _require(row_scales, torch.float32, "row_scales")
+    col_scales = _require(col_scales, torch.float32, "col_scales")
+    K = int(x8.shape[-1])
+    M = x8.numel() // K
+    N = int(w8.shape[0])
+    if w8.shape[1] != K or row_scales.numel() != M or col_scales.numel() != N:
+        raise ValueError("shapes must flatten as [M,K] x [N,K] with row [M] and column [N] scales")
+    flags = 0
+    if bias is not None:
+        bias = _require(bias, torch.bfloat16, "bias")
+        flags |= EPILOGUE_BIAS
+    if gelu:
+        flags |= EPILOGUE_GELU_TANH
+    if out is None:
+        out = torch.empty(tuple(x8.shape[:-1]) + (N,), dtype=torch.bfloat16, device=x8.device)
+    acc = torch.empty((M, N), dtype=torch.int32, device=x8.device) if want_acc else None
+    with torch.cuda.device(x8.device):
+        _lib.check(_lib.lib().difb200_linear_int8_scaled(_ptr(x8), _ptr(w8), _ptr(row_scales), _ptr(col_scales),
+                                                         _ptr(bias), flags, M, N, K, _ptr(out), _ptr(acc),
+                                                         _stream()))
+    return (out, acc) if want_acc else out
+
+
+def poll_status() -> None:
+    """Raises if a kernel recorded that one of its bounded device-side waits ran out."""
+    _lib.check(_lib.lib().difb200_poll_status())

@@ -1,0 +1,85 @@
+/*
+ * difb200: device-resident C entry points of the B200 (sm_100a) implementation of the
+ * quantized DiT hot path of Diffusion Compiler.
+ *
+ * The drop-in boundary towards the reference project is its backend plugin ABI, restated in
+ * difb200/abi.h and exported by the same shared library (dif_backend_get_v2 / _v1). That ABI
+ * only moves host buffers, so the entry points below expose the same operators on device
+ * pointers for callers that keep tensors resident in HBM (the plugin itself is built on them).
+ *
+ * Conventions: every function returns a status whose values equal dif_backend_status
+ * (0 = OK, 1 = invalid argument, 2 = unsupported, 3 = out of memory, 5 = execution error);
+ * difb200_last_error() returns the text of the calling thread's last failure. All pointers
+ * are device pointers on the current CUDA device unless stated otherwise. `stream` is a
+ * cudaStream_t passed as void* (NULL = default stream). Work is asynchronous: kernels are
+ * enqueued and the call returns. There is no CPU fallback.
+ */
+#ifndef DIFB200_H
+#define DIFB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DIFB200_EXPORT __attribute__((visibility("default")))
+
+/* Epilogue ops fused after LinearInt8Scaled (each keeps the bf16 rounding of the separate op). */
+#define DIFB200_EPILOGUE_BIAS 1u      /* BiasAdd: y = bf16(y + bias[n]) */
+#define DIFB200_EPILOGUE_GELU_TANH 2u /* Gelu, tanh form: y = bf16(gelu(y)) */
+
+DIFB200_EXPORT const char *difb200_last_error(void);
+DIFB200_EXPORT int difb200_version(void);
+
+/*
+ * Reads and clears the device-side status words. Kernels with bounded waits (mbarrier spins)
+ * record there when a wait ran out instead of hanging; returns 5 with text in that case.
+ * Synchronises the device.
+ */
+DIFB200_EXPORT int difb200_poll_status(void);
+
+/*
+ * Opcode QuantizeInt8Rows (67). Replaces the reference CPU op
+ * src/runtime/cpu_executor.cpp:124-307 and its generated CUDA kernel
+ * src/compiler/compiler.cpp:635-845 (semantics: include/dif/ir/ir.hpp:123-134,285-293;
+ * verifier src/ir/verify.cpp:949-1027).
+ *   parts / part_widths : HOST arrays of `part_count` (1..8) device pointers to bf16 tensors
+ *                         [rows, part_widths[i]] that are concatenated on the last axis.
+ *   implementation      : Int8RowQuantization, 1 = Direct .. 7 = H4096F32SignedConvRot.
+ *   clip                : static Scale attribute in (0,1]; clip_device, if not NULL, is the
+ *                         F32[1] dynamic clip input and wins.
+ *   codes [rows, sum(widths)] int8, scales [rows] f32; residual_codes / residual_scales are
+ *   the optional second pair (both NULL or both set).
+ * ConvRot variants need widths that are multiples of 16 and 16-byte aligned pointers.
+ */
+DIFB200_EXPORT int difb200_quantize_int8_rows(const void *const *parts, const uint64_t *part_widths,
+                                              uint32_t part_count, uint64_t rows,
+                                              int32_t implementation, float clip,
+                                              const float *clip_device, int8_t *codes,
+                                              float *scales, int8_t *residual_codes,
+                                              float *residual_scales, void *stream);
+
+/*
+ * Opcode LinearInt8Scaled (68), optionally fused with the BiasAdd (10) and Gelu (49, tanh)
+ * ops that follow it in a W8A8-rewritten program. Replaces the reference CPU op
+ * src/runtime/cpu_executor.cpp:309-335 and the CUTLASS Sm80 kernel
+ * src/runtime/cutlass_gemm.cu:185-303,745-778 (BiasAdd: cpu_executor.cpp:1288-1296, Gelu:
+ * :93-113).
+ *   x [M,K] int8, w [N,K] int8, row_scales [M] f32, col_scales [N] f32, bias [N] bf16 or NULL,
+ *   out [M,N] bf16: out = bf16((float(acc) * row_scales[m]) * col_scales[n]) then the epilogue.
+ *   acc_out, if not NULL, additionally receives the raw INT32 accumulators [M,N] (checking aid).
+ * K must be a multiple of 16; x and w 16-byte aligned.
+ */
+DIFB200_EXPORT int difb200_linear_int8_scaled(const int8_t *x, const int8_t *w,
+                                              const float *row_scales, const float *col_scales,
+                                              const void *bias, uint32_t epilogue, uint64_t M,
+                                              uint64_t N, uint64_t K, void *out, int32_t *acc_out,
+                                              void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DIFB200_H */

@@ -1,0 +1,120 @@
+"""GPU parity of the W8A8 linear path (QuantizeInt8Rows + LinearInt8Scaled) against the CPU
+oracle, through the C-ABI of libdifb200.so. INT8 codes, F32 scales and INT32 accumulators must
+be bit-exact; bf16 outputs bit-exact without GELU and within rel-L2 <= 2e-3 with it."""
+import numpy as np
+import pytest
+
+import oracle_bridge as ob
+from helpers import activations, bf16_normal, cosine, from_torch_bf16, rel_l2, to_torch_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import torch
+    from diffusion_compiler_b200 import ops as _ops
+    assert torch.cuda.is_available()
+    return _ops
+
+
+def _quant_case(ops, rng, impl, rows, K, clip, residual, parts=None):
+    import torch
+    x = activations(rng, rows, K)
+    x[rows // 2] = 0  # an all-zero row exercises the guarded scale
+    if parts is None:
+        parts = [K]
+    cuts = np.cumsum([0] + list(parts))
+    xs = [np.ascontiguousarray(x[:, cuts[i]:cuts[i + 1]]) for i in range(len(parts))]
+    want = ob.orc().quantize_int8_rows(xs, impl, clip, residual)
+    got = ops.quantize_int8_rows([to_torch_bf16(a) for a in xs], impl, clip, residual=residual)
+    torch.cuda.synchronize()
+    names = ["codes", "scales", "rcodes", "rscales"]
+    for name, w, g in zip(names, want, got):
+        g = g.cpu().numpy().reshape(w.shape)
+        assert np.array_equal(w.view(np.uint8), g.view(np.uint8)), \
+            "%s differ: impl=%d rows=%d K=%d (%d mismatches)" % (
+                name, impl, rows, K, int(np.sum(w.view(np.uint8) != g.view(np.uint8))))
+
+
+@pytest.mark.parametrize("impl", [1, 2, 3, 5, 6])
+@pytest.mark.parametrize("rows,K", [(1, 256), (37, 768), (64, 3072), (5, 12288)])
+def test_quantize_h256_bit_exact(ops, impl, rows, K):
+    rng = np.random.default_rng(100 + impl)
+    _quant_case(ops, rng, impl, rows, K, 1.0, False)
+    _quant_case(ops, rng, impl, rows, K, 0.9995, True)
+
+
+@pytest.mark.parametrize("impl", [4, 7])
+@pytest.mark.parametrize("rows,K", [(3, 4096), (9, 12288)])
+def test_quantize_h4096_bit_exact(ops, impl, rows, K):
+    rng = np.random.default_rng(200 + impl)
+    _quant_case(ops, rng, impl, rows, K, 1.0, False)
+    _quant_case(ops, rng, impl, rows, K, 0.97, True)
+
+
+@pytest.mark.parametrize("impl", [1, 2, 6])
+def test_quantize_concatenated_inputs(ops, impl):
+    rng = np.random.default_rng(7)
+    _quant_case(ops, rng, impl, 19, 1024, 1.0, False, parts=[256, 512, 256])
+
+
+def test_quantize_direct_per_token_head(ops):
+    """Direct on [B,S,H,128]: the per-token-per-head quantisation of attention Q/K."""
+    rng = np.random.default_rng(8)
+    _quant_case(ops, rng, 1, 2 * 33 * 4, 128, 1.0, False)
+    _quant_case(ops, rng, 1, 11, 100, 1.0, True)  # odd width: scalar path
+
+
+def _weights(rng, N, K, impl):
+    wf = bf16_normal(rng, (N, K), 0.02)
+    return ob.orc().quantize_int8_rows([wf], impl, 1.0)
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 256, 256), (100, 512, 200), (300, 1024, 520), (1024, 3072, 3072)])
+def test_linear_int8_scaled_bit_exact(ops, M, K, N):
+    import torch
+    rng = np.random.default_rng(M + N)
+    ob.orc().lib.orc_set_threads(8)
+    x = activations(rng, M, K)
+    w8, ws = _weights(rng, N, K, 2)
+    x8, xs = ob.orc().quantize_int8_rows([x], 2, 1.0)
+    bias = bf16_normal(rng, (N,), 0.01)
+    want, want_acc = ob.orc().linear_int8_scaled(x8, w8, xs, ws, want_acc=True)
+    t = lambda a: torch.from_numpy(a).cuda()
+    got, acc = ops.linear_int8_scaled(t(x8), t(w8), t(xs), t(ws), want_acc=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(acc.cpu().numpy(), want_acc), "INT32 accumulators differ"
+    assert np.array_equal(from_torch_bf16(got), want), "bf16 dequantised outputs differ"
+    # + BiasAdd keeps the intermediate bf16 rounding of the two-op program
+    want_b = ob.orc().bias_add(want, bias)
+    got_b = ops.linear_int8_scaled(t(x8), t(w8), t(xs), t(ws), bias=to_torch_bf16(bias))
+    assert np.array_equal(from_torch_bf16(got_b), want_b), "bias epilogue differs"
+    # + Gelu(tanh): libm tanhf vs device tanhf, tolerance from the north star
+    want_g = ob.orc().gelu_tanh(want_b)
+    got_g = from_torch_bf16(ops.linear_int8_scaled(t(x8), t(w8), t(xs), t(ws), bias=to_torch_bf16(bias), gelu=True))
+    a, b = ob.bf16_to_f32(got_g), ob.bf16_to_f32(want_g)
+    assert rel_l2(a, b) <= 2e-3 and cosine(a, b) >= 0.9999
+    assert np.mean(got_g != want_g) < 1e-3
+    ops.poll_status()
+
+
+def test_w8a8_linear_end_to_end_config0(ops):
+    """BASELINE config 0: M=1024, K=N=3072, H256ConvRot activations, bias; GPU quant + GEMM chained."""
+    import torch
+    rng = np.random.default_rng(0)
+    ob.orc().lib.orc_set_threads(8)
+    M = K = N = None
+    M, K, N = 1024, 3072, 3072
+    x = activations(rng, M, K)
+    w8, ws = _weights(rng, N, K, 2)
+    bias = bf16_normal(rng, (N,), 0.01)
+    x8, xs = ob.orc().quantize_int8_rows([x], 2, 1.0)
+    want = ob.orc().bias_add(ob.orc().linear_int8_scaled(x8, w8, xs, ws), bias)
+    codes, scales = ops.quantize_int8_rows([to_torch_bf16(x)], 2)
+    got = ops.linear_int8_scaled(codes, torch.from_numpy(w8).cuda(), scales, torch.from_numpy(ws).cuda(),
+                                 bias=to_torch_bf16(bias))
+    torch.cuda.synchronize()
+    assert np.array_equal(codes.cpu().numpy(), x8)
+    assert np.array_equal(from_torch_bf16(got), want)
+    ops.poll_status()
