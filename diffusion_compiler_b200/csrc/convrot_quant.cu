@@ -71,26 +71,6 @@ __device__ __forceinline__ float absmax2(float m, uint64_t v) {
   return fmaxf(fmaxf(m, fabsf(lo)), fabsf(hi));
 }
 
-// Loads 16 consecutive bf16 of the logical (concatenated) row starting at `column`.
-// Part widths are multiples of 16 on this path, so a run never straddles two parts.
-__device__ __forceinline__ void load16(const QuantParams &p, uint64_t row, uint32_t column,
-                                       uint4 &a, uint4 &b) {
-  uint32_t c = column;
-  const uint16_t *src = nullptr;
-#pragma unroll
-  for (int i = 0; i < kMaxParts; ++i) {
-    if (i < (int)p.part_count && src == nullptr) {
-      if (c < p.width[i])
-        src = p.part[i] + row * p.width[i] + c;
-      else
-        c -= p.width[i];
-    }
-  }
-  const uint4 *v = reinterpret_cast<const uint4 *>(src);
-  a = __ldg(v);
-  b = __ldg(v + 1);
-}
-
 // Correctly rounded fp32 quotient a/b from y = RN(1/b): two Markstein refinements.
 __device__ __forceinline__ uint64_t div2_exact(uint64_t a, uint64_t y, uint64_t negb) {
   uint64_t q = mul2(a, y);
@@ -137,14 +117,57 @@ __device__ __forceinline__ void quantize_pair(uint64_t value, uint64_t y, uint64
   }
 }
 
+// ---- shared-memory access through 32-bit shared addresses (cheap address arithmetic) ----
+__device__ __forceinline__ void sts128(uint32_t addr, float x, float y, float z, float w) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(x), "f"(y), "f"(z), "f"(w)
+               : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ uint64_t lds64(uint32_t addr) {
+  uint64_t v;
+  asm volatile("ld.shared.b64 %0, [%1+%2];" : "=l"(v) : "r"(addr), "n"(OFF) : "memory");
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ void sts8(uint32_t addr, int v) {
+  asm volatile("st.shared.u8 [%0+%1], %2;" ::"r"(addr), "n"(OFF), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float lds32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+
 // Shared memory per warp: 4 groups x 256 fp32 (two swizzled 16x32-word transposes), reused
-// for the code bytes; plus two words per warp for the row maxima.
-constexpr int kWarpWords = 1024;
+// for the code bytes; plus words for the row maxima after all warps' areas.
+constexpr int kWarpBytes = 4096;
+
+// Code bytes of one row are staged at index(col) = col + 64 * (col >> 9): one byte per column
+// with a 64-byte skew per 512 columns, so that the two half-warps hit different banks.
+template <bool H4096, int J>
+__device__ __forceinline__ void stage_pair(uint32_t base_a, uint32_t base_b, int ca, int cb) {
+  // 256-wide variants: element J of the thread sits 16*J bytes after its base.
+  // 4096-wide variants: group J of the block sits 256*J columns on, i.e. 256*J + 64*(J>>1).
+  constexpr int off = H4096 ? (256 * J + 64 * (J >> 1)) : 16 * J;
+  sts8<off>(base_a, ca);
+  sts8<off>(base_b, cb);
+}
 
 template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL>
 __global__ void __launch_bounds__(512, 2)
 convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int rows_per_cta) {
-  extern __shared__ __align__(16) uint32_t smem[];
+  extern __shared__ __align__(128) uint32_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = warp / warps_per_row;         // which row of this CTA's batch
   const int wrow = warp - slot * warps_per_row;  // warp index inside the row
@@ -152,12 +175,56 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
   const uint32_t groups = p.columns >> 8;
   const uint32_t group_a = 4u * wrow + 2u * h;   // first group of this thread's pair
   const bool act_a = group_a < groups, act_b = group_a + 1u < groups;
-  uint32_t *wsm = smem + warp * kWarpWords;
-  float *red = reinterpret_cast<float *>(smem + (blockDim.x >> 5) * kWarpWords);
   const int total_warps = blockDim.x >> 5;
+  const uint32_t smem_addr = smem_u32(smem);
+  const uint32_t warp_addr = smem_addr + warp * kWarpBytes;
+  float *red = reinterpret_cast<float *>(smem + total_warps * (kWarpBytes / 4));
   const float clip = p.clip_device ? __ldg(p.clip_device) : p.clip;
   // The values carried through the rotation are scaled by 2^stages.
   constexpr float kCarry = H4096 ? 64.0f : 16.0f;
+
+  // Where this thread's two 16-element runs live in global memory (the logical row is the
+  // concatenation of the parts; widths are multiples of 16, so a run never straddles two).
+  const uint16_t *src_a = nullptr, *src_b = nullptr;
+  uint32_t pitch_a = 0, pitch_b = 0;
+  {
+    uint32_t ca = group_a * 256u + 16u * a, cb = ca + 256u;
+    bool fa = !act_a, fb = !act_b;
+    for (uint32_t i = 0; i < p.part_count; ++i) {
+      const uint32_t w = p.width[i];
+      if (!fa) {
+        if (ca < w) { src_a = p.part[i] + ca; pitch_a = w; fa = true; } else ca -= w;
+      }
+      if (!fb) {
+        if (cb < w) { src_b = p.part[i] + cb; pitch_b = w; fb = true; } else cb -= w;
+      }
+    }
+  }
+
+  // Transpose addressing (per half-warp area of 2048 bytes; rows of 128 bytes = 16 pairs):
+  // thread a writes its 8 chunks of 2 pairs at chunk position c ^ (a & 7), and reads pair a of
+  // every row j from chunk position (a >> 1) ^ (j & 7).
+  const uint32_t half_addr = warp_addr + h * 2048u;
+  const uint32_t wr_addr = half_addr + 128u * a + ((a & 7u) << 4);          // ^ (c << 4)
+  const uint32_t rd_addr = half_addr + ((uint32_t)(a >> 1) << 4) + 8u * (a & 1u); // ^ ((j&7)<<4), + 128 j
+
+  // Code staging addresses.
+  uint32_t code_a, code_b;      // byte address of this thread's element/group 0 (A and B lane)
+  uint32_t rowbuf_a = 0, rowbuf_b = 0;
+  if (H4096) {
+    const uint32_t per = p.columns >> 5;
+    const uint32_t u0 = threadIdx.x, u1 = threadIdx.x + per;
+    const uint32_t col0 = (u0 >> 8) * 4096u + (u0 & 255u), col1 = (u1 >> 8) * 4096u + (u1 & 255u);
+    code_a = smem_addr + col0 + ((col0 >> 9) << 6);
+    code_b = smem_addr + col1 + ((col1 >> 9) << 6);
+    rowbuf_a = smem_addr + 4u * col0;
+    rowbuf_b = smem_addr + 4u * col1;
+  } else {
+    code_a = warp_addr + 512u * h + a + 64u * h;
+    code_b = code_a + 256u;
+  }
+  const uint32_t copy_addr = (H4096 ? smem_addr + (uint32_t)wrow * 1152u : warp_addr) + 16u * lane;
+  const uint32_t copy_col = (uint32_t)wrow * 1024u + 16u * lane;
 
   // Sign masks of this thread's 32 columns (bit i: element i of group A, bit 16+i: group B).
   uint32_t signs = 0;
@@ -177,10 +244,16 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
     uint64_t P[16];
     {
       uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, b0 = a0, b1 = a0;
-      if (row_ok && act_a)
-        load16(p, row, group_a * 256u + 16u * a, a0, a1);
-      if (row_ok && act_b)
-        load16(p, row, (group_a + 1u) * 256u + 16u * a, b0, b1);
+      if (row_ok && act_a) {
+        const uint4 *v = reinterpret_cast<const uint4 *>(src_a + row * pitch_a);
+        a0 = __ldg(v);
+        a1 = __ldg(v + 1);
+      }
+      if (row_ok && act_b) {
+        const uint4 *v = reinterpret_cast<const uint4 *>(src_b + row * pitch_b);
+        b0 = __ldg(v);
+        b1 = __ldg(v + 1);
+      }
       const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
@@ -204,29 +277,36 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
 #pragma unroll
     for (int q = 0; q < 4; ++q)
       bfly(P[q], P[q + 4], P[q + 8], P[q + 12]);
-    // 16x16 transpose of pairs through shared memory. Thread a writes its row of 16 pairs
-    // as 8 chunks of 2 pairs; chunk c goes to position c ^ (a & 7).
+    // 16x16 transpose of pairs through shared memory.
     {
-      uint32_t *half = wsm + h * 512;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        uint4 v;
         float x0, x1, x2, x3;
         unpack2(P[2 * c], x0, x1);
         unpack2(P[2 * c + 1], x2, x3);
-        v.x = __float_as_uint(x0);
-        v.y = __float_as_uint(x1);
-        v.z = __float_as_uint(x2);
-        v.w = __float_as_uint(x3);
-        *reinterpret_cast<uint4 *>(half + 32 * a + 4 * (c ^ (a & 7))) = v;
+        sts128(wr_addr ^ (uint32_t)(c << 4), x0, x1, x2, x3);
       }
       __syncwarp();
+      uint32_t rd[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const uint2 v = *reinterpret_cast<const uint2 *>(
-            half + 32 * j + 4 * ((a >> 1) ^ (j & 7)) + 2 * (a & 1));
-        P[j] = pack2(__uint_as_float(v.x), __uint_as_float(v.y));
-      }
+      for (int j = 0; j < 8; ++j)
+        rd[j] = rd_addr ^ (uint32_t)(j << 4);
+      P[0] = lds64<0 * 128>(rd[0]);
+      P[1] = lds64<1 * 128>(rd[1]);
+      P[2] = lds64<2 * 128>(rd[2]);
+      P[3] = lds64<3 * 128>(rd[3]);
+      P[4] = lds64<4 * 128>(rd[4]);
+      P[5] = lds64<5 * 128>(rd[5]);
+      P[6] = lds64<6 * 128>(rd[6]);
+      P[7] = lds64<7 * 128>(rd[7]);
+      P[8] = lds64<8 * 128>(rd[0]);
+      P[9] = lds64<9 * 128>(rd[1]);
+      P[10] = lds64<10 * 128>(rd[2]);
+      P[11] = lds64<11 * 128>(rd[3]);
+      P[12] = lds64<12 * 128>(rd[4]);
+      P[13] = lds64<13 * 128>(rd[5]);
+      P[14] = lds64<14 * 128>(rd[6]);
+      P[15] = lds64<15 * 128>(rd[7]);
       __syncwarp();
     }
     // Now P[j] = element 16*j + a of both groups. stage 2 (stride 16), stage 3 (stride 64).
@@ -237,33 +317,22 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
     for (int q = 0; q < 4; ++q)
       bfly(P[q], P[q + 4], P[q + 8], P[q + 12]);
 
-    // Column of P[j] lane 0 / lane 1 (used for output addressing).
-    uint32_t col_a = group_a * 256u + a, col_b = col_a + 256u; // + 16*j
-    uint32_t col_step = 16u;
-    bool out_a = act_a, out_b = act_b;
     if (H4096) {
-      // Second transpose across the 16 groups of every 4096-wide block (one row per CTA).
-      float *rowbuf = reinterpret_cast<float *>(smem);
+      // Second transpose across the 16 groups of every 4096-wide block (one row per CTA):
+      // write the row in natural order (this warp's own 1024 columns), read 16 groups of one
+      // element position.
+      const uint32_t nat_a = smem_addr + 4u * (group_a * 256u + a), nat_b = nat_a + 1024u;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         float x0, x1;
         unpack2(P[j], x0, x1);
-        if (act_a)
-          rowbuf[col_a + 16u * j] = x0;
-        if (act_b)
-          rowbuf[col_b + 16u * j] = x1;
+        sts32(nat_a + 64u * j, x0);
+        sts32(nat_b + 64u * j, x1);
       }
       __syncthreads();
-      // Thread t takes element e of block G for u = t and u = t + columns/32.
-      const uint32_t per = p.columns >> 5;
-      const uint32_t u0 = threadIdx.x, u1 = threadIdx.x + per;
-      col_a = (u0 >> 8) * 4096u + (u0 & 255u);
-      col_b = (u1 >> 8) * 4096u + (u1 & 255u);
-      col_step = 256u;
-      out_a = out_b = threadIdx.x < per;
 #pragma unroll
       for (int g = 0; g < 16; ++g)
-        P[g] = out_a ? pack2(rowbuf[col_a + 256u * g], rowbuf[col_b + 256u * g]) : pack2(0.f, 0.f);
+        P[g] = pack2(lds32(rowbuf_a + 1024u * g), lds32(rowbuf_b + 1024u * g));
       __syncthreads();
 #pragma unroll
       for (int q = 0; q < 4; ++q)
@@ -299,21 +368,6 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
     if (row_ok && wrow == 0 && lane == 0)
       p.scales[row] = stored;
 
-    // Code bytes alias the transpose area: one byte per column, with a 64-byte skew per 512
-    // columns that keeps the two half-warps on different banks. For the 256-wide variants
-    // every warp stages the 1024 columns it owns in its own area; the 4096-wide variants
-    // index the whole row (writer and owner of a column are different warps there).
-    int8_t *code_bytes = reinterpret_cast<int8_t *>(smem);
-    const uint32_t code_base = H4096 ? 0u : (uint32_t)warp * kWarpWords * 4u;
-    const uint32_t code_col0 = H4096 ? 0u : (uint32_t)wrow * 1024u;
-#define DIFB200_CODE_ADDR(col) \
-  (code_base + ((col) - code_col0) + ((((col) - code_col0) >> 9) << 6))
-    auto stage_code = [&](int j, int ca, int cb) {
-      if (out_a)
-        code_bytes[DIFB200_CODE_ADDR(col_a + col_step * j)] = (int8_t)ca;
-      if (out_b)
-        code_bytes[DIFB200_CODE_ADDR(col_b + col_step * j)] = (int8_t)cb;
-    };
     auto flush_codes = [&](int8_t *dst) {
       if (H4096)
         __syncthreads();
@@ -322,11 +376,9 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
       // every lane copies 2 x 16 bytes of its warp's 1024 columns
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
-        const uint32_t col = (uint32_t)wrow * 1024u + part * 512u + lane * 16u;
-        if (row_ok && col < p.columns) {
-          const uint4 v = *reinterpret_cast<const uint4 *>(code_bytes + DIFB200_CODE_ADDR(col));
-          *reinterpret_cast<uint4 *>(dst + row * p.columns + col) = v;
-        }
+        const uint32_t col = copy_col + part * 512u;
+        if (row_ok && col < p.columns)
+          *reinterpret_cast<uint4 *>(dst + row * p.columns + col) = lds128(copy_addr + part * 576u);
       }
       if (H4096)
         __syncthreads();
@@ -335,16 +387,21 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
     };
 
     int codes_a[RESIDUAL ? 16 : 1], codes_b[RESIDUAL ? 16 : 1];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      int ca, cb;
-      quantize_pair<F32>(P[j], y2, nb2, ca, cb);
-      stage_code(j, ca, cb);
-      if (RESIDUAL) {
-        codes_a[j] = ca;
-        codes_b[j] = cb;
-      }
-    }
+#define DIFB200_QUANT_STEP(J)                                      \
+  {                                                                \
+    int ca, cb;                                                    \
+    quantize_pair<F32>(P[J], y2, nb2, ca, cb);                     \
+    stage_pair<H4096, J>(code_a, code_b, ca, cb);                  \
+    if (RESIDUAL) {                                                \
+      codes_a[RESIDUAL ? J : 0] = ca;                              \
+      codes_b[RESIDUAL ? J : 0] = cb;                              \
+    }                                                              \
+  }
+    DIFB200_QUANT_STEP(0) DIFB200_QUANT_STEP(1) DIFB200_QUANT_STEP(2) DIFB200_QUANT_STEP(3)
+    DIFB200_QUANT_STEP(4) DIFB200_QUANT_STEP(5) DIFB200_QUANT_STEP(6) DIFB200_QUANT_STEP(7)
+    DIFB200_QUANT_STEP(8) DIFB200_QUANT_STEP(9) DIFB200_QUANT_STEP(10) DIFB200_QUANT_STEP(11)
+    DIFB200_QUANT_STEP(12) DIFB200_QUANT_STEP(13) DIFB200_QUANT_STEP(14) DIFB200_QUANT_STEP(15)
+#undef DIFB200_QUANT_STEP
     flush_codes(p.codes);
 
     if (RESIDUAL) {
@@ -361,8 +418,8 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
           x0 = round_bf16(x0);
           x1 = round_bf16(x1);
         }
-        ra[j] = __fmaf_rn(-(float)codes_a[j], stored, x0);
-        rb[j] = __fmaf_rn(-(float)codes_b[j], stored, x1);
+        ra[j] = __fmaf_rn(-(float)codes_a[RESIDUAL ? j : 0], stored, x0);
+        rb[j] = __fmaf_rn(-(float)codes_b[RESIDUAL ? j : 0], stored, x1);
         rm = fmaxf(rm, fmaxf(fabsf(ra[j]), fabsf(rb[j])));
       }
 #pragma unroll
@@ -378,22 +435,35 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
       const float rscale_bf16 = round_bf16(rscale);
       if (row_ok && wrow == 0 && lane == 0)
         p.rscales[row] = (SIGNED && !F32) ? rscale_bf16 : rscale;
+      int ca[16], cb[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         if (F32) {
-          codes_a[j] = max(sat_s8(__fdiv_rn(ra[j], rscale)), -127);
-          codes_b[j] = max(sat_s8(__fdiv_rn(rb[j], rscale)), -127);
+          ca[j] = max(sat_s8(__fdiv_rn(ra[j], rscale)), -127);
+          cb[j] = max(sat_s8(__fdiv_rn(rb[j], rscale)), -127);
         } else {
-          codes_a[j] = sat_s8(round_bf16(__fdiv_rn(round_bf16(ra[j]), rscale_bf16)));
-          codes_b[j] = sat_s8(round_bf16(__fdiv_rn(round_bf16(rb[j]), rscale_bf16)));
+          ca[j] = sat_s8(round_bf16(__fdiv_rn(round_bf16(ra[j]), rscale_bf16)));
+          cb[j] = sat_s8(round_bf16(__fdiv_rn(round_bf16(rb[j]), rscale_bf16)));
         }
       }
-#pragma unroll
-      for (int j = 0; j < 16; ++j)
-        stage_code(j, codes_a[j], codes_b[j]);
+      stage_pair<H4096, 0>(code_a, code_b, ca[0], cb[0]);
+      stage_pair<H4096, 1>(code_a, code_b, ca[1], cb[1]);
+      stage_pair<H4096, 2>(code_a, code_b, ca[2], cb[2]);
+      stage_pair<H4096, 3>(code_a, code_b, ca[3], cb[3]);
+      stage_pair<H4096, 4>(code_a, code_b, ca[4], cb[4]);
+      stage_pair<H4096, 5>(code_a, code_b, ca[5], cb[5]);
+      stage_pair<H4096, 6>(code_a, code_b, ca[6], cb[6]);
+      stage_pair<H4096, 7>(code_a, code_b, ca[7], cb[7]);
+      stage_pair<H4096, 8>(code_a, code_b, ca[8], cb[8]);
+      stage_pair<H4096, 9>(code_a, code_b, ca[9], cb[9]);
+      stage_pair<H4096, 10>(code_a, code_b, ca[10], cb[10]);
+      stage_pair<H4096, 11>(code_a, code_b, ca[11], cb[11]);
+      stage_pair<H4096, 12>(code_a, code_b, ca[12], cb[12]);
+      stage_pair<H4096, 13>(code_a, code_b, ca[13], cb[13]);
+      stage_pair<H4096, 14>(code_a, code_b, ca[14], cb[14]);
+      stage_pair<H4096, 15>(code_a, code_b, ca[15], cb[15]);
       flush_codes(p.rcodes);
     }
-#undef DIFB200_CODE_ADDR
   }
 }
 
@@ -504,7 +574,7 @@ int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
   if ((uint64_t)rows_per_cta > p.rows)
     rows_per_cta = (int)p.rows;
   const int warps = warps_per_row * rows_per_cta;
-  const size_t smem = (size_t)warps * kWarpWords * 4 + (size_t)warps * 4 * sizeof(float) + 64;
+  const size_t smem = (size_t)warps * kWarpBytes + (size_t)warps * 4 * sizeof(float) + 64;
   auto kernel = convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL>;
   if (smem > 48 * 1024) {
     if (int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -62,7 +62,13 @@ constexpr int kUmmaK = 32;
 constexpr uint32_t kABytes = kBM * kBK, kBBytes = kBN * kBK, kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + 256;
+// Epilogue staging: per epilogue warp two [32 rows x 32 bf16] boxes (64-byte rows, 64B TMA
+// swizzle); plus, per epilogue warp, 256 column scales and 256 biases (fp32) of the tile.
+constexpr uint32_t kStoreBoxBytes = 32 * 64;
+constexpr uint32_t kStagingBytes = 4 * 2 * kStoreBoxBytes;
+constexpr uint32_t kScaleBytes = 4 * 2 * kBN * 4;
+constexpr size_t kSmemBytes =
+    1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + kStagingBytes + kScaleBytes + 256;
 
 enum : uint32_t { kEpiBias = 1u, kEpiGeluTanh = 2u };
 
@@ -74,6 +80,7 @@ struct GemmParams {
   int32_t *acc_out;
   uint32_t M, N, K;
   uint32_t epilogue;
+  uint32_t tma_store; // 1: outputs leave through TMA stores (needs N % 8 == 0, aligned out)
   DeviceStatus *status;
 };
 
@@ -86,10 +93,19 @@ __device__ __forceinline__ void report_timeout(DeviceStatus *status, uint32_t ro
 }
 
 __device__ __forceinline__ float gelu_tanh(float v) {
-  // 0.5 * v * (1 + tanh(0.79788456 * (v + 0.044715 * v^3))), evaluated without contraction
-  const float cubic = __fmul_rn(__fmul_rn(v, v), v);
-  const float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(v, __fmul_rn(0.044715f, cubic)));
-  return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(inner)));
+  // Reference form (cpu_executor.cpp:93-113): 0.5 * v * (1 + tanh(u)), u = 0.79788456 * (v +
+  // 0.044715 * v^3). The reference's fp32 sum 1 + tanh(u) cancels for negative v, and that
+  // rounding is part of its result, so the same three roundings are kept here and only tanh
+  // itself is computed differently: tanh|u| = 1 - 2 / (e^(2|u|) + 1) with two MUFU ops
+  // (ex2, rcp), absolute error below one ulp of 1.
+  constexpr float kA = 0.7978845608028654f * 2.0f * 1.4426950408889634f;
+  constexpr float kB = kA * 0.044715f;
+  const float t = fmaf(kB, v * v, kA) * v; // 2u * log2(e), same sign as v
+  float e, r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(fabsf(t)));
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+  const float th = copysignf(fmaf(-2.0f, r, 1.0f), v);
+  return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, th));
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -100,10 +116,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + kStages * kStageBytes;
+  const uint32_t staging_base = smem_base + kStages * kStageBytes;
+  const uint32_t scale_base = staging_base + kStagingBytes;
+  const uint32_t bar_base = scale_base + kScaleBytes;
   // barrier layout (8 bytes each): full[4], empty[4], tmem_full[2], tmem_empty[2]; then a word
   // for the TMEM base address and a word for the abort flag.
   const uint32_t full_bar = bar_base, empty_bar = bar_base + 8 * kStages;
@@ -209,11 +227,25 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     const uint32_t quarter = (uint32_t)warp & 3u;
-    uint32_t local = 0;
-    const bool vec_ok = (p.N % 8u == 0u) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0u);
+    uint32_t local = 0, store_buf = 0;
+    uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    float *scale_smem = reinterpret_cast<float *>(generic_base + (scale_base - smem_base));
+    const uint32_t my_staging = staging_base + quarter * 2u * kStoreBoxBytes;
+    uint8_t *my_staging_ptr = generic_base + (my_staging - smem_base);
     for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
       const uint32_t m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * kBN;
+      // column scales and biases of this tile -> this warp's private shared-memory copy
+      // (warp-private so that no cross-warp barrier is needed)
+      float *cs = scale_smem + quarter * 2 * kBN, *bs = cs + kBN;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < kBN / 32; ++i) {
+        const uint32_t c = lane + 32u * i, n = n0 + c;
+        cs[c] = n < p.N ? __ldg(p.col_scales + n) : 0.0f;
+        bs[c] = ((p.epilogue & kEpiBias) && n < p.N) ? bf16_bits_to_f32(__ldg(p.bias + n)) : 0.0f;
+      }
+      __syncwarp();
       if (*abort_ptr || !ptx::mbar_wait(tfull_bar + 8 * acc, acc_phase)) {
         if (!*abort_ptr && lane == 0)
           report_timeout(p.status, 2, tile);
@@ -239,39 +271,56 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const uint32_t n = n_base + i;
-          const float c0 = n < p.N ? __ldg(p.col_scales + n) : 0.0f;
-          const float c1 = n + 1 < p.N ? __ldg(p.col_scales + n + 1) : 0.0f;
-          float y0 = __fmul_rn(__fmul_rn((float)(int32_t)r[i], rs), c0);
-          float y1 = __fmul_rn(__fmul_rn((float)(int32_t)r[i + 1], rs), c1);
-          uint32_t pk = pack_bf16x2(y0, y1);
-          if (p.epilogue & kEpiBias) {
-            const float b0 = n < p.N ? bf16_bits_to_f32(__ldg(p.bias + n)) : 0.0f;
-            const float b1 = n + 1 < p.N ? bf16_bits_to_f32(__ldg(p.bias + n + 1)) : 0.0f;
-            y0 = __fadd_rn(__uint_as_float(pk << 16), b0);
-            y1 = __fadd_rn(__uint_as_float(pk & 0xffff0000u), b1);
-            pk = pack_bf16x2(y0, y1);
-          }
-          if (p.epilogue & kEpiGeluTanh) {
-            y0 = gelu_tanh(__uint_as_float(pk << 16));
-            y1 = gelu_tanh(__uint_as_float(pk & 0xffff0000u));
-            pk = pack_bf16x2(y0, y1);
-          }
-          packed[i >> 1] = pk;
-        }
-        if (row_ok) {
-          uint16_t *dst = p.out + (size_t)row * p.N + n_base;
-          if (vec_ok && n_base + 32u <= p.N) {
+        for (int g = 0; g < 8; ++g) {
+          const float4 c4 = *reinterpret_cast<const float4 *>(cs + chunk * 32 + 4 * g);
+          const float4 b4 = *reinterpret_cast<const float4 *>(bs + chunk * 32 + 4 * g);
+          const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-            for (int v = 0; v < 4; ++v)
-              reinterpret_cast<uint4 *>(dst)[v] =
-                  make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (n_base + i < p.N)
-                dst[i] = (uint16_t)((packed[i >> 1] >> (16 * (i & 1))) & 0xffffu);
+          for (int h = 0; h < 2; ++h) {
+            const int i = 4 * g + 2 * h;
+            float y0 = __fmul_rn(__fmul_rn((float)(int32_t)r[i], rs), cc[2 * h]);
+            float y1 = __fmul_rn(__fmul_rn((float)(int32_t)r[i + 1], rs), cc[2 * h + 1]);
+            uint32_t pk = pack_bf16x2(y0, y1);
+            if (p.epilogue & kEpiBias) {
+              y0 = __fadd_rn(__uint_as_float(pk << 16), bb[2 * h]);
+              y1 = __fadd_rn(__uint_as_float(pk & 0xffff0000u), bb[2 * h + 1]);
+              pk = pack_bf16x2(y0, y1);
+            }
+            if (p.epilogue & kEpiGeluTanh) {
+              y0 = gelu_tanh(__uint_as_float(pk << 16));
+              y1 = gelu_tanh(__uint_as_float(pk & 0xffff0000u));
+              pk = pack_bf16x2(y0, y1);
+            }
+            packed[i >> 1] = pk;
           }
+        }
+        if (p.tma_store) {
+          // stage this warp's [32 x 32] box (64-byte rows, 16-byte chunk c of row r stored at
+          // c ^ ((r >> 1) & 3): the 64B TMA swizzle, conflict-free), then one TMA store.
+          if (lane == 0)
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+          uint8_t *box = my_staging_ptr + store_buf * kStoreBoxBytes;
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            *reinterpret_cast<uint4 *>(box + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) =
+                make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          ptx::fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                             reinterpret_cast<uint64_t>(&map_c)),
+                         "r"(my_staging + store_buf * kStoreBoxBytes), "r"((int32_t)n_base),
+                         "r"((int32_t)(m0 + quarter * 32u))
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          store_buf ^= 1u;
+        } else if (row_ok) {
+          uint16_t *dst = p.out + (size_t)row * p.N + n_base;
+          for (int i = 0; i < 32; ++i)
+            if (n_base + i < p.N)
+              dst[i] = (uint16_t)((packed[i >> 1] >> (16 * (i & 1))) & 0xffffu);
         }
       }
       ptx::tc_fence_before();
@@ -279,6 +328,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (lane == 0)
         ptx::mbar_arrive(tempty_bar + 8 * acc);
     }
+    if (lane == 0)
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   ptx::tc_fence_before();
@@ -323,6 +374,17 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
                                  CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
 
+  const bool tma_store = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0);
+  CUtensorMap map_c = map_a; // placeholder when stores go out directly
+  if (tma_store) {
+    const uint64_t dims_c[2] = {N, M};
+    const uint64_t strides_c[1] = {N * 2};
+    const uint32_t box_c[2] = {32, 32};
+    if (int rc = encode_tensor_map(&map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out_bf16, dims_c,
+                                   strides_c, box_c, CU_TENSOR_MAP_SWIZZLE_64B))
+      return rc;
+  }
+
   static std::once_flag once;
   static cudaError_t attr_rc = cudaSuccess;
   std::call_once(once, [] {
@@ -342,12 +404,13 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   p.N = (uint32_t)N;
   p.K = (uint32_t)K;
   p.epilogue = epilogue;
+  p.tma_store = tma_store ? 1u : 0u;
   p.status = status;
   const uint64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
   uint64_t grid = (uint64_t)sm_count();
   if (grid > tiles)
     grid = tiles;
-  gemm_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  gemm_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_c, p);
   return check_cuda(cudaGetLastError(), "gemm_i8_kernel launch");
 }
 
