@@ -344,7 +344,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales,
                        const float *col_scales, const void *bias_bf16, uint32_t epilogue, uint64_t M,
-                       uint64_t N, uint64_t K, void *out_bf16, int32_t *acc_out, cudaStream_t stream) {
+                       uint64_t N, uint64_t K, void *out_bf16, int32_t *acc_out, cudaStream_t stream,
+                       DeviceStatus *status_words) {
   if (!x || !w || !row_scales || !col_scales || !out_bf16)
     return fail(kInvalidArgument, "LinearInt8Scaled: null pointer");
   if ((epilogue & kEpiBias) && !bias_bf16)
@@ -359,7 +360,7 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
     return fail(kUnsupported, "LinearInt8Scaled: dimension too large");
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return fail(kUnsupported, "LinearInt8Scaled: operands must be 16-byte aligned");
-  DeviceStatus *status = device_status_words();
+  DeviceStatus *status = status_words ? status_words : device_status_words();
   if (!status)
     return fail(kOutOfMemory, "LinearInt8Scaled: cannot allocate device status words");
 

@@ -96,6 +96,39 @@ def linear_int8_scaled(x8: torch.Tensor, w8: torch.Tensor, row_scales: torch.Ten
     return (out, acc) if want_acc else out
 
 
+def w8a8_linear(x: torch.Tensor, w8: torch.Tensor, col_scales: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, gelu: bool = False, implementation: int = 2,
+                clip: float = 1.0, out: Optional[torch.Tensor] = None,
+                scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+    """The W8A8 int8-convrot linear in one call: quantize x [..,K] bf16, multiply with w8 [N,K].
+    ``scratch`` = (codes int8 [M,K], row scales f32 [M]) may be passed to reuse buffers."""
+    x = _require(x, torch.bfloat16, "x")
+    w8 = _require(w8, torch.int8, "w8")
+    col_scales = _require(col_scales, torch.float32, "col_scales")
+    K = int(x.shape[-1])
+    M = x.numel() // K
+    N = int(w8.shape[0])
+    flags = 0
+    if bias is not None:
+        bias = _require(bias, torch.bfloat16, "bias")
+        flags |= EPILOGUE_BIAS
+    if gelu:
+        flags |= EPILOGUE_GELU_TANH
+    if scratch is None:
+        scratch = (torch.empty((M, K), dtype=torch.int8, device=x.device),
+                   torch.empty((M,), dtype=torch.float32, device=x.device))
+    codes, scales = scratch
+    if codes.numel() < M * K or scales.numel() < M:
+        raise ValueError("scratch buffers are too small")
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (N,), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().difb200_w8a8_linear(_ptr(x), _ptr(w8), _ptr(col_scales), _ptr(bias), flags,
+                                                  int(implementation), float(clip), M, N, K, _ptr(codes),
+                                                  _ptr(scales), _ptr(out), _stream()))
+    return out
+
+
 def poll_status() -> None:
     """Raises if a kernel recorded that one of its bounded device-side waits ran out."""
     _lib.check(_lib.lib().difb200_poll_status())

@@ -78,6 +78,21 @@ DIFB200_EXPORT int difb200_linear_int8_scaled(const int8_t *x, const int8_t *w,
                                               uint64_t N, uint64_t K, void *out, int32_t *acc_out,
                                               void *stream);
 
+/*
+ * The W8A8 `int8-convrot` linear as one call: QuantizeInt8Rows(implementation, clip) on the bf16
+ * activations x [M,K], then LinearInt8Scaled against w [N,K] / col_scales [N] and the optional
+ * epilogue. This is the op pair the reference's W8A8 rewrite puts in place of a Linear
+ * (tools/difflux2sample.cpp:2017-2069, 3187-3219) and what its CUDA executor runs as
+ * launch() + launch_cutlass_int8_scaled_gemm (src/runtime/cuda_executor.cpp:10940-10960).
+ * codes_scratch [M,K] int8 and scales_scratch [M] f32 are scratch buffers supplied by the
+ * caller (they hold the activation codes and row scales between the two kernels).
+ */
+DIFB200_EXPORT int difb200_w8a8_linear(const void *x, const int8_t *w, const float *col_scales,
+                                       const void *bias, uint32_t epilogue, int32_t implementation,
+                                       float clip, uint64_t M, uint64_t N, uint64_t K,
+                                       int8_t *codes_scratch, float *scales_scratch, void *out,
+                                       void *stream);
+
 #ifdef __cplusplus
 }
 #endif

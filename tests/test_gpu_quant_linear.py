@@ -118,3 +118,20 @@ def test_w8a8_linear_end_to_end_config0(ops):
     assert np.array_equal(codes.cpu().numpy(), x8)
     assert np.array_equal(from_torch_bf16(got), want)
     ops.poll_status()
+
+
+def test_w8a8_linear_single_call_matches_two_calls(ops):
+    """difb200_w8a8_linear (caller scratch) == quantize + linear through their own entry points."""
+    import torch
+    rng = np.random.default_rng(3)
+    M, K, N = 640, 1024, 768
+    x = to_torch_bf16(activations(rng, M, K))
+    w8, ws = _weights(rng, N, K, 2)
+    w8, ws = torch.from_numpy(w8).cuda(), torch.from_numpy(ws).cuda()
+    bias = to_torch_bf16(bf16_normal(rng, (N,), 0.01))
+    codes, scales = ops.quantize_int8_rows([x], 2)
+    want = ops.linear_int8_scaled(codes, w8, scales, ws, bias=bias, gelu=True)
+    got = ops.w8a8_linear(x, w8, ws, bias=bias, gelu=True)
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    ops.poll_status()
