@@ -35,6 +35,8 @@ def lib() -> C.CDLL:
         L.difb200_linear_int8_scaled.argtypes = [vp, vp, vp, vp, vp, u32, u64, u64, u64, vp, vp, vp]
         L.difb200_w8a8_linear.restype = C.c_int
         L.difb200_w8a8_linear.argtypes = [vp, vp, vp, vp, u32, i32, f32, u64, u64, u64, vp, vp, vp, vp]
+        L.difb200_w8a8_linear_static.restype = C.c_int
+        L.difb200_w8a8_linear_static.argtypes = [vp, vp, vp, vp, u32, i32, f32, u64, u64, u64, vp, i32, vp]
         _lib = L
     return _lib
 

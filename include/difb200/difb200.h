@@ -93,6 +93,24 @@ DIFB200_EXPORT int difb200_w8a8_linear(const void *x, const int8_t *w, const flo
                                        int8_t *codes_scratch, float *scales_scratch, void *out,
                                        void *stream);
 
+/*
+ * difb200_w8a8_linear with no allocation anywhere (no counterpart in the reference).
+ * Same computation and arguments as difb200_w8a8_linear, but the activation codes, row scales
+ * and the GEMM's status words live in a fixed 40 MiB array inside the library instead of
+ * caller scratch, and neither this call nor anything it runs calls cudaMalloc/cudaFree. It is
+ * for hosts that planned their device memory up front or must not trigger an allocation while
+ * they run a layer. A call needs 256 + roundup(4*M, 256) + M*K bytes; larger problems are
+ * rejected with status 2. The first call on a device resolves the array's address (make that
+ * first call outside any stream capture). All calls share the array: calls that can overlap on
+ * the GPU race, so keep them on one stream or order them. check_previous != 0 first
+ * synchronises `stream` and returns status 5 if a bounded wait ran out in the previous call.
+ */
+DIFB200_EXPORT int difb200_w8a8_linear_static(const void *x, const int8_t *w, const float *col_scales,
+                                              const void *bias, uint32_t epilogue,
+                                              int32_t implementation, float clip, uint64_t M,
+                                              uint64_t N, uint64_t K, void *out,
+                                              int32_t check_previous, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
