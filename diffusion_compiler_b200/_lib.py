@@ -37,6 +37,14 @@ def lib() -> C.CDLL:
         L.difb200_w8a8_linear.argtypes = [vp, vp, vp, vp, u32, i32, f32, u64, u64, u64, vp, vp, vp, vp]
         L.difb200_w8a8_linear_static.restype = C.c_int
         L.difb200_w8a8_linear_static.argtypes = [vp, vp, vp, vp, u32, i32, f32, u64, u64, u64, vp, i32, vp]
+        L.difb200_attention_int8_scratch_bytes.restype = u64
+        L.difb200_attention_int8_scratch_bytes.argtypes = [u64, u64, u64]
+        L.difb200_attention_int8.restype = C.c_int
+        L.difb200_attention_int8.argtypes = [vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, f32, vp, u64, vp, vp]
+        L.difb200_attention_scratch_bytes.restype = u64
+        L.difb200_attention_scratch_bytes.argtypes = [u64, u64, u64, u64]
+        L.difb200_attention.restype = C.c_int
+        L.difb200_attention.argtypes = [vp, vp, vp, vp, u64, u64, u64, u64, u64, f32, vp, u64, vp, vp]
         _lib = L
     return _lib
 

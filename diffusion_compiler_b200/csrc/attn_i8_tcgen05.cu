@@ -1,0 +1,494 @@
+// INT8 attention for sm_100a: INT8 Q.K^T on tcgen05 (kind::i8, INT32 scores in tensor memory),
+// fp32 online softmax with a power-of-two running maximum, bf16 P.V on tcgen05 (kind::f16, fp32
+// output accumulator in tensor memory), flash-style over 128-key tiles with TMA K/V staging.
+// Grouped-query attention and a key-validity mask are supported; non-causal.
+//
+// Semantics. The op replaced is DiffIR Attention (reference src/runtime/cpu_executor.cpp:
+// 1839-1910; GQA head mapping :1853-1863, all-masked-row rule :1881-1887; key mask as produced by
+// BooleanMaskToBias with MaskQueries=false, :627-650) in the INT8 lowering that the reference
+// only ships for sm_86 (src/runtime/h3_owned_attention.cu:646-929). Numerical contract (per
+// query row i of head h, kv head h / (H / KV)):
+//   acc_j = sum_d q8[i,d] * k8[j,d]                 INT32, exact
+//   u_j   = fma(float(acc_j), ks_j, mask_j)         mask_j = 0 for valid keys, -inf otherwise
+//   A     = qs_i * (scale * log2(e))
+//   m     = an integer >= ceil(max_j u_j * A)       (any such integer gives the same result:
+//                                                    bf16 rounding commutes with powers of two)
+//   p_j   = exp2(fma(u_j, A, -m)),  P_j = bf16(p_j)
+//   out   = bf16((sum_j P_j * v_j) / (sum_j p_j))   fp32 accumulation; all keys masked -> 0
+// q8/qs and k8/ks are QuantizeInt8Rows(Direct) of the [B,S,H,128] / [B,S,KV,128] tensors.
+//
+// Structure: one CTA per (batch, head, 256 queries) = two 128-query tiles that share every K/V
+// tile. Warpgroup 0: warp 0 = TMA producer, warp 1 = MMA issuer (warps 2-3 idle). Warpgroups 1
+// and 2: softmax + epilogue of query tile 0 / 1, one thread per query row (the whole 128-key row
+// of scores lives in registers, so no shuffles). The tensor core alternates between the two
+// tiles: while one tile's softmax runs, the other tile's P.V and next Q.K^T execute.
+// Tensor memory (512 columns): S0 | S1 (INT32 scores, 128 columns each; bf16 P overwrites the
+// first 64 columns of its S and is the TMEM A operand of P.V), O0 | O1 (fp32, 128 columns each).
+#include "common.cuh"
+#include "ptx.cuh"
+
+#include <mutex>
+
+namespace difb200 {
+namespace {
+
+constexpr int kTile = 128;          // queries per tile, keys per tile, head dim
+constexpr int kStages = 3;          // K/V ring depth
+constexpr uint32_t kQBytes = 128 * 128;        // int8 [128 x 128]
+constexpr uint32_t kKBytes = 128 * 128;        // int8 [128 keys x 128]
+constexpr uint32_t kVBytes = 128 * 128 * 2;    // bf16 [128 keys x 128] as two 64-wide halves
+constexpr uint32_t kKsBytes = 128 * 8;         // float2 (key scale, mask bias) per key
+constexpr uint32_t kStageBytes = kKBytes + kVBytes + kKsBytes;
+constexpr int kThreads = 384;
+constexpr size_t kSmemBytes = 1024 + 2 * kQBytes + kStages * kStageBytes + 256;
+
+struct AttnParams {
+  const float *qs;       // [B,S,H]
+  const float2 *ksmb;    // [B,KV,S_pad] (key scale, mask bias)
+  uint16_t *out;         // [B,S,H,128] bf16
+  uint32_t B, S, H, KV, S_pad;
+  float scale_log2e;     // scale * log2(e)
+  DeviceStatus *status;
+};
+
+__device__ __forceinline__ void report(DeviceStatus *status, uint32_t role, uint32_t detail) {
+  if (atomicExch(&status->flag, 1u) == 0u) {
+    status->kernel = 3u;
+    status->role = role;
+    status->detail = detail;
+  }
+}
+
+// Builds the per-key (scale, mask bias) table [B,KV,S_pad]: the key scales of the [B,S,KV]
+// row order re-laid contiguous along keys, 0 / -inf from the validity mask, -inf for padding.
+__global__ void key_table_kernel(const float *ks, const uint8_t *key_valid, float2 *ksmb, uint32_t B,
+                                 uint32_t S, uint32_t KV, uint32_t S_pad) {
+  const uint64_t total = (uint64_t)B * KV * S_pad;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t j = (uint32_t)(i % S_pad);
+    const uint32_t kvh = (uint32_t)((i / S_pad) % KV);
+    const uint32_t b = (uint32_t)(i / ((uint64_t)S_pad * KV));
+    float2 v = make_float2(0.0f, -INFINITY);
+    if (j < S) {
+      const bool valid = key_valid == nullptr || key_valid[(uint64_t)b * S + j] != 0;
+      v = make_float2(ks[((uint64_t)b * S + j) * KV + kvh], valid ? 0.0f : -INFINITY);
+    }
+    ksmb[i] = v;
+  }
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t packed;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+  return packed;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - raw_addr);
+  const uint32_t q_addr = base;                       // 2 x 16 KB
+  const uint32_t stage_addr = base + 2 * kQBytes;     // kStages x (K | V | ksmb)
+  const uint32_t bar = stage_addr + kStages * kStageBytes;
+  // barriers (8 bytes each)
+  const uint32_t q_full = bar;
+  const uint32_t k_full = bar + 8, k_empty = k_full + 8 * kStages;
+  const uint32_t v_full = k_empty + 8 * kStages, v_empty = v_full + 8 * kStages;
+  const uint32_t s_full = v_empty + 8 * kStages;      // [2]
+  const uint32_t p_full = s_full + 16;                // [2]
+  const uint32_t pv_done = p_full + 16;               // [2]
+  const uint32_t tmem_slot = pv_done + 16;
+  volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(base_ptr + (tmem_slot - base));
+  volatile uint32_t *abort_ptr = slot_ptr + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t q_blocks = (p.S + 255u) / 256u;
+  const uint32_t qb = blockIdx.x % q_blocks;
+  const uint32_t head = (blockIdx.x / q_blocks) % p.H;
+  const uint32_t batch = blockIdx.x / (q_blocks * p.H);
+  const uint32_t kvh = head / (p.H / p.KV);
+  const uint32_t q0 = qb * 256u;
+  const uint32_t n_kv = (p.S + kTile - 1) / kTile;
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(k_full + 8 * s, 1);
+      ptx::mbar_init(k_empty + 8 * s, 1);
+      ptx::mbar_init(v_full + 8 * s, 1);
+      ptx::mbar_init(v_empty + 8 * s, 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      ptx::mbar_init(s_full + 8 * t, 1);
+      ptx::mbar_init(p_full + 8 * t, 128);
+      ptx::mbar_init(pv_done + 8 * t, 1);
+    }
+    *abort_ptr = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *slot_ptr;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0 && lane == 0) {
+      // ---------------- TMA producer ----------------
+      ptx::mbar_expect_tx(q_full, 2 * kQBytes);
+      ptx::tma_load_4d(q_addr, &map_q, q_full, 0, (int32_t)head, (int32_t)q0, (int32_t)batch);
+      ptx::tma_load_4d(q_addr + kQBytes, &map_q, q_full, 0, (int32_t)head, (int32_t)(q0 + 128u),
+                       (int32_t)batch);
+      const float2 *table = p.ksmb + ((uint64_t)batch * p.KV + kvh) * p.S_pad;
+      for (uint32_t i = 0; i < n_kv; ++i) {
+        const uint32_t s = i % kStages, phase = (i / kStages) & 1u;
+        const uint32_t k_dst = stage_addr + s * kStageBytes, v_dst = k_dst + kKBytes,
+                       t_dst = v_dst + kVBytes;
+        const int32_t key0 = (int32_t)(i * kTile);
+        if (*abort_ptr || !ptx::mbar_wait(k_empty + 8 * s, phase ^ 1u)) {
+          if (!*abort_ptr)
+            report(p.status, 0, i);
+          *abort_ptr = 1;
+          break;
+        }
+        ptx::mbar_expect_tx(k_full + 8 * s, kKBytes);
+        ptx::tma_load_4d(k_dst, &map_k, k_full + 8 * s, 0, (int32_t)kvh, key0, (int32_t)batch);
+        if (*abort_ptr || !ptx::mbar_wait(v_empty + 8 * s, phase ^ 1u)) {
+          if (!*abort_ptr)
+            report(p.status, 1, i);
+          *abort_ptr = 1;
+          break;
+        }
+        ptx::mbar_expect_tx(v_full + 8 * s, kVBytes + kKsBytes);
+        ptx::tma_load_4d(v_dst, &map_v, v_full + 8 * s, 0, (int32_t)kvh, key0, (int32_t)batch);
+        ptx::tma_load_4d(v_dst + kVBytes / 2, &map_v, v_full + 8 * s, 64, (int32_t)kvh, key0,
+                         (int32_t)batch);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                         "r"(t_dst), "l"(reinterpret_cast<uint64_t>(table + (uint64_t)i * kTile)),
+                     "r"(kKsBytes), "r"(v_full + 8 * s)
+                     : "memory");
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc_qk = ptx::make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, 0, 0, 128, 128);
+      constexpr uint32_t idesc_pv = ptx::make_idesc(1 /*F32*/, 1 /*BF16*/, 1 /*BF16*/, 0, 1 /*V is N-major*/, 128, 128);
+      bool ok = true;
+      auto issue_qk = [&](uint32_t t, uint32_t s) {
+        const uint64_t a = ptx::smem_desc_sw128(q_addr + t * kQBytes, 16, 1024);
+        const uint64_t b = ptx::smem_desc_sw128(stage_addr + s * kStageBytes, 16, 1024);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          ptx::mma_i8_ss(tmem + t * 128u, a + (uint64_t)(2 * k), b + (uint64_t)(2 * k), idesc_qk, k != 0);
+        ptx::mma_commit(s_full + 8 * t);
+      };
+      auto issue_pv = [&](uint32_t t, uint32_t s, uint32_t accumulate) {
+        // A = P in tensor memory (64 columns of bf16 pairs at the start of S_t); B = V tile,
+        // N-major: 64-wide halves 16 KB apart (leading offset), 8-key groups 1 KB apart.
+        const uint64_t b = ptx::smem_desc_sw128(stage_addr + s * kStageBytes + kKBytes, kVBytes / 2, 1024);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) // 16 keys per MMA: 8 TMEM columns, 2048 bytes of V
+          ptx::mma_f16_ts(tmem + 256u + t * 128u, tmem + t * 128u + 8u * k, b + (uint64_t)(128 * k),
+                          idesc_pv, (accumulate | (uint32_t)k) != 0u ? 1u : 0u);
+        ptx::mma_commit(pv_done + 8 * t);
+      };
+      if (!ptx::mbar_wait(q_full, 0)) {
+        report(p.status, 2, 0);
+        *abort_ptr = 1;
+        ok = false;
+      }
+      if (ok && !ptx::mbar_wait(k_full, 0)) {
+        report(p.status, 2, 1);
+        *abort_ptr = 1;
+        ok = false;
+      }
+      if (ok) {
+        ptx::tc_fence_after();
+        issue_qk(0, 0);
+        issue_qk(1, 0);
+        ptx::mma_commit(k_empty);
+      }
+      for (uint32_t i = 0; i < n_kv && ok; ++i) {
+        const uint32_t s = i % kStages, phase = (i / kStages) & 1u;
+        const uint32_t sn = (i + 1) % kStages, phase_n = ((i + 1) / kStages) & 1u;
+        const bool more = i + 1 < n_kv;
+        if (*abort_ptr || !ptx::mbar_wait(v_full + 8 * s, phase)) {
+          if (!*abort_ptr)
+            report(p.status, 2, 2);
+          *abort_ptr = 1;
+          break;
+        }
+        for (uint32_t t = 0; t < 2 && ok; ++t) {
+          if (*abort_ptr || !ptx::mbar_wait(p_full + 8 * t, i & 1u)) {
+            if (!*abort_ptr)
+              report(p.status, 2, 3 + t);
+            *abort_ptr = 1;
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          issue_pv(t, s, i != 0u ? 1u : 0u);
+          if (t == 1)
+            ptx::mma_commit(v_empty + 8 * s);
+          if (more) {
+            if (t == 0 && (*abort_ptr || !ptx::mbar_wait(k_full + 8 * sn, phase_n))) {
+              if (!*abort_ptr)
+                report(p.status, 2, 5);
+              *abort_ptr = 1;
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            issue_qk(t, sn);
+            if (t == 1)
+              ptx::mma_commit(k_empty + 8 * sn);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- softmax + epilogue, one thread per query row ----------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const uint32_t t = (uint32_t)(warp - 4) >> 2;       // query tile 0 / 1
+    const uint32_t quarter = (uint32_t)warp & 3u;
+    const uint32_t row_in_tile = quarter * 32u + lane;
+    const uint32_t qrow = q0 + t * 128u + row_in_tile;
+    const bool row_ok = qrow < p.S;
+    const float A = (row_ok ? __ldg(p.qs + ((uint64_t)batch * p.S + qrow) * p.H + head) : 1.0f) *
+                    p.scale_log2e;
+    const uint32_t lane_base = (quarter * 32u) << 16;
+    const uint32_t s_tmem = tmem + lane_base + t * 128u, o_tmem = tmem + lane_base + 256u + t * 128u;
+    float m_run = -INFINITY, l = 0.0f;
+    bool alive = true;
+    for (uint32_t i = 0; i < n_kv; ++i) {
+      const uint32_t s = i % kStages, phase = (i / kStages) & 1u;
+      if (*abort_ptr || !ptx::mbar_wait(s_full + 8 * t, i & 1u) ||
+          !ptx::mbar_wait(v_full + 8 * s, phase)) {
+        if (!*abort_ptr && lane == 0)
+          report(p.status, 3 + t, i);
+        *abort_ptr = 1;
+        alive = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        ptx::tmem_ld_32x32(s_tmem + 32u * c, r[c]);
+      ptx::tmem_ld_wait();
+      const float4 *tab = reinterpret_cast<const float4 *>(base_ptr + (stage_addr - base) + s * kStageBytes +
+                                                           kKBytes + kVBytes);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float4 kk = tab[(c * 32 + j) >> 1]; // (ks_j, mb_j, ks_j+1, mb_j+1)
+          // int32 -> fp32 exactly (|acc| <= 128*128*127 < 2^22): magic-number conversion
+          const float f0 = __int_as_float((int32_t)r[c][j] + 0x4B400000) - 12582912.0f;
+          const float f1 = __int_as_float((int32_t)r[c][j + 1] + 0x4B400000) - 12582912.0f;
+          const float u0 = __fmaf_rn(f0, kk.x, kk.y), u1 = __fmaf_rn(f1, kk.z, kk.w);
+          r[c][j] = __float_as_uint(u0);
+          r[c][j + 1] = __float_as_uint(u1);
+          mx = fmaxf(mx, fmaxf(u0, u1));
+        }
+      }
+      // power-of-two running maximum
+      float m_new = m_run;
+      if (mx != -INFINITY)
+        m_new = fmaxf(m_run, ceilf(mx * A));
+      const bool grow = m_new > m_run && m_run != -INFINITY;
+      if (__any_sync(0xffffffffu, grow)) {
+        // rescale O (and l) by an exact power of two; needs P.V of the previous tile finished
+        if (!ptx::mbar_wait(pv_done + 8 * t, (i - 1u) & 1u)) {
+          if (lane == 0)
+            report(p.status, 5 + t, i);
+          *abort_ptr = 1;
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const float factor = grow ? ex2(m_run - m_new) : 1.0f;
+        l *= factor;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32(o_tmem + 32u * c, o);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
+          ptx::tmem_st_32x32(o_tmem + 32u * c, o);
+        }
+        ptx::tmem_st_wait();
+      }
+      m_run = m_new;
+      const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float p0 = ex2(__fmaf_rn(__uint_as_float(r[c][j]), A, neg_m));
+          const float p1 = ex2(__fmaf_rn(__uint_as_float(r[c][j + 1]), A, neg_m));
+          l += p0;
+          l += p1;
+          pk[(c * 32 + j) >> 1] = pack_bf16(p0, p1);
+        }
+      }
+      {
+        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
+        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
+        ptx::tmem_st_32x32(s_tmem, lo);
+        ptx::tmem_st_32x32(s_tmem + 32u, hi);
+      }
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(p_full + 8 * t);
+    }
+    if (alive && n_kv > 0) {
+      if (!ptx::mbar_wait(pv_done + 8 * t, (n_kv - 1u) & 1u)) {
+        if (lane == 0)
+          report(p.status, 7 + t, 0);
+        *abort_ptr = 1;
+      } else {
+        ptx::tc_fence_after();
+        uint16_t *dst = p.out + (((uint64_t)batch * p.S + qrow) * p.H + head) * kTile;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32(o_tmem + 32u * c, o);
+          ptx::tmem_ld_wait();
+          if (row_ok) {
+            uint32_t w[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float y0 = l > 0.0f ? __fdiv_rn(__uint_as_float(o[j]), l) : 0.0f;
+              const float y1 = l > 0.0f ? __fdiv_rn(__uint_as_float(o[j + 1]), l) : 0.0f;
+              w[j >> 1] = pack_bf16(y0, y1);
+            }
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              reinterpret_cast<uint4 *>(dst + 32 * c)[v] =
+                  make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+}
+
+} // namespace
+
+size_t attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV) {
+  const uint64_t s_pad = (S + kTile - 1) / kTile * kTile;
+  return (size_t)(B * KV * s_pad * sizeof(float2));
+}
+
+int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks, const void *v_bf16,
+                   const uint8_t *key_valid, uint64_t B, uint64_t S, uint64_t H, uint64_t KV, uint64_t D,
+                   float scale, void *scratch, size_t scratch_bytes, void *out_bf16, cudaStream_t stream) {
+  if (!q8 || !qs || !k8 || !ks || !v_bf16 || !out_bf16 || !scratch)
+    return fail(kInvalidArgument, "Attention(INT8): null pointer");
+  if (D != 128)
+    return fail(kUnsupported, "Attention(INT8): head dimension must be 128");
+  if (B == 0 || S == 0 || H == 0)
+    return kOk;
+  if (KV == 0 || H % KV != 0)
+    return fail(kInvalidArgument, "Attention(INT8): KvHeads must divide the head count");
+  if (B * H * ((S + 255) / 256) > 0x7fffffffull || S > 0x7fffff00ull)
+    return fail(kUnsupported, "Attention(INT8): problem too large");
+  if (scratch_bytes < attention_int8_scratch_bytes(B, S, KV))
+    return fail(kInvalidArgument, "Attention(INT8): scratch buffer too small");
+  if ((reinterpret_cast<uintptr_t>(q8) | reinterpret_cast<uintptr_t>(k8) |
+       reinterpret_cast<uintptr_t>(v_bf16) | reinterpret_cast<uintptr_t>(out_bf16) |
+       reinterpret_cast<uintptr_t>(scratch)) & 15)
+    return fail(kUnsupported, "Attention(INT8): pointers must be 16-byte aligned");
+  DeviceStatus *status = device_status_words();
+  if (!status)
+    return fail(kOutOfMemory, "Attention(INT8): cannot allocate device status words");
+  const uint32_t s_pad = (uint32_t)((S + kTile - 1) / kTile * kTile);
+
+  CUtensorMap map_q, map_k, map_v;
+  {
+    const uint64_t dims[4] = {128, H, S, B};
+    const uint64_t strides[3] = {128, H * 128, S * H * 128};
+    const uint32_t box[4] = {128, 1, 128, 1};
+    if (int rc = encode_tensor_map(&map_q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, q8, dims, strides, box,
+                                   CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const uint64_t dims[4] = {128, KV, S, B};
+    const uint64_t strides[3] = {128, KV * 128, S * KV * 128};
+    const uint32_t box[4] = {128, 1, 128, 1};
+    if (int rc = encode_tensor_map(&map_k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, k8, dims, strides, box,
+                                   CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const uint64_t dims[4] = {128, KV, S, B};
+    const uint64_t strides[3] = {256, KV * 256, S * KV * 256};
+    const uint32_t box[4] = {64, 1, 128, 1};
+    if (int rc = encode_tensor_map(&map_v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, v_bf16, dims, strides, box,
+                                   CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  static std::once_flag once;
+  static cudaError_t attr_rc = cudaSuccess;
+  std::call_once(once, [] {
+    attr_rc = cudaFuncSetAttribute(attn_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  });
+  if (int rc = check_cuda(attr_rc, "cudaFuncSetAttribute(attn_i8_kernel)"))
+    return rc;
+
+  float2 *table = static_cast<float2 *>(scratch);
+  {
+    const uint64_t total = B * KV * s_pad;
+    uint64_t blocks = (total + 255) / 256;
+    if (blocks > 4096)
+      blocks = 4096;
+    key_table_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ks, key_valid, table, (uint32_t)B, (uint32_t)S,
+                                                           (uint32_t)KV, s_pad);
+    if (int rc = check_cuda(cudaGetLastError(), "key_table_kernel launch"))
+      return rc;
+  }
+  AttnParams p{};
+  p.qs = qs;
+  p.ksmb = table;
+  p.out = static_cast<uint16_t *>(out_bf16);
+  p.B = (uint32_t)B;
+  p.S = (uint32_t)S;
+  p.H = (uint32_t)H;
+  p.KV = (uint32_t)KV;
+  p.S_pad = s_pad;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.status = status;
+  const uint64_t grid = B * H * ((S + 255) / 256);
+  attn_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+  return check_cuda(cudaGetLastError(), "attn_i8_kernel launch");
+}
+
+} // namespace difb200

@@ -23,6 +23,41 @@ int w8a8_linear(const void *x_bf16, const int8_t *w, const float *col_scales, co
                             out_bf16, nullptr, stream, status_words);
 }
 
+namespace {
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+} // namespace
+
+size_t attention_scratch_bytes(uint64_t B, uint64_t S, uint64_t H, uint64_t KV) {
+  return align256(B * S * H * 128) + align256(B * S * KV * 128) + align256(B * S * H * 4) +
+         align256(B * S * KV * 4) + align256(attention_int8_scratch_bytes(B, S, KV));
+}
+
+int attention_bf16_via_int8(const void *q, const void *k, const void *v, const uint8_t *key_valid, uint64_t B,
+                            uint64_t S, uint64_t H, uint64_t KV, uint64_t D, float scale, void *scratch,
+                            size_t scratch_bytes, void *out_bf16, cudaStream_t stream) {
+  if (D != 128)
+    return fail(kUnsupported, "Attention(INT8): head dimension must be 128");
+  if (!scratch || scratch_bytes < attention_scratch_bytes(B, S, H, KV))
+    return fail(kInvalidArgument, "Attention(INT8): scratch buffer too small");
+  unsigned char *base = static_cast<unsigned char *>(scratch);
+  int8_t *q8 = reinterpret_cast<int8_t *>(base);
+  base += align256(B * S * H * 128);
+  int8_t *k8 = reinterpret_cast<int8_t *>(base);
+  base += align256(B * S * KV * 128);
+  float *qs = reinterpret_cast<float *>(base);
+  base += align256(B * S * H * 4);
+  float *ks = reinterpret_cast<float *>(base);
+  base += align256(B * S * KV * 4);
+  const void *qp[1] = {q}, *kp[1] = {k};
+  const uint64_t w[1] = {128};
+  if (int rc = quantize_int8_rows(qp, w, 1, B * S * H, 1, 1.0f, nullptr, q8, qs, nullptr, nullptr, stream))
+    return rc;
+  if (int rc = quantize_int8_rows(kp, w, 1, B * S * KV, 1, 1.0f, nullptr, k8, ks, nullptr, nullptr, stream))
+    return rc;
+  return attention_int8(q8, qs, k8, ks, v, key_valid, B, S, H, KV, D, scale, base,
+                        attention_int8_scratch_bytes(B, S, KV), out_bf16, stream);
+}
+
 } // namespace difb200
 
 extern "C" {
@@ -54,6 +89,29 @@ int difb200_linear_int8_scaled(const int8_t *x, const int8_t *w, const float *ro
                                void *stream) {
   return linear_int8_scaled(x, w, row_scales, col_scales, bias, epilogue, M, N, K, out, acc_out,
                             static_cast<cudaStream_t>(stream));
+}
+
+uint64_t difb200_attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV) {
+  return attention_int8_scratch_bytes(B, S, KV);
+}
+
+int difb200_attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
+                           const void *v, const uint8_t *key_valid, uint64_t B, uint64_t S, uint64_t H,
+                           uint64_t KV, uint64_t D, float scale, void *scratch, uint64_t scratch_bytes,
+                           void *out, void *stream) {
+  return attention_int8(q8, qs, k8, ks, v, key_valid, B, S, H, KV, D, scale, scratch, scratch_bytes, out,
+                        static_cast<cudaStream_t>(stream));
+}
+
+uint64_t difb200_attention_scratch_bytes(uint64_t B, uint64_t S, uint64_t H, uint64_t KV) {
+  return attention_scratch_bytes(B, S, H, KV);
+}
+
+int difb200_attention(const void *q, const void *k, const void *v, const uint8_t *key_valid, uint64_t B,
+                      uint64_t S, uint64_t H, uint64_t KV, uint64_t D, float scale, void *scratch,
+                      uint64_t scratch_bytes, void *out, void *stream) {
+  return attention_bf16_via_int8(q, k, v, key_valid, B, S, H, KV, D, scale, scratch, scratch_bytes, out,
+                                 static_cast<cudaStream_t>(stream));
 }
 
 int difb200_w8a8_linear(const void *x, const int8_t *w, const float *col_scales, const void *bias,

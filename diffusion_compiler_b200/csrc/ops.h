@@ -29,4 +29,17 @@ int w8a8_linear(const void *x_bf16, const int8_t *w, const float *col_scales, co
                 int8_t *codes_scratch, float *scales_scratch, void *out_bf16, cudaStream_t stream,
                 DeviceStatus *status_words = nullptr);
 
+// INT8 attention on already quantised Q/K (QuantizeInt8Rows Direct per token-head) and bf16 V.
+size_t attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV);
+int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks, const void *v_bf16,
+                   const uint8_t *key_valid, uint64_t B, uint64_t S, uint64_t H, uint64_t KV, uint64_t D,
+                   float scale, void *scratch, size_t scratch_bytes, void *out_bf16, cudaStream_t stream);
+
+// DiffIR Attention on bf16 q/k/v in its INT8 lowering: Direct quantisation of q and k per
+// token-head, then attention_int8. Scratch holds the codes, scales and the key table.
+size_t attention_scratch_bytes(uint64_t B, uint64_t S, uint64_t H, uint64_t KV);
+int attention_bf16_via_int8(const void *q, const void *k, const void *v, const uint8_t *key_valid, uint64_t B,
+                            uint64_t S, uint64_t H, uint64_t KV, uint64_t D, float scale, void *scratch,
+                            size_t scratch_bytes, void *out_bf16, cudaStream_t stream);
+
 } // namespace difb200

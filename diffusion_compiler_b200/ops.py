@@ -129,6 +129,59 @@ def w8a8_linear(x: torch.Tensor, w8: torch.Tensor, col_scales: torch.Tensor,
     return out
 
 
+def attention_int8(q8: torch.Tensor, qs: torch.Tensor, k8: torch.Tensor, ks: torch.Tensor, v: torch.Tensor,
+                   key_valid: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """INT8 attention on quantised Q/K ([B,S,H,128] / [B,S,KV,128] int8 + per token-head f32
+    scales) and bf16 V [B,S,KV,128]; key_valid is an optional [B,S] uint8/bool key mask."""
+    q8 = _require(q8, torch.int8, "q8")
+    k8 = _require(k8, torch.int8, "k8")
+    qs = _require(qs, torch.float32, "qs")
+    ks = _require(ks, torch.float32, "ks")
+    v = _require(v, torch.bfloat16, "v")
+    B, S, H, D = (int(d) for d in q8.shape)
+    KV = int(k8.shape[2])
+    if key_valid is not None:
+        key_valid = key_valid.to(torch.uint8).contiguous()
+    if scale is None:
+        scale = 1.0 / (D ** 0.5)
+    if out is None:
+        out = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=q8.device)
+    L = _lib.lib()
+    nbytes = int(L.difb200_attention_int8_scratch_bytes(B, S, KV))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q8.device)
+    with torch.cuda.device(q8.device):
+        _lib.check(L.difb200_attention_int8(_ptr(q8), _ptr(qs), _ptr(k8), _ptr(ks), _ptr(v), _ptr(key_valid),
+                                            B, S, H, KV, D, float(scale), _ptr(scratch), nbytes, _ptr(out),
+                                            _stream()))
+    return out
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, key_valid: Optional[torch.Tensor] = None,
+              scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+              scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """DiffIR Attention on bf16 q [B,S,H,128], k/v [B,S,KV,128] through the INT8 lowering."""
+    q = _require(q, torch.bfloat16, "q")
+    k = _require(k, torch.bfloat16, "k")
+    v = _require(v, torch.bfloat16, "v")
+    B, S, H, D = (int(d) for d in q.shape)
+    KV = int(k.shape[2])
+    if key_valid is not None:
+        key_valid = key_valid.to(torch.uint8).contiguous()
+    if scale is None:
+        scale = 1.0 / (D ** 0.5)
+    if out is None:
+        out = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=q.device)
+    L = _lib.lib()
+    nbytes = int(L.difb200_attention_scratch_bytes(B, S, H, KV))
+    if scratch is None:
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(L.difb200_attention(_ptr(q), _ptr(k), _ptr(v), _ptr(key_valid), B, S, H, KV, D, float(scale),
+                                       _ptr(scratch), scratch.numel(), _ptr(out), _stream()))
+    return out
+
+
 def poll_status() -> None:
     """Raises if a kernel recorded that one of its bounded device-side waits ran out."""
     _lib.check(_lib.lib().difb200_poll_status())

@@ -79,6 +79,38 @@ DIFB200_EXPORT int difb200_linear_int8_scaled(const int8_t *x, const int8_t *w,
                                               void *stream);
 
 /*
+ * INT8 attention on quantised operands. Replaces the reference's sm_86-only INT8 lowering of
+ * opcode Attention (8): src/runtime/h3_owned_attention.cu:955-1079 (host entry), kernels
+ * :236-295 and :646-929; admission src/runtime/cuda_executor.cpp:3388-3391,10982-10993.
+ * Semantics of the op: src/runtime/cpu_executor.cpp:1839-1910 (GQA: query head h reads kv head
+ * h / (H / KV); a row whose keys are all masked yields zeros).
+ *   q8 [B,S,H,128] int8 with qs [B,S,H] f32, k8 [B,S,KV,128] int8 with ks [B,S,KV] f32: codes
+ *   and scales of QuantizeInt8Rows(Direct) on the bf16 tensors (one row per token-head);
+ *   v [B,S,KV,128] bf16; key_valid [B,S] bytes or NULL (the Bool mask that
+ *   BooleanMaskToBias(MaskQueries=false) would turn into a 0/-inf bias, cpu_executor.cpp:627-650);
+ *   scale = AttentionScale (1/sqrt(128) by default); out [B,S,H,128] bf16.
+ *   scratch: device buffer of difb200_attention_int8_scratch_bytes(B,S,KV) bytes.
+ * Non-causal, head dimension 128 only; everything else returns status 2.
+ */
+DIFB200_EXPORT uint64_t difb200_attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV);
+DIFB200_EXPORT int difb200_attention_int8(const int8_t *q8, const float *qs, const int8_t *k8,
+                                          const float *ks, const void *v, const uint8_t *key_valid,
+                                          uint64_t B, uint64_t S, uint64_t H, uint64_t KV, uint64_t D,
+                                          float scale, void *scratch, uint64_t scratch_bytes,
+                                          void *out, void *stream);
+
+/*
+ * Opcode Attention (8) on bf16 q [B,S,H,128], k/v [B,S,KV,128] in its INT8 lowering: q and k
+ * are quantised per token-head (QuantizeInt8Rows Direct) into scratch, then
+ * difb200_attention_int8 runs. scratch: difb200_attention_scratch_bytes(B,S,H,KV) bytes.
+ */
+DIFB200_EXPORT uint64_t difb200_attention_scratch_bytes(uint64_t B, uint64_t S, uint64_t H, uint64_t KV);
+DIFB200_EXPORT int difb200_attention(const void *q, const void *k, const void *v,
+                                     const uint8_t *key_valid, uint64_t B, uint64_t S, uint64_t H,
+                                     uint64_t KV, uint64_t D, float scale, void *scratch,
+                                     uint64_t scratch_bytes, void *out, void *stream);
+
+/*
  * The W8A8 `int8-convrot` linear as one call: QuantizeInt8Rows(implementation, clip) on the bf16
  * activations x [M,K], then LinearInt8Scaled against w [N,K] / col_scales [N] and the optional
  * epilogue. This is the op pair the reference's W8A8 rewrite puts in place of a Linear
