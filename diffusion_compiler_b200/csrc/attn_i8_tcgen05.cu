@@ -9,7 +9,9 @@
 // only ships for sm_86 (src/runtime/h3_owned_attention.cu:646-929). Numerical contract (per
 // query row i of head h, kv head h / (H / KV)):
 //   acc_j = sum_d q8[i,d] * k8[j,d]                 INT32, exact
-//   u_j   = fma(float(acc_j), ks_j, mask_j)         mask_j = 0 for valid keys, -inf otherwise
+//   u_j   = float(acc_j) * ks'_j                    one fp32 rounding; ks'_j = the key scale rounded
+//                                                   (nearest-even) to 22 significant bits;
+//                                                   u_j = -inf for masked keys
 //   A     = qs_i * (scale * log2(e))
 //   m     = an integer >= ceil(max_j u_j * A)       (any such integer gives the same result:
 //                                                    bf16 rounding commutes with powers of two)
@@ -59,8 +61,12 @@ __device__ __forceinline__ void report(DeviceStatus *status, uint32_t role, uint
   }
 }
 
-// Builds the per-key (scale, mask bias) table [B,KV,S_pad]: the key scales of the [B,S,KV]
-// row order re-laid contiguous along keys, 0 / -inf from the validity mask, -inf for padding.
+// Builds the per-key table [B,KV,S_pad] of (ks', -C * ks') with C = 1.5 * 2^23: the key scales of
+// the [B,S,KV] row order re-laid contiguous along keys. The softmax threads turn an INT32 score
+// into fp32 with one integer add, f' = as_float(acc + bits(C)) = C + acc exactly, and then
+// u = fma(f', ks', -C * ks') = RN(acc * ks'): rounding ks to 22 significant bits makes C * ks'
+// exact, so the fused form has the single rounding of a plain multiply. Masked and padding keys
+// carry (0, -inf), which yields u = -inf.
 __global__ void key_table_kernel(const float *ks, const uint8_t *key_valid, float2 *ksmb, uint32_t B,
                                  uint32_t S, uint32_t KV, uint32_t S_pad) {
   const uint64_t total = (uint64_t)B * KV * S_pad;
@@ -70,9 +76,11 @@ __global__ void key_table_kernel(const float *ks, const uint8_t *key_valid, floa
     const uint32_t kvh = (uint32_t)((i / S_pad) % KV);
     const uint32_t b = (uint32_t)(i / ((uint64_t)S_pad * KV));
     float2 v = make_float2(0.0f, -INFINITY);
-    if (j < S) {
-      const bool valid = key_valid == nullptr || key_valid[(uint64_t)b * S + j] != 0;
-      v = make_float2(ks[((uint64_t)b * S + j) * KV + kvh], valid ? 0.0f : -INFINITY);
+    if (j < S && (key_valid == nullptr || key_valid[(uint64_t)b * S + j] != 0)) {
+      uint32_t bits = __float_as_uint(ks[((uint64_t)b * S + j) * KV + kvh]);
+      bits = (bits + 1u + ((bits >> 2) & 1u)) & ~3u; // nearest-even to 22 significant bits
+      const float k22 = __uint_as_float(bits);
+      v = make_float2(k22, -12582912.0f * k22);
     }
     ksmb[i] = v;
   }
@@ -293,21 +301,22 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       ptx::tmem_ld_wait();
       const float4 *tab = reinterpret_cast<const float4 *>(base_ptr + (stage_addr - base) + s * kStageBytes +
                                                            kKBytes + kVBytes);
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          const float4 kk = tab[(c * 32 + j) >> 1]; // (ks_j, mb_j, ks_j+1, mb_j+1)
-          // int32 -> fp32 exactly (|acc| <= 128*128*127 < 2^22): magic-number conversion
-          const float f0 = __int_as_float((int32_t)r[c][j] + 0x4B400000) - 12582912.0f;
-          const float f1 = __int_as_float((int32_t)r[c][j + 1] + 0x4B400000) - 12582912.0f;
+          const float4 kk = tab[(c * 32 + j) >> 1]; // (ks'_j, -C ks'_j, ks'_j+1, -C ks'_j+1)
+          const float f0 = __int_as_float((int32_t)r[c][j] + 0x4B400000);     // C + acc, exact
+          const float f1 = __int_as_float((int32_t)r[c][j + 1] + 0x4B400000);
           const float u0 = __fmaf_rn(f0, kk.x, kk.y), u1 = __fmaf_rn(f1, kk.z, kk.w);
           r[c][j] = __float_as_uint(u0);
           r[c][j + 1] = __float_as_uint(u1);
-          mx = fmaxf(mx, fmaxf(u0, u1));
+          float &acc_max = mx4[(j >> 1) & 3];
+          asm("max.f32 %0, %0, %1, %2;" : "+f"(acc_max) : "f"(u0), "f"(u1));
         }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // power-of-two running maximum
       float m_new = m_run;
       if (mx != -INFINITY)
@@ -340,16 +349,22 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       m_run = m_new;
       const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
       uint32_t pk[64];
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull}; // 8 partial row sums as packed fp32 pairs
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           const float p0 = ex2(__fmaf_rn(__uint_as_float(r[c][j]), A, neg_m));
           const float p1 = ex2(__fmaf_rn(__uint_as_float(r[c][j + 1]), A, neg_m));
-          l += p0;
-          l += p1;
+          sum2[(j >> 1) & 3] = add2(sum2[(j >> 1) & 3], pack2(p0, p1));
           pk[(c * 32 + j) >> 1] = pack_bf16(p0, p1);
         }
+      }
+      {
+        float a0, a1, b0, b1;
+        unpack2(add2(sum2[0], sum2[1]), a0, a1);
+        unpack2(add2(sum2[2], sum2[3]), b0, b1);
+        l += (a0 + a1) + (b0 + b1);
       }
       {
         uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);

@@ -440,12 +440,15 @@ ORC_EXPORT void orc_attention_exact(const uint16_t *q, const uint16_t *k,
  *   (one row per token-head); v bf16 [B,S,KV,D].
  *
  *   acc   = sum_d q8*k8                      (int32, exact)
- *   u_j   = float(acc) * ks_j                (fp32)
+ *   u_j   = float(acc) * ks'_j               (fp32; ks'_j = ks_j rounded, nearest-even, to 22
+ *                                             significant bits, which lets the kernel fuse the
+ *                                             int->float conversion into one exact fma)
  *   A_i   = qs_i * (scale * log2(e))         (fp32; both products rounded to fp32)
  *   m_i   = ceil(max_j(u_j) * A_i)           (an integer; masked keys excluded)
  *   p_j   = exp2(fma(u_j, A_i, -m_i))        (fp32)
  *   P_j   = bf16(p_j)
- *   out   = bf16( (sum_j P_j * v_j) / (sum_j p_j) )   (fp32 accumulation)
+ *   out   = bf16( (sum_j P_j * v_j) / (sum_j p_j) )   (fp32 accumulation; the kernel adds the
+ *                                                      p_j in a different order)
  *
  * The power-of-two (integer) maximum makes every rescaling of an online-softmax kernel an
  * exact power of two, so the kernel's bf16 P agrees with this two-pass form except for
@@ -482,7 +485,12 @@ static void attention_int8_body(void *vctx, int64_t begin, int64_t end) {
               acc += (int32_t)qr[d] * (int32_t)kr[d];
             if (acc_out && b == 0 && head == 0)
               acc_out[query * S + key] = acc;
-            float uj = (float)acc * ks[(b * S + key) * KV + kvh];
+            uint32_t kbits;
+            memcpy(&kbits, &ks[(b * S + key) * KV + kvh], 4);
+            kbits = (kbits + 1U + ((kbits >> 2U) & 1U)) & ~3U;
+            float k22;
+            memcpy(&k22, &kbits, 4);
+            float uj = (float)acc * k22;
             if (key_valid && !key_valid[b * S + key])
               uj = -INFINITY;
             u[key] = uj;
