@@ -1,0 +1,50 @@
+// Launchers of the block-glue kernels (glue.cu). dtype codes are the DiffIR ones
+// (1 = F32, 2 = BF16, 3 = F16). All return a status code (0 = OK).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace difb200 {
+namespace glue {
+
+int binary(const void *a, const void *b, void *o, uint32_t dt, uint64_t n, bool multiply, cudaStream_t s);
+// kind: 0 = copy/cast, 1 = gelu tanh, 2 = gelu erf, 3 = silu, 4 = sigmoid
+int unary(const void *a, void *o, uint32_t dt_in, uint32_t dt_out, uint64_t n, int kind, cudaStream_t s);
+int bias_add(const void *a, const void *bias, void *o, uint32_t dt, uint64_t n, uint64_t width, cudaStream_t s);
+int affine_last_dim(const void *a, const void *scale, const void *bias, void *o, uint32_t dt, uint64_t n,
+                    uint64_t width, cudaStream_t s);
+int fill(void *o, uint32_t dt, uint64_t n, float value, cudaStream_t s);
+int rms_norm(const void *x, const void *w, void *o, uint32_t dt, uint64_t rows, uint64_t cols, float eps,
+             float weight_offset, cudaStream_t s);
+int layer_norm_modulate(const void *x, const void *w, const void *b, const void *scale, const void *shift, void *o,
+                        uint32_t dt, uint64_t rows, uint64_t cols, uint64_t rows_per_mod, float eps, cudaStream_t s);
+int rms_norm_modulate(const void *x, const void *w, const void *a, const void *b, void *o, uint32_t dt, uint64_t rows,
+                      uint64_t cols, float eps, float weight_offset, bool shared_vector, uint64_t rows_per_vector,
+                      cudaStream_t s);
+int qk_norm_rope(const void *x, const void *w, const void *cosv, const void *sinv, void *o, uint32_t dt,
+                 uint32_t dt_table, uint64_t tokens, uint64_t heads, uint64_t dim, uint64_t rotary,
+                 uint64_t table_width, uint64_t input_seq, uint64_t table_seq, uint64_t table_start, float eps,
+                 bool interleaved_v2, cudaStream_t s);
+int rotary_frequency(const float *pos, const int32_t *pair_axes, const int32_t *pair_idx, const int32_t *axis_dims,
+                     float *cosv, float *sinv, uint64_t tokens, uint64_t axes, uint64_t pairs, double theta_ntk,
+                     unsigned int *bad_flag, cudaStream_t s);
+int rotary_apply(const void *x, const float *cosv, const float *sinv, void *o, uint32_t dt, uint64_t tokens,
+                 uint64_t heads, uint64_t dim, uint64_t pairs, cudaStream_t s);
+int residual_gate(const void *res, const void *branch, const void *gate, void *o, uint32_t dt, uint64_t n,
+                  uint64_t width, uint64_t rows_per_gate, cudaStream_t s);
+int swiglu(const void *x, void *o, uint32_t dt, uint64_t rows, uint64_t width, uint64_t in_width, uint64_t start,
+           bool gate_first, cudaStream_t s);
+// out[i] = in[offset + sum_a coord_a(i) * in_strides[a]] (BroadcastTo: stride 0 on broadcast axes;
+// Slice: offset = start * stride[axis])
+int gather(const void *x, void *o, uint32_t elem_bytes, uint32_t rank, const uint64_t *out_dims,
+           const uint64_t *in_strides, uint64_t offset, cudaStream_t s);
+int concat_part(const void *x, void *o, uint32_t elem_bytes, uint64_t outer, uint64_t chunk, uint64_t out_chunk,
+                uint64_t out_offset, cudaStream_t s);
+int mask_to_bias(const uint8_t *mask, void *o, uint32_t dt, uint64_t B, uint64_t L, bool vector_mask,
+                 bool mask_queries, cudaStream_t s);
+int linear(const void *x, const void *w, const void *bias, void *o, uint32_t dt, uint64_t M, uint64_t N, uint64_t K,
+           cudaStream_t s);
+
+} // namespace glue
+} // namespace difb200

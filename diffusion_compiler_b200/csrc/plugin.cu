@@ -1,0 +1,669 @@
+// Backend plugin entry points dif_backend_get_v2 / dif_backend_get_v1 (difb200/abi.h): the
+// reference's drop-in boundary (reference include/dif/backend/abi.h; host side
+// src/backend/plugin.cpp:60-283). compile() decodes + verifies the DIFIR001 bytes, keeps every
+// tensor resident on the device, uploads constants, and plans one step per operation, fusing
+//   LinearInt8Scaled -> BiasAdd -> Gelu(tanh)       into the GEMM epilogue, and
+//   BooleanMaskToBias(MaskQueries=false) -> Attention into the attention kernel's key mask
+// (the [B,1,S,S] bias is then never materialised). execute() copies inputs in, runs the steps
+// `warmups` + `iterations` times (CUDA events around each timed pass), copies outputs out.
+//
+// Attention runs in its INT8 lowering when it is bf16, head dimension 128, non-causal,
+// Implementation == 2 and either unbiased or biased by a fusable key mask -- the admission rule
+// of the reference's INT8 route (src/runtime/cuda_executor.cpp:8422-8423, 3388-3391). The
+// environment variable DIFB200_INT8_ATTENTION=0 turns the lowering off; an Attention that is not
+// admitted is reported as unsupported (there is no exact-attention kernel and no CPU path here).
+#include "difb200/abi.h"
+
+#include "common.cuh"
+#include "diffir.h"
+#include "glue.h"
+#include "ops.h"
+
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <limits>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace difb200 {
+namespace {
+
+struct Context {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  char device_name[256] = {0};
+};
+
+struct Step {
+  const ir::Op *op = nullptr;
+  uint32_t epilogue = 0;            // LinearInt8Scaled: fused bias / gelu
+  int bias_tensor = -1;             // index of the fused bias tensor
+  int out_tensor = -1;              // index of the tensor the (fused) step writes
+  int mask_tensor = -1;             // Attention: index of the fused Bool key mask
+  bool skip = false;                // op absorbed by a neighbour
+};
+
+struct Executable {
+  Context *ctx = nullptr;
+  ir::Program program;
+  std::vector<void *> dev;          // device buffer per tensor (nullptr when never materialised)
+  std::vector<Step> steps;
+  void *attn_scratch = nullptr;
+  size_t attn_scratch_bytes = 0;
+  unsigned int *flag = nullptr;     // device flag for data-dependent argument errors
+  uint64_t resident_bytes = 0;
+  bool constants_bound = false;     // v2: uploaded at compile
+  ~Executable() {
+    if (ctx)
+      cudaSetDevice(ctx->device);
+    for (void *p : dev)
+      if (p)
+        cudaFree(p);
+    if (attn_scratch)
+      cudaFree(attn_scratch);
+    if (flag)
+      cudaFree(flag);
+  }
+};
+
+void write_error(dif_backend_error *error, const std::string &text) {
+  if (!error || !error->data || error->capacity == 0)
+    return;
+  const size_t n = text.size() < error->capacity - 1 ? text.size() : error->capacity - 1;
+  std::memcpy(error->data, text.data(), n);
+  error->data[n] = '\0';
+}
+
+dif_backend_status status_of(int rc) {
+  return rc >= 0 && rc <= 6 ? static_cast<dif_backend_status>(rc) : DIF_BACKEND_INTERNAL_ERROR;
+}
+
+struct PluginError {
+  int status;
+  std::string text;
+};
+void require(int rc) {
+  if (rc != 0)
+    throw PluginError{rc, last_error()};
+}
+void require_cuda(cudaError_t code, const char *what) { require(check_cuda(code, what)); }
+
+bool int8_attention_enabled() {
+  const char *v = std::getenv("DIFB200_INT8_ATTENTION");
+  return !(v && v[0] == '0');
+}
+
+// ---- planning -------------------------------------------------------------------------------
+void plan(Executable &exe) {
+  const ir::Program &p = exe.program;
+  std::map<uint32_t, int> consumers;
+  std::map<uint32_t, size_t> consumer_op;
+  for (size_t i = 0; i < p.ops.size(); ++i)
+    for (auto id : p.ops[i].in) {
+      consumers[id]++;
+      consumer_op[id] = i;
+    }
+  exe.steps.assign(p.ops.size(), Step{});
+  std::map<uint32_t, size_t> producer;
+  for (size_t i = 0; i < p.ops.size(); ++i) {
+    exe.steps[i].op = &p.ops[i];
+    exe.steps[i].out_tensor = p.ops[i].out.empty() ? -1 : p.index_of(p.ops[i].out[0]);
+    for (auto id : p.ops[i].out)
+      producer[id] = i;
+  }
+  auto sole_consumer = [&](uint32_t id, uint32_t opcode, size_t &idx) {
+    const ir::Tensor *t = p.tensor(id);
+    if (!t || t->has(ir::Output) || consumers[id] != 1)
+      return false;
+    idx = consumer_op[id];
+    return p.ops[idx].opcode == opcode && p.ops[idx].in[0] == id;
+  };
+  for (size_t i = 0; i < p.ops.size(); ++i) {
+    const ir::Op &op = p.ops[i];
+    Step &st = exe.steps[i];
+    if (op.opcode == ir::LinearInt8Scaled) {
+      size_t b = 0, g = 0;
+      if (sole_consumer(op.out[0], ir::BiasAdd, b) && p.tensor(p.ops[b].in[1])->dtype == ir::BF16) {
+        st.epilogue |= 1u;
+        st.bias_tensor = p.index_of(p.ops[b].in[1]);
+        st.out_tensor = p.index_of(p.ops[b].out[0]);
+        exe.steps[b].skip = true;
+        if (sole_consumer(p.ops[b].out[0], ir::Gelu, g) && p.ops[g].u64(ir::Approximation, 0) == 1) {
+          st.epilogue |= 2u;
+          st.out_tensor = p.index_of(p.ops[g].out[0]);
+          exe.steps[g].skip = true;
+        }
+      }
+    } else if (op.opcode == ir::Attention) {
+      const ir::Tensor &q = *p.tensor(op.in[0]);
+      const bool admitted = q.dtype == ir::BF16 && q.last() == 128 && !op.boolean(ir::Causal, false) &&
+                            op.u64(ir::Implementation, 1) == 2 && int8_attention_enabled();
+      if (!admitted)
+        throw PluginError{2, "Attention (op " + std::to_string(op.id) +
+                                 "): only the INT8 lowering exists here (bf16, head dim 128, non-causal, "
+                                 "Implementation 2, DIFB200_INT8_ATTENTION not 0)"};
+      if (op.in.size() == 4) {
+        const auto it = producer.find(op.in[3]);
+        const ir::Tensor *bias = p.tensor(op.in[3]);
+        const bool fusable = it != producer.end() && p.ops[it->second].opcode == ir::BooleanMaskToBias &&
+                             !p.ops[it->second].boolean(ir::MaskQueries, true) &&
+                             p.tensor(p.ops[it->second].in[0])->dims.size() == 2 && consumers[op.in[3]] == 1 &&
+                             !bias->has(ir::Output);
+        if (!fusable)
+          throw PluginError{2, "Attention (op " + std::to_string(op.id) +
+                                   "): an additive bias is supported only as a key mask from "
+                                   "BooleanMaskToBias(MaskQueries=false) consumed by this op alone"};
+        st.mask_tensor = p.index_of(p.ops[it->second].in[0]);
+        exe.steps[it->second].skip = true;
+      }
+    } else if (op.opcode == ir::Linear) {
+      const ir::Tensor &x = *p.tensor(op.in[0]), &w = *p.tensor(op.in[1]);
+      if (2.0 * (double)x.dims[0] * (double)w.dims[0] * (double)w.dims[1] > 2.0e11)
+        throw PluginError{2, "Linear (op " + std::to_string(op.id) +
+                                 "): plain float Linear of this size is outside the quantized path; bind it "
+                                 "as QuantizeInt8Rows + LinearInt8Scaled"};
+    }
+  }
+}
+
+void allocate(Executable &exe) {
+  const ir::Program &p = exe.program;
+  exe.dev.assign(p.tensors.size(), nullptr);
+  // tensors produced only by skipped ops are never materialised
+  std::vector<bool> needed(p.tensors.size(), false);
+  for (size_t i = 0; i < p.tensors.size(); ++i)
+    if (p.tensors[i].has(ir::Input) || p.tensors[i].has(ir::Constant) || p.tensors[i].has(ir::Output))
+      needed[i] = true;
+  for (const Step &st : exe.steps) {
+    if (st.skip)
+      continue;
+    for (auto id : st.op->in) {
+      // the fused attention bias is the only input that is not read
+      if (st.op->opcode == ir::Attention && st.mask_tensor >= 0 && id == st.op->in[3])
+        continue;
+      needed[(size_t)p.index_of(id)] = true;
+    }
+    if (st.op->opcode == ir::LinearInt8Scaled) {
+      needed[(size_t)st.out_tensor] = true;
+      if (st.bias_tensor >= 0)
+        needed[(size_t)st.bias_tensor] = true;
+    } else {
+      for (auto id : st.op->out)
+        needed[(size_t)p.index_of(id)] = true;
+    }
+    if (st.mask_tensor >= 0)
+      needed[(size_t)st.mask_tensor] = true;
+  }
+  for (size_t i = 0; i < p.tensors.size(); ++i) {
+    if (!needed[i])
+      continue;
+    const size_t bytes = (size_t)p.tensors[i].bytes();
+    require_cuda(cudaMalloc(&exe.dev[i], bytes ? bytes : 16), "cudaMalloc(tensor)");
+    exe.resident_bytes += bytes;
+  }
+  size_t scratch = 0;
+  for (const Step &st : exe.steps) {
+    if (st.skip || st.op->opcode != ir::Attention)
+      continue;
+    const ir::Tensor &q = *p.tensor(st.op->in[0]);
+    const bool batched = q.dims.size() == 4;
+    const uint64_t B = batched ? q.dims[0] : 1, S = q.dims[batched ? 1 : 0], H = q.dims[batched ? 2 : 1];
+    const uint64_t KV = st.op->u64(ir::KvHeads, H);
+    const size_t need = attention_scratch_bytes(B, S, H, KV);
+    scratch = need > scratch ? need : scratch;
+  }
+  if (scratch) {
+    require_cuda(cudaMalloc(&exe.attn_scratch, scratch), "cudaMalloc(attention scratch)");
+    exe.attn_scratch_bytes = scratch;
+    exe.resident_bytes += scratch;
+  }
+  require_cuda(cudaMalloc(&exe.flag, sizeof(unsigned int)), "cudaMalloc(flag)");
+  require_cuda(cudaMemset(exe.flag, 0, sizeof(unsigned int)), "cudaMemset(flag)");
+}
+
+// ---- one pass over the program ---------------------------------------------------------------
+void run_steps(Executable &exe) {
+  const ir::Program &p = exe.program;
+  cudaStream_t s = exe.ctx->stream;
+  auto D = [&](uint32_t id) -> void * { return exe.dev[(size_t)p.index_of(id)]; };
+  auto T = [&](uint32_t id) -> const ir::Tensor & { return *p.tensor(id); };
+  for (const Step &st : exe.steps) {
+    if (st.skip)
+      continue;
+    const ir::Op &op = *st.op;
+    switch (op.opcode) {
+    case ir::QuantizeInt8Rows: {
+      const bool dynamic = T(op.in.back()).dtype == ir::F32;
+      const size_t n_data = op.in.size() - (dynamic ? 1 : 0);
+      const void *parts[8];
+      uint64_t widths[8];
+      for (size_t k = 0; k < n_data; ++k) {
+        parts[k] = D(op.in[k]);
+        widths[k] = T(op.in[k]).last();
+      }
+      const bool residual = op.out.size() == 4;
+      require(quantize_int8_rows(parts, widths, (uint32_t)n_data, T(op.in[0]).rows(),
+                                 (int)op.u64(ir::Implementation, 1), (float)op.f64(ir::Scale, 1.0),
+                                 dynamic ? static_cast<const float *>(D(op.in.back())) : nullptr,
+                                 static_cast<int8_t *>(D(op.out[0])), static_cast<float *>(D(op.out[1])),
+                                 residual ? static_cast<int8_t *>(D(op.out[2])) : nullptr,
+                                 residual ? static_cast<float *>(D(op.out[3])) : nullptr, s));
+      break;
+    }
+    case ir::LinearInt8Scaled: {
+      const ir::Tensor &x = T(op.in[0]), &w = T(op.in[1]);
+      require(linear_int8_scaled(static_cast<const int8_t *>(D(op.in[0])), static_cast<const int8_t *>(D(op.in[1])),
+                                 static_cast<const float *>(D(op.in[2])), static_cast<const float *>(D(op.in[3])),
+                                 st.bias_tensor >= 0 ? exe.dev[(size_t)st.bias_tensor] : nullptr, st.epilogue,
+                                 x.rows(), w.dims[0], w.dims[1], exe.dev[(size_t)st.out_tensor], nullptr, s));
+      break;
+    }
+    case ir::Attention: {
+      const ir::Tensor &q = T(op.in[0]);
+      const bool batched = q.dims.size() == 4;
+      const uint64_t B = batched ? q.dims[0] : 1, S = q.dims[batched ? 1 : 0], H = q.dims[batched ? 2 : 1];
+      const uint64_t KV = op.u64(ir::KvHeads, H);
+      const float scale = (float)op.f64(ir::AttentionScale, 1.0 / std::sqrt((double)q.last()));
+      require(attention_bf16_via_int8(D(op.in[0]), D(op.in[1]), D(op.in[2]),
+                                      st.mask_tensor >= 0 ? static_cast<const uint8_t *>(exe.dev[(size_t)st.mask_tensor])
+                                                          : nullptr,
+                                      B, S, H, KV, q.last(), scale, exe.attn_scratch, exe.attn_scratch_bytes,
+                                      D(op.out[0]), s));
+      break;
+    }
+    case ir::Add:
+    case ir::Multiply:
+      require(glue::binary(D(op.in[0]), D(op.in[1]), D(op.out[0]), T(op.in[0]).dtype, T(op.in[0]).elements(),
+                           op.opcode == ir::Multiply, s));
+      break;
+    case ir::Gelu:
+      require(glue::unary(D(op.in[0]), D(op.out[0]), T(op.in[0]).dtype, T(op.out[0]).dtype, T(op.in[0]).elements(),
+                          op.u64(ir::Approximation, 1) == 2 ? 2 : 1, s));
+      break;
+    case ir::SiLU:
+    case ir::Sigmoid:
+    case ir::Cast:
+      require(glue::unary(D(op.in[0]), D(op.out[0]), T(op.in[0]).dtype, T(op.out[0]).dtype, T(op.in[0]).elements(),
+                          op.opcode == ir::SiLU ? 3 : (op.opcode == ir::Sigmoid ? 4 : 0), s));
+      break;
+    case ir::BiasAdd:
+      require(glue::bias_add(D(op.in[0]), D(op.in[1]), D(op.out[0]), T(op.in[0]).dtype, T(op.in[0]).elements(),
+                             T(op.in[0]).last(), s));
+      break;
+    case ir::AffineLastDim:
+      require(glue::affine_last_dim(D(op.in[0]), D(op.in[1]), op.in.size() == 3 ? D(op.in[2]) : nullptr, D(op.out[0]),
+                                    T(op.in[0]).dtype, T(op.in[0]).elements(), T(op.in[0]).last(), s));
+      break;
+    case ir::Fill:
+      require(glue::fill(D(op.out[0]), T(op.out[0]).dtype, T(op.out[0]).elements(), (float)op.f64(ir::Value, 0.0), s));
+      break;
+    case ir::RmsNorm:
+      require(glue::rms_norm(D(op.in[0]), D(op.in[1]), D(op.out[0]), T(op.in[0]).dtype, T(op.in[0]).rows(),
+                             T(op.in[0]).last(), (float)op.f64(ir::Epsilon, 1.0e-5),
+                             (float)op.f64(ir::WeightOffset, 0.0), s));
+      break;
+    case ir::LayerNormModulate:
+      require(glue::layer_norm_modulate(D(op.in[0]), D(op.in[1]), D(op.in[2]), D(op.in[3]), D(op.in[4]), D(op.out[0]),
+                                        T(op.in[0]).dtype, T(op.in[0]).rows(), T(op.in[0]).last(),
+                                        T(op.in[0]).rows() / T(op.in[3]).rows(), (float)op.f64(ir::Epsilon, 1.0e-5), s));
+      break;
+    case ir::RmsNormModulate: {
+      const ir::Tensor &x = T(op.in[0]);
+      const float eps = (float)op.f64(ir::Epsilon, 1.0e-5);
+      if (op.u64(ir::ModulationLayout, 1) == 2) {
+        require(glue::rms_norm_modulate(D(op.in[0]), D(op.in[1]), D(op.in[2]), D(op.in[3]), D(op.out[0]), x.dtype,
+                                        x.dims[0], x.dims[1], eps, (float)op.f64(ir::WeightOffset, 0.0), true,
+                                        x.dims[0] / T(op.in[2]).dims[0], s));
+      } else {
+        const bool weighted = op.in.size() == 4;
+        require(glue::rms_norm_modulate(D(op.in[0]), weighted ? D(op.in[1]) : nullptr, D(op.in[weighted ? 2 : 1]),
+                                        D(op.in[weighted ? 3 : 2]), D(op.out[0]), x.dtype, x.dims[0], x.dims[1], eps,
+                                        0.0f, false, 1, s));
+      }
+      break;
+    }
+    case ir::QkNormPartialRope: {
+      const ir::Tensor &x = T(op.in[0]), &c = T(op.in[2]);
+      const uint64_t dim = x.last(), heads = x.dims[x.dims.size() - 2];
+      const uint64_t tokens = x.elements() / (heads * dim);
+      const uint64_t input_seq = x.dims.size() == 4 ? x.dims[1] : x.dims[0];
+      const uint64_t table_seq = c.dims.size() == 3 ? c.dims[1] : c.dims[0];
+      const bool v2 = op.u64(ir::Implementation, 1) == 2 && op.u64(ir::RotaryLayout, 2) == 1;
+      require(glue::qk_norm_rope(D(op.in[0]), D(op.in[1]), D(op.in[2]), D(op.in[3]), D(op.out[0]), x.dtype, c.dtype,
+                                 tokens, heads, dim, op.u64(ir::RotaryDim, dim), c.last(), input_seq, table_seq,
+                                 op.u64(ir::Start, 0), (float)op.f64(ir::Epsilon, 1.0e-5), v2, s));
+      break;
+    }
+    case ir::RotaryFrequency: {
+      const ir::Tensor &pos = T(op.in[0]);
+      require(glue::rotary_frequency(static_cast<const float *>(D(op.in[0])), static_cast<const int32_t *>(D(op.in[1])),
+                                     static_cast<const int32_t *>(D(op.in[2])), static_cast<const int32_t *>(D(op.in[3])),
+                                     static_cast<float *>(D(op.out[0])), static_cast<float *>(D(op.out[1])),
+                                     pos.dims[0] * pos.dims[1], pos.dims[2], T(op.in[1]).dims[0],
+                                     op.f64(ir::Theta, 10000.0) * op.f64(ir::Ntk, 1.0), exe.flag, s));
+      break;
+    }
+    case ir::RotaryApply: {
+      const ir::Tensor &x = T(op.in[0]);
+      require(glue::rotary_apply(D(op.in[0]), static_cast<const float *>(D(op.in[1])),
+                                 static_cast<const float *>(D(op.in[2])), D(op.out[0]), x.dtype,
+                                 x.dims[0] * x.dims[1], x.dims[2], x.dims[3], T(op.in[1]).dims[2], s));
+      break;
+    }
+    case ir::ResidualGate: {
+      const ir::Tensor &r = T(op.in[0]);
+      require(glue::residual_gate(D(op.in[0]), D(op.in[1]), D(op.in[2]), D(op.out[0]), r.dtype, r.elements(), r.last(),
+                                  r.rows() / T(op.in[2]).rows(), s));
+      break;
+    }
+    case ir::SwiGlu: {
+      const ir::Tensor &o = T(op.out[0]);
+      require(glue::swiglu(D(op.in[0]), D(op.out[0]), o.dtype, o.rows(), o.last(), T(op.in[0]).last(),
+                           op.u64(ir::Start, 0), op.boolean(ir::GateFirst, false), s));
+      break;
+    }
+    case ir::Reshape:
+      require_cuda(cudaMemcpyAsync(D(op.out[0]), D(op.in[0]), (size_t)T(op.out[0]).bytes(), cudaMemcpyDeviceToDevice, s),
+                   "cudaMemcpyAsync(reshape)");
+      break;
+    case ir::BroadcastTo:
+    case ir::Slice: {
+      const ir::Tensor &x = T(op.in[0]), &o = T(op.out[0]);
+      uint64_t in_strides[8] = {0}, full[8] = {0};
+      const size_t rank = o.dims.size(), pad = rank - x.dims.size();
+      uint64_t stride = 1;
+      for (size_t a = x.dims.size(); a-- > 0;) {
+        full[a] = stride;
+        stride *= x.dims[a];
+      }
+      uint64_t offset = 0;
+      for (size_t a = 0; a < rank; ++a) {
+        if (a < pad)
+          in_strides[a] = 0;
+        else
+          in_strides[a] = (op.opcode == ir::BroadcastTo && x.dims[a - pad] == 1) ? 0 : full[a - pad];
+      }
+      if (op.opcode == ir::Slice)
+        offset = op.u64(ir::Start, 0) * full[op.u64(ir::Axis, 0)];
+      require(glue::gather(D(op.in[0]), D(op.out[0]), (uint32_t)ir::dtype_size(o.dtype), (uint32_t)rank,
+                           o.dims.data(), in_strides, offset, s));
+      break;
+    }
+    case ir::Concat: {
+      const ir::Tensor &o = T(op.out[0]);
+      const uint64_t axis = op.u64(ir::Axis, 0);
+      uint64_t outer = 1, inner = 1;
+      for (size_t a = 0; a < axis; ++a)
+        outer *= o.dims[a];
+      for (size_t a = axis + 1; a < o.dims.size(); ++a)
+        inner *= o.dims[a];
+      uint64_t offset = 0;
+      for (auto id : op.in) {
+        const uint64_t chunk = T(id).dims[axis] * inner;
+        require(glue::concat_part(D(id), D(op.out[0]), (uint32_t)ir::dtype_size(o.dtype), outer, chunk,
+                                  o.dims[axis] * inner, offset, s));
+        offset += chunk;
+      }
+      break;
+    }
+    case ir::BooleanMaskToBias: {
+      const ir::Tensor &m = T(op.in[0]), &o = T(op.out[0]);
+      require(glue::mask_to_bias(static_cast<const uint8_t *>(D(op.in[0])), D(op.out[0]), o.dtype, o.dims[0], o.dims[2],
+                                 m.dims.size() == 2, op.boolean(ir::MaskQueries, true), s));
+      break;
+    }
+    case ir::Linear: {
+      const ir::Tensor &x = T(op.in[0]), &w = T(op.in[1]);
+      require(glue::linear(D(op.in[0]), D(op.in[1]), op.in.size() == 3 ? D(op.in[2]) : nullptr, D(op.out[0]), x.dtype,
+                           x.dims[0], w.dims[0], w.dims[1], s));
+      break;
+    }
+    default:
+      throw PluginError{2, std::string("unsupported opcode ") + ir::opcode_name(op.opcode)};
+    }
+  }
+}
+
+// ---- ABI functions ----------------------------------------------------------------------------
+template <typename F>
+dif_backend_status guarded(dif_backend_error *error, F &&body) {
+  try {
+    body();
+    return DIF_BACKEND_OK;
+  } catch (const PluginError &e) {
+    write_error(error, e.text);
+    return status_of(e.status);
+  } catch (const std::bad_alloc &) {
+    write_error(error, "host allocation failed");
+    return DIF_BACKEND_OUT_OF_MEMORY;
+  } catch (const std::exception &e) {
+    write_error(error, std::string("internal error: ") + e.what());
+    return DIF_BACKEND_INTERNAL_ERROR;
+  } catch (...) {
+    write_error(error, "internal error");
+    return DIF_BACKEND_INTERNAL_ERROR;
+  }
+}
+
+dif_backend_status create(int32_t device_ordinal, dif_backend_context *context, dif_backend_error *error) {
+  return guarded(error, [&] {
+    if (!context)
+      throw PluginError{1, "create: null context pointer"};
+    *context = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+      throw PluginError{2, "no CUDA device is available (this backend has no CPU path)"};
+    if (device_ordinal < 0 || device_ordinal >= count)
+      throw PluginError{1, "create: device ordinal out of range"};
+    cudaDeviceProp prop{};
+    require_cuda(cudaGetDeviceProperties(&prop, device_ordinal), "cudaGetDeviceProperties");
+    if (prop.major != 10)
+      throw PluginError{2, std::string("device '") + prop.name + "' is not sm_100 (B200); this backend is sm_100a only"};
+    auto ctx = std::make_unique<Context>();
+    ctx->device = device_ordinal;
+    require_cuda(cudaSetDevice(device_ordinal), "cudaSetDevice");
+    require_cuda(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate");
+    std::snprintf(ctx->device_name, sizeof(ctx->device_name), "%s (difb200 sm_100a, int8-attention %s)", prop.name,
+                  int8_attention_enabled() ? "on" : "off");
+    *context = ctx.release();
+  });
+}
+
+void destroy(dif_backend_context context) {
+  Context *ctx = static_cast<Context *>(context);
+  if (!ctx)
+    return;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream)
+    cudaStreamDestroy(ctx->stream);
+  delete ctx;
+}
+
+void upload(Executable &exe, const dif_backend_tensor_view &view, uint32_t role, const char *what) {
+  const int idx = exe.program.index_of(view.tensor_id);
+  if (idx < 0)
+    throw PluginError{1, std::string(what) + ": unknown tensor id " + std::to_string(view.tensor_id)};
+  const ir::Tensor &t = exe.program.tensors[(size_t)idx];
+  if (!t.has(role) || view.dtype != t.dtype || view.byte_count != t.bytes() || (!view.host_data && t.bytes()))
+    throw PluginError{1, std::string(what) + ": tensor " + std::to_string(view.tensor_id) +
+                             " does not match the program (role, dtype or byte count)"};
+  if (exe.dev[(size_t)idx] && t.bytes())
+    require_cuda(cudaMemcpyAsync(exe.dev[(size_t)idx], view.host_data, (size_t)t.bytes(), cudaMemcpyHostToDevice,
+                                 exe.ctx->stream),
+                 "cudaMemcpyAsync(host to device)");
+}
+
+dif_backend_status compile_common(dif_backend_context context, const uint8_t *diffir, size_t size,
+                                  const dif_backend_tensor_view *constants, size_t constant_count, bool v2,
+                                  uint64_t minimum_free, dif_backend_executable *executable,
+                                  dif_backend_compile_telemetry_v2 *telemetry, dif_backend_error *error) {
+  return guarded(error, [&] {
+    Context *ctx = static_cast<Context *>(context);
+    if (!ctx || !diffir || !executable)
+      throw PluginError{1, "compile: null argument"};
+    *executable = nullptr;
+    require_cuda(cudaSetDevice(ctx->device), "cudaSetDevice");
+    cudaEvent_t e0, e1;
+    require_cuda(cudaEventCreate(&e0), "cudaEventCreate");
+    require_cuda(cudaEventCreate(&e1), "cudaEventCreate");
+    cudaEventRecord(e0, ctx->stream);
+    size_t free_before = 0, total = 0;
+    cudaMemGetInfo(&free_before, &total);
+    auto exe = std::make_unique<Executable>();
+    exe->ctx = ctx;
+    std::string text;
+    if (int rc = ir::decode(diffir, size, exe->program, text))
+      throw PluginError{rc == 2 ? 2 : 4, "DiffIR: " + text};
+    plan(*exe);
+    allocate(*exe);
+    if (v2) {
+      size_t expected = 0;
+      for (const auto &t : exe->program.tensors)
+        expected += t.has(ir::Constant) ? 1 : 0;
+      if (constant_count != expected || (expected && !constants))
+        throw PluginError{1, "compile: expected " + std::to_string(expected) + " constant views, got " +
+                                 std::to_string(constant_count)};
+      for (size_t i = 0; i < constant_count; ++i)
+        upload(*exe, constants[i], ir::Constant, "compile");
+      exe->constants_bound = true;
+    }
+    require_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    size_t free_after = 0;
+    cudaMemGetInfo(&free_after, &total);
+    if (free_after < minimum_free)
+      throw PluginError{3, "compile: free device memory fell below minimum_free_bytes"};
+    cudaEventRecord(e1, ctx->stream);
+    cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (telemetry) {
+      telemetry->preparation_milliseconds = ms;
+      telemetry->resident_bytes = exe->resident_bytes;
+      telemetry->free_bytes_before = free_before;
+      telemetry->free_bytes_after = free_after;
+      std::memcpy(telemetry->device_name, ctx->device_name, sizeof(telemetry->device_name));
+    }
+    *executable = exe.release();
+  });
+}
+
+dif_backend_status compile_v2(dif_backend_context context, const uint8_t *diffir, size_t size,
+                              const dif_backend_tensor_view *constants, size_t constant_count,
+                              const dif_backend_compile_options_v2 *options, dif_backend_executable *executable,
+                              dif_backend_compile_telemetry_v2 *telemetry, dif_backend_error *error) {
+  return compile_common(context, diffir, size, constants, constant_count, true,
+                        options ? options->minimum_free_bytes : 0, executable, telemetry, error);
+}
+dif_backend_status compile_v1(dif_backend_context context, const uint8_t *diffir, size_t size,
+                              dif_backend_executable *executable, dif_backend_error *error) {
+  return compile_common(context, diffir, size, nullptr, 0, false, 0, executable, nullptr, error);
+}
+
+void destroy_executable(dif_backend_executable executable) { delete static_cast<Executable *>(executable); }
+
+dif_backend_status execute(dif_backend_executable executable, const dif_backend_tensor_view *inputs,
+                           size_t input_count, dif_backend_tensor_view *outputs, size_t output_count,
+                           const dif_backend_run_options *options, dif_backend_telemetry *telemetry,
+                           dif_backend_error *error) {
+  return guarded(error, [&] {
+    Executable *exe = static_cast<Executable *>(executable);
+    if (!exe || !options || (input_count && !inputs) || (output_count && !outputs))
+      throw PluginError{1, "execute: null argument"};
+    if (options->iterations == 0)
+      throw PluginError{1, "execute: iterations must be positive"};
+    Context *ctx = exe->ctx;
+    require_cuda(cudaSetDevice(ctx->device), "cudaSetDevice");
+    size_t free_before = 0, total = 0;
+    cudaMemGetInfo(&free_before, &total);
+    if (free_before < options->minimum_free_bytes)
+      throw PluginError{3, "execute: free device memory is below minimum_free_bytes"};
+    // v2: exactly the Input-role tensors; v1: Inputs followed by Constants
+    size_t n_in = 0, n_const = 0, n_out = 0;
+    for (const auto &t : exe->program.tensors) {
+      n_in += t.has(ir::Input) ? 1 : 0;
+      n_const += t.has(ir::Constant) ? 1 : 0;
+      n_out += t.has(ir::Output) ? 1 : 0;
+    }
+    const size_t expected = exe->constants_bound ? n_in : n_in + n_const;
+    if (input_count != expected)
+      throw PluginError{1, "execute: expected " + std::to_string(expected) + " input views, got " +
+                               std::to_string(input_count)};
+    for (size_t i = 0; i < input_count; ++i) {
+      const int idx = exe->program.index_of(inputs[i].tensor_id);
+      const bool is_const = idx >= 0 && exe->program.tensors[(size_t)idx].has(ir::Constant);
+      upload(*exe, inputs[i], is_const ? ir::Constant : ir::Input, "execute");
+    }
+    for (uint32_t w = 0; w < options->warmups; ++w)
+      run_steps(*exe);
+    cudaEvent_t e0, e1;
+    require_cuda(cudaEventCreate(&e0), "cudaEventCreate");
+    require_cuda(cudaEventCreate(&e1), "cudaEventCreate");
+    double sum = 0.0, lo = std::numeric_limits<double>::max(), hi = 0.0;
+    for (uint32_t it = 0; it < options->iterations; ++it) {
+      cudaEventRecord(e0, ctx->stream);
+      run_steps(*exe);
+      cudaEventRecord(e1, ctx->stream);
+      require_cuda(cudaEventSynchronize(e1), "cudaEventSynchronize");
+      float ms = 0.0f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      sum += ms;
+      lo = ms < lo ? ms : lo;
+      hi = ms > hi ? ms : hi;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (output_count > n_out)
+      throw PluginError{1, "execute: more output views than Output-role tensors"};
+    for (size_t i = 0; i < output_count; ++i) {
+      const int idx = exe->program.index_of(outputs[i].tensor_id);
+      if (idx < 0 || !exe->program.tensors[(size_t)idx].has(ir::Output) ||
+          outputs[i].byte_count != exe->program.tensors[(size_t)idx].bytes() ||
+          (!outputs[i].host_data && outputs[i].byte_count))
+        throw PluginError{1, "execute: output view " + std::to_string(outputs[i].tensor_id) +
+                                 " does not match an Output-role tensor"};
+      if (outputs[i].byte_count)
+        require_cuda(cudaMemcpyAsync(outputs[i].host_data, exe->dev[(size_t)idx], (size_t)outputs[i].byte_count,
+                                     cudaMemcpyDeviceToHost, ctx->stream),
+                     "cudaMemcpyAsync(device to host)");
+    }
+    unsigned int flag = 0;
+    require_cuda(cudaMemcpyAsync(&flag, exe->flag, sizeof(flag), cudaMemcpyDeviceToHost, ctx->stream),
+                 "cudaMemcpyAsync(flag)");
+    require_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    if (flag) {
+      cudaMemset(exe->flag, 0, sizeof(flag));
+      throw PluginError{5, "RotaryFrequency pair map is outside its declared axis"};
+    }
+    require(poll_device_status("execute"));
+    if (telemetry) {
+      size_t free_after = 0;
+      cudaMemGetInfo(&free_after, &total);
+      telemetry->mean_milliseconds = sum / options->iterations;
+      telemetry->minimum_milliseconds = lo;
+      telemetry->maximum_milliseconds = hi;
+      telemetry->free_bytes_before = free_before;
+      telemetry->free_bytes_after = free_after;
+      std::memcpy(telemetry->device_name, ctx->device_name, sizeof(telemetry->device_name));
+    }
+  });
+}
+
+const uint64_t kCapabilities = DIF_BACKEND_CAP_F32 | DIF_BACKEND_CAP_BF16 | DIF_BACKEND_CAP_F16 | DIF_BACKEND_CAP_I8;
+
+const dif_backend_api_v1 kApiV1 = {sizeof(dif_backend_api_v1), DIF_BACKEND_ABI_VERSION_V1, "difb200", kCapabilities,
+                                   create, destroy, compile_v1, destroy_executable, execute};
+const dif_backend_api_v2 kApiV2 = {sizeof(dif_backend_api_v2), DIF_BACKEND_ABI_VERSION_V2, "difb200", kCapabilities,
+                                   create, destroy, compile_v2, destroy_executable, execute};
+
+} // namespace
+} // namespace difb200
+
+extern "C" {
+const dif_backend_api_v1 *dif_backend_get_v1(void) { return &difb200::kApiV1; }
+const dif_backend_api_v2 *dif_backend_get_v2(void) { return &difb200::kApiV2; }
+}

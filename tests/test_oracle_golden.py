@@ -1,0 +1,128 @@
+"""CPU: the C restatement (oracle/diforacle.c) against the committed vectors that the reference's
+own CPU executor produced (tests/golden/hotpath_golden.npz, generator make_golden.py), and, where
+the reference build is present, directly against it on fresh seeded inputs. Also the DIFIR001
+codec against the reference's decoder/encoder."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_bridge as ob
+from diffusion_compiler_b200 import diffir as ir
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "hotpath_golden.npz"))
+
+
+def _eq(a, b):
+    return np.array_equal(np.ascontiguousarray(a).view(np.uint8).ravel(), np.ascontiguousarray(b).view(np.uint8).ravel())
+
+
+def test_reference_unit_test_linear_vectors():
+    g = GOLDEN
+    codes, scales = ob.orc().quantize_int8_rows([g["reftest_linear/x"]], 1, 0.98)
+    assert _eq(codes, g["reftest_linear/codes"]) and _eq(scales, g["reftest_linear/row_scales"])
+    y = ob.orc().linear_int8_scaled(codes, g["reftest_linear/w"], scales, g["reftest_linear/cs"])
+    assert _eq(y, g["reftest_linear/y"])
+
+
+@pytest.mark.parametrize("impl", [2, 3, 5, 6])
+def test_reference_unit_test_h256_vectors(impl):
+    clip = 0.9995 if impl in (5, 6) else 1.0
+    got = ob.orc().quantize_int8_rows([GOLDEN["reftest_h256/x"]], impl, np.float32(clip), residual=True)
+    for name, a in zip(("codes", "scales", "rcodes", "rscales"), got):
+        assert _eq(a, GOLDEN["reftest_h256/impl%d_%s" % (impl, name)]), name
+
+
+@pytest.mark.parametrize("impl", [4, 7])
+def test_reference_unit_test_h4096_vectors(impl):
+    codes, scales = ob.orc().quantize_int8_rows([GOLDEN["reftest_h4096/x"]], impl)
+    assert _eq(codes, GOLDEN["reftest_h4096/impl%d_codes" % impl])
+    assert _eq(scales, GOLDEN["reftest_h4096/impl%d_scales" % impl])
+
+
+@pytest.mark.parametrize("impl", range(1, 8))
+def test_seeded_quant_vectors(impl):
+    x = GOLDEN["seeded_quant/impl%d_x" % impl]
+    K = x.shape[1]
+    parts = [np.ascontiguousarray(x[:, :K // 2]), np.ascontiguousarray(x[:, K // 2:])]
+    got = ob.orc().quantize_int8_rows(parts, impl, 0.97, residual=True)
+    for name, a in zip(("codes", "scales", "rcodes", "rscales"), got):
+        assert _eq(a, GOLDEN["seeded_quant/impl%d_%s" % (impl, name)]), name
+
+
+def test_seeded_linear_vectors():
+    g = GOLDEN
+    w8, ws = ob.orc().quantize_int8_rows([g["seeded_linear/w_bf16"]], 2)
+    assert _eq(w8, g["seeded_linear/w8"]) and _eq(ws, g["seeded_linear/ws"])
+    codes, scales = ob.orc().quantize_int8_rows([g["seeded_linear/x"]], 2)
+    assert _eq(codes, g["seeded_linear/codes"]) and _eq(scales, g["seeded_linear/row_scales"])
+    yb = ob.orc().bias_add(ob.orc().linear_int8_scaled(codes, w8, scales, ws), g["seeded_linear/bias"])
+    assert _eq(yb, g["seeded_linear/y_bias"])
+    assert _eq(ob.orc().gelu_tanh(yb), g["seeded_linear/y_gelu"])
+
+
+def test_seeded_attention_vectors():
+    g = GOLDEN
+    out = ob.orc().attention_exact(g["seeded_attention/q"], g["seeded_attention/k"], g["seeded_attention/v"],
+                                   g["seeded_attention/mask"])
+    assert _eq(out, g["seeded_attention/out_exact"])
+
+
+def test_int8_attention_contract_tracks_exact_attention():
+    """The INT8 contract (ours) stays within the reference's own bar for its INT8 attention,
+    cosine >= 0.9999 against exact attention (reference tests/owned_attention_tests.cpp:122-157)."""
+    rng = np.random.default_rng(1)
+    B, S, H, KV, D = 1, 192, 2, 1, 128
+    one = ob.f32_to_bf16(np.ones(D, np.float32))
+    q = ob.orc().rms_norm(ob.f32_to_bf16(rng.standard_normal((B, S, H, D)).astype(np.float32)), one, 1e-6)
+    k = ob.orc().rms_norm(ob.f32_to_bf16(rng.standard_normal((B, S, KV, D)).astype(np.float32)), one, 1e-6)
+    v = ob.f32_to_bf16(rng.standard_normal((B, S, KV, D)).astype(np.float32))
+    q8, qs = ob.orc().quantize_int8_rows([q.reshape(-1, D)], 1)
+    k8, ks = ob.orc().quantize_int8_rows([k.reshape(-1, D)], 1)
+    a = ob.bf16_to_f32(ob.orc().attention_int8(q8.reshape(B, S, H, D), qs, k8.reshape(B, S, KV, D), ks, v))
+    e = ob.bf16_to_f32(ob.orc().attention_exact(q, k, v))
+    cos = float(np.dot(a.ravel(), e.ravel()) / (np.linalg.norm(a) * np.linalg.norm(e)))
+    assert cos >= 0.9999
+
+
+def test_thread_count_does_not_change_results():
+    rng = np.random.default_rng(3)
+    x = ob.f32_to_bf16(rng.standard_normal((33, 768)).astype(np.float32))
+    ob.orc().lib.orc_set_threads(1)
+    a = ob.orc().quantize_int8_rows([x], 3)
+    ob.orc().lib.orc_set_threads(5)
+    b = ob.orc().quantize_int8_rows([x], 3)
+    ob.orc().lib.orc_set_threads(1)
+    assert _eq(a[0], b[0]) and _eq(a[1], b[1])
+
+
+def test_codec_roundtrip():
+    pr = ir.w8a8_linear_program(8, 256, 16, 2, bias=True, gelu=True)["program"]
+    data = ir.encode(pr)
+    again = ir.decode(data)
+    assert ir.encode(again) == data
+    with pytest.raises(ValueError):
+        ir.decode(data[:-1] + bytes([data[-1] ^ 1]))
+    with pytest.raises(ValueError):
+        ir.decode(b"XXXXXXXX" + data[8:])
+
+
+@pytest.mark.skipif(not ob.ref_available(), reason="reference build (oracle/_ref) not present")
+def test_codec_against_reference_decoder():
+    for pr in (ir.w8a8_linear_program(8, 256, 16, 5, bias=True, gelu=True),
+               ir.quantize_program([3, 512], 3, residual=True, dynamic_clip=True),
+               ir.attention_program(2, 16, 4, 2, 128, True)):
+        ob.ref().encode_check(ir.encode(pr["program"]))
+
+
+@pytest.mark.skipif(not ob.ref_available(), reason="reference build (oracle/_ref) not present")
+@pytest.mark.parametrize("impl", range(1, 8))
+def test_restatement_equals_reference_on_fresh_inputs(impl):
+    rng = np.random.default_rng(50 + impl)
+    K = 4096 if impl in (4, 7) else 768
+    x = ob.f32_to_bf16((rng.standard_normal((7, K)) * rng.uniform(0.01, 30)).astype(np.float32))
+    pr = ir.quantize_program([7, K], impl, clip=0.9, residual=True)
+    res, _ = ob.ref().run(pr["program"], {pr["ids"]["x"][0]: x})
+    got = ob.orc().quantize_int8_rows([x], impl, 0.9, residual=True)
+    for name, a in zip(("codes", "scales", "rcodes", "rscales"), got):
+        assert _eq(a, res[pr["ids"][name]]), name
