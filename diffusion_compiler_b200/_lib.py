@@ -40,11 +40,20 @@ def lib() -> C.CDLL:
         L.difb200_attention_int8_scratch_bytes.restype = u64
         L.difb200_attention_int8_scratch_bytes.argtypes = [u64, u64, u64]
         L.difb200_attention_int8.restype = C.c_int
-        L.difb200_attention_int8.argtypes = [vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, f32, vp, u64, vp, vp]
+        L.difb200_attention_int8.argtypes = [vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, u64, f32, vp, u64, vp, vp]
         L.difb200_attention_scratch_bytes.restype = u64
         L.difb200_attention_scratch_bytes.argtypes = [u64, u64, u64, u64]
         L.difb200_attention.restype = C.c_int
         L.difb200_attention.argtypes = [vp, vp, vp, vp, u64, u64, u64, u64, u64, f32, vp, u64, vp, vp]
+        for name, args in (
+                ("difb200_rms_norm_modulate", [vp, vp, vp, vp, vp, u32, u64, u64, f32, vp]),
+                ("difb200_layer_norm_modulate", [vp, vp, vp, vp, vp, vp, u32, u64, u64, u64, f32, vp]),
+                ("difb200_qk_norm_rope", [vp, vp, vp, vp, vp, u32, u32, u64, u64, u64, u64, u64, u64, u64, u64, f32,
+                                          i32, vp]),
+                ("difb200_residual_gate", [vp, vp, vp, vp, u32, u64, u64, u64, vp]),
+                ("difb200_swiglu", [vp, vp, u32, u64, u64, u64, u64, i32, vp])):
+            getattr(L, name).restype = C.c_int
+            getattr(L, name).argtypes = args
         _lib = L
     return _lib
 

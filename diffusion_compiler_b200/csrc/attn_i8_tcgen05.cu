@@ -48,7 +48,7 @@ struct AttnParams {
   const float *qs;       // [B,S,H]
   const float2 *ksmb;    // [B,KV,S_pad] (key scale, mask bias)
   uint16_t *out;         // [B,S,H,128] bf16
-  uint32_t B, S, H, KV, S_pad;
+  uint32_t B, Sq, Sk, H, KV, S_pad; // Sq query tokens, Sk key tokens (S_pad = Sk rounded up to 128)
   float scale_log2e;     // scale * log2(e)
   DeviceStatus *status;
 };
@@ -119,13 +119,13 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   volatile uint32_t *abort_ptr = slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t q_blocks = (p.S + 255u) / 256u;
+  const uint32_t q_blocks = (p.Sq + 255u) / 256u;
   const uint32_t qb = blockIdx.x % q_blocks;
   const uint32_t head = (blockIdx.x / q_blocks) % p.H;
   const uint32_t batch = blockIdx.x / (q_blocks * p.H);
   const uint32_t kvh = head / (p.H / p.KV);
   const uint32_t q0 = qb * 256u;
-  const uint32_t n_kv = (p.S + kTile - 1) / kTile;
+  const uint32_t n_kv = (p.Sk + kTile - 1) / kTile;
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
@@ -276,8 +276,8 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t quarter = (uint32_t)warp & 3u;
     const uint32_t row_in_tile = quarter * 32u + lane;
     const uint32_t qrow = q0 + t * 128u + row_in_tile;
-    const bool row_ok = qrow < p.S;
-    const float A = (row_ok ? __ldg(p.qs + ((uint64_t)batch * p.S + qrow) * p.H + head) : 1.0f) *
+    const bool row_ok = qrow < p.Sq;
+    const float A = (row_ok ? __ldg(p.qs + ((uint64_t)batch * p.Sq + qrow) * p.H + head) : 1.0f) *
                     p.scale_log2e;
     const uint32_t lane_base = (quarter * 32u) << 16;
     const uint32_t s_tmem = tmem + lane_base + t * 128u, o_tmem = tmem + lane_base + 256u + t * 128u;
@@ -383,7 +383,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         *abort_ptr = 1;
       } else {
         ptx::tc_fence_after();
-        uint16_t *dst = p.out + (((uint64_t)batch * p.S + qrow) * p.H + head) * kTile;
+        uint16_t *dst = p.out + (((uint64_t)batch * p.Sq + qrow) * p.H + head) * kTile;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
@@ -423,17 +423,21 @@ size_t attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV) {
 }
 
 int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks, const void *v_bf16,
-                   const uint8_t *key_valid, uint64_t B, uint64_t S, uint64_t H, uint64_t KV, uint64_t D,
-                   float scale, void *scratch, size_t scratch_bytes, void *out_bf16, cudaStream_t stream) {
+                   const uint8_t *key_valid, uint64_t B, uint64_t Sq, uint64_t S, uint64_t H, uint64_t KV,
+                   uint64_t D, float scale, void *scratch, size_t scratch_bytes, void *out_bf16,
+                   cudaStream_t stream) {
+  // S is the number of key/value tokens from here on; Sq the number of query tokens.
   if (!q8 || !qs || !k8 || !ks || !v_bf16 || !out_bf16 || !scratch)
     return fail(kInvalidArgument, "Attention(INT8): null pointer");
   if (D != 128)
     return fail(kUnsupported, "Attention(INT8): head dimension must be 128");
-  if (B == 0 || S == 0 || H == 0)
+  if (B == 0 || Sq == 0 || H == 0)
     return kOk;
+  if (S == 0)
+    return fail(kInvalidArgument, "Attention(INT8): no keys");
   if (KV == 0 || H % KV != 0)
     return fail(kInvalidArgument, "Attention(INT8): KvHeads must divide the head count");
-  if (B * H * ((S + 255) / 256) > 0x7fffffffull || S > 0x7fffff00ull)
+  if (B * H * ((Sq + 255) / 256) > 0x7fffffffull || S > 0x7fffff00ull || Sq > 0x7fffff00ull)
     return fail(kUnsupported, "Attention(INT8): problem too large");
   if (scratch_bytes < attention_int8_scratch_bytes(B, S, KV))
     return fail(kInvalidArgument, "Attention(INT8): scratch buffer too small");
@@ -448,8 +452,8 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
 
   CUtensorMap map_q, map_k, map_v;
   {
-    const uint64_t dims[4] = {128, H, S, B};
-    const uint64_t strides[3] = {128, H * 128, S * H * 128};
+    const uint64_t dims[4] = {128, H, Sq, B};
+    const uint64_t strides[3] = {128, H * 128, Sq * H * 128};
     const uint32_t box[4] = {128, 1, 128, 1};
     if (int rc = encode_tensor_map(&map_q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, q8, dims, strides, box,
                                    CU_TENSOR_MAP_SWIZZLE_128B))
@@ -495,13 +499,14 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
   p.ksmb = table;
   p.out = static_cast<uint16_t *>(out_bf16);
   p.B = (uint32_t)B;
-  p.S = (uint32_t)S;
+  p.Sq = (uint32_t)Sq;
+  p.Sk = (uint32_t)S;
   p.H = (uint32_t)H;
   p.KV = (uint32_t)KV;
   p.S_pad = s_pad;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = status;
-  const uint64_t grid = B * H * ((S + 255) / 256);
+  const uint64_t grid = B * H * ((Sq + 255) / 256);
   attn_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
   return check_cuda(cudaGetLastError(), "attn_i8_kernel launch");
 }

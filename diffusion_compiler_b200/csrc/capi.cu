@@ -2,6 +2,7 @@
 #include "difb200/difb200.h"
 
 #include "common.cuh"
+#include "glue.h"
 #include "ops.h"
 
 using namespace difb200;
@@ -54,7 +55,7 @@ int attention_bf16_via_int8(const void *q, const void *k, const void *v, const u
     return rc;
   if (int rc = quantize_int8_rows(kp, w, 1, B * S * KV, 1, 1.0f, nullptr, k8, ks, nullptr, nullptr, stream))
     return rc;
-  return attention_int8(q8, qs, k8, ks, v, key_valid, B, S, H, KV, D, scale, base,
+  return attention_int8(q8, qs, k8, ks, v, key_valid, B, S, S, H, KV, D, scale, base,
                         attention_int8_scratch_bytes(B, S, KV), out_bf16, stream);
 }
 
@@ -96,10 +97,10 @@ uint64_t difb200_attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t K
 }
 
 int difb200_attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
-                           const void *v, const uint8_t *key_valid, uint64_t B, uint64_t S, uint64_t H,
-                           uint64_t KV, uint64_t D, float scale, void *scratch, uint64_t scratch_bytes,
-                           void *out, void *stream) {
-  return attention_int8(q8, qs, k8, ks, v, key_valid, B, S, H, KV, D, scale, scratch, scratch_bytes, out,
+                           const void *v, const uint8_t *key_valid, uint64_t B, uint64_t Sq, uint64_t Sk,
+                           uint64_t H, uint64_t KV, uint64_t D, float scale, void *scratch,
+                           uint64_t scratch_bytes, void *out, void *stream) {
+  return attention_int8(q8, qs, k8, ks, v, key_valid, B, Sq, Sk, H, KV, D, scale, scratch, scratch_bytes, out,
                         static_cast<cudaStream_t>(stream));
 }
 
@@ -112,6 +113,53 @@ int difb200_attention(const void *q, const void *k, const void *v, const uint8_t
                       uint64_t scratch_bytes, void *out, void *stream) {
   return attention_bf16_via_int8(q, k, v, key_valid, B, S, H, KV, D, scale, scratch, scratch_bytes, out,
                                  static_cast<cudaStream_t>(stream));
+}
+
+int difb200_rms_norm_modulate(const void *x, const void *weight, const void *scale, const void *shift, void *out,
+                              uint32_t dtype, uint64_t rows, uint64_t cols, float epsilon, void *stream) {
+  if (!x || !scale || !shift || !out || dtype < 1 || dtype > 3)
+    return fail(kInvalidArgument, "difb200_rms_norm_modulate: bad argument");
+  return glue::rms_norm_modulate(x, weight, scale, shift, out, dtype, rows, cols, epsilon, 0.0f, false, 1,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int difb200_layer_norm_modulate(const void *x, const void *weight, const void *bias, const void *scale,
+                                const void *shift, void *out, uint32_t dtype, uint64_t rows, uint64_t cols,
+                                uint64_t modulation_rows, float epsilon, void *stream) {
+  if (!x || !weight || !bias || !scale || !shift || !out || dtype < 1 || dtype > 3 || modulation_rows == 0 ||
+      rows % modulation_rows != 0)
+    return fail(kInvalidArgument, "difb200_layer_norm_modulate: bad argument");
+  return glue::layer_norm_modulate(x, weight, bias, scale, shift, out, dtype, rows, cols, rows / modulation_rows,
+                                   epsilon, static_cast<cudaStream_t>(stream));
+}
+
+int difb200_qk_norm_rope(const void *x, const void *weight, const void *cosine, const void *sine, void *out,
+                         uint32_t dtype, uint32_t table_dtype, uint64_t tokens, uint64_t heads, uint64_t dim,
+                         uint64_t rotary, uint64_t table_width, uint64_t input_sequence, uint64_t table_sequence,
+                         uint64_t table_start, float epsilon, int32_t interleaved_v2, void *stream) {
+  if (!x || !weight || !cosine || !sine || !out || dtype < 1 || dtype > 3 || table_dtype < 1 || table_dtype > 3 ||
+      rotary > dim || (rotary & 1) || (table_width != rotary && table_width != rotary / 2) || input_sequence == 0 ||
+      table_start + input_sequence > table_sequence)
+    return fail(kInvalidArgument, "difb200_qk_norm_rope: bad argument");
+  return glue::qk_norm_rope(x, weight, cosine, sine, out, dtype, table_dtype, tokens, heads, dim, rotary, table_width,
+                            input_sequence, table_sequence, table_start, epsilon, interleaved_v2 != 0,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int difb200_residual_gate(const void *residual, const void *branch, const void *gate, void *out, uint32_t dtype,
+                          uint64_t rows, uint64_t width, uint64_t gate_rows, void *stream) {
+  if (!residual || !branch || !gate || !out || dtype < 1 || dtype > 3 || gate_rows == 0 || rows % gate_rows != 0)
+    return fail(kInvalidArgument, "difb200_residual_gate: bad argument");
+  return glue::residual_gate(residual, branch, gate, out, dtype, rows * width, width, rows / gate_rows,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int difb200_swiglu(const void *x, void *out, uint32_t dtype, uint64_t rows, uint64_t width, uint64_t input_width,
+                   uint64_t start, int32_t gate_first, void *stream) {
+  if (!x || !out || dtype < 1 || dtype > 3 || start + 2 * width > input_width)
+    return fail(kInvalidArgument, "difb200_swiglu: bad argument");
+  return glue::swiglu(x, out, dtype, rows, width, input_width, start, gate_first != 0,
+                      static_cast<cudaStream_t>(stream));
 }
 
 int difb200_w8a8_linear(const void *x, const int8_t *w, const float *col_scales, const void *bias,

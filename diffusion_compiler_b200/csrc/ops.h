@@ -32,8 +32,9 @@ int w8a8_linear(const void *x_bf16, const int8_t *w, const float *col_scales, co
 // INT8 attention on already quantised Q/K (QuantizeInt8Rows Direct per token-head) and bf16 V.
 size_t attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV);
 int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks, const void *v_bf16,
-                   const uint8_t *key_valid, uint64_t B, uint64_t S, uint64_t H, uint64_t KV, uint64_t D,
-                   float scale, void *scratch, size_t scratch_bytes, void *out_bf16, cudaStream_t stream);
+                   const uint8_t *key_valid, uint64_t B, uint64_t Sq, uint64_t Sk, uint64_t H, uint64_t KV,
+                   uint64_t D, float scale, void *scratch, size_t scratch_bytes, void *out_bf16,
+                   cudaStream_t stream);
 
 // DiffIR Attention on bf16 q/k/v in its INT8 lowering: Direct quantisation of q and k per
 // token-head, then attention_int8. Scratch holds the codes, scales and the key table.

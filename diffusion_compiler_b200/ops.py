@@ -131,29 +131,35 @@ def w8a8_linear(x: torch.Tensor, w8: torch.Tensor, col_scales: torch.Tensor,
 
 def attention_int8(q8: torch.Tensor, qs: torch.Tensor, k8: torch.Tensor, ks: torch.Tensor, v: torch.Tensor,
                    key_valid: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """INT8 attention on quantised Q/K ([B,S,H,128] / [B,S,KV,128] int8 + per token-head f32
-    scales) and bf16 V [B,S,KV,128]; key_valid is an optional [B,S] uint8/bool key mask."""
+                   out: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """INT8 attention on quantised Q/K ([B,Sq,H,128] / [B,Sk,KV,128] int8 + per token-head f32
+    scales) and bf16 V [B,Sk,KV,128]; key_valid is an optional [B,Sk] uint8/bool key mask.
+    Sq < Sk is the token-sharded form (local queries, all-gathered keys/values)."""
     q8 = _require(q8, torch.int8, "q8")
     k8 = _require(k8, torch.int8, "k8")
     qs = _require(qs, torch.float32, "qs")
     ks = _require(ks, torch.float32, "ks")
     v = _require(v, torch.bfloat16, "v")
-    B, S, H, D = (int(d) for d in q8.shape)
-    KV = int(k8.shape[2])
+    B, Sq, H, D = (int(d) for d in q8.shape)
+    Sk, KV = int(k8.shape[1]), int(k8.shape[2])
+    if tuple(v.shape) != (B, Sk, KV, D) or qs.numel() != B * Sq * H or ks.numel() != B * Sk * KV:
+        raise ValueError("q8/qs, k8/ks and v shapes do not agree")
     if key_valid is not None:
         key_valid = key_valid.to(torch.uint8).contiguous()
+        if key_valid.numel() != B * Sk:
+            raise ValueError("key_valid must be [B,Sk]")
     if scale is None:
         scale = 1.0 / (D ** 0.5)
     if out is None:
-        out = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=q8.device)
+        out = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q8.device)
     L = _lib.lib()
-    nbytes = int(L.difb200_attention_int8_scratch_bytes(B, S, KV))
-    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q8.device)
+    nbytes = int(L.difb200_attention_int8_scratch_bytes(B, Sk, KV))
+    if scratch is None or scratch.numel() < nbytes:
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=q8.device)
     with torch.cuda.device(q8.device):
         _lib.check(L.difb200_attention_int8(_ptr(q8), _ptr(qs), _ptr(k8), _ptr(ks), _ptr(v), _ptr(key_valid),
-                                            B, S, H, KV, D, float(scale), _ptr(scratch), nbytes, _ptr(out),
-                                            _stream()))
+                                            B, Sq, Sk, H, KV, D, float(scale), _ptr(scratch), scratch.numel(),
+                                            _ptr(out), _stream()))
     return out
 
 

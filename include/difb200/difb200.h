@@ -84,20 +84,22 @@ DIFB200_EXPORT int difb200_linear_int8_scaled(const int8_t *x, const int8_t *w,
  * :236-295 and :646-929; admission src/runtime/cuda_executor.cpp:3388-3391,10982-10993.
  * Semantics of the op: src/runtime/cpu_executor.cpp:1839-1910 (GQA: query head h reads kv head
  * h / (H / KV); a row whose keys are all masked yields zeros).
- *   q8 [B,S,H,128] int8 with qs [B,S,H] f32, k8 [B,S,KV,128] int8 with ks [B,S,KV] f32: codes
- *   and scales of QuantizeInt8Rows(Direct) on the bf16 tensors (one row per token-head);
- *   v [B,S,KV,128] bf16; key_valid [B,S] bytes or NULL (the Bool mask that
+ *   q8 [B,Sq,H,128] int8 with qs [B,Sq,H] f32, k8 [B,Sk,KV,128] int8 with ks [B,Sk,KV] f32:
+ *   codes and scales of QuantizeInt8Rows(Direct) on the bf16 tensors (one row per token-head);
+ *   v [B,Sk,KV,128] bf16; key_valid [B,Sk] bytes or NULL (the Bool mask that
  *   BooleanMaskToBias(MaskQueries=false) would turn into a 0/-inf bias, cpu_executor.cpp:627-650);
- *   scale = AttentionScale (1/sqrt(128) by default); out [B,S,H,128] bf16.
- *   scratch: device buffer of difb200_attention_int8_scratch_bytes(B,S,KV) bytes.
+ *   scale = AttentionScale (1/sqrt(128) by default); out [B,Sq,H,128] bf16.
+ *   Sq == Sk for the DiffIR op; Sq < Sk is the token-sharded form, where a GPU holds the queries
+ *   of its token slice and the all-gathered keys/values of the whole sequence.
+ *   scratch: device buffer of difb200_attention_int8_scratch_bytes(B,Sk,KV) bytes.
  * Non-causal, head dimension 128 only; everything else returns status 2.
  */
 DIFB200_EXPORT uint64_t difb200_attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV);
 DIFB200_EXPORT int difb200_attention_int8(const int8_t *q8, const float *qs, const int8_t *k8,
                                           const float *ks, const void *v, const uint8_t *key_valid,
-                                          uint64_t B, uint64_t S, uint64_t H, uint64_t KV, uint64_t D,
-                                          float scale, void *scratch, uint64_t scratch_bytes,
-                                          void *out, void *stream);
+                                          uint64_t B, uint64_t Sq, uint64_t Sk, uint64_t H, uint64_t KV,
+                                          uint64_t D, float scale, void *scratch,
+                                          uint64_t scratch_bytes, void *out, void *stream);
 
 /*
  * Opcode Attention (8) on bf16 q [B,S,H,128], k/v [B,S,KV,128] in its INT8 lowering: q and k
@@ -109,6 +111,39 @@ DIFB200_EXPORT int difb200_attention(const void *q, const void *k, const void *v
                                      const uint8_t *key_valid, uint64_t B, uint64_t S, uint64_t H,
                                      uint64_t KV, uint64_t D, float scale, void *scratch,
                                      uint64_t scratch_bytes, void *out, void *stream);
+
+/*
+ * Block glue on device pointers: the row-local, memory-bound ops that sit between the quantized
+ * linears and attention in a DiT block. dtype codes are DiffIR's (1 = F32, 2 = BF16, 3 = F16).
+ * They follow the reference CPU executor's arithmetic and storage-dtype rounding points:
+ *   difb200_rms_norm_modulate    RmsNormModulate, ExplicitScaleShift layout: out = rmsnorm(x) [* weight]
+ *                                * (1 + scale) + shift with full-shape scale/shift
+ *                                (src/runtime/cpu_executor.cpp:1241-1265); weight may be NULL
+ *   difb200_layer_norm_modulate  LayerNormModulate (cpu_executor.cpp:1108-1148); scale/shift have
+ *                                modulation_rows rows that broadcast over groups of input rows
+ *   difb200_qk_norm_rope         QkNormPartialRope (cpu_executor.cpp:1741-1837); interleaved_v2 != 0
+ *                                selects Implementation 2 with the interleaved layout, else half-split
+ *   difb200_residual_gate        ResidualGate (cpu_executor.cpp:1703-1719)
+ *   difb200_swiglu               SwiGlu (cpu_executor.cpp:1267-1286)
+ */
+DIFB200_EXPORT int difb200_rms_norm_modulate(const void *x, const void *weight, const void *scale,
+                                             const void *shift, void *out, uint32_t dtype, uint64_t rows,
+                                             uint64_t cols, float epsilon, void *stream);
+DIFB200_EXPORT int difb200_layer_norm_modulate(const void *x, const void *weight, const void *bias,
+                                               const void *scale, const void *shift, void *out,
+                                               uint32_t dtype, uint64_t rows, uint64_t cols,
+                                               uint64_t modulation_rows, float epsilon, void *stream);
+DIFB200_EXPORT int difb200_qk_norm_rope(const void *x, const void *weight, const void *cosine,
+                                        const void *sine, void *out, uint32_t dtype, uint32_t table_dtype,
+                                        uint64_t tokens, uint64_t heads, uint64_t dim, uint64_t rotary,
+                                        uint64_t table_width, uint64_t input_sequence,
+                                        uint64_t table_sequence, uint64_t table_start, float epsilon,
+                                        int32_t interleaved_v2, void *stream);
+DIFB200_EXPORT int difb200_residual_gate(const void *residual, const void *branch, const void *gate,
+                                         void *out, uint32_t dtype, uint64_t rows, uint64_t width,
+                                         uint64_t gate_rows, void *stream);
+DIFB200_EXPORT int difb200_swiglu(const void *x, void *out, uint32_t dtype, uint64_t rows, uint64_t width,
+                                  uint64_t input_width, uint64_t start, int32_t gate_first, void *stream);
 
 /*
  * The W8A8 `int8-convrot` linear as one call: QuantizeInt8Rows(implementation, clip) on the bf16
