@@ -34,10 +34,12 @@ def _require(t: torch.Tensor, dtype: torch.dtype, name: str) -> torch.Tensor:
 
 
 def quantize_int8_rows(parts: Sequence[torch.Tensor], implementation: int = 2, clip: float = 1.0,
-                       clip_tensor: Optional[torch.Tensor] = None, residual: bool = False
-                       ) -> Tuple[torch.Tensor, ...]:
+                       clip_tensor: Optional[torch.Tensor] = None, residual: bool = False,
+                       out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Tuple[torch.Tensor, ...]:
     """QuantizeInt8Rows: bf16 inputs concatenated on the last axis -> (codes i8, scales f32
-    [, residual codes, residual scales]). ``implementation`` is the Int8RowQuantization value."""
+    [, residual codes, residual scales]). ``implementation`` is the Int8RowQuantization value.
+    ``out`` = (codes, scales) writes into existing contiguous buffers (e.g. a slice of an
+    all-gather buffer)."""
     if isinstance(parts, torch.Tensor):
         parts = [parts]
     parts = [_require(p, torch.bfloat16, "input") for p in parts]
@@ -51,8 +53,14 @@ def quantize_int8_rows(parts: Sequence[torch.Tensor], implementation: int = 2, c
             raise ValueError("all inputs must share their leading dimensions")
     total = sum(widths)
     dev = parts[0].device
-    codes = torch.empty(tuple(lead) + (total,), dtype=torch.int8, device=dev)
-    scales = torch.empty((rows,), dtype=torch.float32, device=dev)
+    if out is not None:
+        codes, scales = out
+        if (codes.dtype != torch.int8 or scales.dtype != torch.float32 or not codes.is_contiguous()
+                or not scales.is_contiguous() or codes.numel() != rows * total or scales.numel() != rows):
+            raise ValueError("out buffers must be contiguous int8 [rows*width] and float32 [rows]")
+    else:
+        codes = torch.empty(tuple(lead) + (total,), dtype=torch.int8, device=dev)
+        scales = torch.empty((rows,), dtype=torch.float32, device=dev)
     rcodes = torch.empty_like(codes) if residual else None
     rscales = torch.empty_like(scales) if residual else None
     n = len(parts)

@@ -1,0 +1,201 @@
+"""Token-sharded execution of the video DiT block on 1/2/4/8 GPUs (one process per GPU).
+
+The reference has no multi-GPU layer (one device per Executor, reference
+``include/dif/runtime/executor.hpp:683``); this is the sequence-partitioned form of the block that
+``blocks.video_block_program`` describes. Rank r owns a contiguous slice of the tokens. Weights,
+norm weights and RoPE tables are replicated. Everything except attention is row-local, so every
+op runs on the local slice; the one exchange step per block is an all-gather along tokens of the
+INT8 key codes, their per-token-head scales and the bf16 values. Queries stay local and each rank
+attends from its own queries to all keys (``ops.attention_int8`` with Sq < Sk); nothing is reduced
+afterwards.
+
+The K quantiser and the V projection write straight into this rank's slice of the gather
+buffers (no staging copy), and the collective is an in-place ``all_gather_into_tensor`` over
+NCCL/NVLink. Slices are padded to a common length; padded keys are masked.
+
+The shard arithmetic and the gather work on CPU tensors with the gloo backend too, which is how
+the N > 1 path is tested without GPUs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+H256 = 2
+DIRECT = 1
+
+
+@dataclass
+class ShardPlan:
+    """Contiguous token slices of equal padded length."""
+    tokens: int
+    world: int
+    slice_len: int  # padded length of every slice
+
+    @staticmethod
+    def make(tokens: int, world: int) -> "ShardPlan":
+        if tokens <= 0 or world <= 0:
+            raise ValueError("tokens and world must be positive")
+        return ShardPlan(tokens, world, (tokens + world - 1) // world)
+
+    def bounds(self, rank: int) -> Tuple[int, int]:
+        lo = min(rank * self.slice_len, self.tokens)
+        return lo, min(lo + self.slice_len, self.tokens)
+
+    def local_tokens(self, rank: int) -> int:
+        lo, hi = self.bounds(rank)
+        return hi - lo
+
+    @property
+    def padded_tokens(self) -> int:
+        return self.slice_len * self.world
+
+    def key_valid(self, device="cpu") -> Optional[torch.Tensor]:
+        """[1, padded_tokens] uint8 mask of real keys in gathered order, or None if no padding."""
+        if self.padded_tokens == self.tokens:
+            return None
+        valid = torch.zeros(self.padded_tokens, dtype=torch.uint8)
+        for r in range(self.world):
+            valid[r * self.slice_len: r * self.slice_len + self.local_tokens(r)] = 1
+        return valid.reshape(1, -1).to(device)
+
+
+class GatherBuffers:
+    """Full-sequence K codes / K scales / V buffers whose local slice the producers write."""
+
+    def __init__(self, plan: ShardPlan, rank: int, kv_heads: int, dim: int, device):
+        self.plan, self.rank = plan, rank
+        P = plan.padded_tokens
+        self.k8 = torch.zeros((P, kv_heads, dim), dtype=torch.int8, device=device)
+        self.ks = torch.zeros((P, kv_heads), dtype=torch.float32, device=device)
+        self.v = torch.zeros((P, kv_heads, dim), dtype=torch.bfloat16, device=device)
+
+    def local(self, t: torch.Tensor) -> torch.Tensor:
+        lo = self.rank * self.plan.slice_len
+        return t[lo: lo + self.plan.slice_len]
+
+    def all_gather(self, group=None) -> None:
+        """In-place all-gather of the three buffers (each rank contributes its slice)."""
+        import torch.distributed as dist
+        if self.plan.world == 1:
+            return
+        for t in (self.k8, self.ks, self.v):
+            dist.all_gather_into_tensor(t, self.local(t), group=group)
+
+
+class VideoBlock:
+    """Device-resident weights of one video block and its (optionally token-sharded) forward.
+
+    ``tensors`` maps the constant names of ``blocks.video_block_program`` to numpy arrays:
+    norm1, norm2, q_norm, k_norm, cos, sin (bf16 bit patterns) and, per linear, (w8, col_scales).
+    """
+
+    def __init__(self, tensors: Dict[str, object], hidden: int, heads: int, dim: int, ffn: int, rotary: int,
+                 device):
+        from . import ops
+        self.ops = ops
+        self.hidden, self.heads, self.dim, self.ffn, self.rotary = hidden, heads, dim, ffn, rotary
+        self.device = device
+
+        def bf(a):
+            return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).to(device).view(torch.bfloat16)
+
+        self.norm1, self.norm2 = bf(tensors["norm1"]), bf(tensors["norm2"])
+        self.q_norm, self.k_norm = bf(tensors["q_norm"]), bf(tensors["k_norm"])
+        self.cos, self.sin = bf(tensors["cos"]), bf(tensors["sin"])
+        self.lin = {name: (torch.from_numpy(w).to(device), torch.from_numpy(s).to(device))
+                    for name, (w, s) in tensors["linears"].items()}
+        self._scratch = None
+
+    def _glue(self, name, *args):
+        from . import _lib
+        _lib.check(getattr(_lib.lib(), name)(*args))
+
+    def pre_attention(self, x: torch.Tensor, mods: List[torch.Tensor], plan: ShardPlan, rank: int,
+                      gb: GatherBuffers):
+        """Row-local part up to the exchange: norm+modulate, q/k/v projections, q/k norm + RoPE,
+        per-token-head quantisation. K codes/scales and V land in this rank's slice of ``gb``.
+        Returns the local query codes and scales."""
+        import ctypes as C
+        ops = self.ops
+        S_loc = x.shape[0]
+        lo, _ = plan.bounds(rank)
+        H, D, hid = self.heads, self.dim, self.hidden
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: C.c_void_p(t.data_ptr())
+        new = lambda *shape: torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+        h = new(S_loc, hid)
+        self._glue("difb200_rms_norm_modulate", p(x), p(self.norm1), p(mods[0]), p(mods[1]), p(h), 2, S_loc, hid,
+                   1e-5, stream)
+        codes, scales = ops.quantize_int8_rows([h], H256)
+        q = ops.linear_int8_scaled(codes, *self._w("q", scales))
+        k = ops.linear_int8_scaled(codes, *self._w("k", scales))
+        v_local = gb.local(gb.v)[:S_loc]
+        ops.linear_int8_scaled(codes, *self._w("v", scales), out=v_local.view(S_loc, H * D))  # into the gather buffer
+        qr, kr = new(S_loc, H, D), new(S_loc, H, D)
+        for src, w, dst in ((q, self.q_norm, qr), (k, self.k_norm, kr)):
+            self._glue("difb200_qk_norm_rope", p(src), p(w), p(self.cos), p(self.sin), p(dst), 2, 2, S_loc, H, D,
+                       self.rotary, self.rotary, S_loc, self.cos.shape[0], lo, 1e-5, 0, stream)
+        q8, qs = ops.quantize_int8_rows([qr.view(S_loc * H, D)], DIRECT)
+        # K codes and scales are produced directly inside this rank's slice of the gather buffers
+        ops.quantize_int8_rows([kr.view(S_loc * H, D)], DIRECT,
+                               out=(gb.local(gb.k8)[:S_loc].view(S_loc * H, D), gb.local(gb.ks)[:S_loc].view(-1)))
+        return q8.view(1, S_loc, H, D), qs
+
+    def attend(self, q8: torch.Tensor, qs: torch.Tensor, plan: ShardPlan, gb: GatherBuffers) -> torch.Tensor:
+        """Local queries against the gathered keys/values of the whole sequence."""
+        H, D, P = self.heads, self.dim, plan.padded_tokens
+        return self.ops.attention_int8(q8, qs, gb.k8.view(1, P, H, D), gb.ks, gb.v.view(1, P, H, D),
+                                       plan.key_valid(self.device), scale=1.0 / float(np.sqrt(D)))
+
+    def post_attention(self, x: torch.Tensor, attn: torch.Tensor, mods: List[torch.Tensor]) -> torch.Tensor:
+        """Row-local part after attention: out-proj, gated residual, norm+modulate, SwiGLU MLP."""
+        import ctypes as C
+        ops = self.ops
+        S_loc = x.shape[0]
+        H, D, hid = self.heads, self.dim, self.hidden
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: C.c_void_p(t.data_ptr())
+        new = lambda *shape: torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+        o = ops.w8a8_linear(attn.view(S_loc, H * D), *self.lin["o"])
+        r1 = new(S_loc, hid)
+        self._glue("difb200_residual_gate", p(x), p(o), p(mods[2]), p(r1), 2, S_loc, hid, S_loc, stream)
+        h2 = new(S_loc, hid)
+        self._glue("difb200_rms_norm_modulate", p(r1), p(self.norm2), p(mods[3]), p(mods[4]), p(h2), 2, S_loc, hid,
+                   1e-5, stream)
+        fc1 = ops.w8a8_linear(h2, *self.lin["fc1"])
+        act = new(S_loc, self.ffn)
+        self._glue("difb200_swiglu", p(fc1), p(act), 2, S_loc, self.ffn, 2 * self.ffn, 0, 0, stream)
+        fc2 = ops.w8a8_linear(act, *self.lin["fc2"])
+        out = new(S_loc, hid)
+        self._glue("difb200_residual_gate", p(r1), p(fc2), p(mods[5]), p(out), 2, S_loc, hid, S_loc, stream)
+        return out
+
+    def forward(self, x: torch.Tensor, mods: List[torch.Tensor], plan: ShardPlan, rank: int, group=None,
+                gb: Optional[GatherBuffers] = None, events: Optional[dict] = None) -> torch.Tensor:
+        """x and the six modulation tensors are this rank's [S_local, hidden] slices."""
+        def mark(name):
+            if events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                events.setdefault(name, []).append(ev)
+
+        if gb is None:
+            gb = GatherBuffers(plan, rank, self.heads, self.dim, self.device)
+        mark("start")
+        q8, qs = self.pre_attention(x, mods, plan, rank, gb)
+        mark("pre_attention")
+        gb.all_gather(group)
+        mark("gathered")
+        attn = self.attend(q8, qs, plan, gb)
+        mark("attention")
+        out = self.post_attention(x, attn, mods)
+        mark("end")
+        return out
+
+    def _w(self, name, scales):
+        w8, cs = self.lin[name]
+        return w8, scales, cs
