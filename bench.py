@@ -144,6 +144,162 @@ def run_step(ops, layers, events=None):
             events[i][2].record()
 
 
+def plugin_e2e(torch, layers, device_index, steps, barrier):
+    """Times execute() of the plugin on the projection-set program with pinned host buffers."""
+    import numpy as np
+    from diffusion_compiler_b200 import diffir, plugin
+    p = diffir.Program()
+    consts, inputs, outputs = {}, {}, {}
+    for L in layers:
+        K, N = L["K"], L["N"]
+        x = p.add_tensor(diffir.DType.BF16, [M_TOKENS, K], diffir.Role.Input)
+        codes = p.add_tensor(diffir.DType.I8, [M_TOKENS, K])
+        row = p.add_tensor(diffir.DType.F32, [M_TOKENS])
+        w = p.add_tensor(diffir.DType.I8, [N, K], diffir.Role.Constant)
+        cs = p.add_tensor(diffir.DType.F32, [N], diffir.Role.Constant)
+        b = p.add_tensor(diffir.DType.BF16, [N], diffir.Role.Constant)
+        y = p.add_tensor(diffir.DType.BF16, [M_TOKENS, N])
+        yb = p.add_tensor(diffir.DType.BF16, [M_TOKENS, N], diffir.Role.Internal if L["gelu"] else diffir.Role.Output)
+        p.add_op(diffir.Opcode.QuantizeInt8Rows, [x], [codes, row],
+                 [diffir.Attribute.u64(diffir.AttrKey.BlockSize, 256),
+                  diffir.Attribute.u64(diffir.AttrKey.Implementation, H256_CONVROT)])
+        p.add_op(diffir.Opcode.LinearInt8Scaled, [codes, w, row, cs], [y])
+        p.add_op(diffir.Opcode.BiasAdd, [y, b], [yb])
+        out_id = yb
+        if L["gelu"]:
+            out_id = p.add_tensor(diffir.DType.BF16, [M_TOKENS, N], diffir.Role.Output)
+            p.add_op(diffir.Opcode.Gelu, [yb], [out_id], [diffir.Attribute.u64(diffir.AttrKey.Approximation, 1)])
+        consts[w] = L["w8"].cpu().numpy()
+        consts[cs] = L["ws"].cpu().numpy()
+        consts[b] = L["bias"].view(torch.int16).cpu().numpy().view(np.uint16)
+        inputs[x] = L["x_host"].view(torch.int16).numpy().view(np.uint16)          # pinned
+        host_out = torch.empty((M_TOKENS, N), dtype=torch.int16).pin_memory()
+        outputs[out_id] = host_out.numpy().view(np.uint16)                        # pinned
+    ex = plugin.PluginExecutor(device_index)
+    prepared = ex.prepare(p, consts)
+    prepared.run(inputs, warmups=1, iterations=1, outputs=outputs)
+    barrier()
+    t0 = time.perf_counter()
+    device_ms = 0.0
+    for _ in range(steps):
+        _, tel = prepared.run(inputs, warmups=0, iterations=1, outputs=outputs)
+        device_ms += tel.mean_milliseconds
+    wall_ms = (time.perf_counter() - t0) * 1e3 / steps
+    barrier()
+    h2d = sum(a.nbytes for a in inputs.values())
+    d2h = sum(a.nbytes for a in outputs.values())
+    prepared.close()
+    ex.close()
+    return wall_ms, h2d, d2h, device_ms / steps
+
+
+def attention_extra(torch, ops, device):
+    """BASELINE config 2: INT8 attention, B=2 H=24 S=4608 D=128; dense and GQA(8)+key mask."""
+    res = []
+    for KV, masked in ((24, False), (8, True)):
+        B, S, H, D = 2, 4608, 24, 128
+        g = torch.Generator(device=device).manual_seed(2)
+        rms = lambda t: (t.float() / t.float().pow(2).mean(-1, keepdim=True).add(1e-6).sqrt()).to(torch.bfloat16)
+        q = rms(torch.randn(B, S, H, D, device=device, generator=g, dtype=torch.float32))
+        k = rms(torch.randn(B, S, KV, D, device=device, generator=g, dtype=torch.float32))
+        v = torch.randn(B, S, KV, D, device=device, generator=g, dtype=torch.float32).to(torch.bfloat16)
+        valid, sk = None, S
+        if masked:
+            valid = torch.ones(B, S, dtype=torch.uint8, device=device)
+            valid[:, 4096 + 384:] = 0  # the last 128 text tokens are padding
+            sk = S - 128
+        q8, qs = ops.quantize_int8_rows([q.view(-1, D)], 1)
+        k8, ks = ops.quantize_int8_rows([k.view(-1, D)], 1)
+        q8, k8 = q8.view(B, S, H, D), k8.view(B, S, KV, D)
+        out = torch.empty_like(q)
+        for _ in range(3):
+            ops.attention_int8(q8, qs, k8, ks, v, valid, out=out)
+        n = 10
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        ev[0].record()
+        for i in range(n):
+            ops.attention_int8(q8, qs, k8, ks, v, valid, out=out)
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        ms = sum(ev[i].elapsed_time(ev[i + 1]) for i in range(n)) / n
+        half = 2.0 * B * H * S * sk * D
+        t_ideal_ms = (half / 4500e12 + half / 2250e12) * 1e3
+        res.append({"kv_heads": KV, "key_mask": masked, "ms": ms, "tops_qk_plus_pv": 2 * half / (ms * 1e-3) / 1e12,
+                    "t_ideal_over_t_nominal": t_ideal_ms / ms})
+    return res
+
+
+def mmdit_block_extra(torch, device_index):
+    """BASELINE config 3: the MMDiT double-stream block (hidden 3072, 24x128, MLP 12288, 4096 image +
+    512 text tokens, batch 2) as one DiffIR program through the plugin."""
+    import numpy as np
+    from diffusion_compiler_b200 import blocks, plugin
+    rng = np.random.default_rng(3)
+    p, ids, consts, inputs = blocks.synth_mmdit_block(rng, 2, (64, 64), 512, 3072, 24, 12288,
+                                                      blocks.gpu_weight_quantizer("cuda:%d" % device_index))
+    ex = plugin.PluginExecutor(device_index)
+    prepared = ex.prepare(p, consts)
+    t0 = time.perf_counter()
+    _, tel = prepared.run(inputs, warmups=2, iterations=5)
+    wall = time.perf_counter() - t0
+    tokens = 2 * (4096 + 512)
+    res = {"tokens": tokens, "device_ms": tel.mean_milliseconds, "tokens_per_s": tokens / (tel.mean_milliseconds * 1e-3),
+           "operations": len(p.operations), "resident_gb": prepared.compile_telemetry.resident_bytes / 1e9,
+           "execute_wall_s_7_passes_with_copies": wall}
+    prepared.close()
+    ex.close()
+    return res
+
+
+def video_block_extra(torch, device, rank, world, dist, iters=5):
+    """BASELINE config 4: the video DiT block, 33272 tokens sharded along tokens over `world` GPUs,
+    all-gather of quantised K (+scales) and bf16 V over NCCL. Strong scaling."""
+    import numpy as np
+    from diffusion_compiler_b200 import blocks
+    from diffusion_compiler_b200.sequence_shard import GatherBuffers, ShardPlan, VideoBlock
+    S, hidden, heads, dim, ffn, rotary = 21 * 30 * 52 + 512, 3072, 24, 128, 8192, 96
+    rng = np.random.default_rng(4)  # same weights on every rank
+    quantize = blocks.gpu_weight_quantizer(str(device))
+    linears = {}
+    for name, (N, K) in (("q", (hidden, hidden)), ("k", (hidden, hidden)), ("v", (hidden, hidden)),
+                         ("o", (hidden, hidden)), ("fc1", (2 * ffn, hidden)), ("fc2", (hidden, ffn))):
+        linears[name] = quantize(blocks.random_bf16(rng, (N, K), 0.02))
+    cosv, sinv = blocks.rope_tables_3axis(blocks.video_positions(), rotary)
+    one_h, one_d = blocks.f32_to_bf16(np.ones(hidden, np.float32)), blocks.f32_to_bf16(np.ones(dim, np.float32))
+    block = VideoBlock({"norm1": one_h, "norm2": one_h, "q_norm": one_d, "k_norm": one_d, "cos": cosv, "sin": sinv,
+                        "linears": linears}, hidden, heads, dim, ffn, rotary, device)
+    plan = ShardPlan.make(S, world)
+    lo, hi = plan.bounds(rank)
+    g = torch.Generator(device=device).manual_seed(100 + rank)
+    x = torch.randn(hi - lo, hidden, device=device, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    mods = [(torch.randn(1, hidden, device=device, generator=g, dtype=torch.float32) * 0.1).to(torch.bfloat16)
+            .expand(hi - lo, hidden).contiguous() for _ in range(6)]
+    gb = GatherBuffers(plan, rank, heads, dim, device)
+    for _ in range(2):
+        block.forward(x, mods, plan, rank, gb=gb)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    events = {}
+    for _ in range(iters):
+        block.forward(x, mods, plan, rank, gb=gb, events=events)
+    torch.cuda.synchronize()
+    names = ["start", "pre_attention", "gathered", "attention", "end"]
+    seg = {b: sum(events[a][i].elapsed_time(events[b][i]) for i in range(iters)) / iters
+           for a, b in zip(names[:-1], names[1:])}
+    total = sum(events["start"][i].elapsed_time(events["end"][i]) for i in range(iters)) / iters
+    t = torch.tensor([total, seg["pre_attention"], seg["gathered"], seg["attention"], seg["end"]],
+                     dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total = float(t[0])
+    gather_bytes = (world - 1) * plan.slice_len * heads * (dim + 4 + 2 * dim)
+    return {"tokens": S, "ms_per_block": total, "tokens_per_s": S / (total * 1e-3), "scaling": "strong",
+            "ms_pre_attention": float(t[1]), "ms_all_gather": float(t[2]), "ms_attention": float(t[3]),
+            "ms_post_attention": float(t[4]), "all_gather_bytes_received_per_rank": gather_bytes,
+            "tokens_per_rank": plan.slice_len}
+
+
 def cpu_reference_sample(threads: int, rows_per_thread: int):
     """Times the reference CPU executor (oracle/_ref) -- or, where it was not built, the C
     restatement -- on a row sample of the same four projections, `threads` host threads."""
@@ -193,6 +349,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the attention / block configs")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -208,7 +365,7 @@ def main():
         if rank != 0:
             return
         threads = os.cpu_count() or 1
-        rows = 64
+        rows = 256
         steps = max(1, min(args.steps, 3))
         vals = []
         for _ in range(min(args.warmup, 1)):
@@ -264,28 +421,10 @@ def main():
     barrier()
     elapsed_ms = start.elapsed_time(stop)
     ops.poll_status()
-    # --- end-to-end: host inputs -> device, compute, result -> host, every step ---
-    out_host = [torch.empty_like(L["out"], device="cpu").pin_memory() for L in layers]
-    h2d = sum(L["x_host"].numel() * 2 for L in layers)
-    d2h = sum(o.numel() * 2 for o in out_host)
-
-    def e2e_step():
-        for L, oh in zip(layers, out_host):
-            L["x"].copy_(L["x_host"], non_blocking=True)
-        run_step(ops, layers)
-        for L, oh in zip(layers, out_host):
-            oh.copy_(L["out"], non_blocking=True)
-
-    e2e_step()
-    barrier()
-    e2e_steps = max(3, min(args.steps, 10))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    # --- end-to-end: the reference-facing call. The same four projections as ONE DiffIR program
+    # through the backend plugin C-ABI (dif_backend_get_v2: compile once, then execute per step)
+    # with pinned HOST buffers: every step copies the activations in and the bf16 outputs out. ---
+    e2e_ms, h2d, d2h, e2e_device_ms = plugin_e2e(torch, layers, local_rank, max(3, min(args.steps, 10)), barrier)
     clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
@@ -314,7 +453,9 @@ def main():
             "data": "synthetic", "config": config,
             "e2e": {"value": world * total_ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "path": "pinned host activations -> device, 4x(quantize+linear), bf16 outputs -> pinned host"},
+                    "device_ms_per_step": e2e_device_ms,
+                    "path": "backend plugin C-ABI (dif_backend_get_v2 execute): pinned host activations in, "
+                            "4x(QuantizeInt8Rows+LinearInt8Scaled+BiasAdd[+Gelu]) on device, bf16 outputs to pinned host"},
             "gpu_launches": args.steps * 2 * len(layers),
             "roofline": {"bound": "tensor", "kernel": "gemm_i8_kernel (tcgen05 kind::i8)",
                          "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s", "frac": gemm_tops / int8_peak,
@@ -331,8 +472,19 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            res, _ = cpu_reference_sample(threads, 64)
+            res, _ = cpu_reference_sample(threads, 512)
             line["cpu_baseline"] = res
+    extras = {}
+    if not args.no_extras:
+        # further configs of BASELINE.json, reported beside the headline (not part of `value`)
+        extras["video_block"] = video_block_extra(torch, device, rank, world, dist)
+        if rank == 0:
+            extras["attention"] = attention_extra(torch, ops, device)
+            if world == 1:
+                extras["mmdit_block"] = mmdit_block_extra(torch, local_rank)
+        ops.poll_status()
+    if rank == 0:
+        line.update(extras)
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
