@@ -164,8 +164,10 @@ __device__ __forceinline__ void stage_pair(uint32_t base_a, uint32_t base_b, int
   sts8<off>(base_b, cb);
 }
 
-template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL>
-__global__ void __launch_bounds__(512, 2)
+// MAXT bounds the block size so that the register budget (about 80 per thread, which the
+// prefetch needs) is known at compile time: 256 -> 3 blocks/SM, 384 -> 2, 512 -> 1.
+template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL, int MAXT>
+__global__ void __launch_bounds__(MAXT, MAXT == 256 ? 3 : (MAXT == 384 ? 2 : 1))
 convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int rows_per_cta) {
   extern __shared__ __align__(128) uint32_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -236,6 +238,26 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
     }
   }
 
+  // Software pipeline: the 64 bytes of the next row are requested before the current row is
+  // processed, so the HBM latency of row i+1 hides under the arithmetic of row i.
+  auto fetch = [&](uint64_t row, uint4 &a0, uint4 &a1, uint4 &b0, uint4 &b1) {
+    a0 = a1 = b0 = b1 = make_uint4(0, 0, 0, 0);
+    if (row < p.rows) {
+      if (act_a) {
+        const uint4 *v = reinterpret_cast<const uint4 *>(src_a + row * pitch_a);
+        a0 = __ldg(v);
+        a1 = __ldg(v + 1);
+      }
+      if (act_b) {
+        const uint4 *v = reinterpret_cast<const uint4 *>(src_b + row * pitch_b);
+        b0 = __ldg(v);
+        b1 = __ldg(v + 1);
+      }
+    }
+  };
+  uint4 na0, na1, nb0, nb1;
+  fetch((uint64_t)blockIdx.x * rows_per_cta + slot, na0, na1, nb0, nb1);
+
   uint32_t parity = 0;
   for (uint64_t row0 = (uint64_t)blockIdx.x * rows_per_cta; row0 < p.rows;
        row0 += (uint64_t)gridDim.x * rows_per_cta, parity ^= 1u) {
@@ -243,17 +265,8 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
     const bool row_ok = row < p.rows;
     uint64_t P[16];
     {
-      uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, b0 = a0, b1 = a0;
-      if (row_ok && act_a) {
-        const uint4 *v = reinterpret_cast<const uint4 *>(src_a + row * pitch_a);
-        a0 = __ldg(v);
-        a1 = __ldg(v + 1);
-      }
-      if (row_ok && act_b) {
-        const uint4 *v = reinterpret_cast<const uint4 *>(src_b + row * pitch_b);
-        b0 = __ldg(v);
-        b1 = __ldg(v + 1);
-      }
+      const uint4 a0 = na0, a1 = na1, b0 = nb0, b1 = nb1;
+      fetch(row + (uint64_t)gridDim.x * rows_per_cta, na0, na1, nb0, nb1);
       const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
@@ -575,7 +588,10 @@ int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
     rows_per_cta = (int)p.rows;
   const int warps = warps_per_row * rows_per_cta;
   const size_t smem = (size_t)warps * kWarpBytes + (size_t)warps * 4 * sizeof(float) + 64;
-  auto kernel = convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL>;
+  const int threads_needed = warps * 32;
+  auto kernel = threads_needed <= 256   ? convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, 256>
+                : threads_needed <= 384 ? convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, 384>
+                                        : convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, 512>;
   if (smem > 48 * 1024) {
     if (int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)smem),

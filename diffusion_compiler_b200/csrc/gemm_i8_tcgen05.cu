@@ -4,15 +4,28 @@
 // first, then column scale), BiasAdd :1288-1296, Gelu :93-113; it replaces the reference's
 // Sm80 mma.sync CUTLASS kernel (src/runtime/cutlass_gemm.cu:185-303).
 //
-// Structure: persistent CTAs, one per SM, 128x256 output tiles. Both operands are K-major
-// INT8, brought in by TMA as 128-byte-swizzled [rows x 128 B] boxes into a 4-stage ring.
-// One thread issues tcgen05.mma kind::i8 (M128 N256 K32) into one of two 256-column INT32
-// accumulators in tensor memory, so the epilogue of tile i overlaps the MMAs of tile i+1.
-// Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2..5 = epilogue (each reads the
-// TMEM lane quarter warp_id % 4).
+// Structure: persistent CTAs, one per SM. Both operands are K-major INT8, brought in by TMA as
+// 128-byte-swizzled [rows x 128 B] boxes into a shared-memory ring. One thread issues
+// tcgen05.mma kind::i8 into one of two 256-column INT32 accumulators in tensor memory, so the
+// epilogue of tile i overlaps the MMAs of tile i+1. Warp roles: 0 = TMA producer, 1 = TMEM owner
+// + MMA issuer, 2..5 = epilogue (each reads the TMEM lane quarter warp_id % 4).
+//
+// Two forms of the same kernel (template parameter CTAS):
+//   CTAS = 1: 128x256 tile per CTA, cta_group::1, 4 stages of 48 KB.
+//   CTAS = 2: a CTA pair (cluster of 2) computes a 256x256 tile with cta_group::2 MMAs: each CTA
+//             stages its 128 rows of A and only its 128 rows (half) of the B tile, 6 stages of
+//             32 KB. This halves the B bytes every SM moves through shared memory per MAC -- at
+//             8192 INT8 MACs/clk/SM the 128x256 single-CTA tile needs 48 KB written plus 48 KB read
+//             per 512 clocks, which is what bounds the CTAS = 1 form. The leader CTA (cluster rank
+//             0) issues the MMAs; both CTAs load, and both run the epilogue on their own 128 rows.
+//             TMA loads never use multicast and complete on the loading CTA's own mbarrier; a
+//             relay thread in the peer forwards one arrive per stage to the leader's barrier. The
+//             leader releases stages and publishes accumulators to both CTAs with one
+//             tcgen05.commit that signals the mbarrier of both CTAs.
 #include "common.cuh"
 #include "ptx.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace difb200 {
@@ -56,19 +69,29 @@ int encode_tensor_map(CUtensorMap *out, CUtensorMapDataType type, uint32_t rank,
 
 namespace {
 
-constexpr int kBM = 128, kBN = 256, kBK = 128; // BK in bytes == INT8 elements
-constexpr int kStages = 4;
+constexpr int kBM = 128, kBN = 256, kBK = 128; // per-CTA rows, tile columns, BK in bytes == INT8 elements
 constexpr int kUmmaK = 32;
-constexpr uint32_t kABytes = kBM * kBK, kBBytes = kBN * kBK, kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kABytes = kBM * kBK;
 constexpr int kThreads = 192;
+template <int CTAS>
+struct Cfg {
+  static constexpr int kStages = CTAS == 2 ? 6 : 4;
+  static constexpr uint32_t kBRows = kBN / CTAS;                 // rows of the B tile this CTA stages
+  static constexpr uint32_t kBBytes = kBRows * kBK;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kTileM = kBM * CTAS;                 // rows of the (pair's) output tile
+};
 constexpr uint32_t kTmemCols = 512;
 // Epilogue staging: per epilogue warp two [32 rows x 32 bf16] boxes (64-byte rows, 64B TMA
 // swizzle); plus, per epilogue warp, 256 column scales and 256 biases (fp32) of the tile.
 constexpr uint32_t kStoreBoxBytes = 32 * 64;
 constexpr uint32_t kStagingBytes = 4 * 2 * kStoreBoxBytes;
 constexpr uint32_t kScaleBytes = 4 * 2 * kBN * 4;
-constexpr size_t kSmemBytes =
-    1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + kStagingBytes + kScaleBytes + 256;
+template <int CTAS>
+constexpr size_t smem_bytes() {
+  return 1024 /*alignment slack*/ + (size_t)Cfg<CTAS>::kStages * Cfg<CTAS>::kStageBytes + kStagingBytes +
+         kScaleBytes + 256;
+}
 
 enum : uint32_t { kEpiBias = 1u, kEpiGeluTanh = 2u };
 
@@ -80,9 +103,19 @@ struct GemmParams {
   int32_t *acc_out;
   uint32_t M, N, K;
   uint32_t epilogue;
+  unsigned long long *trace; // measurement aid: timestamps of the first k-blocks of unit 0
+  uint32_t debug;     // measurement aid: 1 = issue no MMAs, 2 = issue no TMA loads (results are garbage)
   uint32_t tma_store; // 1: outputs leave through TMA stores (needs N % 8 == 0, aligned out)
   DeviceStatus *status;
 };
+
+__device__ __forceinline__ void stamp(const GemmParams &p, uint32_t unit, uint32_t slot, uint32_t i) {
+  if (p.trace && unit == 0 && i < 64) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[slot * 64 + i] = t;
+  }
+}
 
 __device__ __forceinline__ void report_timeout(DeviceStatus *status, uint32_t role, uint32_t detail) {
   if (atomicExch(&status->flag, 1u) == 0u) {
@@ -114,10 +147,17 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return packed;
 }
 
+template <int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+  constexpr int kStages = Cfg<CTAS>::kStages;
+  constexpr uint32_t kStageBytes = Cfg<CTAS>::kStageBytes;
+  constexpr uint32_t kTileM = Cfg<CTAS>::kTileM;
   extern __shared__ uint8_t smem_raw[];
+  const uint32_t cta_rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;  // 0 = leader of the pair
+  const uint32_t unit = CTAS == 2 ? blockIdx.x >> 1 : blockIdx.x;      // tile-scheduling unit
+  const uint32_t units = CTAS == 2 ? gridDim.x >> 1 : gridDim.x;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t staging_base = smem_base + kStages * kStageBytes;
   const uint32_t scale_base = staging_base + kStagingBytes;
@@ -132,18 +172,19 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile uint32_t *abort_ptr = slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t tiles_m = (p.M + kBM - 1) / kBM, tiles_n = (p.N + kBN - 1) / kBN;
+  const uint32_t tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + kBN - 1) / kBN;
   const uint32_t num_tiles = tiles_m * tiles_n;
   const uint32_t k_blocks = (p.K + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(full_bar + 8 * s, 1);
+      // leader: its own producer's arrive.expect_tx plus, for a pair, the peer's relay arrive
+      ptx::mbar_init(full_bar + 8 * s, (CTAS == 2 && cta_rank == 0) ? 2 : 1);
       ptx::mbar_init(empty_bar + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(tfull_bar + 8 * b, 1);
-      ptx::mbar_init(tempty_bar + 8 * b, 4);
+      ptx::mbar_init(tempty_bar + 8 * b, 4 * CTAS);    // epilogue warps of every CTA of the pair
     }
     *abort_ptr = 0;
     ptx::fence_barrier_init();
@@ -151,11 +192,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     ptx::prefetch_tensormap(&map_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, kTmemCols);
-    ptx::tmem_relinquish();
+    if (CTAS == 2) {
+      ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(tmem_slot, kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if (CTAS == 2)
+    ptx::cluster_sync(); // the peer's barriers are initialised before anything arrives on them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *slot_ptr;
 
@@ -163,8 +211,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int32_t m0 = (int32_t)((tile / tiles_n) * kBM), n0 = (int32_t)((tile % tiles_n) * kBN);
+      for (uint32_t tile = unit; tile < num_tiles && ok; tile += units) {
+        const int32_t m0 = (int32_t)((tile / tiles_n) * kTileM + cta_rank * kBM);
+        const int32_t n0 = (int32_t)((tile % tiles_n) * kBN + cta_rank * Cfg<CTAS>::kBRows);
         for (uint32_t kb = 0; kb < k_blocks; ++kb) {
           if (*abort_ptr || !ptx::mbar_wait(empty_bar + 8 * stage, phase ^ 1u)) {
             if (!*abort_ptr)
@@ -174,9 +223,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
-          ptx::mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
-          ptx::tma_load_2d(a_dst, &map_a, full_bar + 8 * stage, (int32_t)(kb * kBK), m0);
-          ptx::tma_load_2d(b_dst, &map_b, full_bar + 8 * stage, (int32_t)(kb * kBK), n0);
+          stamp(p, unit, cta_rank * 2, (tile - unit) / units * k_blocks + kb);
+          if (p.debug == 2) {
+            ptx::mbar_arrive(full_bar + 8 * stage);
+          } else {
+            // Every CTA counts its bytes on its own barrier (a pair's peer then relays one
+            // arrive per stage to the leader, see below: letting the peer's TMA complete its
+            // bytes on the leader's barrier directly cut the load rate to a quarter).
+            ptx::mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
+            ptx::tma_load_2d(a_dst, &map_a, full_bar + 8 * stage, (int32_t)(kb * kBK), m0);
+            ptx::tma_load_2d(b_dst, &map_b, full_bar + 8 * stage, (int32_t)(kb * kBK), n0);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -185,11 +242,40 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, 0, 0, kBM, kBN);
+    if (CTAS == 2 && lane == 0 && cta_rank == 1) {
+      // Relay of the pair's peer CTA: when a stage of this CTA has landed, tell the leader.
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t tile = unit; tile < num_tiles && ok; tile += units) {
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+          if (*abort_ptr || !ptx::mbar_wait(full_bar + 8 * stage, phase)) {
+            if (!*abort_ptr)
+              report_timeout(p.status, 3, kb);
+            *abort_ptr = 1;
+            ok = false;
+            break;
+          }
+          stamp(p, unit, 3, (tile - unit) / units * k_blocks + kb);
+          ptx::mbar_arrive_cluster(ptx::mapa(full_bar + 8 * stage, 0));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, 0, 0, kTileM, kBN);
       uint32_t stage = 0, phase = 0, local = 0;
       bool ok = true;
-      for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      auto commit = [&](uint32_t bar) { // arrives on `bar` of every CTA of the pair
+        if (CTAS == 2) {
+          ptx::mma_commit_pair_both(bar, (uint16_t)3);
+        } else {
+          ptx::mma_commit(bar);
+        }
+      };
+      for (uint32_t tile = unit; tile < num_tiles && ok; tile += units, ++local) {
         const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
         if (*abort_ptr || !ptx::mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u)) {
           if (!*abort_ptr)
@@ -208,21 +294,29 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           ptx::tc_fence_after();
+          stamp(p, unit, 1, local * k_blocks + kb);
           const uint32_t a_addr = smem_base + stage * kStageBytes, b_addr = a_addr + kABytes;
           const uint64_t a_desc = ptx::smem_desc_sw128(a_addr, 16, 1024);
           const uint64_t b_desc = ptx::smem_desc_sw128(b_addr, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k)
-            ptx::mma_i8_ss(d_tmem, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
-                           idesc, (kb | (uint32_t)k) != 0u ? 1u : 0u);
-          ptx::mma_commit(empty_bar + 8 * stage); // frees the smem stage when these MMAs retire
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t ka = a_desc + (uint64_t)(k * kUmmaK >> 4), kb_desc = b_desc + (uint64_t)(k * kUmmaK >> 4);
+            const uint32_t accumulate = (kb | (uint32_t)k) != 0u ? 1u : 0u;
+            if (p.debug == 1)
+              continue;
+            if (CTAS == 2)
+              ptx::mma_i8_ss_pair(d_tmem, ka, kb_desc, idesc, accumulate);
+            else
+              ptx::mma_i8_ss(d_tmem, ka, kb_desc, idesc, accumulate);
+          }
+          commit(empty_bar + 8 * stage); // frees the smem stage when these MMAs retire
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (ok)
-          ptx::mma_commit(tfull_bar + 8 * acc); // accumulator complete
+          commit(tfull_bar + 8 * acc); // accumulator complete
       }
     }
   } else {
@@ -232,9 +326,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     float *scale_smem = reinterpret_cast<float *>(generic_base + (scale_base - smem_base));
     const uint32_t my_staging = staging_base + quarter * 2u * kStoreBoxBytes;
     uint8_t *my_staging_ptr = generic_base + (my_staging - smem_base);
-    for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+    for (uint32_t tile = unit; tile < num_tiles; tile += units, ++local) {
       const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
-      const uint32_t m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * kBN;
+      const uint32_t m0 = (tile / tiles_n) * kTileM + cta_rank * kBM, n0 = (tile % tiles_n) * kBN;
       // column scales and biases of this tile -> this warp's private shared-memory copy
       // (warp-private so that no cross-warp barrier is needed)
       float *cs = scale_smem + quarter * 2 * kBN, *bs = cs + kBN;
@@ -325,8 +419,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0)
-        ptx::mbar_arrive(tempty_bar + 8 * acc);
+      if (lane == 0) {
+        if (CTAS == 2)
+          ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar + 8 * acc, 0)); // the leader issues the MMAs
+        else
+          ptx::mbar_arrive(tempty_bar + 8 * acc);
+      }
     }
     if (lane == 0)
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -334,9 +432,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   ptx::tc_fence_before();
   __syncthreads();
+  if (CTAS == 2)
+    ptx::cluster_sync(); // neither CTA leaves (or frees TMEM) while the peer may still touch it
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
+    if (CTAS == 2)
+      ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    else
+      ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -364,10 +467,16 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   if (!status)
     return fail(kOutOfMemory, "LinearInt8Scaled: cannot allocate device status words");
 
+  // The single-CTA form is the default; DIFB200_GEMM_CTAS=2 selects the CTA-pair form, which is
+  // bit-identical but currently slower (its load pipeline does not keep up).
+  const uint64_t pair_tiles = ((M + 255) / 256) * ((N + kBN - 1) / kBN);
+  int ctas = 1;
+  if (const char *force = std::getenv("DIFB200_GEMM_CTAS"))
+    ctas = force[0] == '2' ? 2 : (force[0] == '1' ? 1 : ctas);
   CUtensorMap map_a, map_b;
   const uint64_t dims_a[2] = {K, M}, dims_b[2] = {K, N};
   const uint64_t strides[1] = {K};
-  const uint32_t box_a[2] = {(uint32_t)kBK, (uint32_t)kBM}, box_b[2] = {(uint32_t)kBK, (uint32_t)kBN};
+  const uint32_t box_a[2] = {(uint32_t)kBK, (uint32_t)kBM}, box_b[2] = {(uint32_t)kBK, (uint32_t)(kBN / ctas)};
   if (int rc = encode_tensor_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, x, dims_a, strides, box_a,
                                  CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
@@ -389,8 +498,11 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   static std::once_flag once;
   static cudaError_t attr_rc = cudaSuccess;
   std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)kSmemBytes);
+    attr_rc = cudaFuncSetAttribute(gemm_i8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem_bytes<1>());
+    if (attr_rc == cudaSuccess)
+      attr_rc = cudaFuncSetAttribute(gemm_i8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_bytes<2>());
   });
   if (int rc = check_cuda(attr_rc, "cudaFuncSetAttribute(gemm_i8_kernel)"))
     return rc;
@@ -406,12 +518,61 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   p.K = (uint32_t)K;
   p.epilogue = epilogue;
   p.tma_store = tma_store ? 1u : 0u;
+  if (const char *dbg = std::getenv("DIFB200_GEMM_DEBUG"))
+    p.debug = (uint32_t)std::atoi(dbg);
+  if (const char *tr = std::getenv("DIFB200_GEMM_TRACE"))
+    p.trace = reinterpret_cast<unsigned long long *>(std::strtoull(tr, nullptr, 0));
   p.status = status;
+  if (ctas == 2) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3((unsigned)sm_count());
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem_bytes<2>();
+    config.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    config.attrs = &attr;
+    config.numAttrs = 1;
+    // The kernel is persistent: launch exactly as many CTA pairs as can be resident at once
+    // (SM pairs are formed inside a GPC, so this can be fewer than SMs / 2).
+    static int resident_pairs = 0;
+    if (resident_pairs == 0) {
+      int n = 0;
+      if (int rc = check_cuda(cudaOccupancyMaxActiveClusters(&n, gemm_i8_kernel<2>, &config),
+                              "cudaOccupancyMaxActiveClusters"))
+        return rc;
+      resident_pairs = n > 0 ? n : 1;
+    }
+    uint64_t pairs = (uint64_t)resident_pairs;
+    if (pairs > pair_tiles)
+      pairs = pair_tiles;
+    config.gridDim = dim3((unsigned)(2 * pairs));
+    return check_cuda(cudaLaunchKernelEx(&config, gemm_i8_kernel<2>, map_a, map_b, map_c, p),
+                      "gemm_i8_kernel<2> launch");
+  }
   const uint64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
   uint64_t grid = (uint64_t)sm_count();
   if (grid > tiles)
     grid = tiles;
-  gemm_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, map_c, p);
+  if (std::getenv("DIFB200_GEMM_CLUSTER1")) { // measurement aid: single-CTA form launched as clusters of 2
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3((unsigned)(grid & ~1ull));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem_bytes<1>();
+    config.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    config.attrs = &attr;
+    config.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&config, gemm_i8_kernel<1>, map_a, map_b, map_c, p), "launch");
+  }
+  gemm_i8_kernel<1><<<(unsigned)grid, kThreads, smem_bytes<1>(), stream>>>(map_a, map_b, map_c, p);
   return check_cuda(cudaGetLastError(), "gemm_i8_kernel launch");
 }
 

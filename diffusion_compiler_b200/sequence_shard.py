@@ -77,13 +77,20 @@ class GatherBuffers:
         lo = self.rank * self.plan.slice_len
         return t[lo: lo + self.plan.slice_len]
 
-    def all_gather(self, group=None) -> None:
-        """In-place all-gather of the three buffers (each rank contributes its slice)."""
+    def all_gather(self, group=None, names=("k8", "ks", "v"), async_op: bool = False):
+        """In-place all-gather of the named buffers (each rank contributes its slice). With
+        ``async_op`` the collectives are only enqueued and the work handles are returned; their
+        ``wait()`` makes the current stream wait for them."""
         import torch.distributed as dist
+        works = []
         if self.plan.world == 1:
-            return
-        for t in (self.k8, self.ks, self.v):
-            dist.all_gather_into_tensor(t, self.local(t), group=group)
+            return works
+        for name in names:
+            t = getattr(self, name)
+            w = dist.all_gather_into_tensor(t, self.local(t), group=group, async_op=async_op)
+            if async_op:
+                works.append(w)
+        return works
 
 
 class VideoBlock:
@@ -109,16 +116,19 @@ class VideoBlock:
         self.lin = {name: (torch.from_numpy(w).to(device), torch.from_numpy(s).to(device))
                     for name, (w, s) in tensors["linears"].items()}
         self._scratch = None
+        self._comm_stream = None
 
     def _glue(self, name, *args):
         from . import _lib
         _lib.check(getattr(_lib.lib(), name)(*args))
 
     def pre_attention(self, x: torch.Tensor, mods: List[torch.Tensor], plan: ShardPlan, rank: int,
-                      gb: GatherBuffers):
+                      gb: GatherBuffers, on_v_ready=None, on_k_ready=None):
         """Row-local part up to the exchange: norm+modulate, q/k/v projections, q/k norm + RoPE,
         per-token-head quantisation. K codes/scales and V land in this rank's slice of ``gb``.
-        Returns the local query codes and scales."""
+        The order is V, then K, then Q, and ``on_v_ready`` / ``on_k_ready`` are called as soon as
+        the respective slice is enqueued, so that their all-gathers can run under the remaining
+        work. Returns the local query codes and scales."""
         import ctypes as C
         ops = self.ops
         S_loc = x.shape[0]
@@ -131,18 +141,26 @@ class VideoBlock:
         self._glue("difb200_rms_norm_modulate", p(x), p(self.norm1), p(mods[0]), p(mods[1]), p(h), 2, S_loc, hid,
                    1e-5, stream)
         codes, scales = ops.quantize_int8_rows([h], H256)
-        q = ops.linear_int8_scaled(codes, *self._w("q", scales))
-        k = ops.linear_int8_scaled(codes, *self._w("k", scales))
         v_local = gb.local(gb.v)[:S_loc]
         ops.linear_int8_scaled(codes, *self._w("v", scales), out=v_local.view(S_loc, H * D))  # into the gather buffer
-        qr, kr = new(S_loc, H, D), new(S_loc, H, D)
-        for src, w, dst in ((q, self.q_norm, qr), (k, self.k_norm, kr)):
-            self._glue("difb200_qk_norm_rope", p(src), p(w), p(self.cos), p(self.sin), p(dst), 2, 2, S_loc, H, D,
+        if on_v_ready is not None:
+            on_v_ready()
+
+        def norm_rope(name, w):
+            y = ops.linear_int8_scaled(codes, *self._w(name, scales))
+            r = new(S_loc, H, D)
+            self._glue("difb200_qk_norm_rope", p(y), p(w), p(self.cos), p(self.sin), p(r), 2, 2, S_loc, H, D,
                        self.rotary, self.rotary, S_loc, self.cos.shape[0], lo, 1e-5, 0, stream)
-        q8, qs = ops.quantize_int8_rows([qr.view(S_loc * H, D)], DIRECT)
+            return r
+
+        kr = norm_rope("k", self.k_norm)
         # K codes and scales are produced directly inside this rank's slice of the gather buffers
         ops.quantize_int8_rows([kr.view(S_loc * H, D)], DIRECT,
                                out=(gb.local(gb.k8)[:S_loc].view(S_loc * H, D), gb.local(gb.ks)[:S_loc].view(-1)))
+        if on_k_ready is not None:
+            on_k_ready()
+        qr = norm_rope("q", self.q_norm)
+        q8, qs = ops.quantize_int8_rows([qr.view(S_loc * H, D)], DIRECT)
         return q8.view(1, S_loc, H, D), qs
 
     def attend(self, q8: torch.Tensor, qs: torch.Tensor, plan: ShardPlan, gb: GatherBuffers) -> torch.Tensor:
@@ -186,9 +204,28 @@ class VideoBlock:
         if gb is None:
             gb = GatherBuffers(plan, rank, self.heads, self.dim, self.device)
         mark("start")
-        q8, qs = self.pre_attention(x, mods, plan, rank, gb)
+        works = []
+        if plan.world > 1:
+            # The V all-gather runs under the K and Q work, the K all-gather under the Q work:
+            # each is enqueued on a side stream as soon as its producer has been enqueued.
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=self.device)
+            main = torch.cuda.current_stream()
+
+            def launch(names):
+                ready = torch.cuda.Event()
+                ready.record(main)
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(ready)
+                    works.extend(gb.all_gather(group, names=names, async_op=True))
+
+            q8, qs = self.pre_attention(x, mods, plan, rank, gb, on_v_ready=lambda: launch(("v",)),
+                                        on_k_ready=lambda: launch(("k8", "ks")))
+        else:
+            q8, qs = self.pre_attention(x, mods, plan, rank, gb)
         mark("pre_attention")
-        gb.all_gather(group)
+        for w in works:
+            w.wait()  # the main stream waits for the collectives
         mark("gathered")
         attn = self.attend(q8, qs, plan, gb)
         mark("attention")

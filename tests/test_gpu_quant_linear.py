@@ -71,8 +71,17 @@ def _weights(rng, N, K, impl):
     return ob.orc().quantize_int8_rows([wf], impl, 1.0)
 
 
-@pytest.mark.parametrize("M,K,N", [(128, 256, 256), (100, 512, 200), (300, 1024, 520), (1024, 3072, 3072)])
-def test_linear_int8_scaled_bit_exact(ops, M, K, N):
+@pytest.fixture(params=["1", "2"], ids=["single-cta", "cta-pair"])
+def gemm_form(request, monkeypatch):
+    """Runs a test with the 128x256 single-CTA tiles and with the 256x256 CTA-pair (cta_group::2)
+    tiles of the GEMM kernel."""
+    monkeypatch.setenv("DIFB200_GEMM_CTAS", request.param)
+    return request.param
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 256, 256), (100, 512, 200), (300, 1024, 520), (1024, 3072, 3072),
+                                   (2000, 768, 1800)])
+def test_linear_int8_scaled_bit_exact(ops, gemm_form, M, K, N):
     import torch
     rng = np.random.default_rng(M + N)
     ob.orc().lib.orc_set_threads(8)
