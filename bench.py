@@ -300,6 +300,40 @@ def video_block_extra(torch, device, rank, world, dist, iters=5):
             "tokens_per_rank": plan.slice_len}
 
 
+def small_case(name: str):
+    """Three launches of one hot kernel on a case that holds well under 1 GB on the device but
+    exceeds L2 where DRAM figures matter: the commands behind profiles/*.md."""
+    import torch
+    from diffusion_compiler_b200 import ops
+    torch.manual_seed(0)
+    if name == "gemm":    # 37 x 16 tiles of 128x256 = 4 full waves on 148 SMs
+        M, N, K = 4736, 4096, 3072
+        x8 = torch.randint(-127, 128, (M, K), device="cuda", dtype=torch.int8)
+        w8 = torch.randint(-127, 128, (N, K), device="cuda", dtype=torch.int8)
+        rs, cs = torch.rand(M, device="cuda"), torch.rand(N, device="cuda")
+        b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        run = lambda: ops.linear_int8_scaled(x8, w8, rs, cs, bias=b, out=out)
+    elif name == "quant":  # the K=3072 activation of the projection set: 56.6 MB in, 28.3 MB out
+        x = torch.randn(M_TOKENS, 3072, device="cuda", dtype=torch.bfloat16)
+        run = lambda: ops.quantize_int8_rows([x], H256_CONVROT)
+    else:                  # 16 heads of the config-2 sequence: 288 CTAs, about two waves
+        B, S, H, D = 1, 4608, 16, 128
+        q = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+        k = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+        v = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+        q8, qs = ops.quantize_int8_rows([q.view(-1, D)], 1)
+        k8, ks = ops.quantize_int8_rows([k.view(-1, D)], 1)
+        q8, k8 = q8.view(B, S, H, D), k8.view(B, S, H, D)
+        out = torch.empty_like(q)
+        run = lambda: ops.attention_int8(q8, qs, k8, ks, v, out=out)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    ops.poll_status()
+    print("case %s done" % name)
+
+
 def cpu_reference_sample(threads: int, rows_per_thread: int):
     """Times the reference CPU executor (oracle/_ref) -- or, where it was not built, the C
     restatement -- on a row sample of the same four projections, `threads` host threads."""
@@ -350,6 +384,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the attention / block configs")
+    ap.add_argument("--case", choices=["gemm", "quant", "attention"],
+                    help="run 3 launches of one kernel on a small case and exit (the command profiled with ncu)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -361,6 +397,9 @@ def main():
               "parallelism": "token-sharded x%d, weights replicated" % max(world, args.gpus),
               "l2": "inputs+weights+outputs of one step are ~1.1 GB, larger than the 126 MB L2; no flush"}
 
+    if args.case:
+        small_case(args.case)
+        return
     if args.impl == "reference":
         if rank != 0:
             return

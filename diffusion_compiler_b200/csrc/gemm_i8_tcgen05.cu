@@ -103,19 +103,10 @@ struct GemmParams {
   int32_t *acc_out;
   uint32_t M, N, K;
   uint32_t epilogue;
-  unsigned long long *trace; // measurement aid: timestamps of the first k-blocks of unit 0
   uint32_t debug;     // measurement aid: 1 = issue no MMAs, 2 = issue no TMA loads (results are garbage)
   uint32_t tma_store; // 1: outputs leave through TMA stores (needs N % 8 == 0, aligned out)
   DeviceStatus *status;
 };
-
-__device__ __forceinline__ void stamp(const GemmParams &p, uint32_t unit, uint32_t slot, uint32_t i) {
-  if (p.trace && unit == 0 && i < 64) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.trace[slot * 64 + i] = t;
-  }
-}
 
 __device__ __forceinline__ void report_timeout(DeviceStatus *status, uint32_t role, uint32_t detail) {
   if (atomicExch(&status->flag, 1u) == 0u) {
@@ -223,7 +214,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
-          stamp(p, unit, cta_rank * 2, (tile - unit) / units * k_blocks + kb);
           if (p.debug == 2) {
             ptx::mbar_arrive(full_bar + 8 * stage);
           } else {
@@ -255,7 +245,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             ok = false;
             break;
           }
-          stamp(p, unit, 3, (tile - unit) / units * k_blocks + kb);
           ptx::mbar_arrive_cluster(ptx::mapa(full_bar + 8 * stage, 0));
           if (++stage == kStages) {
             stage = 0;
@@ -294,7 +283,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           ptx::tc_fence_after();
-          stamp(p, unit, 1, local * k_blocks + kb);
           const uint32_t a_addr = smem_base + stage * kStageBytes, b_addr = a_addr + kABytes;
           const uint64_t a_desc = ptx::smem_desc_sw128(a_addr, 16, 1024);
           const uint64_t b_desc = ptx::smem_desc_sw128(b_addr, 16, 1024);
@@ -520,8 +508,6 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   p.tma_store = tma_store ? 1u : 0u;
   if (const char *dbg = std::getenv("DIFB200_GEMM_DEBUG"))
     p.debug = (uint32_t)std::atoi(dbg);
-  if (const char *tr = std::getenv("DIFB200_GEMM_TRACE"))
-    p.trace = reinterpret_cast<unsigned long long *>(std::strtoull(tr, nullptr, 0));
   p.status = status;
   if (ctas == 2) {
     cudaLaunchConfig_t config{};

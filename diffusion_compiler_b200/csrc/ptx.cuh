@@ -38,14 +38,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                : "memory");
   return ok != 0;
 }
-// Bounded wait. try_wait itself suspends for a hardware-defined time slice, so the limit
-// below corresponds to seconds, far beyond any legitimate wait in these kernels.
-constexpr uint32_t kWaitLimit = 1u << 24;
+// Bounded wait: gives up after kWaitNanoseconds of wall time (the global nanosecond timer is
+// read every 256 polls), far beyond any legitimate wait in these kernels, so that a protocol
+// error ends in a reported status within seconds instead of a hang.
+constexpr unsigned long long kWaitNanoseconds = 1500ull * 1000ull * 1000ull;
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i)
+  for (int i = 0; i < 256; ++i)
     if (mbar_try_wait(bar, parity))
       return true;
-  return false;
+  const unsigned long long start = global_timer();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity))
+        return true;
+    if (global_timer() - start > kWaitNanoseconds)
+      return false;
+  }
 }
 
 // 2-D tiled TMA load, global -> this CTA's shared memory, completion on an mbarrier.
@@ -228,6 +241,14 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
 __device__ __forceinline__ void mma_commit_pair_both(uint32_t bar, uint16_t cta_mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::
                    "r"(bar), "h"(cta_mask)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+               "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
                : "memory");
 }
 
