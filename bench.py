@@ -48,12 +48,19 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
-def recorded_traffic(kernel: str):
-    """DRAM bytes per launch of `kernel` from the committed ncu capture summary, or None."""
+def recorded_traffic(kernel: str, operand_bytes: float, output_bytes: float):
+    """DRAM bytes (read + written) per launch of `kernel`, or None when no capture is recorded.
+
+    The committed ncu capture holds dram__bytes_read/write of one launch on a small case together
+    with that case's operand and output bytes; reads scale with the operand bytes (every operand
+    byte is fetched once) and writes with the output bytes, so the figure returned is the capture
+    scaled to the average launch of this benchmark (operand_bytes / output_bytes per launch)."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
     try:
         with open(path) as f:
-            return json.load(f).get(kernel)
+            rec = json.load(f)[kernel]
+        return (rec["dram_read_bytes"] * operand_bytes / rec["operand_bytes"]
+                + rec["dram_write_bytes"] * output_bytes / rec["output_bytes"])
     except Exception:
         return None
 
@@ -501,12 +508,20 @@ def main():
                          "peak_source": "2 x %s bf16 burst TFLOP/s (INT8 dense = 2x bf16 on B200); nominal 4500"
                                         % peaks["source"],
                          "frac_of_nominal_4500": gemm_tops / 4500.0,
-                         "traffic": recorded_traffic("gemm_i8_kernel")},
+                         "traffic": recorded_traffic(
+                             "gemm_i8_kernel",
+                             sum(M_TOKENS * K + N * K for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS),
+                             sum(2.0 * M_TOKENS * N for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS)),
+                         "traffic_note": "bytes per launch: ncu capture of M=4736 N=4096 K=3072 scaled by operand "
+                                         "and output bytes to the average of the 4 launches of a step"},
             "roofline_quant": {"bound": "hbm", "kernel": "convrot_quant_kernel",
                                "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                                "unit": "GB/s", "frac": quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                "note": "CUDA events around the 4 quantize launches of every step",
-                               "traffic": recorded_traffic("convrot_quant_kernel")},
+                               "traffic": recorded_traffic(
+                                   "convrot_quant_kernel",
+                                   sum(2.0 * M_TOKENS * K for _, K, _, _ in PROJECTIONS) / len(PROJECTIONS),
+                                   sum(M_TOKENS * K + 4.0 * M_TOKENS for _, K, _, _ in PROJECTIONS) / len(PROJECTIONS))},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
