@@ -313,8 +313,8 @@ def small_case(name: str):
     import torch
     from diffusion_compiler_b200 import ops
     torch.manual_seed(0)
-    if name == "gemm":    # 37 x 16 tiles of 128x256 = 4 full waves on 148 SMs
-        M, N, K = 4736, 4096, 3072
+    if name == "gemm":    # the QKV projection of the step: 36 x 36 pair tiles of 256x256, 227 MB
+        M, N, K = M_TOKENS, 9216, 3072
         x8 = torch.randint(-127, 128, (M, K), device="cuda", dtype=torch.int8)
         w8 = torch.randint(-127, 128, (N, K), device="cuda", dtype=torch.int8)
         rs, cs = torch.rand(M, device="cuda"), torch.rand(N, device="cuda")

@@ -18,10 +18,13 @@
 //             8192 INT8 MACs/clk/SM the 128x256 single-CTA tile needs 48 KB written plus 48 KB read
 //             per 512 clocks, which is what bounds the CTAS = 1 form. The leader CTA (cluster rank
 //             0) issues the MMAs; both CTAs load, and both run the epilogue on their own 128 rows.
-//             TMA loads never use multicast and complete on the loading CTA's own mbarrier; a
-//             relay thread in the peer forwards one arrive per stage to the leader's barrier. The
-//             leader releases stages and publishes accumulators to both CTAs with one
-//             tcgen05.commit that signals the mbarrier of both CTAs.
+//             TMA loads never use multicast. The bytes of both CTAs are counted on the leader's
+//             mbarrier (the peer issues the cta_group::2 form of the load, whose completion may
+//             target the peer CTA's barrier); the leader releases stages and publishes
+//             accumulators to both CTAs with one tcgen05.commit that signals the mbarrier of both
+//             CTAs. The only remaining software signal across the pair is the epilogue's arrive
+//             on the leader's accumulator-empty barrier, with CTA-scope release: a cluster-scope
+//             release arrive per k-block costs microseconds while TMA traffic is in flight.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -163,14 +166,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile uint32_t *abort_ptr = slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool no_mma = (p.debug & 1u) != 0, no_tma = (p.debug & 2u) != 0; // measurement aids
   const uint32_t tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + kBN - 1) / kBN;
   const uint32_t num_tiles = tiles_m * tiles_n;
   const uint32_t k_blocks = (p.K + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      // leader: its own producer's arrive.expect_tx plus, for a pair, the peer's relay arrive
-      ptx::mbar_init(full_bar + 8 * s, (CTAS == 2 && cta_rank == 0) ? 2 : 1);
+      ptx::mbar_init(full_bar + 8 * s, 1);
       ptx::mbar_init(empty_bar + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -198,112 +201,114 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   ptx::tc_fence_after();
   const uint32_t tmem_base = *slot_ptr;
 
-  if (warp == 0) {
+  // The producer warp and the MMA warp run their loops with all 32 lanes and warp-uniform
+  // control flow (every wait ends in a vote) and let one elected lane issue the asynchronous
+  // instructions. Loop state, addresses and descriptors are then warp-uniform values; with a
+  // single-lane loop (divergent code) every operand of every TMA / MMA instruction is first
+  // moved between register files, and that loop needed 640-680 cycles per k-block against the
+  // 512 cycles the four MMAs of a k-block take.
+  auto give_up = [&](uint32_t role, uint32_t detail) {
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      for (uint32_t tile = unit; tile < num_tiles && ok; tile += units) {
-        const int32_t m0 = (int32_t)((tile / tiles_n) * kTileM + cta_rank * kBM);
-        const int32_t n0 = (int32_t)((tile % tiles_n) * kBN + cta_rank * Cfg<CTAS>::kBRows);
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-          if (*abort_ptr || !ptx::mbar_wait(empty_bar + 8 * stage, phase ^ 1u)) {
-            if (!*abort_ptr)
-              report_timeout(p.status, 0, kb);
-            *abort_ptr = 1;
-            ok = false;
-            break;
-          }
-          const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
-          if (p.debug == 2) {
-            ptx::mbar_arrive(full_bar + 8 * stage);
+      if (!*abort_ptr)
+        report_timeout(p.status, role, detail);
+      *abort_ptr = 1;
+    }
+  };
+  if (warp == 0) {
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t tile = unit; tile < num_tiles && ok; tile += units) {
+      const int32_t m0 = (int32_t)((tile / tiles_n) * kTileM + cta_rank * kBM);
+      const int32_t n0 = (int32_t)((tile % tiles_n) * kBN + cta_rank * Cfg<CTAS>::kBRows);
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        if (!ptx::mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1u, abort_ptr)) {
+          give_up(0, kb);
+          ok = false;
+          break;
+        }
+        const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
+        const uint32_t bar = full_bar + 8 * stage;
+        const int32_t k0 = (int32_t)(kb * kBK);
+        if (ptx::elect_one()) {
+          if (no_tma) {
+            if (cta_rank == 0)
+              ptx::mbar_arrive(bar);
+          } else if (CTAS == 2) {
+            // A pair counts the bytes of both CTAs on the leader's barrier: the leader expects
+            // them all, the peer's loads complete their bytes there (cta_group::2 form of the
+            // load) and the peer itself never arrives.
+            if (cta_rank == 0) {
+              ptx::mbar_expect_tx(bar, 2 * kStageBytes);
+              ptx::tma_load_2d(a_dst, &map_a, bar, k0, m0);
+              ptx::tma_load_2d(b_dst, &map_b, bar, k0, n0);
+            } else {
+              const uint32_t leader_bar = ptx::mapa(bar, 0);
+              ptx::tma_load_2d_pair(a_dst, &map_a, leader_bar, k0, m0);
+              ptx::tma_load_2d_pair(b_dst, &map_b, leader_bar, k0, n0);
+            }
           } else {
-            // Every CTA counts its bytes on its own barrier (a pair's peer then relays one
-            // arrive per stage to the leader, see below: letting the peer's TMA complete its
-            // bytes on the leader's barrier directly cut the load rate to a quarter).
-            ptx::mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
-            ptx::tma_load_2d(a_dst, &map_a, full_bar + 8 * stage, (int32_t)(kb * kBK), m0);
-            ptx::tma_load_2d(b_dst, &map_b, full_bar + 8 * stage, (int32_t)(kb * kBK), n0);
+            ptx::mbar_expect_tx(bar, kStageBytes);
+            ptx::tma_load_2d(a_dst, &map_a, bar, k0, m0);
+            ptx::tma_load_2d(b_dst, &map_b, bar, k0, n0);
           }
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+        }
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
   } else if (warp == 1) {
-    if (CTAS == 2 && lane == 0 && cta_rank == 1) {
-      // Relay of the pair's peer CTA: when a stage of this CTA has landed, tell the leader.
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      for (uint32_t tile = unit; tile < num_tiles && ok; tile += units) {
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-          if (*abort_ptr || !ptx::mbar_wait(full_bar + 8 * stage, phase)) {
-            if (!*abort_ptr)
-              report_timeout(p.status, 3, kb);
-            *abort_ptr = 1;
-            ok = false;
-            break;
-          }
-          ptx::mbar_arrive_cluster(ptx::mapa(full_bar + 8 * stage, 0));
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
-    }
-    if (lane == 0 && cta_rank == 0) {
+    if (cta_rank == 0) {
       constexpr uint32_t idesc = ptx::make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, 0, 0, kTileM, kBN);
+      const uint64_t desc0 = ptx::smem_desc_sw128(smem_base, 16, 1024);
       uint32_t stage = 0, phase = 0, local = 0;
       bool ok = true;
       auto commit = [&](uint32_t bar) { // arrives on `bar` of every CTA of the pair
-        if (CTAS == 2) {
+        if (CTAS == 2)
           ptx::mma_commit_pair_both(bar, (uint16_t)3);
-        } else {
+        else
           ptx::mma_commit(bar);
-        }
       };
       for (uint32_t tile = unit; tile < num_tiles && ok; tile += units, ++local) {
         const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
-        if (*abort_ptr || !ptx::mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u)) {
-          if (!*abort_ptr)
-            report_timeout(p.status, 1, 0xffffu);
-          *abort_ptr = 1;
+        if (!ptx::mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_ptr)) {
+          give_up(1, 0xffffu);
           break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-          if (*abort_ptr || !ptx::mbar_wait(full_bar + 8 * stage, phase)) {
-            if (!*abort_ptr)
-              report_timeout(p.status, 1, kb);
-            *abort_ptr = 1;
+          if (!ptx::mbar_wait_warp(full_bar + 8 * stage, phase, abort_ptr)) {
+            give_up(1, kb);
             ok = false;
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t a_addr = smem_base + stage * kStageBytes, b_addr = a_addr + kABytes;
-          const uint64_t a_desc = ptx::smem_desc_sw128(a_addr, 16, 1024);
-          const uint64_t b_desc = ptx::smem_desc_sw128(b_addr, 16, 1024);
+          // descriptors of this stage: only the 14-bit address field (16-byte units) moves
+          const uint64_t a_desc = desc0 + (uint64_t)((stage * kStageBytes) >> 4);
+          const uint64_t b_desc = a_desc + (uint64_t)(kABytes >> 4);
+          if (ptx::elect_one()) {
+            if (!no_mma) {
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            const uint64_t ka = a_desc + (uint64_t)(k * kUmmaK >> 4), kb_desc = b_desc + (uint64_t)(k * kUmmaK >> 4);
-            const uint32_t accumulate = (kb | (uint32_t)k) != 0u ? 1u : 0u;
-            if (p.debug == 1)
-              continue;
-            if (CTAS == 2)
-              ptx::mma_i8_ss_pair(d_tmem, ka, kb_desc, idesc, accumulate);
-            else
-              ptx::mma_i8_ss(d_tmem, ka, kb_desc, idesc, accumulate);
+              for (int k = 0; k < kBK / kUmmaK; ++k) {
+                const uint32_t accumulate = k != 0 ? 1u : (kb != 0u ? 1u : 0u);
+                if (CTAS == 2)
+                  ptx::mma_i8_ss_pair(d_tmem, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
+                                      idesc, accumulate);
+                else
+                  ptx::mma_i8_ss(d_tmem, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
+                                 idesc, accumulate);
+              }
+            }
+            commit(empty_bar + 8 * stage); // frees the smem stage when these MMAs retire
           }
-          commit(empty_bar + 8 * stage); // frees the smem stage when these MMAs retire
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok)
+        if (ok && ptx::elect_one())
           commit(tfull_bar + 8 * acc); // accumulator complete
       }
     }
@@ -409,7 +414,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       __syncwarp();
       if (lane == 0) {
         if (CTAS == 2)
-          ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar + 8 * acc, 0)); // the leader issues the MMAs
+          ptx::mbar_arrive_remote(ptx::mapa(tempty_bar + 8 * acc, 0)); // the leader issues the MMAs
         else
           ptx::mbar_arrive(tempty_bar + 8 * acc);
       }
@@ -455,10 +460,15 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   if (!status)
     return fail(kOutOfMemory, "LinearInt8Scaled: cannot allocate device status words");
 
-  // The single-CTA form is the default; DIFB200_GEMM_CTAS=2 selects the CTA-pair form, which is
-  // bit-identical but currently slower (its load pipeline does not keep up).
+  // Form: the CTA-pair kernel moves a third less through shared memory per MAC and is the faster
+  // one whenever its 256x256 tiles fill the machine as well as 128x256 tiles do; the choice
+  // compares the number of tile waves (a pair wave costs about 0.94 of a single-CTA wave).
+  // DIFB200_GEMM_CTAS=1|2 forces a form (both give identical bits).
   const uint64_t pair_tiles = ((M + 255) / 256) * ((N + kBN - 1) / kBN);
-  int ctas = 1;
+  const uint64_t single_tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+  const uint64_t sms = (uint64_t)sm_count();
+  const uint64_t single_waves = (single_tiles + sms - 1) / sms, pair_waves = (pair_tiles + sms / 2 - 1) / (sms / 2);
+  int ctas = (M > (uint64_t)kBM && 94 * pair_waves <= 100 * single_waves) ? 2 : 1;
   if (const char *force = std::getenv("DIFB200_GEMM_CTAS"))
     ctas = force[0] == '2' ? 2 : (force[0] == '1' ? 1 : ctas);
   CUtensorMap map_a, map_b;
@@ -507,7 +517,7 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   p.epilogue = epilogue;
   p.tma_store = tma_store ? 1u : 0u;
   if (const char *dbg = std::getenv("DIFB200_GEMM_DEBUG"))
-    p.debug = (uint32_t)std::atoi(dbg);
+    p.debug = (uint32_t)std::strtoul(dbg, nullptr, 0);
   p.status = status;
   if (ctas == 2) {
     cudaLaunchConfig_t config{};

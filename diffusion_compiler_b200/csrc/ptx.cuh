@@ -47,6 +47,17 @@ __device__ __forceinline__ unsigned long long global_timer() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// One lane of the (fully active) warp is elected, the same one every time.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t elected;
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "elect.sync _|p, 0xffffffff;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}"
+               : "=r"(elected));
+  return elected != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (int i = 0; i < 256; ++i)
     if (mbar_try_wait(bar, parity))
@@ -59,6 +70,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (global_timer() - start > kWaitNanoseconds)
       return false;
   }
+}
+// The same wait executed by all 32 lanes of a warp with a warp-uniform result (a vote), so that
+// the loop around it keeps uniform control flow and its state can live in uniform registers.
+// The common case is one try_wait and one vote. `abort_flag` (shared memory, set by any role of
+// the CTA that gave up) ends the wait early.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity)))
+    return true;
+  bool ok = false;
+  for (int i = 0; i < 512 && !ok; ++i) // the global timer is slow to read: not on this path
+    ok = mbar_try_wait(bar, parity);
+  if (!ok) {
+    const unsigned long long start = global_timer();
+    for (;;) {
+      for (int i = 0; i < 256 && !ok; ++i)
+        ok = mbar_try_wait(bar, parity);
+      if (ok || *abort_flag || global_timer() - start > kWaitNanoseconds)
+        break;
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
 }
 
 // 2-D tiled TMA load, global -> this CTA's shared memory, completion on an mbarrier.
@@ -200,6 +232,12 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, ui
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Arrive on a peer CTA's mbarrier with CTA-scope release only: enough where the waiter needs no
+// data written by this thread (the cluster-scope release form costs microseconds while TMA
+// traffic is in flight).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load of a CTA pair: data lands in this CTA's shared memory, the completion bytes are
 // counted on an mbarrier that may live in the peer CTA (no multicast involved).

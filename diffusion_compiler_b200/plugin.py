@@ -10,6 +10,7 @@ parity tests read like the reference's own.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Dict, Optional
 
 import numpy as np
@@ -108,6 +109,7 @@ class PreparedExecution:
                  constants: Dict[int, np.ndarray]):
         self._executor, self.program, self._handle, self.compile_telemetry = executor, program, handle, telemetry
         self._v2, self._constants = v2, constants
+        executor._prepared.add(self)
 
     def run(self, inputs: Dict[int, np.ndarray], warmups: int = 0, iterations: int = 1,
             minimum_free_bytes: int = 0, outputs: Optional[Dict[int, np.ndarray]] = None):
@@ -162,6 +164,9 @@ class PluginExecutor:
         if rc != 0:
             raise BackendError(rc, buf.value.decode(errors="replace"))
         self._ctx = ctx
+        # executables must be destroyed before their context (reference src/backend/plugin.cpp:96-99,
+        # 186-191), so the executor closes what it prepared before it destroys the context
+        self._prepared = weakref.WeakSet()
 
     def prepare(self, program: diffir.Program, constants: Dict[int, np.ndarray],
                 minimum_free_bytes: int = 0) -> PreparedExecution:
@@ -185,6 +190,8 @@ class PluginExecutor:
 
     def close(self):
         if self._ctx:
+            for prepared in list(self._prepared):
+                prepared.close()
             self.api.destroy(self._ctx)
             self._ctx = None
 
