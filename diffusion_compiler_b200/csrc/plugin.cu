@@ -33,7 +33,9 @@ namespace {
 
 struct Context {
   int device = 0;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;    // kernels
+  cudaStream_t h2d = nullptr;       // uploads of an overlapped execute
+  cudaStream_t d2h = nullptr;       // downloads of an overlapped execute
   char device_name[256] = {0};
 };
 
@@ -56,9 +58,16 @@ struct Executable {
   unsigned int *flag = nullptr;     // device flag for data-dependent argument errors
   uint64_t resident_bytes = 0;
   bool constants_bound = false;     // v2: uploaded at compile
+  std::vector<cudaEvent_t> uploaded, produced; // per tensor, made on first use by an overlapped execute
   ~Executable() {
     if (ctx)
       cudaSetDevice(ctx->device);
+    for (cudaEvent_t e : uploaded)
+      if (e)
+        cudaEventDestroy(e);
+    for (cudaEvent_t e : produced)
+      if (e)
+        cudaEventDestroy(e);
     for (void *p : dev)
       if (p)
         cudaFree(p);
@@ -224,13 +233,46 @@ void allocate(Executable &exe) {
   require_cuda(cudaMemset(exe.flag, 0, sizeof(unsigned int)), "cudaMemset(flag)");
 }
 
+// State of an overlapped execute (one pass, copies on their own streams): which Input tensors'
+// uploads the kernel stream has not yet waited for, and the order in which Output tensors
+// became final.
+struct Overlap {
+  std::vector<uint8_t> upload_pending;
+  std::vector<int> finished_outputs;
+};
+
 // ---- one pass over the program ---------------------------------------------------------------
-void run_steps(Executable &exe) {
+void run_steps(Executable &exe, Overlap *overlap = nullptr) {
   const ir::Program &p = exe.program;
   cudaStream_t s = exe.ctx->stream;
   auto D = [&](uint32_t id) -> void * { return exe.dev[(size_t)p.index_of(id)]; };
   auto T = [&](uint32_t id) -> const ir::Tensor & { return *p.tensor(id); };
-  for (const Step &st : exe.steps) {
+  auto await_upload = [&](int idx) {
+    if (idx >= 0 && overlap->upload_pending[(size_t)idx]) {
+      require_cuda(cudaStreamWaitEvent(s, exe.uploaded[(size_t)idx], 0), "cudaStreamWaitEvent(upload)");
+      overlap->upload_pending[(size_t)idx] = 0;
+    }
+  };
+  for (size_t step_index = 0; step_index <= exe.steps.size(); ++step_index) {
+    if (overlap && step_index > 0) {
+      // every Output tensor the previous op (run, fused away or skipped) lists is final now
+      for (auto id : exe.steps[step_index - 1].op->out) {
+        const int idx = p.index_of(id);
+        if (idx >= 0 && p.tensors[(size_t)idx].has(ir::Output) && exe.dev[(size_t)idx]) {
+          require_cuda(cudaEventRecord(exe.produced[(size_t)idx], s), "cudaEventRecord(output)");
+          overlap->finished_outputs.push_back(idx);
+        }
+      }
+    }
+    if (step_index == exe.steps.size())
+      break;
+    const Step &st = exe.steps[step_index];
+    if (overlap) {
+      for (auto id : st.op->in)
+        await_upload(p.index_of(id));
+      await_upload(st.bias_tensor);
+      await_upload(st.mask_tensor);
+    }
     if (st.skip)
       continue;
     const ir::Op &op = *st.op;
@@ -466,8 +508,10 @@ dif_backend_status create(int32_t device_ordinal, dif_backend_context *context, 
     ctx->device = device_ordinal;
     require_cuda(cudaSetDevice(device_ordinal), "cudaSetDevice");
     require_cuda(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate");
-    std::snprintf(ctx->device_name, sizeof(ctx->device_name), "%s (difb200 sm_100a, int8-attention %s)", prop.name,
-                  int8_attention_enabled() ? "on" : "off");
+    require_cuda(cudaStreamCreateWithFlags(&ctx->h2d, cudaStreamNonBlocking), "cudaStreamCreate");
+    require_cuda(cudaStreamCreateWithFlags(&ctx->d2h, cudaStreamNonBlocking), "cudaStreamCreate");
+    std::snprintf(ctx->device_name, sizeof(ctx->device_name), "%.200s (difb200 sm_100a, int8-attention %s)",
+                  prop.name, int8_attention_enabled() ? "on" : "off");
     *context = ctx.release();
   });
 }
@@ -479,10 +523,16 @@ void destroy(dif_backend_context context) {
   cudaSetDevice(ctx->device);
   if (ctx->stream)
     cudaStreamDestroy(ctx->stream);
+  if (ctx->h2d)
+    cudaStreamDestroy(ctx->h2d);
+  if (ctx->d2h)
+    cudaStreamDestroy(ctx->d2h);
   delete ctx;
 }
 
-void upload(Executable &exe, const dif_backend_tensor_view &view, uint32_t role, const char *what) {
+// Returns the tensor's index. The copy goes to `stream` (default: the kernel stream).
+int upload(Executable &exe, const dif_backend_tensor_view &view, uint32_t role, const char *what,
+           cudaStream_t stream = nullptr) {
   const int idx = exe.program.index_of(view.tensor_id);
   if (idx < 0)
     throw PluginError{1, std::string(what) + ": unknown tensor id " + std::to_string(view.tensor_id)};
@@ -492,8 +542,9 @@ void upload(Executable &exe, const dif_backend_tensor_view &view, uint32_t role,
                              " does not match the program (role, dtype or byte count)"};
   if (exe.dev[(size_t)idx] && t.bytes())
     require_cuda(cudaMemcpyAsync(exe.dev[(size_t)idx], view.host_data, (size_t)t.bytes(), cudaMemcpyHostToDevice,
-                                 exe.ctx->stream),
+                                 stream ? stream : exe.ctx->stream),
                  "cudaMemcpyAsync(host to device)");
+  return idx;
 }
 
 dif_backend_status compile_common(dif_backend_context context, const uint8_t *diffir, size_t size,
@@ -593,32 +644,9 @@ dif_backend_status execute(dif_backend_executable executable, const dif_backend_
     if (input_count != expected)
       throw PluginError{1, "execute: expected " + std::to_string(expected) + " input views, got " +
                                std::to_string(input_count)};
-    for (size_t i = 0; i < input_count; ++i) {
-      const int idx = exe->program.index_of(inputs[i].tensor_id);
-      const bool is_const = idx >= 0 && exe->program.tensors[(size_t)idx].has(ir::Constant);
-      upload(*exe, inputs[i], is_const ? ir::Constant : ir::Input, "execute");
-    }
-    for (uint32_t w = 0; w < options->warmups; ++w)
-      run_steps(*exe);
-    cudaEvent_t e0, e1;
-    require_cuda(cudaEventCreate(&e0), "cudaEventCreate");
-    require_cuda(cudaEventCreate(&e1), "cudaEventCreate");
-    double sum = 0.0, lo = std::numeric_limits<double>::max(), hi = 0.0;
-    for (uint32_t it = 0; it < options->iterations; ++it) {
-      cudaEventRecord(e0, ctx->stream);
-      run_steps(*exe);
-      cudaEventRecord(e1, ctx->stream);
-      require_cuda(cudaEventSynchronize(e1), "cudaEventSynchronize");
-      float ms = 0.0f;
-      cudaEventElapsedTime(&ms, e0, e1);
-      sum += ms;
-      lo = ms < lo ? ms : lo;
-      hi = ms > hi ? ms : hi;
-    }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
     if (output_count > n_out)
       throw PluginError{1, "execute: more output views than Output-role tensors"};
+    std::vector<int> out_view_of(exe->program.tensors.size(), -1);
     for (size_t i = 0; i < output_count; ++i) {
       const int idx = exe->program.index_of(outputs[i].tensor_id);
       if (idx < 0 || !exe->program.tensors[(size_t)idx].has(ir::Output) ||
@@ -626,15 +654,125 @@ dif_backend_status execute(dif_backend_executable executable, const dif_backend_
           (!outputs[i].host_data && outputs[i].byte_count))
         throw PluginError{1, "execute: output view " + std::to_string(outputs[i].tensor_id) +
                                  " does not match an Output-role tensor"};
-      if (outputs[i].byte_count)
-        require_cuda(cudaMemcpyAsync(outputs[i].host_data, exe->dev[(size_t)idx], (size_t)outputs[i].byte_count,
-                                     cudaMemcpyDeviceToHost, ctx->stream),
+      out_view_of[(size_t)idx] = (int)i;
+    }
+    auto download = [&](size_t view, int idx, cudaStream_t stream) {
+      if (outputs[view].byte_count)
+        require_cuda(cudaMemcpyAsync(outputs[view].host_data, exe->dev[(size_t)idx], (size_t)outputs[view].byte_count,
+                                     cudaMemcpyDeviceToHost, stream),
                      "cudaMemcpyAsync(device to host)");
+    };
+    struct Events { // timing pair, destroyed on every way out
+      cudaEvent_t a = nullptr, b = nullptr;
+      ~Events() {
+        if (a)
+          cudaEventDestroy(a);
+        if (b)
+          cudaEventDestroy(b);
+      }
+    } events;
+    require_cuda(cudaEventCreate(&events.a), "cudaEventCreate");
+    require_cuda(cudaEventCreate(&events.b), "cudaEventCreate");
+    const cudaEvent_t e0 = events.a, e1 = events.b;
+    struct Drain { // on an error, nothing may still be reading or writing the caller's buffers
+      Context *ctx;
+      bool armed = true;
+      ~Drain() {
+        if (armed) {
+          cudaStreamSynchronize(ctx->h2d);
+          cudaStreamSynchronize(ctx->stream);
+          cudaStreamSynchronize(ctx->d2h);
+        }
+      }
+    } drain{ctx};
+    double sum = 0.0, lo = std::numeric_limits<double>::max(), hi = 0.0;
+    // A single pass (no warm-ups, one iteration -- what the host's run() asks for) overlaps the
+    // three phases: uploads go to their own stream in view order, every op waits only for the
+    // uploads it reads, and each Output tensor starts its way back as soon as the op that
+    // completes it has been enqueued. With page-locked host buffers the two copy directions and
+    // the kernels then run concurrently; with pageable buffers the copies block the calling
+    // thread as they always do and the result is the same. The telemetry time of such a pass is
+    // the span of the kernel stream, upload waits included.
+    const bool overlapped = options->warmups == 0 && options->iterations == 1;
+    if (overlapped) {
+      const size_t n = exe->program.tensors.size();
+      if (exe->uploaded.empty()) {
+        exe->uploaded.assign(n, nullptr);
+        exe->produced.assign(n, nullptr);
+        for (size_t i = 0; i < n; ++i) {
+          const ir::Tensor &t = exe->program.tensors[i];
+          if (t.has(ir::Input) || (!exe->constants_bound && t.has(ir::Constant)))
+            require_cuda(cudaEventCreateWithFlags(&exe->uploaded[i], cudaEventDisableTiming), "cudaEventCreate");
+          if (t.has(ir::Output))
+            require_cuda(cudaEventCreateWithFlags(&exe->produced[i], cudaEventDisableTiming), "cudaEventCreate");
+        }
+      }
+      Overlap overlap;
+      overlap.upload_pending.assign(n, 0);
+      // the upload stream starts after whatever the kernel stream still holds of an earlier call
+      require_cuda(cudaEventRecord(e0, ctx->stream), "cudaEventRecord");
+      require_cuda(cudaStreamWaitEvent(ctx->h2d, e0, 0), "cudaStreamWaitEvent");
+      for (size_t i = 0; i < input_count; ++i) {
+        const int idx = exe->program.index_of(inputs[i].tensor_id);
+        const bool is_const = idx >= 0 && exe->program.tensors[(size_t)idx].has(ir::Constant);
+        const int at = upload(*exe, inputs[i], is_const ? ir::Constant : ir::Input, "execute", ctx->h2d);
+        if (exe->uploaded[(size_t)at]) {
+          require_cuda(cudaEventRecord(exe->uploaded[(size_t)at], ctx->h2d), "cudaEventRecord(upload)");
+          overlap.upload_pending[(size_t)at] = 1;
+        }
+      }
+      run_steps(*exe, &overlap);
+      // an upload nothing waited for (an Input no op reads) still has to land before the call ends
+      for (size_t i = 0; i < n; ++i)
+        if (overlap.upload_pending[i])
+          require_cuda(cudaStreamWaitEvent(ctx->stream, exe->uploaded[i], 0), "cudaStreamWaitEvent(upload)");
+      require_cuda(cudaEventRecord(e1, ctx->stream), "cudaEventRecord");
+      std::vector<uint8_t> sent(output_count, 0);
+      for (int idx : overlap.finished_outputs) {
+        const int view = out_view_of[(size_t)idx];
+        if (view < 0 || sent[(size_t)view])
+          continue;
+        require_cuda(cudaStreamWaitEvent(ctx->d2h, exe->produced[(size_t)idx], 0), "cudaStreamWaitEvent(output)");
+        download((size_t)view, idx, ctx->d2h);
+        sent[(size_t)view] = 1;
+      }
+      // outputs no op produces (an Output that is also an Input or a Constant) go last
+      require_cuda(cudaStreamWaitEvent(ctx->d2h, e1, 0), "cudaStreamWaitEvent");
+      for (size_t i = 0; i < output_count; ++i)
+        if (!sent[i])
+          download(i, exe->program.index_of(outputs[i].tensor_id), ctx->d2h);
+      require_cuda(cudaStreamSynchronize(ctx->d2h), "cudaStreamSynchronize(download)");
+      require_cuda(cudaEventSynchronize(e1), "cudaEventSynchronize");
+      float ms = 0.0f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      sum = lo = hi = ms;
+    } else {
+      for (size_t i = 0; i < input_count; ++i) {
+        const int idx = exe->program.index_of(inputs[i].tensor_id);
+        const bool is_const = idx >= 0 && exe->program.tensors[(size_t)idx].has(ir::Constant);
+        upload(*exe, inputs[i], is_const ? ir::Constant : ir::Input, "execute");
+      }
+      for (uint32_t w = 0; w < options->warmups; ++w)
+        run_steps(*exe);
+      for (uint32_t it = 0; it < options->iterations; ++it) {
+        cudaEventRecord(e0, ctx->stream);
+        run_steps(*exe);
+        cudaEventRecord(e1, ctx->stream);
+        require_cuda(cudaEventSynchronize(e1), "cudaEventSynchronize");
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        sum += ms;
+        lo = ms < lo ? ms : lo;
+        hi = ms > hi ? ms : hi;
+      }
+      for (size_t i = 0; i < output_count; ++i)
+        download(i, exe->program.index_of(outputs[i].tensor_id), ctx->stream);
     }
     unsigned int flag = 0;
     require_cuda(cudaMemcpyAsync(&flag, exe->flag, sizeof(flag), cudaMemcpyDeviceToHost, ctx->stream),
                  "cudaMemcpyAsync(flag)");
     require_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    drain.armed = false;
     if (flag) {
       cudaMemset(exe->flag, 0, sizeof(flag));
       throw PluginError{5, "RotaryFrequency pair map is outside its declared axis"};
