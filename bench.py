@@ -513,8 +513,8 @@ def main():
                              "gemm_i8_kernel",
                              sum(M_TOKENS * K + N * K for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS),
                              sum(2.0 * M_TOKENS * N for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS)),
-                         "traffic_note": "bytes per launch: ncu capture of M=4736 N=4096 K=3072 scaled by operand "
-                                         "and output bytes to the average of the 4 launches of a step"},
+                         "traffic_note": "bytes per launch: ncu capture of the QKV launch (M=9216 N=9216 K=3072) scaled by "
+                                         "operand and output bytes to the average of the 4 launches of a step"},
             "roofline_quant": {"bound": "hbm", "kernel": "convrot_quant_kernel",
                                "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                                "unit": "GB/s", "frac": quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
