@@ -13,8 +13,14 @@
 //                                                   (nearest-even) to 22 significant bits;
 //                                                   u_j = -inf for masked keys
 //   A     = qs_i * (scale * log2(e))
-//   m     = an integer >= ceil(max_j u_j * A)       (any such integer gives the same result:
-//                                                    bf16 rounding commutes with powers of two)
+//   m     = an integer >= ceil(max_j u_j * A)       (any such integer gives the same result up
+//                                                    to the rounding of the fma below: bf16
+//                                                    rounding commutes with powers of two). The
+//                                                    kernel takes the Cauchy-Schwarz bound
+//                                                    ceil(A * |q8_i| * max_j(|k8_j| * ks'_j)) when
+//                                                    that is at most 60 (one pass, no running
+//                                                    maximum, no rescaling of the output), else a
+//                                                    running maximum
 //   p_j   = exp2(fma(u_j, A, -m)),  P_j = bf16(p_j)
 //   out   = bf16((sum_j P_j * v_j) / (sum_j p_j))   fp32 accumulation; all keys masked -> 0
 // q8/qs and k8/ks are QuantizeInt8Rows(Direct) of the [B,S,H,128] / [B,S,KV,128] tensors.
@@ -39,14 +45,15 @@ constexpr int kStages = 3;          // K/V ring depth
 constexpr uint32_t kQBytes = 128 * 128;        // int8 [128 x 128]
 constexpr uint32_t kKBytes = 128 * 128;        // int8 [128 keys x 128]
 constexpr uint32_t kVBytes = 128 * 128 * 2;    // bf16 [128 keys x 128] as two 64-wide halves
-constexpr uint32_t kKsBytes = 128 * 8;         // float2 (key scale, mask bias) per key
+constexpr uint32_t kKsBytes = 128 * 8;         // (key scale, mask bias) per key, as float4 per key pair
 constexpr uint32_t kStageBytes = kKBytes + kVBytes + kKsBytes;
 constexpr int kThreads = 384;
 constexpr size_t kSmemBytes = 1024 + 2 * kQBytes + kStages * kStageBytes + 256;
 
 struct AttnParams {
   const float *qs;       // [B,S,H]
-  const float2 *ksmb;    // [B,KV,S_pad] (key scale, mask bias)
+  const float2 *ksmb;    // [B,KV,S_pad/2] x float4 (ks'_j, ks'_j+1, bias_j, bias_j+1)
+  const float *tile_bound; // [B,KV,S_pad/128] max over the tile's valid keys of |k8_j| * ks'_j
   uint16_t *out;         // [B,S,H,128] bf16
   uint32_t B, Sq, Sk, H, KV, S_pad; // Sq query tokens, Sk key tokens (S_pad = Sk rounded up to 128)
   float scale_log2e;     // scale * log2(e)
@@ -62,28 +69,54 @@ __device__ __forceinline__ void report(DeviceStatus *status, uint32_t role, uint
 }
 
 // Builds the per-key table [B,KV,S_pad] of (ks', -C * ks') with C = 1.5 * 2^23: the key scales of
-// the [B,S,KV] row order re-laid contiguous along keys. The softmax threads turn an INT32 score
-// into fp32 with one integer add, f' = as_float(acc + bits(C)) = C + acc exactly, and then
-// u = fma(f', ks', -C * ks') = RN(acc * ks'): rounding ks to 22 significant bits makes C * ks'
-// exact, so the fused form has the single rounding of a plain multiply. Masked and padding keys
-// carry (0, -inf), which yields u = -inf.
-__global__ void key_table_kernel(const float *ks, const uint8_t *key_valid, float2 *ksmb, uint32_t B,
-                                 uint32_t S, uint32_t KV, uint32_t S_pad) {
-  const uint64_t total = (uint64_t)B * KV * S_pad;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (uint64_t)gridDim.x * blockDim.x) {
-    const uint32_t j = (uint32_t)(i % S_pad);
-    const uint32_t kvh = (uint32_t)((i / S_pad) % KV);
-    const uint32_t b = (uint32_t)(i / ((uint64_t)S_pad * KV));
-    float2 v = make_float2(0.0f, -INFINITY);
-    if (j < S && (key_valid == nullptr || key_valid[(uint64_t)b * S + j] != 0)) {
-      uint32_t bits = __float_as_uint(ks[((uint64_t)b * S + j) * KV + kvh]);
-      bits = (bits + 1u + ((bits >> 2) & 1u)) & ~3u; // nearest-even to 22 significant bits
-      const float k22 = __uint_as_float(bits);
-      v = make_float2(k22, -12582912.0f * k22);
+// the [B,S,KV] row order re-laid contiguous along keys, stored per key pair as
+// (ks'_j, ks'_j+1, bias_j, bias_j+1) so that one 16-byte load feeds one packed fma. The softmax
+// threads turn an INT32 score into fp32 with one integer add, f' = as_float(acc + bits(C)) =
+// C + acc exactly, and then u = fma(f', ks', -C * ks') = RN(acc * ks'): rounding ks to 22
+// significant bits makes C * ks' exact, so the fused form has the single rounding of a plain
+// multiply. Masked and padding keys carry (0, -inf), which yields u = -inf.
+// Also writes, per 128-key tile, the largest |k8_j|_2 * ks'_j of its valid keys: with |q8_i|_2 it
+// bounds every score of the tile (Cauchy-Schwarz on the integer codes).
+// One block of 128 threads per (batch, kv head, key tile), one thread per key.
+__global__ void __launch_bounds__(128)
+key_table_kernel(const int8_t *k8, const float *ks, const uint8_t *key_valid, float *table,
+                 float *tile_bound, uint32_t S, uint32_t KV, uint32_t S_pad) {
+  const uint32_t tiles = S_pad / kTile;
+  const uint32_t tile = blockIdx.x % tiles;
+  const uint32_t kvh = (blockIdx.x / tiles) % KV;
+  const uint32_t b = blockIdx.x / (tiles * KV);
+  const uint32_t j = tile * kTile + threadIdx.x;
+  float k22 = 0.0f, bias = -INFINITY, bound = 0.0f;
+  if (j < S && (key_valid == nullptr || key_valid[(uint64_t)b * S + j] != 0)) {
+    uint32_t bits = __float_as_uint(ks[((uint64_t)b * S + j) * KV + kvh]);
+    bits = (bits + 1u + ((bits >> 2) & 1u)) & ~3u; // nearest-even to 22 significant bits
+    k22 = __uint_as_float(bits);
+    bias = -12582912.0f * k22;
+    const uint4 *row = reinterpret_cast<const uint4 *>(k8 + (((uint64_t)b * S + j) * KV + kvh) * kTile);
+    int n2 = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 w = __ldg(row + c);
+      n2 = __dp4a((int)w.x, (int)w.x, n2);
+      n2 = __dp4a((int)w.y, (int)w.y, n2);
+      n2 = __dp4a((int)w.z, (int)w.z, n2);
+      n2 = __dp4a((int)w.w, (int)w.w, n2);
     }
-    ksmb[i] = v;
+    bound = __fmul_rn(__fsqrt_rn((float)n2), k22);
   }
+  float *t = table + (((uint64_t)b * KV + kvh) * S_pad + (j & ~1u)) * 2u + (j & 1u);
+  t[0] = k22;
+  t[2] = bias;
+  __shared__ float warp_max[4];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, o));
+  if ((threadIdx.x & 31) == 0)
+    warp_max[threadIdx.x >> 5] = bound;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    tile_bound[((uint64_t)b * KV + kvh) * tiles + tile] =
+        fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3]));
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -283,7 +316,45 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t s_tmem = tmem + lane_base + t * 128u, o_tmem = tmem + lane_base + 256u + t * 128u;
     float m_run = -INFINITY, l = 0.0f;
     bool alive = true;
-    for (uint32_t i = 0; i < n_kv; ++i) {
+    // A bound on every score of this row: |q8_i| * max_j(|k8_j| * ks'_j) * A. When it is small
+    // for the whole warp, its ceiling is the fixed maximum m of the row and a key tile needs one
+    // pass (no maximum, no rescaling); otherwise the warp keeps a running maximum.
+    bool fixed_max = false;
+    {
+      float kmax = 0.0f;
+      const float *bounds = p.tile_bound + ((uint64_t)batch * p.KV + kvh) * n_kv;
+      for (uint32_t i = lane; i < n_kv; i += 32)
+        kmax = fmaxf(kmax, __ldg(bounds + i));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        kmax = fmaxf(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+      if (!ptx::mbar_wait(q_full, 0)) {
+        if (lane == 0)
+          report(p.status, 9 + t, 0);
+        *abort_ptr = 1;
+        alive = false;
+      }
+      // the row's 128 codes: eight 16-byte chunks of one 128-byte row (the swizzle permutes
+      // chunks inside the row, and the sum does not care); lanes start at different chunks
+      const uint4 *qrow = reinterpret_cast<const uint4 *>(base_ptr + (q_addr - base) + t * kQBytes +
+                                                          row_in_tile * 128u);
+      int n2 = 0;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 w = qrow[(c + lane) & 7];
+        n2 = __dp4a((int)w.x, (int)w.x, n2);
+        n2 = __dp4a((int)w.y, (int)w.y, n2);
+        n2 = __dp4a((int)w.z, (int)w.z, n2);
+        n2 = __dp4a((int)w.w, (int)w.w, n2);
+      }
+      const float bound = __fmul_rn(__fmul_rn(A, __fsqrt_rn((float)n2)), kmax);
+      const float m_fixed = ceilf(__fadd_rn(bound, 0.001f));
+      fixed_max = __all_sync(0xffffffffu, m_fixed <= 60.0f);
+      if (fixed_max)
+        m_run = m_fixed;
+    }
+    const uint64_t A2 = pack2(A, A);
+    for (uint32_t i = 0; i < n_kv && alive; ++i) {
       const uint32_t s = i % kStages, phase = (i / kStages) & 1u;
       if (*abort_ptr || !ptx::mbar_wait(s_full + 8 * t, i & 1u) ||
           !ptx::mbar_wait(v_full + 8 * s, phase)) {
@@ -301,63 +372,85 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       ptx::tmem_ld_wait();
       const float4 *tab = reinterpret_cast<const float4 *>(base_ptr + (stage_addr - base) + s * kStageBytes +
                                                            kKBytes + kVBytes);
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float4 kk = tab[(c * 32 + j) >> 1]; // (ks'_j, -C ks'_j, ks'_j+1, -C ks'_j+1)
-          const float f0 = __int_as_float((int32_t)r[c][j] + 0x4B400000);     // C + acc, exact
-          const float f1 = __int_as_float((int32_t)r[c][j + 1] + 0x4B400000);
-          const float u0 = __fmaf_rn(f0, kk.x, kk.y), u1 = __fmaf_rn(f1, kk.z, kk.w);
-          r[c][j] = __float_as_uint(u0);
-          r[c][j + 1] = __float_as_uint(u1);
-          float &acc_max = mx4[(j >> 1) & 3];
-          asm("max.f32 %0, %0, %1, %2;" : "+f"(acc_max) : "f"(u0), "f"(u1));
-        }
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // power-of-two running maximum
-      float m_new = m_run;
-      if (mx != -INFINITY)
-        m_new = fmaxf(m_run, ceilf(mx * A));
-      const bool grow = m_new > m_run && m_run != -INFINITY;
-      if (__any_sync(0xffffffffu, grow)) {
-        // rescale O (and l) by an exact power of two; needs P.V of the previous tile finished
-        if (!ptx::mbar_wait(pv_done + 8 * t, (i - 1u) & 1u)) {
-          if (lane == 0)
-            report(p.status, 5 + t, i);
-          *abort_ptr = 1;
-          alive = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        const float factor = grow ? ex2(m_run - m_new) : 1.0f;
-        l *= factor;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          ptx::tmem_ld_32x32(o_tmem + 32u * c, o);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
-          ptx::tmem_st_32x32(o_tmem + 32u * c, o);
-        }
-        ptx::tmem_st_wait();
-      }
-      m_run = m_new;
-      const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
       uint32_t pk[64];
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull}; // 8 partial row sums as packed fp32 pairs
+      if (fixed_max) {
+        const uint64_t negm2 = pack2(-m_run, -m_run);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float p0 = ex2(__fmaf_rn(__uint_as_float(r[c][j]), A, neg_m));
-          const float p1 = ex2(__fmaf_rn(__uint_as_float(r[c][j + 1]), A, neg_m));
-          sum2[(j >> 1) & 3] = add2(sum2[(j >> 1) & 3], pack2(p0, p1));
-          pk[(c * 32 + j) >> 1] = pack_bf16(p0, p1);
+          for (int j = 0; j < 32; j += 2) {
+            const float4 kk = tab[(c * 32 + j) >> 1]; // (ks'_j, ks'_j+1, -C ks'_j, -C ks'_j+1)
+            const float f0 = __int_as_float((int32_t)r[c][j] + 0x4B400000);     // C + acc, exact
+            const float f1 = __int_as_float((int32_t)r[c][j + 1] + 0x4B400000);
+            const uint64_t u2 = fma2(pack2(f0, f1), pack2(kk.x, kk.y), pack2(kk.z, kk.w));
+            float e0, e1;
+            unpack2(fma2(u2, A2, negm2), e0, e1);
+            const float p0 = ex2(e0), p1 = ex2(e1);
+            sum2[(j >> 1) & 3] = add2(sum2[(j >> 1) & 3], pack2(p0, p1));
+            pk[(c * 32 + j) >> 1] = pack_bf16(p0, p1);
+          }
+        }
+      } else {
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float4 kk = tab[(c * 32 + j) >> 1];
+            const float f0 = __int_as_float((int32_t)r[c][j] + 0x4B400000);
+            const float f1 = __int_as_float((int32_t)r[c][j + 1] + 0x4B400000);
+            float u0, u1;
+            unpack2(fma2(pack2(f0, f1), pack2(kk.x, kk.y), pack2(kk.z, kk.w)), u0, u1);
+            r[c][j] = __float_as_uint(u0);
+            r[c][j + 1] = __float_as_uint(u1);
+            float &acc_max = mx4[(j >> 1) & 3];
+            asm("max.f32 %0, %0, %1, %2;" : "+f"(acc_max) : "f"(u0), "f"(u1));
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // power-of-two running maximum
+        float m_new = m_run;
+        if (mx != -INFINITY)
+          m_new = fmaxf(m_run, ceilf(mx * A));
+        const bool grow = m_new > m_run && m_run != -INFINITY;
+        if (__any_sync(0xffffffffu, grow)) {
+          // rescale O (and l) by an exact power of two; needs P.V of the previous tile finished
+          if (!ptx::mbar_wait(pv_done + 8 * t, (i - 1u) & 1u)) {
+            if (lane == 0)
+              report(p.status, 5 + t, i);
+            *abort_ptr = 1;
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const float factor = grow ? ex2(m_run - m_new) : 1.0f;
+          l *= factor;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            ptx::tmem_ld_32x32(o_tmem + 32u * c, o);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
+            ptx::tmem_st_32x32(o_tmem + 32u * c, o);
+          }
+          ptx::tmem_st_wait();
+        }
+        m_run = m_new;
+        const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
+        const uint64_t negm2 = pack2(neg_m, neg_m);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float e0, e1;
+            unpack2(fma2(pack2(__uint_as_float(r[c][j]), __uint_as_float(r[c][j + 1])), A2, negm2), e0, e1);
+            const float p0 = ex2(e0), p1 = ex2(e1);
+            sum2[(j >> 1) & 3] = add2(sum2[(j >> 1) & 3], pack2(p0, p1));
+            pk[(c * 32 + j) >> 1] = pack_bf16(p0, p1);
+          }
         }
       }
       {
@@ -417,9 +510,10 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
 } // namespace
 
+// Scratch: the key table (8 bytes per padded key and kv head) followed by one bound per key tile.
 size_t attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV) {
   const uint64_t s_pad = (S + kTile - 1) / kTile * kTile;
-  return (size_t)(B * KV * s_pad * sizeof(float2));
+  return (size_t)(B * KV * s_pad * sizeof(float2) + ((B * KV * (s_pad / kTile) * sizeof(float) + 15) & ~15ull));
 }
 
 int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks, const void *v_bf16,
@@ -484,19 +578,20 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
     return rc;
 
   float2 *table = static_cast<float2 *>(scratch);
+  float *tile_bound = reinterpret_cast<float *>(table + B * KV * s_pad);
   {
-    const uint64_t total = B * KV * s_pad;
-    uint64_t blocks = (total + 255) / 256;
-    if (blocks > 4096)
-      blocks = 4096;
-    key_table_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ks, key_valid, table, (uint32_t)B, (uint32_t)S,
-                                                           (uint32_t)KV, s_pad);
+    const uint64_t blocks = B * KV * (s_pad / kTile);
+    if (blocks > 0x7fffffffull)
+      return fail(kUnsupported, "Attention(INT8): problem too large");
+    key_table_kernel<<<(unsigned)blocks, 128, 0, stream>>>(k8, ks, key_valid, reinterpret_cast<float *>(table),
+                                                           tile_bound, (uint32_t)S, (uint32_t)KV, s_pad);
     if (int rc = check_cuda(cudaGetLastError(), "key_table_kernel launch"))
       return rc;
   }
   AttnParams p{};
   p.qs = qs;
   p.ksmb = table;
+  p.tile_bound = tile_bound;
   p.out = static_cast<uint16_t *>(out_bf16);
   p.B = (uint32_t)B;
   p.Sq = (uint32_t)Sq;
