@@ -189,117 +189,137 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const uint32_t tmem = *slot_ptr;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp == 0 && lane == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    // The producer and the MMA warp run their loops with all 32 lanes and warp-uniform control
+    // flow (every wait ends in a vote); one elected lane issues the asynchronous instructions.
+    // Addresses, descriptors and loop state are then warp-uniform values. As single-lane
+    // (divergent) loops every TMA / MMA operand was first moved between register files, and
+    // issuing the 12 MMAs of one tile step took about twice the 768 clocks they execute in.
+    auto give_up = [&](uint32_t role, uint32_t detail) {
+      if (lane == 0) {
+        if (!*abort_ptr)
+          report(p.status, role, detail);
+        *abort_ptr = 1;
+      }
+    };
+    if (warp == 0) {
       // ---------------- TMA producer ----------------
-      ptx::mbar_expect_tx(q_full, 2 * kQBytes);
-      ptx::tma_load_4d(q_addr, &map_q, q_full, 0, (int32_t)head, (int32_t)q0, (int32_t)batch);
-      ptx::tma_load_4d(q_addr + kQBytes, &map_q, q_full, 0, (int32_t)head, (int32_t)(q0 + 128u),
-                       (int32_t)batch);
+      if (ptx::elect_one()) {
+        ptx::mbar_expect_tx(q_full, 2 * kQBytes);
+        ptx::tma_load_4d(q_addr, &map_q, q_full, 0, (int32_t)head, (int32_t)q0, (int32_t)batch);
+        ptx::tma_load_4d(q_addr + kQBytes, &map_q, q_full, 0, (int32_t)head, (int32_t)(q0 + 128u),
+                         (int32_t)batch);
+      }
       const float2 *table = p.ksmb + ((uint64_t)batch * p.KV + kvh) * p.S_pad;
+      uint32_t s = 0, phase = 0;
       for (uint32_t i = 0; i < n_kv; ++i) {
-        const uint32_t s = i % kStages, phase = (i / kStages) & 1u;
         const uint32_t k_dst = stage_addr + s * kStageBytes, v_dst = k_dst + kKBytes,
                        t_dst = v_dst + kVBytes;
         const int32_t key0 = (int32_t)(i * kTile);
-        if (*abort_ptr || !ptx::mbar_wait(k_empty + 8 * s, phase ^ 1u)) {
-          if (!*abort_ptr)
-            report(p.status, 0, i);
-          *abort_ptr = 1;
+        if (!ptx::mbar_wait_warp(k_empty + 8 * s, phase ^ 1u, abort_ptr)) {
+          give_up(0, i);
           break;
         }
-        ptx::mbar_expect_tx(k_full + 8 * s, kKBytes);
-        ptx::tma_load_4d(k_dst, &map_k, k_full + 8 * s, 0, (int32_t)kvh, key0, (int32_t)batch);
-        if (*abort_ptr || !ptx::mbar_wait(v_empty + 8 * s, phase ^ 1u)) {
-          if (!*abort_ptr)
-            report(p.status, 1, i);
-          *abort_ptr = 1;
+        if (ptx::elect_one()) {
+          ptx::mbar_expect_tx(k_full + 8 * s, kKBytes);
+          ptx::tma_load_4d(k_dst, &map_k, k_full + 8 * s, 0, (int32_t)kvh, key0, (int32_t)batch);
+        }
+        if (!ptx::mbar_wait_warp(v_empty + 8 * s, phase ^ 1u, abort_ptr)) {
+          give_up(1, i);
           break;
         }
-        ptx::mbar_expect_tx(v_full + 8 * s, kVBytes + kKsBytes);
-        ptx::tma_load_4d(v_dst, &map_v, v_full + 8 * s, 0, (int32_t)kvh, key0, (int32_t)batch);
-        ptx::tma_load_4d(v_dst + kVBytes / 2, &map_v, v_full + 8 * s, 64, (int32_t)kvh, key0,
-                         (int32_t)batch);
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-                         "r"(t_dst), "l"(reinterpret_cast<uint64_t>(table + (uint64_t)i * kTile)),
-                     "r"(kKsBytes), "r"(v_full + 8 * s)
-                     : "memory");
+        if (ptx::elect_one()) {
+          ptx::mbar_expect_tx(v_full + 8 * s, kVBytes + kKsBytes);
+          ptx::tma_load_4d(v_dst, &map_v, v_full + 8 * s, 0, (int32_t)kvh, key0, (int32_t)batch);
+          ptx::tma_load_4d(v_dst + kVBytes / 2, &map_v, v_full + 8 * s, 64, (int32_t)kvh, key0,
+                           (int32_t)batch);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                           "r"(t_dst), "l"(reinterpret_cast<uint64_t>(table + (uint64_t)i * kTile)),
+                       "r"(kKsBytes), "r"(v_full + 8 * s)
+                       : "memory");
+        }
+        if (++s == kStages) {
+          s = 0;
+          phase ^= 1u;
+        }
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
       // ---------------- MMA issuer ----------------
       constexpr uint32_t idesc_qk = ptx::make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, 0, 0, 128, 128);
       constexpr uint32_t idesc_pv = ptx::make_idesc(1 /*F32*/, 1 /*BF16*/, 1 /*BF16*/, 0, 1 /*V is N-major*/, 128, 128);
+      const uint64_t q_desc = ptx::smem_desc_sw128(q_addr, 16, 1024);
+      const uint64_t k_desc0 = ptx::smem_desc_sw128(stage_addr, 16, 1024);
+      // V tile, N-major: 64-wide halves 16 KB apart (leading offset), 8-key groups 1 KB apart.
+      const uint64_t v_desc0 = ptx::smem_desc_sw128(stage_addr + kKBytes, kVBytes / 2, 1024);
       bool ok = true;
+      // (called inside the elected lane's branch)
       auto issue_qk = [&](uint32_t t, uint32_t s) {
-        const uint64_t a = ptx::smem_desc_sw128(q_addr + t * kQBytes, 16, 1024);
-        const uint64_t b = ptx::smem_desc_sw128(stage_addr + s * kStageBytes, 16, 1024);
+        const uint64_t a = q_desc + (uint64_t)((t * kQBytes) >> 4);
+        const uint64_t b = k_desc0 + (uint64_t)((s * kStageBytes) >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           ptx::mma_i8_ss(tmem + t * 128u, a + (uint64_t)(2 * k), b + (uint64_t)(2 * k), idesc_qk, k != 0);
         ptx::mma_commit(s_full + 8 * t);
       };
       auto issue_pv = [&](uint32_t t, uint32_t s, uint32_t accumulate) {
-        // A = P in tensor memory (64 columns of bf16 pairs at the start of S_t); B = V tile,
-        // N-major: 64-wide halves 16 KB apart (leading offset), 8-key groups 1 KB apart.
-        const uint64_t b = ptx::smem_desc_sw128(stage_addr + s * kStageBytes + kKBytes, kVBytes / 2, 1024);
+        // A = P in tensor memory (64 columns of bf16 pairs at the start of S_t); B = V tile
+        const uint64_t b = v_desc0 + (uint64_t)((s * kStageBytes) >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k) // 16 keys per MMA: 8 TMEM columns, 2048 bytes of V
           ptx::mma_f16_ts(tmem + 256u + t * 128u, tmem + t * 128u + 8u * k, b + (uint64_t)(128 * k),
-                          idesc_pv, (accumulate | (uint32_t)k) != 0u ? 1u : 0u);
+                          idesc_pv, k != 0 ? 1u : accumulate);
         ptx::mma_commit(pv_done + 8 * t);
       };
-      if (!ptx::mbar_wait(q_full, 0)) {
-        report(p.status, 2, 0);
-        *abort_ptr = 1;
+      if (!ptx::mbar_wait_warp(q_full, 0, abort_ptr)) {
+        give_up(2, 0);
         ok = false;
       }
-      if (ok && !ptx::mbar_wait(k_full, 0)) {
-        report(p.status, 2, 1);
-        *abort_ptr = 1;
+      if (ok && !ptx::mbar_wait_warp(k_full, 0, abort_ptr)) {
+        give_up(2, 1);
         ok = false;
       }
       if (ok) {
         ptx::tc_fence_after();
-        issue_qk(0, 0);
-        issue_qk(1, 0);
-        ptx::mma_commit(k_empty);
+        if (ptx::elect_one()) {
+          issue_qk(0, 0);
+          issue_qk(1, 0);
+          ptx::mma_commit(k_empty);
+        }
       }
+      uint32_t s = 0, phase = 0;
       for (uint32_t i = 0; i < n_kv && ok; ++i) {
-        const uint32_t s = i % kStages, phase = (i / kStages) & 1u;
-        const uint32_t sn = (i + 1) % kStages, phase_n = ((i + 1) / kStages) & 1u;
+        const uint32_t sn = s + 1 == kStages ? 0u : s + 1, phase_n = s + 1 == kStages ? phase ^ 1u : phase;
         const bool more = i + 1 < n_kv;
-        if (*abort_ptr || !ptx::mbar_wait(v_full + 8 * s, phase)) {
-          if (!*abort_ptr)
-            report(p.status, 2, 2);
-          *abort_ptr = 1;
+        if (!ptx::mbar_wait_warp(v_full + 8 * s, phase, abort_ptr)) {
+          give_up(2, 2);
           break;
         }
-        for (uint32_t t = 0; t < 2 && ok; ++t) {
-          if (*abort_ptr || !ptx::mbar_wait(p_full + 8 * t, i & 1u)) {
-            if (!*abort_ptr)
-              report(p.status, 2, 3 + t);
-            *abort_ptr = 1;
+#pragma unroll
+        for (uint32_t t = 0; t < 2; ++t) {
+          if (!ptx::mbar_wait_warp(p_full + 8 * t, i & 1u, abort_ptr)) {
+            give_up(2, 3 + t);
+            ok = false;
+            break;
+          }
+          if (more && t == 0 && !ptx::mbar_wait_warp(k_full + 8 * sn, phase_n, abort_ptr)) {
+            give_up(2, 5);
             ok = false;
             break;
           }
           ptx::tc_fence_after();
-          issue_pv(t, s, i != 0u ? 1u : 0u);
-          if (t == 1)
-            ptx::mma_commit(v_empty + 8 * s);
-          if (more) {
-            if (t == 0 && (*abort_ptr || !ptx::mbar_wait(k_full + 8 * sn, phase_n))) {
-              if (!*abort_ptr)
-                report(p.status, 2, 5);
-              *abort_ptr = 1;
-              ok = false;
-              break;
-            }
-            ptx::tc_fence_after();
-            issue_qk(t, sn);
+          if (ptx::elect_one()) {
+            issue_pv(t, s, i != 0u ? 1u : 0u);
             if (t == 1)
-              ptx::mma_commit(k_empty + 8 * sn);
+              ptx::mma_commit(v_empty + 8 * s);
+            if (more) {
+              issue_qk(t, sn);
+              if (t == 1)
+                ptx::mma_commit(k_empty + 8 * sn);
+            }
           }
         }
+        s = sn;
+        phase = phase_n;
       }
     }
   } else {
