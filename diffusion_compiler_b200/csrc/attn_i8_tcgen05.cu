@@ -27,11 +27,14 @@
 //
 // Structure: one CTA per (batch, head, 256 queries) = two 128-query tiles that share every K/V
 // tile. Warpgroup 0: warp 0 = TMA producer, warp 1 = MMA issuer (warps 2-3 idle). Warpgroups 1
-// and 2: softmax + epilogue of query tile 0 / 1, one thread per query row (the whole 128-key row
-// of scores lives in registers, so no shuffles). The tensor core alternates between the two
-// tiles: while one tile's softmax runs, the other tile's P.V and next Q.K^T execute.
-// Tensor memory (512 columns): S0 | S1 (INT32 scores, 128 columns each; bf16 P overwrites the
-// first 64 columns of its S and is the TMEM A operand of P.V), O0 | O1 (fp32, 128 columns each).
+// and 2: softmax + epilogue of query tile 0 / 1, one thread per query row (its scores live in
+// registers, so no shuffles). K/V arrive in 128-key stages; the score / softmax / P.V pipeline
+// works in 64-key steps with the scores of each query tile double-buffered in tensor memory:
+// Q.K^T of step g+2 is issued right after P.V of step g, into the buffer that step's P just left,
+// so when a softmax warp finishes a step the scores of the next one are already there.
+// Tensor memory (512 columns): per query tile two score buffers of 64 columns (INT32; the bf16 P
+// of a step overwrites the first 32 columns of its buffer and is the TMEM A operand of P.V),
+// then O0 | O1 (fp32, 128 columns each).
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -144,10 +147,11 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const uint32_t q_full = bar;
   const uint32_t k_full = bar + 8, k_empty = k_full + 8 * kStages;
   const uint32_t v_full = k_empty + 8 * kStages, v_empty = v_full + 8 * kStages;
-  const uint32_t s_full = v_empty + 8 * kStages;      // [2]
-  const uint32_t p_full = s_full + 16;                // [2]
-  const uint32_t pv_done = p_full + 16;               // [2]
-  const uint32_t tmem_slot = pv_done + 16;
+  const uint32_t s_full = v_empty + 8 * kStages;      // [2 tiles][2 buffers]
+  const uint32_t p_full = s_full + 32;                // [2][2]
+  const uint32_t pv_done = p_full + 32;               // [2] one phase per step (rescaling waits on it)
+  const uint32_t o_done = pv_done + 16;               // [2] completes once, after the last P.V
+  const uint32_t tmem_slot = o_done + 16;
   volatile uint32_t *slot_ptr = reinterpret_cast<volatile uint32_t *>(base_ptr + (tmem_slot - base));
   volatile uint32_t *abort_ptr = slot_ptr + 1;
 
@@ -159,6 +163,8 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const uint32_t kvh = head / (p.H / p.KV);
   const uint32_t q0 = qb * 256u;
   const uint32_t n_kv = (p.Sk + kTile - 1) / kTile;
+  const uint32_t n_steps = 2u * n_kv;               // 64-key steps
+  auto score_col = [](uint32_t t, uint32_t b) { return t * 128u + b * 64u; }; // TMEM column of a score buffer
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
@@ -169,9 +175,12 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       ptx::mbar_init(v_empty + 8 * s, 1);
     }
     for (int t = 0; t < 2; ++t) {
-      ptx::mbar_init(s_full + 8 * t, 1);
-      ptx::mbar_init(p_full + 8 * t, 128);
+      for (int b = 0; b < 2; ++b) {
+        ptx::mbar_init(s_full + 16 * t + 8 * b, 1);
+        ptx::mbar_init(p_full + 16 * t + 8 * b, 128);
+      }
       ptx::mbar_init(pv_done + 8 * t, 1);
+      ptx::mbar_init(o_done + 8 * t, 1);
     }
     *abort_ptr = 0;
     ptx::fence_barrier_init();
@@ -245,29 +254,33 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     } else if (warp == 1) {
       // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc_qk = ptx::make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, 0, 0, 128, 128);
+      constexpr uint32_t idesc_qk = ptx::make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, 0, 0, 128, 64);
       constexpr uint32_t idesc_pv = ptx::make_idesc(1 /*F32*/, 1 /*BF16*/, 1 /*BF16*/, 0, 1 /*V is N-major*/, 128, 128);
       const uint64_t q_desc = ptx::smem_desc_sw128(q_addr, 16, 1024);
       const uint64_t k_desc0 = ptx::smem_desc_sw128(stage_addr, 16, 1024);
       // V tile, N-major: 64-wide halves 16 KB apart (leading offset), 8-key groups 1 KB apart.
       const uint64_t v_desc0 = ptx::smem_desc_sw128(stage_addr + kKBytes, kVBytes / 2, 1024);
       bool ok = true;
-      // (called inside the elected lane's branch)
-      auto issue_qk = [&](uint32_t t, uint32_t s) {
+      // (both are called inside the elected lane's branch) step g covers keys 64 g .. 64 g + 63,
+      // i.e. half g & 1 of the 128-key stage (g / 2) % kStages, and score buffer g & 1.
+      auto issue_qk = [&](uint32_t t, uint32_t g) {
+        const uint32_t h = g & 1u, st = (g >> 1) % kStages;
         const uint64_t a = q_desc + (uint64_t)((t * kQBytes) >> 4);
-        const uint64_t b = k_desc0 + (uint64_t)((s * kStageBytes) >> 4);
+        const uint64_t b = k_desc0 + (uint64_t)((st * kStageBytes + h * 64u * 128u) >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          ptx::mma_i8_ss(tmem + t * 128u, a + (uint64_t)(2 * k), b + (uint64_t)(2 * k), idesc_qk, k != 0);
-        ptx::mma_commit(s_full + 8 * t);
+          ptx::mma_i8_ss(tmem + score_col(t, h), a + (uint64_t)(2 * k), b + (uint64_t)(2 * k), idesc_qk, k != 0);
+        ptx::mma_commit(s_full + 16 * t + 8 * h);
       };
-      auto issue_pv = [&](uint32_t t, uint32_t s, uint32_t accumulate) {
-        // A = P in tensor memory (64 columns of bf16 pairs at the start of S_t); B = V tile
-        const uint64_t b = v_desc0 + (uint64_t)((s * kStageBytes) >> 4);
+      auto issue_pv = [&](uint32_t t, uint32_t g) {
+        // A = P in tensor memory (32 columns of bf16 pairs at the start of the score buffer);
+        // B = the 64 keys of the V stage: 16 keys per MMA = 8 TMEM columns, 2048 bytes of V
+        const uint32_t h = g & 1u, st = (g >> 1) % kStages;
+        const uint64_t b = v_desc0 + (uint64_t)((st * kStageBytes + h * 64u * 128u) >> 4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) // 16 keys per MMA: 8 TMEM columns, 2048 bytes of V
-          ptx::mma_f16_ts(tmem + 256u + t * 128u, tmem + t * 128u + 8u * k, b + (uint64_t)(128 * k),
-                          idesc_pv, k != 0 ? 1u : accumulate);
+        for (int k = 0; k < 4; ++k)
+          ptx::mma_f16_ts(tmem + 256u + t * 128u, tmem + score_col(t, h) + 8u * k, b + (uint64_t)(128 * k),
+                          idesc_pv, k != 0 ? 1u : (g != 0u ? 1u : 0u));
         ptx::mma_commit(pv_done + 8 * t);
       };
       if (!ptx::mbar_wait_warp(q_full, 0, abort_ptr)) {
@@ -283,43 +296,47 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (ptx::elect_one()) {
           issue_qk(0, 0);
           issue_qk(1, 0);
+          issue_qk(0, 1);
+          issue_qk(1, 1);
           ptx::mma_commit(k_empty);
         }
       }
-      uint32_t s = 0, phase = 0;
-      for (uint32_t i = 0; i < n_kv && ok; ++i) {
-        const uint32_t sn = s + 1 == kStages ? 0u : s + 1, phase_n = s + 1 == kStages ? phase ^ 1u : phase;
-        const bool more = i + 1 < n_kv;
-        if (!ptx::mbar_wait_warp(v_full + 8 * s, phase, abort_ptr)) {
-          give_up(2, 2);
-          break;
+      for (uint32_t g = 0; g < n_steps && ok; ++g) {
+        const uint32_t h = g & 1u, use = g >> 1;               // use-th time this score buffer is filled
+        const uint32_t st = use % kStages, phase = (use / kStages) & 1u;
+        const uint32_t use_n = use + 1u, st_n = use_n % kStages, phase_n = (use_n / kStages) & 1u;
+        const bool more = g + 2u < n_steps;
+        if (h == 0u) {
+          if (!ptx::mbar_wait_warp(v_full + 8 * st, phase, abort_ptr)) {
+            give_up(2, 2);
+            break;
+          }
+          if (more && !ptx::mbar_wait_warp(k_full + 8 * st_n, phase_n, abort_ptr)) {
+            give_up(2, 5);
+            break;
+          }
         }
 #pragma unroll
         for (uint32_t t = 0; t < 2; ++t) {
-          if (!ptx::mbar_wait_warp(p_full + 8 * t, i & 1u, abort_ptr)) {
+          if (!ptx::mbar_wait_warp(p_full + 16 * t + 8 * h, use & 1u, abort_ptr)) {
             give_up(2, 3 + t);
-            ok = false;
-            break;
-          }
-          if (more && t == 0 && !ptx::mbar_wait_warp(k_full + 8 * sn, phase_n, abort_ptr)) {
-            give_up(2, 5);
             ok = false;
             break;
           }
           ptx::tc_fence_after();
           if (ptx::elect_one()) {
-            issue_pv(t, s, i != 0u ? 1u : 0u);
-            if (t == 1)
-              ptx::mma_commit(v_empty + 8 * s);
+            issue_pv(t, g);
+            if (g + 1u == n_steps)
+              ptx::mma_commit(o_done + 8 * t);
+            if (t == 1 && h == 1u)
+              ptx::mma_commit(v_empty + 8 * st);
             if (more) {
-              issue_qk(t, sn);
-              if (t == 1)
-                ptx::mma_commit(k_empty + 8 * sn);
+              issue_qk(t, g + 2u); // into the buffer P of step g is being read from: same pipe, in order
+              if (t == 1 && h == 1u)
+                ptx::mma_commit(k_empty + 8 * st_n);
             }
           }
         }
-        s = sn;
-        phase = phase_n;
       }
     }
   } else {
@@ -374,30 +391,34 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         m_run = m_fixed;
     }
     const uint64_t A2 = pack2(A, A);
-    for (uint32_t i = 0; i < n_kv && alive; ++i) {
-      const uint32_t s = i % kStages, phase = (i / kStages) & 1u;
-      if (*abort_ptr || !ptx::mbar_wait(s_full + 8 * t, i & 1u) ||
-          !ptx::mbar_wait(v_full + 8 * s, phase)) {
+    for (uint32_t g = 0; g < n_steps && alive; ++g) {
+      const uint32_t h = g & 1u, use = g >> 1;
+      const uint32_t s = use % kStages, phase = (use / kStages) & 1u;
+      // scores of this step; at the first half of a stage also the stage's key table (it arrives
+      // on the barrier of the V tile)
+      if (*abort_ptr || !ptx::mbar_wait(s_full + 16 * t + 8 * h, use & 1u) ||
+          (h == 0u && !ptx::mbar_wait(v_full + 8 * s, phase))) {
         if (!*abort_ptr && lane == 0)
-          report(p.status, 3 + t, i);
+          report(p.status, 3 + t, g);
         *abort_ptr = 1;
         alive = false;
         break;
       }
       ptx::tc_fence_after();
-      uint32_t r[4][32];
+      const uint32_t sc_tmem = s_tmem + h * 64u;
+      uint32_t r[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        ptx::tmem_ld_32x32(s_tmem + 32u * c, r[c]);
+      for (int c = 0; c < 2; ++c)
+        ptx::tmem_ld_32x32(sc_tmem + 32u * c, r[c]);
       ptx::tmem_ld_wait();
       const float4 *tab = reinterpret_cast<const float4 *>(base_ptr + (stage_addr - base) + s * kStageBytes +
-                                                           kKBytes + kVBytes);
-      uint32_t pk[64];
+                                                           kKBytes + kVBytes) + h * 32u;
+      uint32_t pk[32];
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull}; // 8 partial row sums as packed fp32 pairs
       if (fixed_max) {
         const uint64_t negm2 = pack2(-m_run, -m_run);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
             const float4 kk = tab[(c * 32 + j) >> 1]; // (ks'_j, ks'_j+1, -C ks'_j, -C ks'_j+1)
@@ -414,7 +435,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       } else {
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
             const float4 kk = tab[(c * 32 + j) >> 1];
@@ -435,10 +456,11 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           m_new = fmaxf(m_run, ceilf(mx * A));
         const bool grow = m_new > m_run && m_run != -INFINITY;
         if (__any_sync(0xffffffffu, grow)) {
-          // rescale O (and l) by an exact power of two; needs P.V of the previous tile finished
-          if (!ptx::mbar_wait(pv_done + 8 * t, (i - 1u) & 1u)) {
+          // rescale O (and l) by an exact power of two; needs P.V of the previous step finished
+          // (grow implies an earlier step with a valid key, so g > 0)
+          if (!ptx::mbar_wait(pv_done + 8 * t, (g - 1u) & 1u)) {
             if (lane == 0)
-              report(p.status, 5 + t, i);
+              report(p.status, 5 + t, g);
             *abort_ptr = 1;
             alive = false;
             break;
@@ -462,7 +484,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
         const uint64_t negm2 = pack2(neg_m, neg_m);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
             float e0, e1;
@@ -479,18 +501,13 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         unpack2(add2(sum2[2], sum2[3]), b0, b1);
         l += (a0 + a1) + (b0 + b1);
       }
-      {
-        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
-        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
-        ptx::tmem_st_32x32(s_tmem, lo);
-        ptx::tmem_st_32x32(s_tmem + 32u, hi);
-      }
+      ptx::tmem_st_32x32(sc_tmem, pk);
       ptx::tmem_st_wait();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(p_full + 8 * t);
+      ptx::mbar_arrive(p_full + 16 * t + 8 * h);
     }
     if (alive && n_kv > 0) {
-      if (!ptx::mbar_wait(pv_done + 8 * t, (n_kv - 1u) & 1u)) {
+      if (!ptx::mbar_wait(o_done + 8 * t, 0)) {
         if (lane == 0)
           report(p.status, 7 + t, 0);
         *abort_ptr = 1;
