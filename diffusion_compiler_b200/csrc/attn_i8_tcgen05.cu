@@ -287,7 +287,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         give_up(2, 0);
         ok = false;
       }
-      if (ok && !ptx::mbar_wait_warp(k_full, 0, abort_ptr)) {
+      if (ok && (!ptx::mbar_wait_warp(k_full, 0, abort_ptr) || !ptx::mbar_wait_warp(v_full, 0, abort_ptr))) {
         give_up(2, 1);
         ok = false;
       }
@@ -303,18 +303,17 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       for (uint32_t g = 0; g < n_steps && ok; ++g) {
         const uint32_t h = g & 1u, use = g >> 1;               // use-th time this score buffer is filled
-        const uint32_t st = use % kStages, phase = (use / kStages) & 1u;
+        const uint32_t st = use % kStages;
         const uint32_t use_n = use + 1u, st_n = use_n % kStages, phase_n = (use_n / kStages) & 1u;
         const bool more = g + 2u < n_steps;
-        if (h == 0u) {
-          if (!ptx::mbar_wait_warp(v_full + 8 * st, phase, abort_ptr)) {
-            give_up(2, 2);
-            break;
-          }
-          if (more && !ptx::mbar_wait_warp(k_full + 8 * st_n, phase_n, abort_ptr)) {
-            give_up(2, 5);
-            break;
-          }
+        // K, V and the key table of the next stage, before the first Q.K^T on it (the softmax
+        // warps take the completion of that Q.K^T as their signal for the table, and this
+        // stage's V was awaited the same way one stage earlier)
+        if (h == 0u && more &&
+            (!ptx::mbar_wait_warp(k_full + 8 * st_n, phase_n, abort_ptr) ||
+             !ptx::mbar_wait_warp(v_full + 8 * st_n, phase_n, abort_ptr))) {
+          give_up(2, 5);
+          break;
         }
 #pragma unroll
         for (uint32_t t = 0; t < 2; ++t) {
@@ -393,11 +392,11 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint64_t A2 = pack2(A, A);
     for (uint32_t g = 0; g < n_steps && alive; ++g) {
       const uint32_t h = g & 1u, use = g >> 1;
-      const uint32_t s = use % kStages, phase = (use / kStages) & 1u;
-      // scores of this step; at the first half of a stage also the stage's key table (it arrives
-      // on the barrier of the V tile)
-      if (*abort_ptr || !ptx::mbar_wait(s_full + 16 * t + 8 * h, use & 1u) ||
-          (h == 0u && !ptx::mbar_wait(v_full + 8 * s, phase))) {
+      const uint32_t s = use % kStages;
+      // The scores of this step. The stage's key table needs no wait of its own: it arrives on
+      // the barrier of the V tile, which the MMA warp has seen complete before it issued the
+      // Q.K^T whose completion is awaited here.
+      if (!ptx::mbar_wait_abortable(s_full + 16 * t + 8 * h, use & 1u, abort_ptr)) {
         if (!*abort_ptr && lane == 0)
           report(p.status, 3 + t, g);
         *abort_ptr = 1;

@@ -71,6 +71,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
       return false;
   }
 }
+// Per-thread wait whose common case is a single try_wait; `abort_flag` (shared memory, set by
+// any role of the CTA that gave up) ends it early.
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+  if (mbar_try_wait(bar, parity))
+    return true;
+  for (int i = 0; i < 512; ++i)
+    if (mbar_try_wait(bar, parity))
+      return true;
+  const unsigned long long start = global_timer();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity))
+        return true;
+    if (*abort_flag || global_timer() - start > kWaitNanoseconds)
+      return false;
+  }
+}
 // The same wait executed by all 32 lanes of a warp with a warp-uniform result (a vote), so that
 // the loop around it keeps uniform control flow and its state can live in uniform registers.
 // The common case is one try_wait and one vote. `abort_flag` (shared memory, set by any role of
