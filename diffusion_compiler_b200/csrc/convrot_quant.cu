@@ -54,11 +54,11 @@ __device__ __forceinline__ uint32_t sign_bit(uint32_t column) {
 __device__ __forceinline__ void bfly(uint64_t &x0, uint64_t &x1, uint64_t &x2, uint64_t &x3) {
   const uint64_t s = add2(x0, x1);
   const uint64_t t = sub2(x0, x1);
-  const uint64_t n = sub2(x1, x0);
   const uint64_t y0 = sub2(add2(s, x2), x3);
   const uint64_t y1 = add2(sub2(s, x2), x3);
   const uint64_t y2 = add2(add2(t, x2), x3);
-  const uint64_t y3 = add2(add2(n, x2), x3);
+  // the reference forms (x1 - x0) + x2: x1 - x0 = -t exactly, and (-t) + x2 = x2 - t
+  const uint64_t y3 = add2(sub2(x2, t), x3);
   x0 = y0;
   x1 = y1;
   x2 = y2;
