@@ -50,6 +50,8 @@ def lib() -> C.CDLL:
                 ("difb200_layer_norm_modulate", [vp, vp, vp, vp, vp, vp, u32, u64, u64, u64, f32, vp]),
                 ("difb200_qk_norm_rope", [vp, vp, vp, vp, vp, u32, u32, u64, u64, u64, u64, u64, u64, u64, u64, f32,
                                           i32, vp]),
+                ("difb200_qk_norm_rope_quant", [vp, vp, vp, vp, vp, vp, vp, u32, u64, u64, u64, u64, u64, u64, u64,
+                                                f32, i32, vp]),
                 ("difb200_residual_gate", [vp, vp, vp, vp, u32, u64, u64, u64, vp]),
                 ("difb200_swiglu", [vp, vp, u32, u64, u64, u64, u64, i32, vp])):
             getattr(L, name).restype = C.c_int

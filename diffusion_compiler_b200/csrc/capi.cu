@@ -146,6 +146,23 @@ int difb200_qk_norm_rope(const void *x, const void *weight, const void *cosine, 
                             static_cast<cudaStream_t>(stream));
 }
 
+int difb200_qk_norm_rope_quant(const void *x, const void *weight, const void *cosine, const void *sine, void *out,
+                               int8_t *codes, float *scales, uint32_t table_dtype, uint64_t tokens, uint64_t heads,
+                               uint64_t rotary, uint64_t table_width, uint64_t input_sequence,
+                               uint64_t table_sequence, uint64_t table_start, float epsilon, int32_t interleaved_v2,
+                               void *stream) {
+  if (!x || !weight || !cosine || !sine || (!out && !codes) || (codes && !scales) || rotary > 128 || (rotary & 1) ||
+      input_sequence == 0 || table_start + input_sequence > table_sequence)
+    return fail(kInvalidArgument, "difb200_qk_norm_rope_quant: bad argument");
+  int rc = 0;
+  if (!glue::qk_norm_rope_fast(x, weight, cosine, sine, out, codes, scales, 2, table_dtype, tokens, heads, 128, rotary,
+                               table_width, input_sequence, table_sequence, table_start, epsilon,
+                               interleaved_v2 != 0, static_cast<cudaStream_t>(stream), &rc))
+    return fail(kUnsupported, "difb200_qk_norm_rope_quant: needs bf16 rows of 128, rotary 64 / 96 / 128, bf16 or "
+                              "f32 tables whose rows are multiples of 16 bytes, 16-byte aligned pointers");
+  return rc;
+}
+
 int difb200_residual_gate(const void *residual, const void *branch, const void *gate, void *out, uint32_t dtype,
                           uint64_t rows, uint64_t width, uint64_t gate_rows, void *stream) {
   if (!residual || !branch || !gate || !out || dtype < 1 || dtype > 3 || gate_rows == 0 || rows % gate_rows != 0)

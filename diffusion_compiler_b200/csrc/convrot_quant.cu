@@ -19,6 +19,7 @@
 // thread the 16 elements of stride 16, on which stages 2-3 run. The 4096-wide variants add a
 // second, CTA-wide transpose across 16 groups for stages 4-5.
 #include "common.cuh"
+#include "glue.h"
 
 #include <cstdio>
 
@@ -662,6 +663,11 @@ int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, ui
     const uint64_t cap = (uint64_t)sm_count() * 16;
     if (blocks > cap)
       blocks = cap;
+    if (part_count == 1 && columns == 128 && !rcodes && !clip_device) { // per token-head rows: a thread per row
+      int rc = 0;
+      if (glue::direct_quant_rows128(parts[0], codes, scales, rows, clip, stream, &rc))
+        return rc;
+    }
     const bool vec = part_count == 1 && aligned8 && (reinterpret_cast<uintptr_t>(codes) & 7) == 0;
     if (vec)
       direct_quant_kernel<true><<<(unsigned)blocks, threads, 0, stream>>>(p);

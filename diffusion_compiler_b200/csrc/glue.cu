@@ -383,6 +383,9 @@ int layer_norm_modulate(const void *x, const void *w, const void *b, const void 
 int rms_norm_modulate(const void *x, const void *w, const void *a, const void *b, void *o, uint32_t dt, uint64_t rows,
                       uint64_t cols, float eps, float weight_offset, bool shared_vector, uint64_t rows_per_vector,
                       cudaStream_t s) {
+  int rc = 0;
+  if (!shared_vector && weight_offset == 0.0f && rms_norm_modulate_fast(x, w, a, b, o, dt, rows, cols, eps, s, &rc))
+    return rc;
   k_rms_norm_modulate<<<row_blocks(rows), 256, 0, s>>>(x, w, a, b, o, dt, rows, cols, eps, weight_offset,
                                                        shared_vector ? 1 : 0, rows_per_vector);
   return done("k_rms_norm_modulate");
@@ -391,6 +394,10 @@ int qk_norm_rope(const void *x, const void *w, const void *cosv, const void *sin
                  uint32_t dt_table, uint64_t tokens, uint64_t heads, uint64_t dim, uint64_t rotary,
                  uint64_t table_width, uint64_t input_seq, uint64_t table_seq, uint64_t table_start, float eps,
                  bool interleaved_v2, cudaStream_t s) {
+  int rc = 0;
+  if (qk_norm_rope_fast(x, w, cosv, sinv, o, nullptr, nullptr, dt, dt_table, tokens, heads, dim, rotary, table_width,
+                        input_seq, table_seq, table_start, eps, interleaved_v2, s, &rc))
+    return rc;
   RopeParams p{x, w, cosv, sinv, o, dt, dt_table, tokens, heads, dim, rotary, table_width, input_seq, table_seq,
                table_start, eps, interleaved_v2 ? 1 : 0};
   k_qk_norm_rope<<<row_blocks(tokens * heads), 256, 0, s>>>(p);
@@ -410,11 +417,17 @@ int rotary_apply(const void *x, const float *cosv, const float *sinv, void *o, u
 }
 int residual_gate(const void *res, const void *branch, const void *gate, void *o, uint32_t dt, uint64_t n,
                   uint64_t width, uint64_t rows_per_gate, cudaStream_t s) {
+  int rc = 0;
+  if (residual_gate_fast(res, branch, gate, o, dt, n, width, rows_per_gate, s, &rc))
+    return rc;
   k_residual_gate<<<blocks_for(n), 256, 0, s>>>(res, branch, gate, o, dt, n, width, rows_per_gate);
   return done("k_residual_gate");
 }
 int swiglu(const void *x, void *o, uint32_t dt, uint64_t rows, uint64_t width, uint64_t in_width, uint64_t start,
            bool gate_first, cudaStream_t s) {
+  int rc = 0;
+  if (swiglu_fast(x, o, dt, rows, width, in_width, start, gate_first, s, &rc))
+    return rc;
   k_swiglu<<<blocks_for(rows * width), 256, 0, s>>>(x, o, dt, rows, width, in_width, start, gate_first ? 1 : 0);
   return done("k_swiglu");
 }

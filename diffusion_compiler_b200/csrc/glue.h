@@ -46,5 +46,22 @@ int mask_to_bias(const uint8_t *mask, void *o, uint32_t dt, uint64_t B, uint64_t
 int linear(const void *x, const void *w, const void *bias, void *o, uint32_t dt, uint64_t M, uint64_t N, uint64_t K,
            cudaStream_t s);
 
+// bf16 fast paths (glue_fast.cu). Each returns false when dtype, widths or alignment are not
+// covered (nothing launched; the caller runs the generic kernel), else true with the launch
+// status in *rc.
+bool residual_gate_fast(const void *res, const void *branch, const void *gate, void *o, uint32_t dt, uint64_t n,
+                        uint64_t width, uint64_t rows_per_gate, cudaStream_t s, int *rc);
+bool swiglu_fast(const void *x, void *o, uint32_t dt, uint64_t rows, uint64_t width, uint64_t in_width,
+                 uint64_t start, bool gate_first, cudaStream_t s, int *rc);
+bool rms_norm_modulate_fast(const void *x, const void *w, const void *a, const void *b, void *o, uint32_t dt,
+                            uint64_t rows, uint64_t cols, float eps, cudaStream_t s, int *rc);
+// o (bf16 result) and codes/scales (QuantizeInt8Rows Direct of that result) are each optional.
+bool qk_norm_rope_fast(const void *x, const void *w, const void *cosv, const void *sinv, void *o, int8_t *codes,
+                       float *scales, uint32_t dt, uint32_t dt_table, uint64_t tokens, uint64_t heads, uint64_t dim,
+                       uint64_t rotary, uint64_t table_width, uint64_t input_seq, uint64_t table_seq,
+                       uint64_t table_start, float eps, bool interleaved_v2, cudaStream_t s, int *rc);
+bool direct_quant_rows128(const void *x, int8_t *codes, float *scales, uint64_t rows, float clip, cudaStream_t s,
+                          int *rc);
+
 } // namespace glue
 } // namespace difb200

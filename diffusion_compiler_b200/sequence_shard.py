@@ -146,21 +146,21 @@ class VideoBlock:
         if on_v_ready is not None:
             on_v_ready()
 
-        def norm_rope(name, w):
-            y = ops.linear_int8_scaled(codes, *self._w(name, scales))
-            r = new(S_loc, H, D)
-            self._glue("difb200_qk_norm_rope", p(y), p(w), p(self.cos), p(self.sin), p(r), 2, 2, S_loc, H, D,
-                       self.rotary, self.rotary, S_loc, self.cos.shape[0], lo, 1e-5, 0, stream)
-            return r
+        def norm_rope_quant(name, w, codes, scales):
+            """q/k projection, then QkNormPartialRope + per-token-head quantisation in one kernel:
+            codes and scales are written where the caller wants them."""
+            y = ops.linear_int8_scaled(codes_in, *self._w(name, scales_in))
+            self._glue("difb200_qk_norm_rope_quant", p(y), p(w), p(self.cos), p(self.sin), None, p(codes), p(scales),
+                       2, S_loc, H, self.rotary, self.rotary, S_loc, self.cos.shape[0], lo, 1e-5, 0, stream)
 
-        kr = norm_rope("k", self.k_norm)
+        codes_in, scales_in = codes, scales
         # K codes and scales are produced directly inside this rank's slice of the gather buffers
-        ops.quantize_int8_rows([kr.view(S_loc * H, D)], DIRECT,
-                               out=(gb.local(gb.k8)[:S_loc].view(S_loc * H, D), gb.local(gb.ks)[:S_loc].view(-1)))
+        norm_rope_quant("k", self.k_norm, gb.local(gb.k8)[:S_loc], gb.local(gb.ks)[:S_loc])
         if on_k_ready is not None:
             on_k_ready()
-        qr = norm_rope("q", self.q_norm)
-        q8, qs = ops.quantize_int8_rows([qr.view(S_loc * H, D)], DIRECT)
+        q8 = torch.empty((S_loc, H, D), dtype=torch.int8, device=self.device)
+        qs = torch.empty((S_loc * H,), dtype=torch.float32, device=self.device)
+        norm_rope_quant("q", self.q_norm, q8, qs)
         return q8.view(1, S_loc, H, D), qs
 
     def attend(self, q8: torch.Tensor, qs: torch.Tensor, plan: ShardPlan, gb: GatherBuffers) -> torch.Tensor:

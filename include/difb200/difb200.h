@@ -123,6 +123,10 @@ DIFB200_EXPORT int difb200_attention(const void *q, const void *k, const void *v
  *                                modulation_rows rows that broadcast over groups of input rows
  *   difb200_qk_norm_rope         QkNormPartialRope (cpu_executor.cpp:1741-1837); interleaved_v2 != 0
  *                                selects Implementation 2 with the interleaved layout, else half-split
+ *   difb200_qk_norm_rope_quant   the same op on bf16 heads of 128 followed by QuantizeInt8Rows(Direct) of
+ *                                its result (cpu_executor.cpp:124-307, Direct branch) in one kernel: the
+ *                                producer of INT8 attention's q8/qs and k8/ks. out (the bf16 result) and
+ *                                codes/scales are each optional. The reference runs these as two ops.
  *   difb200_residual_gate        ResidualGate (cpu_executor.cpp:1703-1719)
  *   difb200_swiglu               SwiGlu (cpu_executor.cpp:1267-1286)
  */
@@ -139,6 +143,13 @@ DIFB200_EXPORT int difb200_qk_norm_rope(const void *x, const void *weight, const
                                         uint64_t table_width, uint64_t input_sequence,
                                         uint64_t table_sequence, uint64_t table_start, float epsilon,
                                         int32_t interleaved_v2, void *stream);
+DIFB200_EXPORT int difb200_qk_norm_rope_quant(const void *x, const void *weight, const void *cosine,
+                                              const void *sine, void *out, int8_t *codes, float *scales,
+                                              uint32_t table_dtype, uint64_t tokens, uint64_t heads,
+                                              uint64_t rotary, uint64_t table_width,
+                                              uint64_t input_sequence, uint64_t table_sequence,
+                                              uint64_t table_start, float epsilon, int32_t interleaved_v2,
+                                              void *stream);
 DIFB200_EXPORT int difb200_residual_gate(const void *residual, const void *branch, const void *gate,
                                          void *out, uint32_t dtype, uint64_t rows, uint64_t width,
                                          uint64_t gate_rows, void *stream);
