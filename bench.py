@@ -313,6 +313,10 @@ def small_case(name: str):
     import torch
     from diffusion_compiler_b200 import ops
     torch.manual_seed(0)
+    if name == "mmdit_block":  # the config-3 block through the plugin, 7 passes (launch lists only)
+        res = mmdit_block_extra(torch, 0)
+        print("case mmdit_block done: %.2f ms" % res["device_ms"])
+        return
     if name == "video_block":  # three forwards of the 33272-token block on one GPU (launch lists only)
         res = video_block_extra(torch, torch.device("cuda:0"), 0, 1, None, iters=1)
         print("case video_block done: %.2f ms" % res["ms_per_block"])
@@ -395,7 +399,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the attention / block configs")
-    ap.add_argument("--case", choices=["gemm", "quant", "attention", "video_block"],
+    ap.add_argument("--case", choices=["gemm", "quant", "attention", "video_block", "mmdit_block"],
                     help="run 3 launches of one kernel on a small case and exit (the command profiled with ncu)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -33,6 +33,22 @@ size_t attention_scratch_bytes(uint64_t B, uint64_t S, uint64_t H, uint64_t KV) 
          align256(B * S * KV * 4) + align256(attention_int8_scratch_bytes(B, S, KV));
 }
 
+AttentionScratch attention_scratch_layout(void *scratch, uint64_t B, uint64_t S, uint64_t H, uint64_t KV) {
+  unsigned char *base = static_cast<unsigned char *>(scratch);
+  AttentionScratch l{};
+  l.q8 = reinterpret_cast<int8_t *>(base);
+  base += align256(B * S * H * 128);
+  l.k8 = reinterpret_cast<int8_t *>(base);
+  base += align256(B * S * KV * 128);
+  l.qs = reinterpret_cast<float *>(base);
+  base += align256(B * S * H * 4);
+  l.ks = reinterpret_cast<float *>(base);
+  base += align256(B * S * KV * 4);
+  l.rest = base;
+  return l;
+}
+
+// q / k null: their codes and scales are already in the scratch buffer (attention_scratch_layout).
 int attention_bf16_via_int8(const void *q, const void *k, const void *v, const uint8_t *key_valid, uint64_t B,
                             uint64_t S, uint64_t H, uint64_t KV, uint64_t D, float scale, void *scratch,
                             size_t scratch_bytes, void *out_bf16, cudaStream_t stream) {
@@ -40,22 +56,16 @@ int attention_bf16_via_int8(const void *q, const void *k, const void *v, const u
     return fail(kUnsupported, "Attention(INT8): head dimension must be 128");
   if (!scratch || scratch_bytes < attention_scratch_bytes(B, S, H, KV))
     return fail(kInvalidArgument, "Attention(INT8): scratch buffer too small");
-  unsigned char *base = static_cast<unsigned char *>(scratch);
-  int8_t *q8 = reinterpret_cast<int8_t *>(base);
-  base += align256(B * S * H * 128);
-  int8_t *k8 = reinterpret_cast<int8_t *>(base);
-  base += align256(B * S * KV * 128);
-  float *qs = reinterpret_cast<float *>(base);
-  base += align256(B * S * H * 4);
-  float *ks = reinterpret_cast<float *>(base);
-  base += align256(B * S * KV * 4);
+  const AttentionScratch l = attention_scratch_layout(scratch, B, S, H, KV);
   const void *qp[1] = {q}, *kp[1] = {k};
   const uint64_t w[1] = {128};
-  if (int rc = quantize_int8_rows(qp, w, 1, B * S * H, 1, 1.0f, nullptr, q8, qs, nullptr, nullptr, stream))
-    return rc;
-  if (int rc = quantize_int8_rows(kp, w, 1, B * S * KV, 1, 1.0f, nullptr, k8, ks, nullptr, nullptr, stream))
-    return rc;
-  return attention_int8(q8, qs, k8, ks, v, key_valid, B, S, S, H, KV, D, scale, base,
+  if (q)
+    if (int rc = quantize_int8_rows(qp, w, 1, B * S * H, 1, 1.0f, nullptr, l.q8, l.qs, nullptr, nullptr, stream))
+      return rc;
+  if (k)
+    if (int rc = quantize_int8_rows(kp, w, 1, B * S * KV, 1, 1.0f, nullptr, l.k8, l.ks, nullptr, nullptr, stream))
+      return rc;
+  return attention_int8(l.q8, l.qs, l.k8, l.ks, v, key_valid, B, S, S, H, KV, D, scale, l.rest,
                         attention_int8_scratch_bytes(B, S, KV), out_bf16, stream);
 }
 
@@ -111,6 +121,8 @@ uint64_t difb200_attention_scratch_bytes(uint64_t B, uint64_t S, uint64_t H, uin
 int difb200_attention(const void *q, const void *k, const void *v, const uint8_t *key_valid, uint64_t B,
                       uint64_t S, uint64_t H, uint64_t KV, uint64_t D, float scale, void *scratch,
                       uint64_t scratch_bytes, void *out, void *stream) {
+  if (!q || !k)
+    return fail(kInvalidArgument, "difb200_attention: null pointer");
   return attention_bf16_via_int8(q, k, v, key_valid, B, S, H, KV, D, scale, scratch, scratch_bytes, out,
                                  static_cast<cudaStream_t>(stream));
 }
@@ -157,7 +169,7 @@ int difb200_qk_norm_rope_quant(const void *x, const void *weight, const void *co
   int rc = 0;
   if (!glue::qk_norm_rope_fast(x, weight, cosine, sine, out, codes, scales, 2, table_dtype, tokens, heads, 128, rotary,
                                table_width, input_sequence, table_sequence, table_start, epsilon,
-                               interleaved_v2 != 0, static_cast<cudaStream_t>(stream), &rc))
+                               interleaved_v2 != 0, nullptr, static_cast<cudaStream_t>(stream), &rc))
     return fail(kUnsupported, "difb200_qk_norm_rope_quant: needs bf16 rows of 128, rotary 64 / 96 / 128, bf16 or "
                               "f32 tables whose rows are multiples of 16 bytes, 16-byte aligned pointers");
   return rc;

@@ -377,6 +377,9 @@ int rms_norm(const void *x, const void *w, void *o, uint32_t dt, uint64_t rows, 
 }
 int layer_norm_modulate(const void *x, const void *w, const void *b, const void *scale, const void *shift, void *o,
                         uint32_t dt, uint64_t rows, uint64_t cols, uint64_t rows_per_mod, float eps, cudaStream_t s) {
+  int rc = 0;
+  if (layer_norm_modulate_fast(x, w, b, scale, shift, o, dt, rows, cols, rows_per_mod, eps, s, &rc))
+    return rc;
   k_layer_norm_modulate<<<row_blocks(rows), 256, 0, s>>>(x, w, b, scale, shift, o, dt, rows, cols, rows_per_mod, eps);
   return done("k_layer_norm_modulate");
 }
@@ -396,7 +399,7 @@ int qk_norm_rope(const void *x, const void *w, const void *cosv, const void *sin
                  bool interleaved_v2, cudaStream_t s) {
   int rc = 0;
   if (qk_norm_rope_fast(x, w, cosv, sinv, o, nullptr, nullptr, dt, dt_table, tokens, heads, dim, rotary, table_width,
-                        input_seq, table_seq, table_start, eps, interleaved_v2, s, &rc))
+                        input_seq, table_seq, table_start, eps, interleaved_v2, nullptr, s, &rc))
     return rc;
   RopeParams p{x, w, cosv, sinv, o, dt, dt_table, tokens, heads, dim, rotary, table_width, input_seq, table_seq,
                table_start, eps, interleaved_v2 ? 1 : 0};

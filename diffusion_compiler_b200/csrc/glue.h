@@ -53,13 +53,25 @@ bool residual_gate_fast(const void *res, const void *branch, const void *gate, v
                         uint64_t width, uint64_t rows_per_gate, cudaStream_t s, int *rc);
 bool swiglu_fast(const void *x, void *o, uint32_t dt, uint64_t rows, uint64_t width, uint64_t in_width,
                  uint64_t start, bool gate_first, cudaStream_t s, int *rc);
+bool layer_norm_modulate_fast(const void *x, const void *w, const void *b, const void *scale, const void *shift,
+                              void *o, uint32_t dt, uint64_t rows, uint64_t cols, uint64_t rows_per_mod, float eps,
+                              cudaStream_t s, int *rc);
 bool rms_norm_modulate_fast(const void *x, const void *w, const void *a, const void *b, void *o, uint32_t dt,
                             uint64_t rows, uint64_t cols, float eps, cudaStream_t s, int *rc);
-// o (bf16 result) and codes/scales (QuantizeInt8Rows Direct of that result) are each optional.
+// Where QkNormPartialRope reads and writes when it is fused with its neighbours (elements /
+// tokens): a token's heads start at x + token * in_token_stride + in_offset (a last-axis Slice
+// read in place), and the result goes to token (token / input_seq) * out_seq + out_start +
+// token % input_seq of the destination (a Concat along tokens written in place).
+struct RopeLayout {
+  uint64_t in_token_stride, in_offset, out_seq, out_start;
+};
+// o (bf16 result) and codes/scales (QuantizeInt8Rows Direct of that result) are each optional;
+// layout may be null (dense input, output rows = input rows).
 bool qk_norm_rope_fast(const void *x, const void *w, const void *cosv, const void *sinv, void *o, int8_t *codes,
                        float *scales, uint32_t dt, uint32_t dt_table, uint64_t tokens, uint64_t heads, uint64_t dim,
                        uint64_t rotary, uint64_t table_width, uint64_t input_seq, uint64_t table_seq,
-                       uint64_t table_start, float eps, bool interleaved_v2, cudaStream_t s, int *rc);
+                       uint64_t table_start, float eps, bool interleaved_v2, const RopeLayout *layout, cudaStream_t s,
+                       int *rc);
 bool direct_quant_rows128(const void *x, int8_t *codes, float *scales, uint64_t rows, float clip, cudaStream_t s,
                           int *rc);
 

@@ -120,6 +120,67 @@ k_rms_norm_modulate_bf16(const uint4 *x, const uint4 *w, const uint4 *a, const u
   }
 }
 
+// ---- LayerNormModulate (cpu_executor.cpp:1108-1148): rounds to bf16 after the affine norm,
+// after 1 + scale and after their product; scale / shift rows broadcast over rows_per_mod rows ----
+template <int CHUNKS>
+__global__ void __launch_bounds__(256)
+k_layer_norm_modulate_bf16(const uint4 *x, const uint4 *w, const uint4 *b, const uint4 *scale, const uint4 *shift,
+                           uint4 *o, uint64_t rows, uint32_t cols, uint64_t rows_per_mod, float eps) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const uint64_t nwarps = (uint64_t)gridDim.x * (blockDim.x >> 5);
+  const uint32_t cols8 = cols >> 3, chunks = CHUNKS > 0 ? (uint32_t)CHUNKS : cols >> 8;
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    const uint4 *xr = x + r * cols8;
+    uint4 kept[CHUNKS > 0 ? CHUNKS : 1];
+    float mean = 0.0f;
+#pragma unroll
+    for (uint32_t k = 0; k < chunks; ++k) {
+      const uint4 v = __ldg(xr + lane + 32u * k);
+      if (CHUNKS > 0)
+        kept[CHUNKS > 0 ? k : 0] = v;
+      float f[8];
+      unpack8(v, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        mean += f[e];
+    }
+    mean = __fdiv_rn(warp_sum(mean), (float)cols);
+    float var = 0.0f;
+#pragma unroll
+    for (uint32_t k = 0; k < chunks; ++k) {
+      float f[8];
+      unpack8(CHUNKS > 0 ? kept[CHUNKS > 0 ? k : 0] : __ldg(xr + lane + 32u * k), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float d = __fsub_rn(f[e], mean);
+        var = __fmaf_rn(d, d, var);
+      }
+    }
+    var = warp_sum(var);
+    const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(var, (float)cols), eps)));
+    const uint64_t mrow = (r / rows_per_mod) * cols8;
+#pragma unroll
+    for (uint32_t k = 0; k < chunks; ++k) {
+      const uint32_t c = lane + 32u * k;
+      float f[8], wv[8], bv[8], sc[8], sh[8], y[8];
+      unpack8(CHUNKS > 0 ? kept[CHUNKS > 0 ? k : 0] : __ldg(xr + c), f);
+      unpack8(__ldg(w + c), wv);
+      unpack8(__ldg(b + c), bv);
+      unpack8(__ldg(scale + mrow + c), sc);
+      unpack8(__ldg(shift + mrow + c), sh);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float normalized =
+            round_bf16(__fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(f[e], mean), inv), wv[e]), bv[e]));
+        const float one_plus = round_bf16(__fadd_rn(1.0f, sc[e]));
+        y[e] = __fadd_rn(round_bf16(__fmul_rn(normalized, one_plus)), sh[e]);
+      }
+      o[r * cols8 + c] = pack8(y);
+    }
+  }
+}
+
 // ---- QkNormPartialRope on 128-wide heads (cpu_executor.cpp:1741-1837), optionally followed by
 // QuantizeInt8Rows(Direct) of the result (cpu_executor.cpp:124-307, Direct branch) ----
 // One thread per (token, head) row: the sum of squares runs in the reference's sequential order
@@ -133,6 +194,8 @@ struct RowRopeParams {
   int8_t *codes;        // Direct codes or nullptr
   float *scales;
   uint64_t rows, heads, input_seq, table_seq, table_start;
+  uint64_t in_token_stride16, in_offset16; // where a token's heads start in x, in 16-byte units
+  uint64_t out_seq, out_start;            // output token = (token / input_seq) * out_seq + out_start + token % input_seq
   uint32_t table_width, table_f32;
   float eps;
 };
@@ -158,12 +221,14 @@ k_qk_norm_rope_row128(const RowRopeParams p) {
   const uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= p.rows)
     return;
-  const uint64_t token = row / p.heads;
+  const uint64_t token = row / p.heads, head = row - token * p.heads;
+  const uint4 *src = p.x + token * p.in_token_stride16 + p.in_offset16 + head * 16;
+  const uint64_t out_row = ((token / p.input_seq) * p.out_seq + p.out_start + token % p.input_seq) * p.heads + head;
   float n[128];
 #pragma unroll
   for (int c = 0; c < 16; ++c) {
     float f[8];
-    unpack8(__ldg(p.x + row * 16 + c), f);
+    unpack8(__ldg(src + c), f);
 #pragma unroll
     for (int e = 0; e < 8; ++e)
       n[8 * c + e] = f[e];
@@ -229,13 +294,13 @@ k_qk_norm_rope_row128(const RowRopeParams p) {
 #pragma unroll
       for (int e = 0; e < 8; ++e)
         f[e] = n[8 * c + e];
-      p.o[row * 16 + c] = pack8(f);
+      p.o[out_row * 16 + c] = pack8(f);
     }
   }
   if (p.codes) {
     const float scale = fmaxf(__fdiv_rn(m, 127.0f), 1.0e-30f); // clip 1: max * 1 / 127
-    p.scales[row] = scale;
-    uint4 *dst = reinterpret_cast<uint4 *>(p.codes + row * 128);
+    p.scales[out_row] = scale;
+    uint4 *dst = reinterpret_cast<uint4 *>(p.codes + out_row * 128);
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       uint32_t word[4];
@@ -340,12 +405,38 @@ bool rms_norm_modulate_fast(const void *x, const void *w, const void *a, const v
   return true;
 }
 
+bool layer_norm_modulate_fast(const void *x, const void *w, const void *b, const void *scale, const void *shift,
+                              void *o, uint32_t dt, uint64_t rows, uint64_t cols, uint64_t rows_per_mod, float eps,
+                              cudaStream_t s, int *rc) {
+  if (dt != 2 || cols == 0 || cols % 256 != 0 || cols > 0xffffff00ull || !aligned16(x) || !aligned16(w) ||
+      !aligned16(b) || !aligned16(scale) || !aligned16(shift) || !aligned16(o))
+    return false;
+  uint64_t blocks = (rows + 7) / 8;
+  const uint64_t cap = (uint64_t)sm_count() * 16;
+  blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+  const auto X = static_cast<const uint4 *>(x), W = static_cast<const uint4 *>(w), B = static_cast<const uint4 *>(b),
+             SC = static_cast<const uint4 *>(scale), SH = static_cast<const uint4 *>(shift);
+  if (cols == 3072)
+    k_layer_norm_modulate_bf16<12><<<(unsigned)blocks, 256, 0, s>>>(X, W, B, SC, SH, static_cast<uint4 *>(o), rows,
+                                                                    (uint32_t)cols, rows_per_mod, eps);
+  else
+    k_layer_norm_modulate_bf16<0><<<(unsigned)blocks, 256, 0, s>>>(X, W, B, SC, SH, static_cast<uint4 *>(o), rows,
+                                                                   (uint32_t)cols, rows_per_mod, eps);
+  *rc = done("k_layer_norm_modulate_bf16");
+  return true;
+}
+
 // QkNormPartialRope (+ optional Direct quantisation) for bf16 rows of 128; false when the shape is
 // not covered (the caller then runs the generic kernel).
 bool qk_norm_rope_fast(const void *x, const void *w, const void *cosv, const void *sinv, void *o, int8_t *codes,
                        float *scales, uint32_t dt, uint32_t dt_table, uint64_t tokens, uint64_t heads, uint64_t dim,
                        uint64_t rotary, uint64_t table_width, uint64_t input_seq, uint64_t table_seq,
-                       uint64_t table_start, float eps, bool interleaved_v2, cudaStream_t s, int *rc) {
+                       uint64_t table_start, float eps, bool interleaved_v2, const RopeLayout *layout, cudaStream_t s,
+                       int *rc) {
+  const RopeLayout dense{heads * 128, 0, input_seq, 0};
+  const RopeLayout &l = layout ? *layout : dense;
+  if (l.in_token_stride % 8 != 0 || l.in_offset % 8 != 0)
+    return false;
   if (dt != 2 || dim != 128 || (dt_table != 1 && dt_table != 2) || !aligned16(x) || !aligned16(w) ||
       !aligned16(cosv) || !aligned16(sinv) || (o && !aligned16(o)) || (codes && !aligned16(codes)))
     return false;
@@ -358,8 +449,8 @@ bool qk_norm_rope_fast(const void *x, const void *w, const void *cosv, const voi
   if (interleaved_v2 ? table_width != rotary / 2 : (table_width != rotary && table_width != rotary / 2))
     return false;
   RowRopeParams p{static_cast<const uint4 *>(x), static_cast<const uint4 *>(w), cosv, sinv, static_cast<uint4 *>(o),
-                  codes, scales, tokens * heads, heads, input_seq, table_seq, table_start, (uint32_t)table_width,
-                  dt_table == 1 ? 1u : 0u, eps};
+                  codes, scales, tokens * heads, heads, input_seq, table_seq, table_start, l.in_token_stride / 8,
+                  l.in_offset / 8, l.out_seq, l.out_start, (uint32_t)table_width, dt_table == 1 ? 1u : 0u, eps};
   const unsigned blocks = (unsigned)((p.rows + 127) / 128);
   if (p.rows + 127 > 0x7fffffffull * 128ull)
     return false;

@@ -39,6 +39,14 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
 // DiffIR Attention on bf16 q/k/v in its INT8 lowering: Direct quantisation of q and k per
 // token-head, then attention_int8. Scratch holds the codes, scales and the key table.
 size_t attention_scratch_bytes(uint64_t B, uint64_t S, uint64_t H, uint64_t KV);
+// Where the INT8 lowering keeps its operands inside that scratch buffer: a producer that
+// quantises q or k itself writes here and passes a null q / k to attention_bf16_via_int8.
+struct AttentionScratch {
+  int8_t *q8, *k8;
+  float *qs, *ks;
+  void *rest;
+};
+AttentionScratch attention_scratch_layout(void *scratch, uint64_t B, uint64_t S, uint64_t H, uint64_t KV);
 int attention_bf16_via_int8(const void *q, const void *k, const void *v, const uint8_t *key_valid, uint64_t B,
                             uint64_t S, uint64_t H, uint64_t KV, uint64_t D, float scale, void *scratch,
                             size_t scratch_bytes, void *out_bf16, cudaStream_t stream);

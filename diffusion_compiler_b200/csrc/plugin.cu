@@ -45,13 +45,23 @@ struct Step {
   int bias_tensor = -1;             // index of the fused bias tensor
   int out_tensor = -1;              // index of the tensor the (fused) step writes
   int mask_tensor = -1;             // Attention: index of the fused Bool key mask
-  bool skip = false;                // op absorbed by a neighbour
+  bool skip = false;                // op absorbed by a neighbour, or a Reshape served by aliasing
+  bool alias = false;               // Reshape: the output shares the input's buffer
+  // QkNormPartialRope fused with its neighbours
+  int rope_source = -1;             // tensor read in place (an absorbed last-axis Slice), else in[0]
+  uint64_t rope_in_stride = 0, rope_in_offset = 0;
+  int rope_attention = -1;          // step of the Attention whose INT8 q / k this op writes directly
+  int rope_role = 0;                // 0 = q, 1 = k
+  uint64_t rope_out_seq = 0, rope_out_start = 0;
+  // Attention whose q / k arrive already quantised in the scratch buffer
+  bool q_quantised = false, k_quantised = false;
 };
 
 struct Executable {
   Context *ctx = nullptr;
   ir::Program program;
   std::vector<void *> dev;          // device buffer per tensor (nullptr when never materialised)
+  std::vector<uint8_t> owned;       // 0 where dev[i] aliases another tensor's buffer (Reshape)
   std::vector<Step> steps;
   void *attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
@@ -68,9 +78,9 @@ struct Executable {
     for (cudaEvent_t e : produced)
       if (e)
         cudaEventDestroy(e);
-    for (void *p : dev)
-      if (p)
-        cudaFree(p);
+    for (size_t i = 0; i < dev.size(); ++i)
+      if (dev[i] && (i >= owned.size() || owned[i]))
+        cudaFree(dev[i]);
     if (attn_scratch)
       cudaFree(attn_scratch);
     if (flag)
@@ -168,12 +178,131 @@ void plan(Executable &exe) {
         st.mask_tensor = p.index_of(p.ops[it->second].in[0]);
         exe.steps[it->second].skip = true;
       }
+    } else if (op.opcode == ir::Reshape) {
+      // same bytes in the same order (cpu_executor.cpp:496-502 copies them): share the buffer
+      st.alias = true;
+      st.skip = true;
     } else if (op.opcode == ir::Linear) {
       const ir::Tensor &x = *p.tensor(op.in[0]), &w = *p.tensor(op.in[1]);
       if (2.0 * (double)x.dims[0] * (double)w.dims[0] * (double)w.dims[1] > 2.0e11)
         throw PluginError{2, "Linear (op " + std::to_string(op.id) +
                                  "): plain float Linear of this size is outside the quantized path; bind it "
                                  "as QuantizeInt8Rows + LinearInt8Scaled"};
+    }
+  }
+
+  // ---- QkNormPartialRope and its neighbours (all on 128-wide bf16 heads) ----
+  // DIFB200_ROPE_FUSION=0 keeps the ops separate (same bits, more traffic): a test aid.
+  if (const char *v = std::getenv("DIFB200_ROPE_FUSION"))
+    if (v[0] == '0')
+      return;
+  auto private_to = [&](uint32_t id, size_t consumer) { // one reader, not an output of the program
+    const ir::Tensor *t = p.tensor(id);
+    return t && !t->has(ir::Output) && consumers[id] == 1 && consumer_op[id] == consumer;
+  };
+  auto rope_kernel_covers = [&](const ir::Op &op) {
+    const ir::Tensor &x = *p.tensor(op.in[0]), &c = *p.tensor(op.in[2]);
+    const uint64_t rotary = op.u64(ir::RotaryDim, x.last());
+    const bool v2 = op.u64(ir::Implementation, 1) == 2 && op.u64(ir::RotaryLayout, 2) == 1;
+    const uint64_t entry = c.dtype == ir::F32 ? 4 : 2;
+    return x.dtype == ir::BF16 && x.last() == 128 && (c.dtype == ir::F32 || c.dtype == ir::BF16) &&
+           (rotary == 64 || rotary == 96 || rotary == 128) && (c.last() * entry) % 16 == 0 &&
+           (v2 ? c.last() == rotary / 2 : (c.last() == rotary || c.last() == rotary / 2));
+  };
+  for (size_t r = 0; r < p.ops.size(); ++r) {
+    const ir::Op &rope = p.ops[r];
+    if (rope.opcode != ir::QkNormPartialRope || !rope_kernel_covers(rope))
+      continue;
+    // (1) Slice on the last axis [-> Reshape] -> this op: read the slice in place
+    auto it = producer.find(rope.in[0]);
+    if (it == producer.end())
+      continue;
+    size_t reshape = p.ops.size(), slice = it->second;
+    if (p.ops[slice].opcode == ir::Reshape && private_to(rope.in[0], r)) {
+      reshape = slice;
+      const auto up = producer.find(p.ops[reshape].in[0]);
+      if (up == producer.end())
+        continue;
+      slice = up->second;
+    }
+    const ir::Op &sl = p.ops[slice];
+    if (sl.opcode != ir::Slice)
+      continue;
+    const ir::Tensor &z = *p.tensor(sl.in[0]), &y = *p.tensor(sl.out[0]), &x = *p.tensor(rope.in[0]);
+    const uint64_t heads = x.dims[x.dims.size() - 2];
+    if (sl.u64(ir::Axis, 0) + 1 != z.dims.size() || y.last() != heads * 128 || z.last() % 8 != 0 ||
+        sl.u64(ir::Start, 0) % 8 != 0 || !private_to(sl.out[0], reshape < p.ops.size() ? reshape : r) ||
+        exe.steps[slice].skip)
+      continue;
+    Step &st = exe.steps[r];
+    st.rope_source = p.index_of(sl.in[0]);
+    st.rope_in_stride = z.last();
+    st.rope_in_offset = sl.u64(ir::Start, 0);
+    exe.steps[slice].skip = true;
+    if (reshape < p.ops.size()) {
+      exe.steps[reshape].alias = false; // nothing left to alias: neither tensor is materialised
+      exe.steps[reshape].skip = true;
+    }
+  }
+  // (2) this op [-> Concat along tokens] -> Attention q / k: write the INT8 codes the attention
+  // kernel reads, straight into its scratch buffer
+  size_t previous_attention = 0;
+  bool seen_attention = false;
+  for (size_t a = 0; a < p.ops.size(); ++a) {
+    const ir::Op &att = p.ops[a];
+    if (att.opcode != ir::Attention)
+      continue;
+    const size_t fence = seen_attention ? previous_attention : 0; // the scratch buffer is shared
+    const bool has_fence = seen_attention;
+    previous_attention = a;
+    seen_attention = true;
+    const ir::Tensor &q = *p.tensor(att.in[0]);
+    const size_t token_axis = q.dims.size() - 3;
+    for (int role = 0; role < 2; ++role) {
+      const uint32_t id = att.in[(size_t)role];
+      const auto it = producer.find(id);
+      if (it == producer.end() || !private_to(id, a))
+        continue;
+      std::vector<std::pair<size_t, uint64_t>> parts; // rope step, first output token
+      size_t concat = p.ops.size();
+      const ir::Op &src = p.ops[it->second];
+      if (src.opcode == ir::QkNormPartialRope) {
+        parts.push_back({it->second, 0});
+      } else if (src.opcode == ir::Concat && src.u64(ir::Axis, 0) == token_axis) {
+        concat = it->second;
+        uint64_t start = 0;
+        bool ok = true;
+        for (auto part : src.in) {
+          const auto pr = producer.find(part);
+          if (pr == producer.end() || p.ops[pr->second].opcode != ir::QkNormPartialRope ||
+              !private_to(part, concat)) {
+            ok = false;
+            break;
+          }
+          parts.push_back({pr->second, start});
+          start += p.tensor(part)->dims[token_axis];
+        }
+        if (!ok)
+          continue;
+      } else {
+        continue;
+      }
+      bool ok = !parts.empty();
+      for (const auto &part : parts)
+        ok = ok && rope_kernel_covers(p.ops[part.first]) && exe.steps[part.first].rope_attention < 0 &&
+             (!has_fence || part.first > fence) && part.first < a;
+      if (!ok)
+        continue;
+      for (const auto &part : parts) {
+        Step &st = exe.steps[part.first];
+        st.rope_attention = (int)a;
+        st.rope_role = role;
+        st.rope_out_seq = q.dims[token_axis];
+        st.rope_out_start = part.second;
+      }
+      if (concat < p.ops.size())
+        exe.steps[concat].skip = true;
+      (role == 0 ? exe.steps[a].q_quantised : exe.steps[a].k_quantised) = true;
     }
   }
 }
@@ -187,18 +316,29 @@ void allocate(Executable &exe) {
     if (p.tensors[i].has(ir::Input) || p.tensors[i].has(ir::Constant) || p.tensors[i].has(ir::Output))
       needed[i] = true;
   for (const Step &st : exe.steps) {
+    if (st.alias)
+      needed[(size_t)p.index_of(st.op->in[0])] = true;
     if (st.skip)
       continue;
-    for (auto id : st.op->in) {
-      // the fused attention bias is the only input that is not read
-      if (st.op->opcode == ir::Attention && st.mask_tensor >= 0 && id == st.op->in[3])
+    for (size_t k = 0; k < st.op->in.size(); ++k) {
+      const uint32_t id = st.op->in[k];
+      // inputs that a fused step does not read: the materialised attention bias, q / k that
+      // arrive as INT8 codes in the scratch buffer, the slice a rope op reads in place
+      if (st.op->opcode == ir::Attention && ((st.mask_tensor >= 0 && k == 3) || (st.q_quantised && k == 0) ||
+                                             (st.k_quantised && k == 1)))
         continue;
+      if (st.op->opcode == ir::QkNormPartialRope && st.rope_source >= 0 && k == 0) {
+        needed[(size_t)st.rope_source] = true;
+        continue;
+      }
       needed[(size_t)p.index_of(id)] = true;
     }
     if (st.op->opcode == ir::LinearInt8Scaled) {
       needed[(size_t)st.out_tensor] = true;
       if (st.bias_tensor >= 0)
         needed[(size_t)st.bias_tensor] = true;
+    } else if (st.op->opcode == ir::QkNormPartialRope && st.rope_attention >= 0) {
+      // writes INT8 codes into the attention scratch buffer, no bf16 tensor
     } else {
       for (auto id : st.op->out)
         needed[(size_t)p.index_of(id)] = true;
@@ -206,13 +346,24 @@ void allocate(Executable &exe) {
     if (st.mask_tensor >= 0)
       needed[(size_t)st.mask_tensor] = true;
   }
+  std::vector<bool> aliased(p.tensors.size(), false);
+  for (const Step &st : exe.steps)
+    if (st.alias)
+      aliased[(size_t)p.index_of(st.op->out[0])] = true;
+  exe.owned.assign(p.tensors.size(), 1);
   for (size_t i = 0; i < p.tensors.size(); ++i) {
-    if (!needed[i])
+    if (!needed[i] || aliased[i])
       continue;
     const size_t bytes = (size_t)p.tensors[i].bytes();
     require_cuda(cudaMalloc(&exe.dev[i], bytes ? bytes : 16), "cudaMalloc(tensor)");
     exe.resident_bytes += bytes;
   }
+  for (const Step &st : exe.steps) // program order: a chain of reshapes resolves front to back
+    if (st.alias) {
+      const size_t out = (size_t)p.index_of(st.op->out[0]);
+      exe.dev[out] = exe.dev[(size_t)p.index_of(st.op->in[0])];
+      exe.owned[out] = 0;
+    }
   size_t scratch = 0;
   for (const Step &st : exe.steps) {
     if (st.skip || st.op->opcode != ir::Attention)
@@ -309,7 +460,8 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
       const uint64_t B = batched ? q.dims[0] : 1, S = q.dims[batched ? 1 : 0], H = q.dims[batched ? 2 : 1];
       const uint64_t KV = op.u64(ir::KvHeads, H);
       const float scale = (float)op.f64(ir::AttentionScale, 1.0 / std::sqrt((double)q.last()));
-      require(attention_bf16_via_int8(D(op.in[0]), D(op.in[1]), D(op.in[2]),
+      require(attention_bf16_via_int8(st.q_quantised ? nullptr : D(op.in[0]), st.k_quantised ? nullptr : D(op.in[1]),
+                                      D(op.in[2]),
                                       st.mask_tensor >= 0 ? static_cast<const uint8_t *>(exe.dev[(size_t)st.mask_tensor])
                                                           : nullptr,
                                       B, S, H, KV, q.last(), scale, exe.attn_scratch, exe.attn_scratch_bytes,
@@ -374,9 +526,43 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
       const uint64_t input_seq = x.dims.size() == 4 ? x.dims[1] : x.dims[0];
       const uint64_t table_seq = c.dims.size() == 3 ? c.dims[1] : c.dims[0];
       const bool v2 = op.u64(ir::Implementation, 1) == 2 && op.u64(ir::RotaryLayout, 2) == 1;
-      require(glue::qk_norm_rope(D(op.in[0]), D(op.in[1]), D(op.in[2]), D(op.in[3]), D(op.out[0]), x.dtype, c.dtype,
-                                 tokens, heads, dim, op.u64(ir::RotaryDim, dim), c.last(), input_seq, table_seq,
-                                 op.u64(ir::Start, 0), (float)op.f64(ir::Epsilon, 1.0e-5), v2, s));
+      const uint64_t rotary = op.u64(ir::RotaryDim, dim), start = op.u64(ir::Start, 0);
+      const float eps = (float)op.f64(ir::Epsilon, 1.0e-5);
+      if (st.rope_source < 0 && st.rope_attention < 0) {
+        require(glue::qk_norm_rope(D(op.in[0]), D(op.in[1]), D(op.in[2]), D(op.in[3]), D(op.out[0]), x.dtype, c.dtype,
+                                   tokens, heads, dim, rotary, c.last(), input_seq, table_seq, start, eps, v2, s));
+        break;
+      }
+      // fused with a Slice before it and / or the Attention after it (see plan())
+      glue::RopeLayout layout{heads * dim, 0, input_seq, 0};
+      const void *source = D(op.in[0]);
+      if (st.rope_source >= 0) {
+        source = exe.dev[(size_t)st.rope_source];
+        layout.in_token_stride = st.rope_in_stride;
+        layout.in_offset = st.rope_in_offset;
+      }
+      void *out = nullptr;
+      int8_t *codes = nullptr;
+      float *scales = nullptr;
+      if (st.rope_attention >= 0) {
+        const ir::Op &att = *exe.steps[(size_t)st.rope_attention].op;
+        const ir::Tensor &q = T(att.in[0]);
+        const bool batched = q.dims.size() == 4;
+        const uint64_t B = batched ? q.dims[0] : 1, S = q.dims[batched ? 1 : 0], H = q.dims[batched ? 2 : 1];
+        const AttentionScratch l = attention_scratch_layout(exe.attn_scratch, B, S, H, att.u64(ir::KvHeads, H));
+        codes = st.rope_role == 0 ? l.q8 : l.k8;
+        scales = st.rope_role == 0 ? l.qs : l.ks;
+        layout.out_seq = st.rope_out_seq;
+        layout.out_start = st.rope_out_start;
+      } else {
+        out = D(op.out[0]);
+      }
+      int rc = 0;
+      if (!glue::qk_norm_rope_fast(source, D(op.in[1]), D(op.in[2]), D(op.in[3]), out, codes, scales, x.dtype, c.dtype,
+                                   tokens, heads, dim, rotary, c.last(), input_seq, table_seq, start, eps, v2, &layout,
+                                   s, &rc))
+        throw PluginError{6, "QkNormPartialRope (op " + std::to_string(op.id) + "): fused form not applicable"};
+      require(rc);
       break;
     }
     case ir::RotaryFrequency: {
@@ -411,8 +597,24 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
       require_cuda(cudaMemcpyAsync(D(op.out[0]), D(op.in[0]), (size_t)T(op.out[0]).bytes(), cudaMemcpyDeviceToDevice, s),
                    "cudaMemcpyAsync(reshape)");
       break;
-    case ir::BroadcastTo:
     case ir::Slice: {
+      // one axis of a contiguous tensor: `outer` runs of `run` bytes, `pitch` bytes apart in the source
+      const ir::Tensor &x = T(op.in[0]), &o = T(op.out[0]);
+      const uint64_t axis = op.u64(ir::Axis, 0), elem = ir::dtype_size(o.dtype);
+      uint64_t outer = 1, inner = elem;
+      for (size_t a = 0; a < axis; ++a)
+        outer *= o.dims[a];
+      for (size_t a = axis + 1; a < o.dims.size(); ++a)
+        inner *= o.dims[a];
+      const uint64_t run = o.dims[axis] * inner, pitch = x.dims[axis] * inner;
+      const char *src = static_cast<const char *>(D(op.in[0])) + op.u64(ir::Start, 0) * inner;
+      if (run && outer)
+        require_cuda(cudaMemcpy2DAsync(D(op.out[0]), (size_t)run, src, (size_t)pitch, (size_t)run, (size_t)outer,
+                                       cudaMemcpyDeviceToDevice, s),
+                     "cudaMemcpy2DAsync(slice)");
+      break;
+    }
+    case ir::BroadcastTo: {
       const ir::Tensor &x = T(op.in[0]), &o = T(op.out[0]);
       uint64_t in_strides[8] = {0}, full[8] = {0};
       const size_t rank = o.dims.size(), pad = rank - x.dims.size();
@@ -421,32 +623,28 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
         full[a] = stride;
         stride *= x.dims[a];
       }
-      uint64_t offset = 0;
-      for (size_t a = 0; a < rank; ++a) {
-        if (a < pad)
-          in_strides[a] = 0;
-        else
-          in_strides[a] = (op.opcode == ir::BroadcastTo && x.dims[a - pad] == 1) ? 0 : full[a - pad];
-      }
-      if (op.opcode == ir::Slice)
-        offset = op.u64(ir::Start, 0) * full[op.u64(ir::Axis, 0)];
+      for (size_t a = 0; a < rank; ++a)
+        in_strides[a] = (a < pad || x.dims[a - pad] == 1) ? 0 : full[a - pad];
       require(glue::gather(D(op.in[0]), D(op.out[0]), (uint32_t)ir::dtype_size(o.dtype), (uint32_t)rank,
-                           o.dims.data(), in_strides, offset, s));
+                           o.dims.data(), in_strides, 0, s));
       break;
     }
     case ir::Concat: {
       const ir::Tensor &o = T(op.out[0]);
-      const uint64_t axis = op.u64(ir::Axis, 0);
-      uint64_t outer = 1, inner = 1;
+      const uint64_t axis = op.u64(ir::Axis, 0), elem = ir::dtype_size(o.dtype);
+      uint64_t outer = 1, inner = elem;
       for (size_t a = 0; a < axis; ++a)
         outer *= o.dims[a];
       for (size_t a = axis + 1; a < o.dims.size(); ++a)
         inner *= o.dims[a];
+      const uint64_t pitch = o.dims[axis] * inner;
       uint64_t offset = 0;
       for (auto id : op.in) {
         const uint64_t chunk = T(id).dims[axis] * inner;
-        require(glue::concat_part(D(id), D(op.out[0]), (uint32_t)ir::dtype_size(o.dtype), outer, chunk,
-                                  o.dims[axis] * inner, offset, s));
+        if (chunk && outer)
+          require_cuda(cudaMemcpy2DAsync(static_cast<char *>(D(op.out[0])) + offset, (size_t)pitch, D(id),
+                                         (size_t)chunk, (size_t)chunk, (size_t)outer, cudaMemcpyDeviceToDevice, s),
+                       "cudaMemcpy2DAsync(concat)");
         offset += chunk;
       }
       break;

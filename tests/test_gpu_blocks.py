@@ -32,6 +32,25 @@ def test_video_block_through_plugin_matches_reference_executor():
     ex.close()
 
 
+def test_plugin_rope_fusions_keep_the_bits(monkeypatch):
+    """The planner reads last-axis slices in place from QkNormPartialRope and lets that op write
+    the attention kernel's INT8 q / k directly (through a Concat along tokens too). Same arithmetic,
+    so the block output must not change by a bit against the unfused plan."""
+    from diffusion_compiler_b200 import plugin
+    rng = np.random.default_rng(6)
+    p, ids, consts, inputs = blocks.synth_mmdit_block(rng, batch=2, grid=(8, 8), text_tokens=24, hidden=512, heads=4,
+                                                     mlp=1024, quantize=_cpu_quantize)
+    results = []
+    for fusion in ("1", "0"):
+        monkeypatch.setenv("DIFB200_ROPE_FUSION", fusion)
+        ex = plugin.PluginExecutor(0)
+        got, _ = ex.prepare(p, consts).run(inputs)
+        ex.close()
+        results.append(got)
+    for key in ("image_out", "text_out"):
+        assert np.array_equal(results[0][ids[key]], results[1][ids[key]])
+
+
 @pytest.mark.skipif(not ob.ref_available(), reason="reference build (oracle/_ref) not present")
 def test_mmdit_double_stream_block_through_plugin_matches_reference_executor():
     from diffusion_compiler_b200 import plugin
