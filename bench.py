@@ -448,6 +448,9 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        # stdout carries exactly one JSON line: NCCL's own messages (its version banner under
+        # NCCL_DEBUG=VERSION/INFO goes to stdout by default) are sent to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
     layers = synth_inputs(torch, device, seed=rank)
 
