@@ -391,7 +391,17 @@ def cpu_reference_sample(threads: int, rows_per_thread: int):
                       % (rows_per_thread, threads, dt)}, dt
 
 
+def emit_json_line(fd: int, line: dict) -> None:
+    os.write(fd, (json.dumps(line) + "\n").encode())
+
+
 def main():
+    # stdout must carry exactly one JSON line, but libraries print there too (NCCL's version
+    # banner under NCCL_DEBUG=VERSION/WARN, for one): keep the real stdout aside for that line and
+    # let everything else that writes to file descriptor 1 land on stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -436,7 +446,8 @@ def main():
                 "e2e": {"value": best["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "note": "reference CPU executor on host cores; ms_per_step is the full-workload time "
                         "extrapolated from the row sample"}
-        print(json.dumps(line))
+        sys.stdout.flush()
+        emit_json_line(json_fd, line)
         return
 
     import torch
@@ -448,9 +459,6 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        # stdout carries exactly one JSON line: NCCL's own messages (its version banner under
-        # NCCL_DEBUG=VERSION/INFO goes to stdout by default) are sent to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
     layers = synth_inputs(torch, device, seed=rank)
 
@@ -551,7 +559,8 @@ def main():
         ops.poll_status()
     if rank == 0:
         line.update(extras)
-        print(json.dumps(line))
+        sys.stdout.flush()
+        emit_json_line(json_fd, line)
     if dist is not None:
         dist.destroy_process_group()
 
