@@ -229,14 +229,25 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
   const uint32_t copy_addr = (H4096 ? smem_addr + (uint32_t)wrow * 1152u : warp_addr) + 16u * lane;
   const uint32_t copy_col = (uint32_t)wrow * 1024u + 16u * lane;
 
-  // Sign masks of this thread's 32 columns (bit i: element i of group A, bit 16+i: group B).
-  uint32_t signs = 0;
+  // Sign flips of this thread's 32 columns as XOR masks on the packed bf16 pairs (bits 15 and
+  // 31 of word i: elements 2i and 2i+1), kept in shared memory: words 0-7 group A, 8-15 group B,
+  // stored as four 16-byte vectors per thread, vector q of all threads contiguous.
+  const uint32_t mask_addr = smem_addr + (uint32_t)total_warps * (kWarpBytes + 16u) + 64u + threadIdx.x * 16u;
+  const uint32_t mask_step = blockDim.x * 16u;
   if (SIGNED) {
+    uint32_t mw[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      signs |= sign_bit(group_a * 256u + 16u * a + i) << i;
-      signs |= sign_bit((group_a + 1u) * 256u + 16u * a + i) << (16 + i);
+    for (int i = 0; i < 8; ++i) {
+      mw[i] = (sign_bit(group_a * 256u + 16u * a + 2 * i) << 15) |
+              (sign_bit(group_a * 256u + 16u * a + 2 * i + 1) << 31);
+      mw[8 + i] = (sign_bit((group_a + 1u) * 256u + 16u * a + 2 * i) << 15) |
+                  (sign_bit((group_a + 1u) * 256u + 16u * a + 2 * i + 1) << 31);
     }
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(mask_addr + q * mask_step), "r"(mw[4 * q]),
+                   "r"(mw[4 * q + 1]), "r"(mw[4 * q + 2]), "r"(mw[4 * q + 3])
+                   : "memory");
   }
 
   // Software pipeline: the 64 bytes of the next row are requested before the current row is
@@ -268,18 +279,23 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
     {
       const uint4 a0 = na0, a1 = na1, b0 = nb0, b1 = nb1;
       fetch(row + (uint64_t)gridDim.x * rows_per_cta, na0, na1, nb0, nb1);
-      const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-      const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      if (SIGNED) {
+        const uint4 m0 = lds128(mask_addr), m1 = lds128(mask_addr + mask_step);
+        const uint4 m2 = lds128(mask_addr + 2u * mask_step), m3 = lds128(mask_addr + 3u * mask_step);
+        const uint32_t ma[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        const uint32_t mb[8] = {m2.x, m2.y, m2.z, m2.w, m3.x, m3.y, m3.z, m3.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          wa[i] ^= ma[i];
+          wb[i] ^= mb[i];
+        }
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        uint32_t alo = wa[i] << 16, ahi = wa[i] & 0xffff0000u;
-        uint32_t blo = wb[i] << 16, bhi = wb[i] & 0xffff0000u;
-        if (SIGNED) {
-          alo ^= ((signs >> (2 * i)) & 1u) << 31;
-          ahi ^= ((signs >> (2 * i + 1)) & 1u) << 31;
-          blo ^= ((signs >> (16 + 2 * i)) & 1u) << 31;
-          bhi ^= ((signs >> (17 + 2 * i)) & 1u) << 31;
-        }
+        const uint32_t alo = wa[i] << 16, ahi = wa[i] & 0xffff0000u;
+        const uint32_t blo = wb[i] << 16, bhi = wb[i] & 0xffff0000u;
         P[2 * i] = pack2(__uint_as_float(alo), __uint_as_float(blo));
         P[2 * i + 1] = pack2(__uint_as_float(ahi), __uint_as_float(bhi));
       }
@@ -588,7 +604,9 @@ int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
   if ((uint64_t)rows_per_cta > p.rows)
     rows_per_cta = (int)p.rows;
   const int warps = warps_per_row * rows_per_cta;
-  const size_t smem = (size_t)warps * kWarpBytes + (size_t)warps * 4 * sizeof(float) + 64;
+  // per warp: transpose / staging area; row maxima; for the signed variants 16 XOR masks per thread
+  const size_t smem = (size_t)warps * kWarpBytes + (size_t)warps * 4 * sizeof(float) + 64 +
+                      (SIGNED ? (size_t)warps * 32 * 64 : 0);
   const int threads_needed = warps * 32;
   auto kernel = threads_needed <= 256   ? convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, 256>
                 : threads_needed <= 384 ? convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, 384>
