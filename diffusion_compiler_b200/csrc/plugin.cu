@@ -891,7 +891,8 @@ dif_backend_status execute(dif_backend_executable executable, const dif_backend_
     // the kernels then run concurrently; with pageable buffers the copies block the calling
     // thread as they always do and the result is the same. The telemetry time of such a pass is
     // the span of the kernel stream, upload waits included.
-    const bool overlapped = options->warmups == 0 && options->iterations == 1;
+    const char *overlap_env = std::getenv("DIFB200_EXECUTE_OVERLAP"); // "0": one stream, the three phases in turn
+    const bool overlapped = options->warmups == 0 && options->iterations == 1 && !(overlap_env && overlap_env[0] == '0');
     if (overlapped) {
       const size_t n = exe->program.tensors.size();
       if (exe->uploaded.empty()) {
