@@ -117,6 +117,8 @@ class VideoBlock:
                     for name, (w, s) in tensors["linears"].items()}
         self._scratch = None
         self._comm_stream = None
+        self._graphs = {}
+        self._valid = {}
 
     def _glue(self, name, *args):
         from . import _lib
@@ -166,8 +168,11 @@ class VideoBlock:
     def attend(self, q8: torch.Tensor, qs: torch.Tensor, plan: ShardPlan, gb: GatherBuffers) -> torch.Tensor:
         """Local queries against the gathered keys/values of the whole sequence."""
         H, D, P = self.heads, self.dim, plan.padded_tokens
+        key = (plan.tokens, plan.world)
+        if key not in self._valid:  # built once (a host-to-device copy has no place in a graph capture)
+            self._valid[key] = plan.key_valid(self.device)
         return self.ops.attention_int8(q8, qs, gb.k8.view(1, P, H, D), gb.ks, gb.v.view(1, P, H, D),
-                                       plan.key_valid(self.device), scale=1.0 / float(np.sqrt(D)))
+                                       self._valid[key], scale=1.0 / float(np.sqrt(D)))
 
     def post_attention(self, x: torch.Tensor, attn: torch.Tensor, mods: List[torch.Tensor]) -> torch.Tensor:
         """Row-local part after attention: out-proj, gated residual, norm+modulate, SwiGLU MLP."""
@@ -193,8 +198,13 @@ class VideoBlock:
         return out
 
     def forward(self, x: torch.Tensor, mods: List[torch.Tensor], plan: ShardPlan, rank: int, group=None,
-                gb: Optional[GatherBuffers] = None, events: Optional[dict] = None) -> torch.Tensor:
-        """x and the six modulation tensors are this rank's [S_local, hidden] slices."""
+                gb: Optional[GatherBuffers] = None, events: Optional[dict] = None,
+                graphs: bool = False) -> torch.Tensor:
+        """x and the six modulation tensors are this rank's [S_local, hidden] slices. With
+        ``graphs`` the kernels of the block are replayed from four CUDA graphs (V part, K part,
+        Q part, attention + rest; the collectives stay outside), captured on the first call for
+        these very tensors: a rank's share of a block is short enough at 8 GPUs for the launch
+        overhead of ~20 kernels to show."""
         def mark(name):
             if events is not None:
                 ev = torch.cuda.Event(enable_timing=True)
@@ -203,22 +213,14 @@ class VideoBlock:
 
         if gb is None:
             gb = GatherBuffers(plan, rank, self.heads, self.dim, self.device)
+        if graphs:
+            return self._forward_graphed(x, mods, plan, rank, group, gb, mark)
         mark("start")
         works = []
         if plan.world > 1:
             # The V all-gather runs under the K and Q work, the K all-gather under the Q work:
             # each is enqueued on a side stream as soon as its producer has been enqueued.
-            if self._comm_stream is None:
-                self._comm_stream = torch.cuda.Stream(device=self.device)
-            main = torch.cuda.current_stream()
-
-            def launch(names):
-                ready = torch.cuda.Event()
-                ready.record(main)
-                with torch.cuda.stream(self._comm_stream):
-                    self._comm_stream.wait_event(ready)
-                    works.extend(gb.all_gather(group, names=names, async_op=True))
-
+            launch = self._gather_launcher(gb, group, works)
             q8, qs = self.pre_attention(x, mods, plan, rank, gb, on_v_ready=lambda: launch(("v",)),
                                         on_k_ready=lambda: launch(("k8", "ks")))
         else:
@@ -232,6 +234,74 @@ class VideoBlock:
         out = self.post_attention(x, attn, mods)
         mark("end")
         return out
+
+    def _gather_launcher(self, gb: GatherBuffers, group, works: list):
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=self.device)
+        main = torch.cuda.current_stream()
+
+        def launch(names):
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ready)
+                works.extend(gb.all_gather(group, names=names, async_op=True))
+        return launch
+
+    def _forward_graphed(self, x, mods, plan, rank, group, gb, mark):
+        key = (x.data_ptr(), tuple(m.data_ptr() for m in mods), gb.k8.data_ptr(), plan.tokens, plan.world, rank)
+        state = self._graphs.get(key)
+        if state is None:
+            state = self._capture(x, mods, plan, rank, gb)
+            self._graphs[key] = state
+        mark("start")
+        works = []
+        launch = self._gather_launcher(gb, group, works) if plan.world > 1 else None
+        state["v"].replay()
+        if launch:
+            launch(("v",))
+        state["k"].replay()
+        if launch:
+            launch(("k8", "ks"))
+        state["q"].replay()
+        mark("pre_attention")
+        for w in works:
+            w.wait()
+        mark("gathered")
+        state["rest"].replay()
+        mark("end")
+        return state["out"]
+
+    def _capture(self, x, mods, plan, rank, gb):
+        """Records the four kernel sequences of this block for these very tensors (every rank
+        does this in its first graphed call, so the warm-up pass with its collectives lines up).
+        pre_attention reports the end of its V and K parts through callbacks: a capture ends and
+        the next begins inside them. The returned output tensor is overwritten by every replay."""
+        self.forward(x, mods, plan, rank, gb=gb)  # lazy allocations and one-time set-up, outside a capture
+        torch.cuda.synchronize()
+        pool = torch.cuda.graph_pool_handle()
+        graph = {name: torch.cuda.CUDAGraph() for name in ("v", "k", "q", "rest")}
+        current = {"name": "v"}
+
+        def switch(to):
+            graph[current["name"]].capture_end()
+            current["name"] = to
+            graph[to].capture_begin(pool=pool)
+
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            graph["v"].capture_begin(pool=pool)
+            q8, qs = self.pre_attention(x, mods, plan, rank, gb, on_v_ready=lambda: switch("k"),
+                                        on_k_ready=lambda: switch("q"))
+            switch("rest")
+            attn = self.attend(q8, qs, plan, gb)
+            out = self.post_attention(x, attn, mods)
+            graph["rest"].capture_end()
+        torch.cuda.current_stream().wait_stream(stream)
+        state = dict(graph)
+        state["out"] = out
+        return state
 
     def _w(self, name, scales):
         w8, cs = self.lin[name]

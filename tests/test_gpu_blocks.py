@@ -32,6 +32,33 @@ def test_video_block_through_plugin_matches_reference_executor():
     ex.close()
 
 
+def test_video_block_replayed_from_cuda_graphs_keeps_the_bits():
+    """The block's kernels replayed from four CUDA graphs (captured on the first call for fixed
+    tensors) give the bits of the kernel-by-kernel run, also after the inputs change in place."""
+    import torch
+    from diffusion_compiler_b200 import ops
+    from diffusion_compiler_b200.sequence_shard import GatherBuffers, ShardPlan, VideoBlock
+    rng = np.random.default_rng(8)
+    S, hidden, heads, dim, ffn, rotary = 437, 512, 4, 128, 1024, 96
+    p, ids, consts, inputs = blocks.synth_video_block(rng, S, hidden, heads, dim, ffn, rotary, _cpu_quantize)
+    tensors = {"norm1": consts[ids["norm1"]], "norm2": consts[ids["norm2"]], "q_norm": consts[ids["q_norm"]],
+               "k_norm": consts[ids["k_norm"]], "cos": consts[ids["cos"]], "sin": consts[ids["sin"]],
+               "linears": {n: (consts[w], consts[cs]) for n, (w, cs, b, N, K) in ids["linears"].items()}}
+    block = VideoBlock(tensors, hidden, heads, dim, ffn, rotary, "cuda")
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda().view(torch.bfloat16)
+    x = dev(inputs[ids["x"]])
+    mods = [dev(inputs[m]) for m in ids["mods"]]
+    plan = ShardPlan.make(S, 1)
+    gb = GatherBuffers(plan, 0, heads, dim, "cuda")
+    for trial in range(2):
+        want = block.forward(x, mods, plan, 0, gb=gb).clone()
+        got = block.forward(x, mods, plan, 0, gb=gb, graphs=True).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(want.view(torch.int16), got.view(torch.int16))
+        x.mul_(0.5)  # same storage, new values: the second trial replays the graphs of the first
+    ops.poll_status()
+
+
 def test_plugin_rope_fusions_keep_the_bits(monkeypatch):
     """The planner reads last-axis slices in place from QkNormPartialRope and lets that op write
     the attention kernel's INT8 q / k directly (through a Concat along tokens too). Same arithmetic,
