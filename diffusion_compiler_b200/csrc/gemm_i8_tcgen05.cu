@@ -8,7 +8,9 @@
 // 128-byte-swizzled [rows x 128 B] boxes into a shared-memory ring. One thread issues
 // tcgen05.mma kind::i8 into one of two 256-column INT32 accumulators in tensor memory, so the
 // epilogue of tile i overlaps the MMAs of tile i+1. Warp roles: 0 = TMA producer, 1 = TMEM owner
-// + MMA issuer, 2..5 = epilogue (each reads the TMEM lane quarter warp_id % 4).
+// + MMA issuer, 2..9 = epilogue: two warps per TMEM lane quarter (warp_id % 4), one for each
+// 128-column half of the tile (four epilogue warps could not keep up with the K = 3072 main
+// loop once bias and GELU are fused in).
 //
 // Two forms of the same kernel (template parameter CTAS):
 //   CTAS = 1: 128x256 tile per CTA, cta_group::1, 4 stages of 48 KB.
@@ -75,10 +77,15 @@ namespace {
 constexpr int kBM = 128, kBN = 256, kBK = 128; // per-CTA rows, tile columns, BK in bytes == INT8 elements
 constexpr int kUmmaK = 32;
 constexpr uint32_t kABytes = kBM * kBK;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kEpilogueWarps = 8;
 template <int CTAS>
 struct Cfg {
-  static constexpr int kStages = CTAS == 2 ? 6 : 4;
+  static constexpr int kStages = CTAS == 2 ? 5 : 4;
+  // staging boxes per epilogue warp (two let a TMA store drain while the next box is filled;
+  // the single-CTA form has room for one)
+  static constexpr uint32_t kBoxes = CTAS == 2 ? 2 : 1;
+  static constexpr uint32_t kStagingBytes = 8 /*epilogue warps*/ * kBoxes * 32 * 64;
   static constexpr uint32_t kBRows = kBN / CTAS;                 // rows of the B tile this CTA stages
   static constexpr uint32_t kBBytes = kBRows * kBK;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
@@ -88,11 +95,10 @@ constexpr uint32_t kTmemCols = 512;
 // Epilogue staging: per epilogue warp two [32 rows x 32 bf16] boxes (64-byte rows, 64B TMA
 // swizzle); plus, per epilogue warp, 256 column scales and 256 biases (fp32) of the tile.
 constexpr uint32_t kStoreBoxBytes = 32 * 64;
-constexpr uint32_t kStagingBytes = 4 * 2 * kStoreBoxBytes;
-constexpr uint32_t kScaleBytes = 4 * 2 * kBN * 4;
+constexpr uint32_t kScaleBytes = kEpilogueWarps * 2 * (kBN / 2) * 4; // per warp: scales and biases of its 128 columns
 template <int CTAS>
 constexpr size_t smem_bytes() {
-  return 1024 /*alignment slack*/ + (size_t)Cfg<CTAS>::kStages * Cfg<CTAS>::kStageBytes + kStagingBytes +
+  return 1024 /*alignment slack*/ + (size_t)Cfg<CTAS>::kStages * Cfg<CTAS>::kStageBytes + Cfg<CTAS>::kStagingBytes +
          kScaleBytes + 256;
 }
 
@@ -154,7 +160,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t units = CTAS == 2 ? gridDim.x >> 1 : gridDim.x;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t staging_base = smem_base + kStages * kStageBytes;
-  const uint32_t scale_base = staging_base + kStagingBytes;
+  const uint32_t scale_base = staging_base + Cfg<CTAS>::kStagingBytes;
   const uint32_t bar_base = scale_base + kScaleBytes;
   // barrier layout (8 bytes each): full[4], empty[4], tmem_full[2], tmem_empty[2]; then a word
   // for the TMEM base address and a word for the abort flag.
@@ -178,7 +184,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(tfull_bar + 8 * b, 1);
-      ptx::mbar_init(tempty_bar + 8 * b, 4 * CTAS);    // epilogue warps of every CTA of the pair
+      ptx::mbar_init(tempty_bar + 8 * b, kEpilogueWarps * CTAS);    // epilogue warps of every CTA of the pair
     }
     *abort_ptr = 0;
     ptx::fence_barrier_init();
@@ -313,22 +319,24 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
-    const uint32_t quarter = (uint32_t)warp & 3u;
+    const uint32_t quarter = (uint32_t)warp & 3u;        // TMEM lane quarter of this warp
+    const uint32_t ewarp = (uint32_t)warp - 2u;          // 0..7
+    const uint32_t col_half = ewarp >> 2;                // columns [128 col_half, 128 col_half + 128)
     uint32_t local = 0, store_buf = 0;
     uint8_t *generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
     float *scale_smem = reinterpret_cast<float *>(generic_base + (scale_base - smem_base));
-    const uint32_t my_staging = staging_base + quarter * 2u * kStoreBoxBytes;
+    const uint32_t my_staging = staging_base + ewarp * Cfg<CTAS>::kBoxes * kStoreBoxBytes;
     uint8_t *my_staging_ptr = generic_base + (my_staging - smem_base);
     for (uint32_t tile = unit; tile < num_tiles; tile += units, ++local) {
       const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
       const uint32_t m0 = (tile / tiles_n) * kTileM + cta_rank * kBM, n0 = (tile % tiles_n) * kBN;
       // column scales and biases of this tile -> this warp's private shared-memory copy
       // (warp-private so that no cross-warp barrier is needed)
-      float *cs = scale_smem + quarter * 2 * kBN, *bs = cs + kBN;
+      float *cs = scale_smem + ewarp * kBN, *bs = cs + kBN / 2; // this warp's 128 columns
       __syncwarp();
 #pragma unroll
-      for (int i = 0; i < kBN / 32; ++i) {
-        const uint32_t c = lane + 32u * i, n = n0 + c;
+      for (int i = 0; i < kBN / 64; ++i) {
+        const uint32_t c = lane + 32u * i, n = n0 + col_half * (kBN / 2) + c;
         cs[c] = n < p.N ? __ldg(p.col_scales + n) : 0.0f;
         bs[c] = ((p.epilogue & kEpiBias) && n < p.N) ? bf16_bits_to_f32(__ldg(p.bias + n)) : 0.0f;
       }
@@ -344,7 +352,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool row_ok = row < p.M;
       const float rs = row_ok ? __ldg(p.row_scales + row) : 0.0f;
 #pragma unroll 1
-      for (uint32_t chunk = 0; chunk < kBN / 32; ++chunk) {
+      for (uint32_t sub = 0; sub < kBN / 64; ++sub) {
+        const uint32_t chunk = col_half * (kBN / 64) + sub; // 32-column chunk of the tile
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * kBN + chunk * 32u, r);
         ptx::tmem_ld_wait();
@@ -359,8 +368,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t packed[16];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          const float4 c4 = *reinterpret_cast<const float4 *>(cs + chunk * 32 + 4 * g);
-          const float4 b4 = *reinterpret_cast<const float4 *>(bs + chunk * 32 + 4 * g);
+          const float4 c4 = *reinterpret_cast<const float4 *>(cs + sub * 32 + 4 * g);
+          const float4 b4 = *reinterpret_cast<const float4 *>(bs + sub * 32 + 4 * g);
           const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -384,8 +393,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (p.tma_store) {
           // stage this warp's [32 x 32] box (64-byte rows, 16-byte chunk c of row r stored at
           // c ^ ((r >> 1) & 3): the 64B TMA swizzle, conflict-free), then one TMA store.
-          if (lane == 0)
-            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          if (lane == 0) { // the box about to be filled must have been read by its last store
+            if (Cfg<CTAS>::kBoxes == 2)
+              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            else
+              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
           __syncwarp();
           uint8_t *box = my_staging_ptr + store_buf * kStoreBoxBytes;
 #pragma unroll
@@ -402,7 +415,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                          : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
-          store_buf ^= 1u;
+          store_buf = Cfg<CTAS>::kBoxes == 2 ? store_buf ^ 1u : 0u;
         } else if (row_ok) {
           uint16_t *dst = p.out + (size_t)row * p.N + n_base;
           for (int i = 0; i < 32; ++i)
