@@ -168,7 +168,7 @@ __device__ __forceinline__ void stage_pair(uint32_t base_a, uint32_t base_b, int
 // MAXT bounds the block size so that the register budget (about 80 per thread, which the
 // prefetch needs) is known at compile time: 256 -> 3 blocks/SM, 384 -> 2, 512 -> 1.
 template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL, int MAXT>
-__global__ void __launch_bounds__(MAXT, MAXT == 256 ? 3 : (MAXT == 384 ? 2 : 1))
+__global__ void __launch_bounds__(MAXT, MAXT == 256 ? 4 : (MAXT == 384 ? 2 : 1))
 convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int rows_per_cta) {
   extern __shared__ __align__(128) uint32_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -270,6 +270,15 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
   uint4 na0, na1, nb0, nb1;
   fetch((uint64_t)blockIdx.x * rows_per_cta + slot, na0, na1, nb0, nb1);
 
+  // Only the warps of one row exchange maxima: a named barrier per row slot, so that the rows a
+  // CTA works on at the same time do not wait for each other (the 4096-wide variants have one
+  // row per CTA and CTA-wide transposes anyway).
+  auto row_barrier = [&]() {
+    if (H4096)
+      __syncthreads();
+    else
+      asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "r"(warps_per_row * 32) : "memory");
+  };
   uint32_t parity = 0;
   for (uint64_t row0 = (uint64_t)blockIdx.x * rows_per_cta; row0 < p.rows;
        row0 += (uint64_t)gridDim.x * rows_per_cta, parity ^= 1u) {
@@ -383,7 +392,7 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
     float *redp = red + parity * 2 * total_warps;
     if (lane == 0)
       redp[warp] = m;
-    __syncthreads();
+    row_barrier();
     m = 0.0f;
     for (int w = 0; w < warps_per_row; ++w)
       m = fmaxf(m, redp[slot * warps_per_row + w]);
@@ -457,7 +466,7 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
         rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, o));
       if (lane == 0)
         redp[total_warps + warp] = rm;
-      __syncthreads();
+      row_barrier();
       rm = 0.0f;
       for (int w = 0; w < warps_per_row; ++w)
         rm = fmaxf(rm, redp[total_warps + slot * warps_per_row + w]);
