@@ -168,7 +168,7 @@ __device__ __forceinline__ void stage_pair(uint32_t base_a, uint32_t base_b, int
 // MAXT bounds the block size so that the register budget (about 80 per thread, which the
 // prefetch needs) is known at compile time: 256 -> 3 blocks/SM, 384 -> 2, 512 -> 1.
 template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL, int MAXT>
-__global__ void __launch_bounds__(MAXT, MAXT == 256 ? 4 : (MAXT == 384 ? 2 : 1))
+__global__ void __launch_bounds__(MAXT, MAXT == 256 ? 3 : (MAXT == 384 ? 2 : 1))
 convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int rows_per_cta) {
   extern __shared__ __align__(128) uint32_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
