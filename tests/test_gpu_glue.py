@@ -113,6 +113,57 @@ def test_qk_norm_partial_rope():
     _one_ulp(got, want, o)
 
 
+@pytest.mark.parametrize("interleaved,rotary,table_f32", [(False, 96, False), (True, 128, True), (False, 64, False)])
+def test_qk_norm_rope_quant_matches_the_two_reference_ops(interleaved, rotary, table_f32):
+    """difb200_qk_norm_rope_quant (one kernel) against the reference executor running
+    QkNormPartialRope and then QuantizeInt8Rows(Direct) on its output: codes and scales bit for bit,
+    written into the tail of a longer destination (the in-place slice and concat forms of the
+    kernel are exercised by the MMDiT block tests)."""
+    import ctypes as C
+    import torch
+    from diffusion_compiler_b200 import _lib
+    d, p = _program()
+    rng = np.random.default_rng(7)
+    tokens, heads, dim = 70, 3, 128
+    x = p.add_tensor(d.DType.BF16, [tokens, heads, dim], d.Role.Input)
+    w = p.add_tensor(d.DType.BF16, [dim], d.Role.Constant)
+    width = rotary // 2 if interleaved else rotary
+    tdt = d.DType.F32 if table_f32 else d.DType.BF16
+    c = p.add_tensor(tdt, [tokens, width], d.Role.Constant)
+    s = p.add_tensor(tdt, [tokens, width], d.Role.Constant)
+    r = p.add_tensor(d.DType.BF16, [tokens, heads, dim])
+    codes = p.add_tensor(d.DType.I8, [tokens, heads, dim], d.Role.Output)
+    scales = p.add_tensor(d.DType.F32, [tokens * heads], d.Role.Output)
+    attrs = [d.Attribute.f64(d.AttrKey.Epsilon, 1e-5), d.Attribute.u64(d.AttrKey.RotaryDim, rotary),
+             d.Attribute.u64(d.AttrKey.BlockSize, 128)]
+    if interleaved:
+        attrs += [d.Attribute.u64(d.AttrKey.Implementation, 2), d.Attribute.u64(d.AttrKey.RotaryLayout, 1)]
+    p.add_op(d.Opcode.QkNormPartialRope, [x, w, c, s], [r], attrs)
+    p.add_op(d.Opcode.QuantizeInt8Rows, [r], [codes, scales],
+             [d.Attribute.u64(d.AttrKey.BlockSize, 256), d.Attribute.u64(d.AttrKey.Implementation, 1)])
+    angle = rng.uniform(0, 6.28, [tokens, width]).astype(np.float32)
+    cos_t, sin_t = np.cos(angle), np.sin(angle)
+    if not table_f32:
+        cos_t, sin_t = ob.f32_to_bf16(cos_t), ob.f32_to_bf16(sin_t)
+    xv, wv = _bf(rng, [tokens, heads, dim]), _bf(rng, [dim])
+    want, _ = ob.ref().run(p, {w: wv, c: cos_t, s: sin_t, x: xv})
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    dense, dw = t(xv.view(np.int16)), t(wv.view(np.int16))
+    dc, ds = t(cos_t if table_f32 else cos_t.view(np.int16)), t(sin_t if table_f32 else sin_t.view(np.int16))
+    lead = 5  # destination starts 5 tokens into a longer sequence
+    out_codes = torch.zeros((tokens + lead, heads, dim), dtype=torch.int8, device="cuda")
+    out_scales = torch.zeros((tokens + lead) * heads, dtype=torch.float32, device="cuda")
+    L = _lib.lib()
+    ptr = lambda tensor: C.c_void_p(tensor.data_ptr())
+    _lib.check(L.difb200_qk_norm_rope_quant(ptr(dense), ptr(dw), ptr(dc), ptr(ds), None, ptr(out_codes[lead:]),
+                                            ptr(out_scales[lead * heads:]), 1 if table_f32 else 2, tokens, heads,
+                                            rotary, width, tokens, tokens, 0, 1e-5, 1 if interleaved else 0, None))
+    torch.cuda.synchronize()
+    assert np.array_equal(out_codes[lead:].cpu().numpy(), want[codes])
+    assert np.array_equal(out_scales[lead * heads:].cpu().numpy().view(np.uint32), want[scales].view(np.uint32))
+    assert torch.count_nonzero(out_codes[:lead]) == 0
+
+
 def test_residual_gate_swiglu_gelu_bits():
     d, p = _program()
     rng = np.random.default_rng(5)
