@@ -201,7 +201,7 @@ def plugin_e2e(torch, layers, device_index, steps, barrier):
 
 
 def attention_extra(torch, ops, device):
-    """BASELINE config 2: INT8 attention, B=2 H=24 S=4608 D=128; dense and GQA(8)+key mask."""
+    """Benchmark configuration 2: INT8 attention, B=2 H=24 S=4608 D=128; dense and GQA(8)+key mask."""
     res = []
     for KV, masked in ((24, False), (8, True)):
         B, S, H, D = 2, 4608, 24, 128
@@ -237,7 +237,7 @@ def attention_extra(torch, ops, device):
 
 
 def mmdit_block_extra(torch, device_index):
-    """BASELINE config 3: the MMDiT double-stream block (hidden 3072, 24x128, MLP 12288, 4096 image +
+    """Benchmark configuration 3: the MMDiT double-stream block (hidden 3072, 24x128, MLP 12288, 4096 image +
     512 text tokens, batch 2) as one DiffIR program through the plugin."""
     import numpy as np
     from diffusion_compiler_b200 import blocks, plugin
@@ -259,7 +259,7 @@ def mmdit_block_extra(torch, device_index):
 
 
 def video_block_extra(torch, device, rank, world, dist, iters=5):
-    """BASELINE config 4: the video DiT block, 33272 tokens sharded along tokens over `world` GPUs,
+    """Benchmark configuration 4: the video DiT block, 33272 tokens sharded along tokens over `world` GPUs,
     all-gather of quantised K (+scales) and bf16 V over NCCL. Strong scaling."""
     import numpy as np
     from diffusion_compiler_b200 import blocks
@@ -416,7 +416,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     total_ops = sum(2.0 * M_TOKENS * N * K for _, K, N, _ in PROJECTIONS)
-    config = {"workload": "DiT projection set (BASELINE config 1): M=2x4608 tokens per GPU, W8A8 int8-convrot "
+    config = {"workload": "DiT projection set (benchmark configuration 1): M=2x4608 tokens per GPU, W8A8 int8-convrot "
                           "QKV 3072->9216, out 3072->3072, MLP up 3072->12288 +GELU, MLP down 12288->3072",
               "tokens_per_gpu": M_TOKENS, "quantization": "H256ConvRot activations + per-channel INT8 weights",
               "parallelism": "token-sharded x%d, weights replicated" % max(world, args.gpus),
@@ -550,7 +550,7 @@ def main():
             line["cpu_baseline"] = res
     extras = {}
     if not args.no_extras:
-        # further configs of BASELINE.json, reported beside the headline (not part of `value`)
+        # the further benchmark configurations, reported beside the headline (not part of `value`)
         extras["video_block"] = video_block_extra(torch, device, rank, world, dist)
         if rank == 0:
             extras["attention"] = attention_extra(torch, ops, device)

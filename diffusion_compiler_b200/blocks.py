@@ -9,11 +9,11 @@ LinearInt8Scaled, the pattern of reference ``tools/difflux2sample.cpp:2017-2069`
   (LayerNormModulate) -> fused QKV -> slice/reshape -> RMS-norm + interleaved RoPE
   (QkNormPartialRope, Implementation 2) -> concat(text, image) -> joint Attention -> slice ->
   out-proj -> gated residual -> adaLN -> MLP (GELU-tanh) -> gated residual. Dimensions are free
-  (BASELINE config 3: hidden 3072, 24 heads x 128, MLP 12288, 2-axis RoPE theta 10000).
+  (benchmark configuration 3: hidden 3072, 24 heads x 128, MLP 12288, 2-axis RoPE theta 10000).
 * ``video_block_program``: the single-stream video block the reference emits with
   ``difc make-h3-block-bf16`` (``tools/difc.cpp:261-345``): RmsNormModulate -> q/k/v -> half-split
   partial RoPE -> Attention -> out -> ResidualGate -> RmsNormModulate -> fc1 -> SwiGlu -> fc2 ->
-  ResidualGate (BASELINE config 4: 33272 tokens, hidden 3072, 24 x 128, FFN 8192, rotary 96).
+  ResidualGate (benchmark configuration 4: 33272 tokens, hidden 3072, 24 x 128, FFN 8192, rotary 96).
 
 Everything here is host-side graph/tensor construction (numpy); kernels are reached through the
 plugin (``plugin.py``) or the device API (``ops.py``).
@@ -308,7 +308,7 @@ def synth_video_block(rng: np.random.Generator, S: int, hidden: int, heads: int,
                       quantize, positions: np.ndarray = None):
     """(program, ids, constants, inputs) of a video block with seeded synthetic tensors.
     Modulation tensors are broadcast from one conditioning vector through a random linear map,
-    as BASELINE config 4 describes."""
+    as benchmark configuration 4 describes."""
     p, ids = video_block_program(S, hidden, heads, dim, ffn, rotary)
     consts = synth_linears(rng, ids["linears"], quantize)
     one_h = f32_to_bf16(np.ones(hidden, np.float32))

@@ -1,5 +1,6 @@
 """Generates tests/golden/hotpath_golden.npz by running the REFERENCE project's own CPU executor
-(oracle/_ref/libdifref.so, built from /root/reference by oracle/Makefile) on
+(oracle/_ref/libdifref.so, built by oracle/Makefile from the reference checkout its REF variable
+names) on
 
   * the inputs of the reference's own unit tests for this path
     (tests/dif_tests.cpp:4259-4312 generic scaled INT8 linear; :4607-4665 H256 ConvRot, four
@@ -8,7 +9,7 @@
   * seeded cases: all seven QuantizeInt8Rows variants with residual outputs and a zero row, a
     W8A8 linear with bias and tanh-GELU, and exact Attention with GQA and a key mask.
 
-Run it where /root/reference is mounted:  python tests/golden/make_golden.py
+Run it where that checkout is present:  python tests/golden/make_golden.py
 Every array is stored under "<case>/<name>"; bf16 tensors are uint16 bit patterns.
 """
 import os

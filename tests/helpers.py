@@ -12,7 +12,7 @@ def bf16_normal(rng: np.random.Generator, shape, std: float = 1.0) -> np.ndarray
 
 
 def activations(rng: np.random.Generator, M: int, K: int, outliers: int = 32) -> np.ndarray:
-    """bf16 N(0,1) activations with `outliers` fixed channels scaled x16 (BASELINE config 0)."""
+    """bf16 N(0,1) activations with `outliers` fixed channels scaled x16 (benchmark configuration 0)."""
     x = rng.standard_normal((M, K)).astype(np.float32)
     chans = np.random.default_rng(0).choice(K, size=min(outliers, K), replace=False)
     x[:, chans] *= 16.0
