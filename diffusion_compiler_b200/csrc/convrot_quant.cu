@@ -40,6 +40,7 @@ struct QuantParams {
   float *scales;
   int8_t *rcodes;
   float *rscales;
+  uint32_t mse;   // weight rows: choose the row scale by the offline packer's MSE search
 };
 
 // Fixed Rademacher diagonal of the signed variants (reference cpu_executor.cpp:183-189).
@@ -167,7 +168,10 @@ __device__ __forceinline__ void stage_pair(uint32_t base_a, uint32_t base_b, int
 
 // MAXT bounds the block size so that the register budget (about 80 per thread, which the
 // prefetch needs) is known at compile time: 256 -> 3 blocks/SM, 384 -> 2, 512 -> 1.
-template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL, int MAXT>
+// MSE (weight rows only): the scale is the one of seven clipped candidates with the lowest squared
+// error over every fourth rotated element, the offline packer's rule (reference
+// tools/difflux2sample.cpp:1225-1259; row encoder :2994-3059).
+template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL, bool MSE, int MAXT>
 __global__ void __launch_bounds__(MAXT, MAXT == 256 ? 3 : (MAXT == 384 ? 2 : 1))
 convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int rows_per_cta) {
   extern __shared__ __align__(128) uint32_t smem[];
@@ -398,9 +402,60 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
       m = fmaxf(m, redp[slot * warps_per_row + w]);
 
     const float maximum = m * (1.0f / kCarry);
-    const float scale = fmaxf(__fdiv_rn(__fmul_rn(maximum, clip), 127.0f), 1.0e-30f);
+    float scale = fmaxf(__fdiv_rn(__fmul_rn(maximum, clip), 127.0f), 1.0e-30f);
+    if (MSE) {
+      // Every thread evaluates the seven candidates on its sampled elements (column % 4 == 0, i.e.
+      // a % 4 == 0 in this layout), in double like the reference; partial sums meet per warp and
+      // then per row in a fixed order (the reference adds sequentially: its sum can differ in
+      // the last bits of a double, which matters only for candidates that tie to 1e-15).
+      const float factors[7] = {1.0f, 0.96f, 0.92f, 0.88f, 0.84f, 0.80f, 0.76f};
+      double *errors = reinterpret_cast<double *>(
+          reinterpret_cast<unsigned char *>(smem) + (size_t)total_warps * (kWarpBytes + 16) + 64 +
+          (SIGNED ? (size_t)total_warps * 32 * 64 : 0));
+      float candidate[7];
+#pragma unroll 1
+      for (int f = 0; f < 7; ++f) {
+        candidate[f] = round_bf16(fmaxf(__fdiv_rn(__fmul_rn(maximum, factors[f]), 127.0f), 1.0e-30f));
+        double e = 0.0;
+        if ((a & 3) == 0) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float v[2];
+            unpack2(P[j], v[0], v[1]);
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+              const float value = round_bf16(v[g] * (1.0f / kCarry));
+              const float divided = round_bf16(__fdiv_rn(value, candidate[f]));
+              const int encoded = min(max(__float2int_rn(divided), -128), 127);
+              const double delta = __dsub_rn((double)value, __dmul_rn((double)encoded, (double)candidate[f]));
+              e = __dadd_rn(e, __dmul_rn(delta, delta));
+            }
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+          e = __dadd_rn(e, __shfl_xor_sync(0xffffffffu, e, o));
+        if (lane == 0)
+          errors[f * total_warps + warp] = e;
+      }
+      row_barrier();
+      double best = 0.0;
+#pragma unroll 1
+      for (int f = 0; f < 7; ++f) {
+        double e = 0.0;
+        for (int w = 0; w < warps_per_row; ++w)
+          e = __dadd_rn(e, errors[f * total_warps + slot * warps_per_row + w]);
+        if (f == 0 || e < best) {
+          best = e;
+          scale = candidate[f];
+        }
+      }
+      if (maximum == 0.0f)
+        scale = 1.0e-30f;
+      row_barrier(); // the error slots are reused by the next row
+    }
     const float scale_bf16 = round_bf16(scale);
-    const float stored = (SIGNED && !F32) ? scale_bf16 : scale;
+    const float stored = ((SIGNED || MSE) && !F32) ? scale_bf16 : scale;
     const float divisor = (F32 ? scale : scale_bf16) * kCarry;
     const float recip = __frcp_rn(divisor);
     const uint64_t y2 = pack2(recip, recip), nb2 = pack2(-divisor, -divisor);
@@ -601,7 +656,7 @@ direct_quant_kernel(const QuantParams p) {
   }
 }
 
-template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL>
+template <bool SIGNED, bool F32, bool H4096, bool RESIDUAL, bool MSE = false>
 int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
   const uint32_t groups = p.columns >> 8;
   const int warps_per_row = (int)((groups + 3u) / 4u);
@@ -615,11 +670,11 @@ int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
   const int warps = warps_per_row * rows_per_cta;
   // per warp: transpose / staging area; row maxima; for the signed variants 16 XOR masks per thread
   const size_t smem = (size_t)warps * kWarpBytes + (size_t)warps * 4 * sizeof(float) + 64 +
-                      (SIGNED ? (size_t)warps * 32 * 64 : 0);
+                      (SIGNED ? (size_t)warps * 32 * 64 : 0) + (MSE ? (size_t)warps * 7 * sizeof(double) : 0);
   const int threads_needed = warps * 32;
-  auto kernel = threads_needed <= 256   ? convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, 256>
-                : threads_needed <= 384 ? convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, 384>
-                                        : convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, 512>;
+  auto kernel = threads_needed <= 256   ? convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, MSE, 256>
+                : threads_needed <= 384 ? convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, MSE, 384>
+                                        : convrot_quant_kernel<SIGNED, F32, H4096, RESIDUAL, MSE, 512>;
   if (smem > 48 * 1024) {
     if (int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)smem),
@@ -643,6 +698,12 @@ int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
 
 template <bool SIGNED, bool F32, bool H4096>
 int launch_convrot(const QuantParams &p, cudaStream_t stream) {
+  if (p.mse) {
+    if (H4096 || p.rcodes)
+      return fail(kUnsupported, "QuantizeInt8Rows: the MSE weight scale exists for the 256-wide variants "
+                                "without residual outputs");
+    return launch_convrot_impl<SIGNED, F32, false, false, true>(p, stream);
+  }
   return p.rcodes ? launch_convrot_impl<SIGNED, F32, H4096, true>(p, stream)
                   : launch_convrot_impl<SIGNED, F32, H4096, false>(p, stream);
 }
@@ -652,7 +713,7 @@ int launch_convrot(const QuantParams &p, cudaStream_t stream) {
 int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, uint32_t part_count,
                        uint64_t rows, int implementation, float clip, const float *clip_device,
                        int8_t *codes, float *scales, int8_t *rcodes, float *rscales,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, bool mse_weight_scale) {
   if (part_count == 0 || part_count > kMaxParts)
     return fail(kUnsupported, "QuantizeInt8Rows: 1..8 concatenated inputs are supported");
   if (!codes || !scales || (rcodes == nullptr) != (rscales == nullptr))
@@ -682,8 +743,12 @@ int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, ui
   p.scales = scales;
   p.rcodes = rcodes;
   p.rscales = rscales;
+  p.mse = mse_weight_scale ? 1u : 0u;
   if (rows == 0)
     return kOk;
+  if (mse_weight_scale && (implementation == 1 || clip_device))
+    return fail(kUnsupported, "QuantizeInt8Rows: the MSE weight scale applies to the ConvRot variants with a "
+                              "static clip");
   if (implementation == 1) {
     const int threads = 256;
     uint64_t blocks = (rows + 7) / 8;

@@ -75,6 +75,22 @@ def quantize_int8_rows(parts: Sequence[torch.Tensor], implementation: int = 2, c
     return (codes, scales, rcodes, rscales) if residual else (codes, scales)
 
 
+def quantize_weight_rows(weight: torch.Tensor, implementation: int = 2, mse_scale: bool = False):
+    """Weight-side packing of a bf16 [N, K] matrix: I8 codes [N, K] and per-output-channel scales
+    [N] (reference tools/difflux2sample.cpp:2994-3059); ``mse_scale`` picks each row's scale by the
+    offline packer's MSE search (:1225-1259)."""
+    weight = _require(weight, torch.bfloat16, "weight")
+    if weight.dim() != 2:
+        raise ValueError("weight must be a bf16 [N, K] matrix")
+    N, K = weight.shape
+    codes = torch.empty((N, K), dtype=torch.int8, device=weight.device)
+    scales = torch.empty((N,), dtype=torch.float32, device=weight.device)
+    _lib.check(_lib.lib().difb200_quantize_weight_rows(C.c_void_p(weight.data_ptr()), N, K, implementation,
+                                                        1 if mse_scale else 0, C.c_void_p(codes.data_ptr()),
+                                                        C.c_void_p(scales.data_ptr()), _stream()))
+    return codes, scales
+
+
 def linear_int8_scaled(x8: torch.Tensor, w8: torch.Tensor, row_scales: torch.Tensor,
                        col_scales: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
                        want_acc: bool = False, out: Optional[torch.Tensor] = None):

@@ -62,6 +62,20 @@ DIFB200_EXPORT int difb200_quantize_int8_rows(const void *const *parts, const ui
                                               float *residual_scales, void *stream);
 
 /*
+ * Weight-side packing: the bf16 weight matrix [rows = N, columns = K] quantised row by row with
+ * the same rotation and quantiser as the activations (clip 1), giving the I8 weight and the
+ * per-output-channel scales that LinearInt8Scaled binds as constants. This is the encoder of the
+ * reference's offline packer (tools/difflux2sample.cpp:2994-3059; GPU variant
+ * tools/difh3convrot.cpp:364-446). mse_scale != 0 selects the row scale by the packer's MSE search
+ * over seven clip factors on every fourth rotated element (tools/difflux2sample.cpp:1225-1259;
+ * 256-wide ConvRot variants 2, 3, 5, 6 only); the stored scale is then the bf16-rounded one.
+ * Input equalisation (:2967-2990) is a host-side column scaling applied before this call.
+ */
+DIFB200_EXPORT int difb200_quantize_weight_rows(const void *weight, uint64_t rows, uint64_t columns,
+                                                int32_t implementation, int32_t mse_scale,
+                                                int8_t *codes, float *scales, void *stream);
+
+/*
  * Opcode LinearInt8Scaled (68), optionally fused with the BiasAdd (10) and Gelu (49, tanh)
  * ops that follow it in a W8A8-rewritten program. Replaces the reference CPU op
  * src/runtime/cpu_executor.cpp:309-335 and the CUTLASS Sm80 kernel

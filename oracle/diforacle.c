@@ -119,7 +119,39 @@ typedef struct {
   float *scales;
   int8_t *rcodes;
   float *rscales;
+  int mse; /* weight rows: scale from the offline packer's MSE search */
 } quant_ctx;
+
+/* tools/difflux2sample.cpp:1225-1259 (choose_mse_int8_weight_scale): seven clip factors, the
+ * bf16-rounded scale of each, squared error over every fourth element in double, first best
+ * wins. No test of the reference pins this function (it lives in a tool's anonymous namespace
+ * and cannot be linked): parity of this one restatement is UNPINNED. */
+static float choose_mse_weight_scale(const float *values, uint64_t count) {
+  static const float factors[7] = {1.0F, 0.96F, 0.92F, 0.88F, 0.84F, 0.80F, 0.76F};
+  float maximum = 0.0F;
+  for (uint64_t i = 0; i < count; ++i)
+    maximum = fmaxf(maximum, fabsf(values[i]));
+  if (maximum == 0.0F)
+    return 1.0e-30F;
+  float best_scale = INFINITY;
+  double best_error = INFINITY;
+  for (int f = 0; f < 7; ++f) {
+    const float scale = rbf(fmaxf(maximum * factors[f] / 127.0F, 1.0e-30F));
+    double error = 0.0;
+    for (uint64_t i = 0; i < count; i += 4U) {
+      const float value = rbf(values[i]);
+      const float divided = rbf(value / scale);
+      const int encoded = clampi((int)nearbyintf(divided), -128, 127);
+      const double delta = (double)value - (double)encoded * scale;
+      error += delta * delta;
+    }
+    if (error < best_error) {
+      best_error = error;
+      best_scale = scale;
+    }
+  }
+  return best_scale;
+}
 
 static void quant_body(void *vctx, int64_t row_begin, int64_t row_end) {
   const quant_ctx *ctx = (const quant_ctx *)vctx;
@@ -178,9 +210,12 @@ static void quant_body(void *vctx, int64_t row_begin, int64_t row_end) {
       }
       for (uint64_t c = 0; c < columns; ++c)
         maximum = fmaxf(maximum, fabsf(t[c])); /* :230-235 */
-      const float scale = fmaxf(maximum * clip / 127.0F, 1.0e-30F); /* :236-237 */
+      /* :236-237; for weight rows packed with the MSE search,
+       * tools/difflux2sample.cpp:3020-3031 (scale) and :3032-3037 (what is stored) */
+      const float scale = (ctx->mse && convrot) ? choose_mse_weight_scale(t, columns)
+                                                : fmaxf(maximum * clip / 127.0F, 1.0e-30F);
       const float scale_bf16 = rbf(scale);
-      const float stored = (sgn && !f32) ? scale_bf16 : scale; /* :239-240 */
+      const float stored = ((sgn || (ctx->mse && convrot)) && !f32) ? scale_bf16 : scale; /* :239-240 */
       scales[row] = stored;
       for (uint64_t c = 0; c < columns; ++c) {
         int rounded;
@@ -242,7 +277,29 @@ ORC_EXPORT int orc_quantize_int8_rows(const uint16_t *const *parts,
   if (implementation != ORC_DIRECT && columns % group != 0U)
     return 1;
   quant_ctx ctx = {parts, part_widths, part_count, columns, implementation,
-                   clip,  codes,       scales,     rcodes,  rscales};
+                   clip,  codes,       scales,     rcodes,  rscales, 0};
+  parallel_for((int64_t)rows, quant_body, &ctx);
+  return 0;
+}
+
+/* Weight-side packing of a bf16 [rows, columns] matrix, tools/difflux2sample.cpp:2994-3059
+ * (clip 1, no residual); mse != 0 uses choose_mse_weight_scale. Without mse this is
+ * orc_quantize_int8_rows on one part, which is pinned against the reference executor. */
+ORC_EXPORT int orc_quantize_weight_rows(const uint16_t *weight, uint64_t rows,
+                                        uint64_t columns, int implementation,
+                                        int mse, int8_t *codes, float *scales) {
+  if (implementation < ORC_H256 || implementation > ORC_H4096_F32_SIGNED)
+    return 1;
+  const uint64_t group = (implementation == ORC_H4096_SIGNED ||
+                          implementation == ORC_H4096_F32_SIGNED)
+                             ? 4096U
+                             : 256U;
+  if (columns % group != 0U)
+    return 1;
+  const uint16_t *parts[1] = {weight};
+  const uint64_t widths[1] = {columns};
+  quant_ctx ctx = {parts, widths, 1,     columns, implementation, 1.0F,
+                   codes, scales, NULL, NULL,    mse};
   parallel_for((int64_t)rows, quant_body, &ctx);
   return 0;
 }

@@ -66,6 +66,25 @@ def test_quantize_direct_per_token_head(ops):
     _quant_case(ops, rng, 1, 11, 100, 1.0, True)  # odd width: scalar path
 
 
+@pytest.mark.parametrize("impl", [2, 3, 5, 6])
+@pytest.mark.parametrize("N,K", [(5, 256), (40, 768), (64, 3072), (6, 12288)])
+def test_weight_rows_with_mse_scale_bit_exact(ops, impl, N, K):
+    """Weight-side packing (offline packer's encoder, reference tools/difflux2sample.cpp:2994-3059)
+    with and without the MSE scale search (:1225-1259) against the CPU restatement."""
+    import torch
+    rng = np.random.default_rng(1000 * impl + K)
+    w = ob.f32_to_bf16((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    w[N // 2] = 0
+    dw = torch.from_numpy(w.view(np.int16)).cuda().view(torch.bfloat16)
+    for mse in (False, True):
+        want_codes, want_scales = ob.orc().quantize_weight_rows(w, impl, mse=mse)
+        codes, scales = ops.quantize_weight_rows(dw, impl, mse_scale=mse)
+        torch.cuda.synchronize()
+        assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_scales.view(np.uint32)), mse
+        assert np.array_equal(codes.cpu().numpy(), want_codes), mse
+    ops.poll_status()
+
+
 def _weights(rng, N, K, impl):
     wf = bf16_normal(rng, (N, K), 0.02)
     return ob.orc().quantize_int8_rows([wf], impl, 1.0)

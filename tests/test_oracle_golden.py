@@ -126,3 +126,21 @@ def test_restatement_equals_reference_on_fresh_inputs(impl):
     got = ob.orc().quantize_int8_rows([x], impl, 0.9, residual=True)
     for name, a in zip(("codes", "scales", "rcodes", "rscales"), got):
         assert _eq(a, res[pr["ids"][name]]), name
+
+
+def test_weight_rows_without_mse_equal_the_pinned_quantiser():
+    """orc_quantize_weight_rows without the MSE search is the activation quantiser at clip 1,
+    which is pinned against the reference executor; with the search the chosen scale is one of
+    the seven candidates and never above the absmax scale."""
+    rng = np.random.default_rng(11)
+    w = ob.f32_to_bf16((rng.standard_normal((24, 768)) * 0.02).astype(np.float32))
+    w[3] = 0  # an all-zero output channel
+    for impl in (2, 3, 5, 6):
+        codes, scales = ob.orc().quantize_weight_rows(w, impl)
+        want_codes, want_scales = ob.orc().quantize_int8_rows([w], impl)
+        assert np.array_equal(codes, want_codes) and np.array_equal(scales.view(np.uint32), want_scales.view(np.uint32))
+        mcodes, mscales = ob.orc().quantize_weight_rows(w, impl, mse=True)
+        assert (mscales <= ob.bf16_to_f32(ob.f32_to_bf16(scales)) * (1 + 2.0 ** -7)).all()
+        assert mscales[3] == np.float32(1.0e-30) or mscales[3] == ob.bf16_to_f32(ob.f32_to_bf16(np.float32([1e-30])))[0]
+        ratio = mscales[scales > 1e-20] / scales[scales > 1e-20]
+        assert ((ratio > 0.75) & (ratio < 1.01)).all()
