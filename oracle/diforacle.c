@@ -6,10 +6,13 @@
  * Parity status: PINNED. Every function that restates a reference function is checked
  * bit-for-bit against the reference's own CPU executor (built from the reference sources
  * by the Makefile in this directory) through the committed fixtures under tests/golden/.
- * The one exception is orc_attention_int8: the reference has no CPU form of INT8
+ * Two exceptions, both UNPINNED. orc_attention_int8: the reference has no CPU form of INT8
  * attention, so that function defines this repository's own numerical contract; its Q/K
  * codes and scales are the reference's (QuantizeInt8Rows, Direct) and it is additionally
- * compared, with a tolerance, against the reference's exact Attention.
+ * compared, with a tolerance, against the reference's exact Attention. And the MSE scale
+ * search of orc_quantize_weight_rows: it restates a function that the reference keeps in a
+ * command-line tool's anonymous namespace, which no test of the reference exercises and no
+ * library exports; without the search that entry is the pinned quantiser.
  *
  * Each function cites the reference file:line it follows (paths inside the reference
  * project). Build flags: -O3 without -march, so x86-64 never contracts a*b+c into an fma
