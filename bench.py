@@ -528,6 +528,7 @@ def main():
                          "peak_source": "2 x %s bf16 burst TFLOP/s (INT8 dense = 2x bf16 on B200); nominal 4500"
                                         % peaks["source"],
                          "frac_of_nominal_4500": gemm_tops / 4500.0,
+                         "frac_of_2x_sustained_bf16": gemm_tops / (2.0 * peaks["bf16_tflops_sustained"]),
                          "traffic": recorded_traffic(
                              "gemm_i8_kernel",
                              sum(M_TOKENS * K + N * K for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS),
