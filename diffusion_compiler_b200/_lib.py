@@ -32,7 +32,7 @@ def lib() -> C.CDLL:
         L.difb200_quantize_int8_rows.argtypes = [C.POINTER(vp), C.POINTER(u64), u32, u64, i32, f32, vp,
                                                  vp, vp, vp, vp, vp]
         L.difb200_quantize_weight_rows.restype = C.c_int
-        L.difb200_quantize_weight_rows.argtypes = [vp, u64, u64, i32, i32, vp, vp, vp]
+        L.difb200_quantize_weight_rows.argtypes = [vp, vp, u64, u64, i32, i32, vp, vp, vp]
         L.difb200_linear_int8_scaled.restype = C.c_int
         L.difb200_linear_int8_scaled.argtypes = [vp, vp, vp, vp, vp, u32, u64, u64, u64, vp, vp, vp]
         L.difb200_w8a8_linear.restype = C.c_int

@@ -94,14 +94,15 @@ int difb200_quantize_int8_rows(const void *const *parts, const uint64_t *part_wi
                             static_cast<cudaStream_t>(stream));
 }
 
-int difb200_quantize_weight_rows(const void *weight, uint64_t rows, uint64_t columns, int32_t implementation,
-                                 int32_t mse_scale, int8_t *codes, float *scales, void *stream) {
+int difb200_quantize_weight_rows(const void *weight, const void *input_scale, uint64_t rows, uint64_t columns,
+                                 int32_t implementation, int32_t mse_scale, int8_t *codes, float *scales,
+                                 void *stream) {
   if (!weight)
     return fail(kInvalidArgument, "difb200_quantize_weight_rows: null weight");
   const void *parts[1] = {weight};
   const uint64_t widths[1] = {columns};
   return quantize_int8_rows(parts, widths, 1, rows, implementation, 1.0f, nullptr, codes, scales, nullptr, nullptr,
-                            static_cast<cudaStream_t>(stream), mse_scale != 0);
+                            static_cast<cudaStream_t>(stream), mse_scale != 0, input_scale);
 }
 
 int difb200_linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales,

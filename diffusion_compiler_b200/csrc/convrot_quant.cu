@@ -41,6 +41,7 @@ struct QuantParams {
   int8_t *rcodes;
   float *rscales;
   uint32_t mse;   // weight rows: choose the row scale by the offline packer's MSE search
+  const uint16_t *equalise; // weight rows: bf16 [columns], every element is divided by its entry first
 };
 
 // Fixed Rademacher diagonal of the signed variants (reference cpu_executor.cpp:183-189).
@@ -305,10 +306,29 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
           wb[i] ^= mb[i];
         }
       }
+      // weight rows with input equalisation: w / e in fp32 before anything else (reference
+      // tools/difflux2sample.cpp:3005-3014; the sign flip commutes with the division)
+      uint32_t ea[8], eb[8];
+      const bool equalise = MSE && p.equalise != nullptr;
+      if (equalise) {
+        const uint32_t col = group_a * 256u + 16u * a;
+        const uint4 z = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u); // bf16 ones
+        const uint4 *ep = reinterpret_cast<const uint4 *>(p.equalise + col);
+        const uint4 e0 = act_a ? __ldg(ep) : z, e1 = act_a ? __ldg(ep + 1) : z;
+        const uint4 e2 = act_b ? __ldg(ep + 32) : z, e3 = act_b ? __ldg(ep + 33) : z;
+        ea[0] = e0.x, ea[1] = e0.y, ea[2] = e0.z, ea[3] = e0.w, ea[4] = e1.x, ea[5] = e1.y, ea[6] = e1.z, ea[7] = e1.w;
+        eb[0] = e2.x, eb[1] = e2.y, eb[2] = e2.z, eb[3] = e2.w, eb[4] = e3.x, eb[5] = e3.y, eb[6] = e3.z, eb[7] = e3.w;
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const uint32_t alo = wa[i] << 16, ahi = wa[i] & 0xffff0000u;
-        const uint32_t blo = wb[i] << 16, bhi = wb[i] & 0xffff0000u;
+        uint32_t alo = wa[i] << 16, ahi = wa[i] & 0xffff0000u;
+        uint32_t blo = wb[i] << 16, bhi = wb[i] & 0xffff0000u;
+        if (equalise) {
+          alo = __float_as_uint(__fdiv_rn(__uint_as_float(alo), __uint_as_float(ea[i] << 16)));
+          ahi = __float_as_uint(__fdiv_rn(__uint_as_float(ahi), __uint_as_float(ea[i] & 0xffff0000u)));
+          blo = __float_as_uint(__fdiv_rn(__uint_as_float(blo), __uint_as_float(eb[i] << 16)));
+          bhi = __float_as_uint(__fdiv_rn(__uint_as_float(bhi), __uint_as_float(eb[i] & 0xffff0000u)));
+        }
         P[2 * i] = pack2(__uint_as_float(alo), __uint_as_float(blo));
         P[2 * i + 1] = pack2(__uint_as_float(ahi), __uint_as_float(bhi));
       }
@@ -403,7 +423,7 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
 
     const float maximum = m * (1.0f / kCarry);
     float scale = fmaxf(__fdiv_rn(__fmul_rn(maximum, clip), 127.0f), 1.0e-30f);
-    if (MSE) {
+    if (MSE && p.mse) {
       // Every thread evaluates the seven candidates on its sampled elements (column % 4 == 0, i.e.
       // a % 4 == 0 in this layout), in double like the reference; partial sums meet per warp and
       // then per row in a fixed order (the reference adds sequentially: its sum can differ in
@@ -455,7 +475,7 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
       row_barrier(); // the error slots are reused by the next row
     }
     const float scale_bf16 = round_bf16(scale);
-    const float stored = ((SIGNED || MSE) && !F32) ? scale_bf16 : scale;
+    const float stored = ((SIGNED || (MSE && p.mse)) && !F32) ? scale_bf16 : scale;
     const float divisor = (F32 ? scale : scale_bf16) * kCarry;
     const float recip = __frcp_rn(divisor);
     const uint64_t y2 = pack2(recip, recip), nb2 = pack2(-divisor, -divisor);
@@ -698,10 +718,10 @@ int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
 
 template <bool SIGNED, bool F32, bool H4096>
 int launch_convrot(const QuantParams &p, cudaStream_t stream) {
-  if (p.mse) {
+  if (p.mse || p.equalise) { // the weight-packing form of the kernel
     if (H4096 || p.rcodes)
-      return fail(kUnsupported, "QuantizeInt8Rows: the MSE weight scale exists for the 256-wide variants "
-                                "without residual outputs");
+      return fail(kUnsupported, "QuantizeInt8Rows: weight packing (MSE scale, input equalisation) exists for "
+                                "the 256-wide variants without residual outputs");
     return launch_convrot_impl<SIGNED, F32, false, false, true>(p, stream);
   }
   return p.rcodes ? launch_convrot_impl<SIGNED, F32, H4096, true>(p, stream)
@@ -713,7 +733,7 @@ int launch_convrot(const QuantParams &p, cudaStream_t stream) {
 int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, uint32_t part_count,
                        uint64_t rows, int implementation, float clip, const float *clip_device,
                        int8_t *codes, float *scales, int8_t *rcodes, float *rscales,
-                       cudaStream_t stream, bool mse_weight_scale) {
+                       cudaStream_t stream, bool mse_weight_scale, const void *equalise_bf16) {
   if (part_count == 0 || part_count > kMaxParts)
     return fail(kUnsupported, "QuantizeInt8Rows: 1..8 concatenated inputs are supported");
   if (!codes || !scales || (rcodes == nullptr) != (rscales == nullptr))
@@ -744,11 +764,14 @@ int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, ui
   p.rcodes = rcodes;
   p.rscales = rscales;
   p.mse = mse_weight_scale ? 1u : 0u;
+  p.equalise = static_cast<const uint16_t *>(equalise_bf16);
   if (rows == 0)
     return kOk;
-  if (mse_weight_scale && (implementation == 1 || clip_device))
-    return fail(kUnsupported, "QuantizeInt8Rows: the MSE weight scale applies to the ConvRot variants with a "
+  if ((mse_weight_scale || equalise_bf16) && (implementation == 1 || clip_device || part_count != 1))
+    return fail(kUnsupported, "QuantizeInt8Rows: weight packing applies to one input, the ConvRot variants and a "
                               "static clip");
+  if (equalise_bf16 && (reinterpret_cast<uintptr_t>(equalise_bf16) & 15))
+    return fail(kUnsupported, "QuantizeInt8Rows: the equalisation vector must be 16-byte aligned");
   if (implementation == 1) {
     const int threads = 256;
     uint64_t blocks = (rows + 7) / 8;

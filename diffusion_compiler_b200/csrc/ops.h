@@ -15,7 +15,7 @@ const std::string &last_error();
 int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, uint32_t part_count,
                        uint64_t rows, int implementation, float clip, const float *clip_device,
                        int8_t *codes, float *scales, int8_t *rcodes, float *rscales,
-                       cudaStream_t stream, bool mse_weight_scale = false);
+                       cudaStream_t stream, bool mse_weight_scale = false, const void *equalise_bf16 = nullptr);
 
 int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales,
                        const float *col_scales, const void *bias_bf16, uint32_t epilogue, uint64_t M,

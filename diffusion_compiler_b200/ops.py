@@ -75,19 +75,37 @@ def quantize_int8_rows(parts: Sequence[torch.Tensor], implementation: int = 2, c
     return (codes, scales, rcodes, rscales) if residual else (codes, scales)
 
 
-def quantize_weight_rows(weight: torch.Tensor, implementation: int = 2, mse_scale: bool = False):
+def weight_equalization(weight: torch.Tensor) -> torch.Tensor:
+    """The offline packer's input-equalisation vector for a bf16 [N, K] weight (reference
+    tools/difflux2sample.cpp:2967-2990): sqrt(column absmax / geometric mean of the column
+    absmaxes), clamped to [0.5, 2], as bf16 [K]. Weights are divided by it before packing and
+    activations multiplied by it at run time."""
+    weight = _require(weight, torch.bfloat16, "weight")
+    maxima = weight.float().abs().amax(dim=0)
+    logs = torch.log(torch.clamp(maxima, min=1.0e-30)).double()
+    center = torch.exp(logs.sum() / maxima.numel()).float()
+    ratio = torch.sqrt(maxima / torch.clamp(center, min=1.0e-30))
+    return torch.clamp(ratio, 0.5, 2.0).to(torch.bfloat16)
+
+
+def quantize_weight_rows(weight: torch.Tensor, implementation: int = 2, mse_scale: bool = False,
+                         input_scale: Optional[torch.Tensor] = None):
     """Weight-side packing of a bf16 [N, K] matrix: I8 codes [N, K] and per-output-channel scales
     [N] (reference tools/difflux2sample.cpp:2994-3059); ``mse_scale`` picks each row's scale by the
-    offline packer's MSE search (:1225-1259)."""
+    offline packer's MSE search (:1225-1259); ``input_scale`` is the bf16 [K] equalisation vector
+    the weights are divided by first."""
     weight = _require(weight, torch.bfloat16, "weight")
     if weight.dim() != 2:
         raise ValueError("weight must be a bf16 [N, K] matrix")
     N, K = weight.shape
+    if input_scale is not None:
+        input_scale = _require(input_scale, torch.bfloat16, "input_scale")
+        if input_scale.numel() != K:
+            raise ValueError("input_scale must have K entries")
     codes = torch.empty((N, K), dtype=torch.int8, device=weight.device)
     scales = torch.empty((N,), dtype=torch.float32, device=weight.device)
-    _lib.check(_lib.lib().difb200_quantize_weight_rows(C.c_void_p(weight.data_ptr()), N, K, implementation,
-                                                        1 if mse_scale else 0, C.c_void_p(codes.data_ptr()),
-                                                        C.c_void_p(scales.data_ptr()), _stream()))
+    _lib.check(_lib.lib().difb200_quantize_weight_rows(_ptr(weight), _ptr(input_scale), N, K, implementation,
+                                                        1 if mse_scale else 0, _ptr(codes), _ptr(scales), _stream()))
     return codes, scales
 
 

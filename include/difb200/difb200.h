@@ -69,11 +69,15 @@ DIFB200_EXPORT int difb200_quantize_int8_rows(const void *const *parts, const ui
  * tools/difh3convrot.cpp:364-446). mse_scale != 0 selects the row scale by the packer's MSE search
  * over seven clip factors on every fourth rotated element (tools/difflux2sample.cpp:1225-1259;
  * 256-wide ConvRot variants 2, 3, 5, 6 only); the stored scale is then the bf16-rounded one.
- * Input equalisation (:2967-2990) is a host-side column scaling applied before this call.
+ * input_scale (may be NULL) is the packer's input-equalisation vector, bf16 [columns]
+ * (:2967-2990: sqrt(column absmax / geometric mean of the column absmaxes), clamped to [0.5, 2]):
+ * every weight is divided by its column's entry in fp32 before the rotation (:3005-3014), and the
+ * activations are multiplied by the same vector at run time.
  */
-DIFB200_EXPORT int difb200_quantize_weight_rows(const void *weight, uint64_t rows, uint64_t columns,
-                                                int32_t implementation, int32_t mse_scale,
-                                                int8_t *codes, float *scales, void *stream);
+DIFB200_EXPORT int difb200_quantize_weight_rows(const void *weight, const void *input_scale, uint64_t rows,
+                                                uint64_t columns, int32_t implementation,
+                                                int32_t mse_scale, int8_t *codes, float *scales,
+                                                void *stream);
 
 /*
  * Opcode LinearInt8Scaled (68), optionally fused with the BiasAdd (10) and Gelu (49, tanh)

@@ -10,9 +10,9 @@
  * attention, so that function defines this repository's own numerical contract; its Q/K
  * codes and scales are the reference's (QuantizeInt8Rows, Direct) and it is additionally
  * compared, with a tolerance, against the reference's exact Attention. And the MSE scale
- * search of orc_quantize_weight_rows: it restates a function that the reference keeps in a
- * command-line tool's anonymous namespace, which no test of the reference exercises and no
- * library exports; without the search that entry is the pinned quantiser.
+ * search of orc_quantize_weight_rows with orc_weight_equalization: they restate functions that
+ * the reference keeps in a command-line tool's anonymous namespace, which no test of the
+ * reference exercises and no library exports; without them that entry is the pinned quantiser.
  *
  * Each function cites the reference file:line it follows (paths inside the reference
  * project). Build flags: -O3 without -march, so x86-64 never contracts a*b+c into an fma
@@ -123,6 +123,7 @@ typedef struct {
   int8_t *rcodes;
   float *rscales;
   int mse; /* weight rows: scale from the offline packer's MSE search */
+  const uint16_t *equalise; /* weight rows: bf16 [columns] divisor, or NULL */
 } quant_ctx;
 
 /* tools/difflux2sample.cpp:1225-1259 (choose_mse_int8_weight_scale): seven clip factors, the
@@ -190,6 +191,9 @@ static void quant_body(void *vctx, int64_t row_begin, int64_t row_end) {
           t[c0 + c] = bf2f(src[c]);
         c0 += part_widths[p];
       }
+      if (ctx->equalise) /* tools/difflux2sample.cpp:3005-3014: w / e, then the sign */
+        for (uint64_t c = 0; c < columns; ++c)
+          t[c] = t[c] / bf2f(ctx->equalise[c]);
       float maximum = 0.0F;
       if (convrot) {
         if (sgn)
@@ -280,15 +284,37 @@ ORC_EXPORT int orc_quantize_int8_rows(const uint16_t *const *parts,
   if (implementation != ORC_DIRECT && columns % group != 0U)
     return 1;
   quant_ctx ctx = {parts, part_widths, part_count, columns, implementation,
-                   clip,  codes,       scales,     rcodes,  rscales, 0};
+                   clip,  codes,       scales,     rcodes,  rscales, 0, NULL};
   parallel_for((int64_t)rows, quant_body, &ctx);
   return 0;
+}
+
+/* Input equalisation of the offline packer, tools/difflux2sample.cpp:2967-2990: per column the
+ * absmax over the rows, their geometric mean as the centre, sqrt(max / centre) clamped to
+ * [0.5, 2] and stored as bf16. Unpinned like the MSE search (same tool, same reason). */
+ORC_EXPORT void orc_weight_equalization(const uint16_t *weight, uint64_t rows,
+                                        uint64_t columns, uint16_t *out) {
+  float *maxima = (float *)calloc((size_t)columns, sizeof(float));
+  for (uint64_t r = 0; r < rows; ++r)
+    for (uint64_t c = 0; c < columns; ++c)
+      maxima[c] = fmaxf(maxima[c], fabsf(bf2f(weight[r * columns + c])));
+  double log_sum = 0.0;
+  for (uint64_t c = 0; c < columns; ++c)
+    log_sum += logf(fmaxf(maxima[c], 1.0e-30F));
+  const float center = (float)exp(log_sum / (double)columns);
+  for (uint64_t c = 0; c < columns; ++c) {
+    float v = sqrtf(maxima[c] / fmaxf(center, 1.0e-30F));
+    v = v < 0.5F ? 0.5F : (v > 2.0F ? 2.0F : v);
+    out[c] = f2bf(v);
+  }
+  free(maxima);
 }
 
 /* Weight-side packing of a bf16 [rows, columns] matrix, tools/difflux2sample.cpp:2994-3059
  * (clip 1, no residual); mse != 0 uses choose_mse_weight_scale. Without mse this is
  * orc_quantize_int8_rows on one part, which is pinned against the reference executor. */
-ORC_EXPORT int orc_quantize_weight_rows(const uint16_t *weight, uint64_t rows,
+ORC_EXPORT int orc_quantize_weight_rows(const uint16_t *weight,
+                                        const uint16_t *equalise, uint64_t rows,
                                         uint64_t columns, int implementation,
                                         int mse, int8_t *codes, float *scales) {
   if (implementation < ORC_H256 || implementation > ORC_H4096_F32_SIGNED)
@@ -302,7 +328,7 @@ ORC_EXPORT int orc_quantize_weight_rows(const uint16_t *weight, uint64_t rows,
   const uint16_t *parts[1] = {weight};
   const uint64_t widths[1] = {columns};
   quant_ctx ctx = {parts, widths, 1,     columns, implementation, 1.0F,
-                   codes, scales, NULL, NULL,    mse};
+                   codes, scales, NULL, NULL,    mse,     equalise};
   parallel_for((int64_t)rows, quant_body, &ctx);
   return 0;
 }

@@ -94,18 +94,31 @@ class _Orc:
             raise ValueError("illegal width for this ConvRot variant")
         return (codes, scales, rcodes, rscales) if residual else (codes, scales)
 
-    def quantize_weight_rows(self, weight: np.ndarray, implementation: int, mse: bool = False):
+    def quantize_weight_rows(self, weight: np.ndarray, implementation: int, mse: bool = False,
+                             equalise: Optional[np.ndarray] = None):
         weight = np.ascontiguousarray(weight, dtype=np.uint16)
         rows, columns = weight.shape
         codes = np.empty((rows, columns), np.int8)
         scales = np.empty(rows, np.float32)
+        if equalise is not None:
+            equalise = np.ascontiguousarray(equalise, dtype=np.uint16)
         self.lib.orc_quantize_weight_rows.restype = C.c_int
-        self.lib.orc_quantize_weight_rows.argtypes = [_pu16, C.c_uint64, C.c_uint64, C.c_int, C.c_int, _p8, _pf]
-        rc = self.lib.orc_quantize_weight_rows(_ptr(weight, _pu16), rows, columns, int(implementation),
-                                               1 if mse else 0, _ptr(codes, _p8), _ptr(scales, _pf))
+        self.lib.orc_quantize_weight_rows.argtypes = [_pu16, _pu16, C.c_uint64, C.c_uint64, C.c_int, C.c_int, _p8, _pf]
+        rc = self.lib.orc_quantize_weight_rows(_ptr(weight, _pu16), _ptr(equalise, _pu16), rows, columns,
+                                               int(implementation), 1 if mse else 0, _ptr(codes, _p8),
+                                               _ptr(scales, _pf))
         if rc != 0:
             raise ValueError("illegal width or variant for weight packing")
         return codes, scales
+
+    def weight_equalization(self, weight: np.ndarray) -> np.ndarray:
+        weight = np.ascontiguousarray(weight, dtype=np.uint16)
+        rows, columns = weight.shape
+        out = np.empty(columns, np.uint16)
+        self.lib.orc_weight_equalization.restype = None
+        self.lib.orc_weight_equalization.argtypes = [_pu16, C.c_uint64, C.c_uint64, _pu16]
+        self.lib.orc_weight_equalization(_ptr(weight, _pu16), rows, columns, _ptr(out, _pu16))
+        return out
 
     def linear_int8_scaled(self, x8, w8, row, col, want_acc=False):
         x8 = np.ascontiguousarray(x8, np.int8)

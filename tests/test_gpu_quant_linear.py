@@ -85,6 +85,34 @@ def test_weight_rows_with_mse_scale_bit_exact(ops, impl, N, K):
     ops.poll_status()
 
 
+@pytest.mark.parametrize("impl,mse", [(2, False), (3, True), (5, True), (6, False)])
+def test_weight_rows_with_input_equalization(ops, impl, mse):
+    """Input equalisation of the offline packer (reference tools/difflux2sample.cpp:2967-2990 for
+    the vector, :3005-3014 for its use): codes and scales bit-exact given the same vector; the
+    vector computed on the GPU within one bf16 ulp of the CPU restatement (libm's logf against
+    CUDA's)."""
+    import torch
+    rng = np.random.default_rng(77 + impl)
+    N, K = 48, 768
+    gains = np.exp(rng.standard_normal(K) * 0.8).astype(np.float32)  # uneven column magnitudes
+    w = ob.f32_to_bf16((rng.standard_normal((N, K)) * 0.02).astype(np.float32) * gains)
+    eq = ob.orc().weight_equalization(w)
+    dw = torch.from_numpy(w.view(np.int16)).cuda().view(torch.bfloat16)
+    got_eq = ops.weight_equalization(dw)
+    diff = np.abs(got_eq.view(torch.int16).cpu().numpy().astype(np.int32) - eq.view(np.int16).astype(np.int32))
+    assert diff.max() <= 1 and np.count_nonzero(diff) <= K // 50
+    assert ob.bf16_to_f32(eq).min() >= 0.5 and ob.bf16_to_f32(eq).max() <= 2.0 and len(np.unique(eq)) > 8
+    deq = torch.from_numpy(eq.view(np.int16)).cuda().view(torch.bfloat16)
+    want_codes, want_scales = ob.orc().quantize_weight_rows(w, impl, mse=mse, equalise=eq)
+    codes, scales = ops.quantize_weight_rows(dw, impl, mse_scale=mse, input_scale=deq)
+    torch.cuda.synchronize()
+    assert np.array_equal(scales.cpu().numpy().view(np.uint32), want_scales.view(np.uint32))
+    assert np.array_equal(codes.cpu().numpy(), want_codes)
+    plain_codes, _ = ob.orc().quantize_weight_rows(w, impl, mse=mse)
+    assert not np.array_equal(plain_codes, want_codes)  # the vector does change the packing
+    ops.poll_status()
+
+
 def _weights(rng, N, K, impl):
     wf = bf16_normal(rng, (N, K), 0.02)
     return ob.orc().quantize_int8_rows([wf], impl, 1.0)
