@@ -20,6 +20,7 @@
 // second, CTA-wide transpose across 16 groups for stages 4-5.
 #include "common.cuh"
 #include "glue.h"
+#include "ops.h"
 
 #include <cstdio>
 
@@ -42,6 +43,11 @@ struct QuantParams {
   float *rscales;
   uint32_t mse;   // weight rows: choose the row scale by the offline packer's MSE search
   const uint16_t *equalise; // weight rows: bf16 [columns], every element is divided by its entry first
+  // RmsNormModulate in front of the quantiser (explicit scale / shift layout), all bf16:
+  const uint16_t *norm_weight; // [columns] or nullptr
+  const uint16_t *norm_scale;  // [rows, columns]; nullptr = no prologue
+  const uint16_t *norm_shift;  // [rows, columns]
+  float norm_eps;
 };
 
 // Fixed Rademacher diagonal of the signed variants (reference cpu_executor.cpp:183-189).
@@ -295,6 +301,71 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
       fetch(row + (uint64_t)gridDim.x * rows_per_cta, na0, na1, nb0, nb1);
       uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      if (MSE && p.norm_scale != nullptr) {
+        // RmsNormModulate fused in front (reference cpu_executor.cpp:1241-1264 followed by the
+        // quantiser; the reference's own fused precedent is cuda_executor.cpp:5417-5466): the
+        // words are replaced by the bf16 result h the unfused op would have stored. The row's sum
+        // of squares meets per warp and then per row in a fixed order.
+        float xs[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xs[2 * i] = __uint_as_float(wa[i] << 16);
+          xs[2 * i + 1] = __uint_as_float(wa[i] & 0xffff0000u);
+          xs[16 + 2 * i] = __uint_as_float(wb[i] << 16);
+          xs[16 + 2 * i + 1] = __uint_as_float(wb[i] & 0xffff0000u);
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          ss = __fmaf_rn(xs[i], xs[i], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+          ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+        float *stat = red + parity * 2 * total_warps + total_warps;
+        if (lane == 0)
+          stat[warp] = ss;
+        row_barrier();
+        ss = 0.0f;
+        for (int w = 0; w < warps_per_row; ++w)
+          ss = __fadd_rn(ss, stat[slot * warps_per_row + w]);
+        const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)p.columns), p.norm_eps)));
+        const uint32_t col = group_a * 256u + 16u * a;
+        const uint64_t at = (row_ok ? row : 0) * (uint64_t)p.columns + col;
+        const uint4 one = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const bool act = g == 0 ? act_a : act_b;
+          const uint4 *wp = reinterpret_cast<const uint4 *>(p.norm_weight + col + 256u * g);
+          const uint4 *sp = reinterpret_cast<const uint4 *>(p.norm_scale + at + 256u * g);
+          const uint4 *hp = reinterpret_cast<const uint4 *>(p.norm_shift + at + 256u * g);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const uint4 wq = (act && p.norm_weight) ? __ldg(wp + half) : one;
+            const uint4 sq = act ? __ldg(sp + half) : zero, hq = act ? __ldg(hp + half) : zero;
+            const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w}, sw[4] = {sq.x, sq.y, sq.z, sq.w},
+                           hw[4] = {hq.x, hq.y, hq.z, hq.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int e = 16 * g + 8 * half + 2 * i;
+              float y[2];
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {
+                const float wv = __uint_as_float(k ? (ww[i] & 0xffff0000u) : (ww[i] << 16));
+                const float sv = __uint_as_float(k ? (sw[i] & 0xffff0000u) : (sw[i] << 16));
+                const float hv = __uint_as_float(k ? (hw[i] & 0xffff0000u) : (hw[i] << 16));
+                const float normalized = __fmul_rn(__fmul_rn(xs[e + k], inv), wv);
+                y[k] = __fadd_rn(__fmul_rn(normalized, __fadd_rn(1.0f, sv)), hv);
+              }
+              uint32_t packed;
+              asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(y[1]), "f"(y[0]));
+              if (g == 0)
+                wa[4 * half + i] = packed;
+              else
+                wb[4 * half + i] = packed;
+            }
+          }
+        }
+      }
       if (SIGNED) {
         const uint4 m0 = lds128(mask_addr), m1 = lds128(mask_addr + mask_step);
         const uint4 m2 = lds128(mask_addr + 2u * mask_step), m3 = lds128(mask_addr + 3u * mask_step);
@@ -718,7 +789,7 @@ int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
 
 template <bool SIGNED, bool F32, bool H4096>
 int launch_convrot(const QuantParams &p, cudaStream_t stream) {
-  if (p.mse || p.equalise) { // the weight-packing form of the kernel
+  if (p.mse || p.equalise || p.norm_scale) { // the form of the kernel with the rarely used extras
     if (H4096 || p.rcodes)
       return fail(kUnsupported, "QuantizeInt8Rows: weight packing (MSE scale, input equalisation) exists for "
                                 "the 256-wide variants without residual outputs");
@@ -733,7 +804,8 @@ int launch_convrot(const QuantParams &p, cudaStream_t stream) {
 int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, uint32_t part_count,
                        uint64_t rows, int implementation, float clip, const float *clip_device,
                        int8_t *codes, float *scales, int8_t *rcodes, float *rscales,
-                       cudaStream_t stream, bool mse_weight_scale, const void *equalise_bf16) {
+                       cudaStream_t stream, bool mse_weight_scale, const void *equalise_bf16,
+                       const NormPrologue *norm) {
   if (part_count == 0 || part_count > kMaxParts)
     return fail(kUnsupported, "QuantizeInt8Rows: 1..8 concatenated inputs are supported");
   if (!codes || !scales || (rcodes == nullptr) != (rscales == nullptr))
@@ -765,6 +837,19 @@ int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, ui
   p.rscales = rscales;
   p.mse = mse_weight_scale ? 1u : 0u;
   p.equalise = static_cast<const uint16_t *>(equalise_bf16);
+  if (norm) {
+    if (!norm->scale || !norm->shift)
+      return fail(kInvalidArgument, "QuantizeInt8Rows: norm prologue without scale / shift");
+    if (implementation < 2 || implementation == 4 || implementation == 7 || part_count != 1 || rcodes ||
+        ((reinterpret_cast<uintptr_t>(norm->scale) | reinterpret_cast<uintptr_t>(norm->shift) |
+          reinterpret_cast<uintptr_t>(norm->weight)) & 15))
+      return fail(kUnsupported, "QuantizeInt8Rows: the norm prologue needs one input, a 256-wide ConvRot variant, no "
+                                "residual outputs and 16-byte aligned pointers");
+    p.norm_weight = static_cast<const uint16_t *>(norm->weight);
+    p.norm_scale = static_cast<const uint16_t *>(norm->scale);
+    p.norm_shift = static_cast<const uint16_t *>(norm->shift);
+    p.norm_eps = norm->epsilon;
+  }
   if (rows == 0)
     return kOk;
   if ((mse_weight_scale || equalise_bf16) && (implementation == 1 || clip_device || part_count != 1))

@@ -12,10 +12,18 @@ struct DeviceStatus;
 
 const std::string &last_error();
 
+// RmsNormModulate (explicit scale / shift layout, bf16) computed in front of the quantiser in the
+// same kernel: weight [columns] or null, scale / shift [rows, columns].
+struct NormPrologue {
+  const void *weight, *scale, *shift;
+  float epsilon;
+};
+
 int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, uint32_t part_count,
                        uint64_t rows, int implementation, float clip, const float *clip_device,
                        int8_t *codes, float *scales, int8_t *rcodes, float *rscales,
-                       cudaStream_t stream, bool mse_weight_scale = false, const void *equalise_bf16 = nullptr);
+                       cudaStream_t stream, bool mse_weight_scale = false, const void *equalise_bf16 = nullptr,
+                       const NormPrologue *norm = nullptr);
 
 int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales,
                        const float *col_scales, const void *bias_bf16, uint32_t epilogue, uint64_t M,

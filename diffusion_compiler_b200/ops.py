@@ -75,6 +75,25 @@ def quantize_int8_rows(parts: Sequence[torch.Tensor], implementation: int = 2, c
     return (codes, scales, rcodes, rscales) if residual else (codes, scales)
 
 
+def rms_norm_modulate_quant(x: torch.Tensor, weight: Optional[torch.Tensor], scale: torch.Tensor,
+                            shift: torch.Tensor, epsilon: float = 1e-5, implementation: int = 2, clip: float = 1.0):
+    """RmsNormModulate (explicit scale / shift) + QuantizeInt8Rows in one kernel: bf16 [M, K] inputs
+    -> (codes i8 [M, K], row scales f32 [M]); the normalised tensor is never written."""
+    x = _require(x, torch.bfloat16, "x")
+    scale, shift = _require(scale, torch.bfloat16, "scale"), _require(shift, torch.bfloat16, "shift")
+    if weight is not None:
+        weight = _require(weight, torch.bfloat16, "weight")
+    M, K = x.shape
+    if scale.shape != x.shape or shift.shape != x.shape:
+        raise ValueError("scale and shift must have the shape of x")
+    codes = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scales = torch.empty((M,), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().difb200_rms_norm_modulate_quant(_ptr(x), _ptr(weight), _ptr(scale), _ptr(shift), M, K,
+                                                           epsilon, implementation, clip, _ptr(codes), _ptr(scales),
+                                                           _stream()))
+    return codes, scales
+
+
 def weight_equalization(weight: torch.Tensor) -> torch.Tensor:
     """The offline packer's input-equalisation vector for a bf16 [N, K] weight (reference
     tools/difflux2sample.cpp:2967-2990): sqrt(column absmax / geometric mean of the column

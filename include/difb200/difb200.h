@@ -62,6 +62,20 @@ DIFB200_EXPORT int difb200_quantize_int8_rows(const void *const *parts, const ui
                                               float *residual_scales, void *stream);
 
 /*
+ * RmsNormModulate (ExplicitScaleShift layout, src/runtime/cpu_executor.cpp:1241-1264) and
+ * QuantizeInt8Rows (a 256-wide ConvRot variant, static clip) in one kernel: the bf16 tensor between
+ * the two ops is never written. The reference runs them as two ops on its generic path and has a
+ * fused producer of its own for one model (src/runtime/cuda_executor.cpp:5417-5466). x, scale,
+ * shift: bf16 [rows, columns]; weight: bf16 [columns] or NULL. The row statistic is summed in
+ * parallel, as in difb200_rms_norm_modulate (a different order than there, so the two forms agree
+ * to the last bit of the statistic, not beyond).
+ */
+DIFB200_EXPORT int difb200_rms_norm_modulate_quant(const void *x, const void *weight, const void *scale,
+                                                   const void *shift, uint64_t rows, uint64_t columns,
+                                                   float epsilon, int32_t implementation, float clip,
+                                                   int8_t *codes, float *row_scales, void *stream);
+
+/*
  * Weight-side packing: the bf16 weight matrix [rows = N, columns = K] quantised row by row with
  * the same rotation and quantiser as the activations (clip 1), giving the I8 weight and the
  * per-output-channel scales that LinearInt8Scaled binds as constants. This is the encoder of the
