@@ -55,6 +55,8 @@ struct Step {
   uint64_t rope_out_seq = 0, rope_out_start = 0;
   // Attention whose q / k arrive already quantised in the scratch buffer
   bool q_quantised = false, k_quantised = false;
+  // QuantizeInt8Rows that also runs the RmsNormModulate (explicit scale / shift) producing its input
+  int norm_step = -1;
 };
 
 struct Executable {
@@ -190,6 +192,29 @@ void plan(Executable &exe) {
                                  "as QuantizeInt8Rows + LinearInt8Scaled"};
     }
   }
+
+  // ---- RmsNormModulate (explicit scale / shift) -> QuantizeInt8Rows (256-wide ConvRot) ----
+  // One kernel normalises, modulates, rotates and quantises; the normalised tensor is not
+  // materialised. The row statistic is summed in another order than by the separate norm kernel
+  // (both are parallel sums; the reference sums sequentially, cpu_executor.cpp:1241-1264), so a
+  // few codes in 10^5 can move by one. DIFB200_NORM_FUSION=0 keeps the two kernels.
+  const char *norm_fusion = std::getenv("DIFB200_NORM_FUSION");
+  if (!(norm_fusion && norm_fusion[0] == '0'))
+    for (size_t n = 0; n < p.ops.size(); ++n) {
+      const ir::Op &norm = p.ops[n];
+      size_t qi = 0;
+      if (norm.opcode != ir::RmsNormModulate || norm.u64(ir::ModulationLayout, 1) == 2 ||
+          !sole_consumer(norm.out[0], ir::QuantizeInt8Rows, qi))
+        continue;
+      const ir::Op &quant = p.ops[qi];
+      const ir::Tensor &x = *p.tensor(norm.in[0]);
+      const uint64_t impl = quant.u64(ir::Implementation, 1);
+      if (quant.in.size() != 1 || quant.out.size() != 2 || x.dtype != ir::BF16 || x.dims.size() != 2 ||
+          x.last() % 256 != 0 || !(impl == 2 || impl == 3 || impl == 5 || impl == 6))
+        continue;
+      exe.steps[qi].norm_step = (int)n;
+      exe.steps[n].skip = true;
+    }
 
   // ---- QkNormPartialRope and its neighbours (all on 128-wide bf16 heads) ----
   // DIFB200_ROPE_FUSION=0 keeps the ops separate (same bits, more traffic): a test aid.
@@ -331,6 +356,11 @@ void allocate(Executable &exe) {
         needed[(size_t)st.rope_source] = true;
         continue;
       }
+      if (st.op->opcode == ir::QuantizeInt8Rows && st.norm_step >= 0) { // reads the norm's inputs instead
+        for (auto nid : exe.steps[(size_t)st.norm_step].op->in)
+          needed[(size_t)p.index_of(nid)] = true;
+        continue;
+      }
       needed[(size_t)p.index_of(id)] = true;
     }
     if (st.op->opcode == ir::LinearInt8Scaled) {
@@ -429,6 +459,19 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
     const ir::Op &op = *st.op;
     switch (op.opcode) {
     case ir::QuantizeInt8Rows: {
+      if (st.norm_step >= 0) {
+        const ir::Op &norm = *exe.steps[(size_t)st.norm_step].op;
+        const bool weighted = norm.in.size() == 4;
+        const NormPrologue prologue{weighted ? D(norm.in[1]) : nullptr, D(norm.in[weighted ? 2 : 1]),
+                                    D(norm.in[weighted ? 3 : 2]), (float)norm.f64(ir::Epsilon, 1.0e-5)};
+        const void *part = D(norm.in[0]);
+        const uint64_t width = T(norm.in[0]).last();
+        require(quantize_int8_rows(&part, &width, 1, T(norm.in[0]).rows(), (int)op.u64(ir::Implementation, 1),
+                                   (float)op.f64(ir::Scale, 1.0), nullptr, static_cast<int8_t *>(D(op.out[0])),
+                                   static_cast<float *>(D(op.out[1])), nullptr, nullptr, s, false, nullptr,
+                                   &prologue));
+        break;
+      }
       const bool dynamic = T(op.in.back()).dtype == ir::F32;
       const size_t n_data = op.in.size() - (dynamic ? 1 : 0);
       const void *parts[8];

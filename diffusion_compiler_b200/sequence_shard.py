@@ -139,10 +139,8 @@ class VideoBlock:
         stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         p = lambda t: C.c_void_p(t.data_ptr())
         new = lambda *shape: torch.empty(shape, dtype=torch.bfloat16, device=self.device)
-        h = new(S_loc, hid)
-        self._glue("difb200_rms_norm_modulate", p(x), p(self.norm1), p(mods[0]), p(mods[1]), p(h), 2, S_loc, hid,
-                   1e-5, stream)
-        codes, scales = ops.quantize_int8_rows([h], H256)
+        # norm + modulate + ConvRot quantisation in one kernel: the normalised tensor is never written
+        codes, scales = ops.rms_norm_modulate_quant(x, self.norm1, mods[0], mods[1], 1e-5, H256)
         v_local = gb.local(gb.v)[:S_loc]
         ops.linear_int8_scaled(codes, *self._w("v", scales), out=v_local.view(S_loc, H * D))  # into the gather buffer
         if on_v_ready is not None:
@@ -186,10 +184,8 @@ class VideoBlock:
         o = ops.w8a8_linear(attn.view(S_loc, H * D), *self.lin["o"])
         r1 = new(S_loc, hid)
         self._glue("difb200_residual_gate", p(x), p(o), p(mods[2]), p(r1), 2, S_loc, hid, S_loc, stream)
-        h2 = new(S_loc, hid)
-        self._glue("difb200_rms_norm_modulate", p(r1), p(self.norm2), p(mods[3]), p(mods[4]), p(h2), 2, S_loc, hid,
-                   1e-5, stream)
-        fc1 = ops.w8a8_linear(h2, *self.lin["fc1"])
+        codes2, scales2 = ops.rms_norm_modulate_quant(r1, self.norm2, mods[3], mods[4], 1e-5, H256)
+        fc1 = ops.linear_int8_scaled(codes2, *self._w("fc1", scales2))
         act = new(S_loc, self.ffn)
         self._glue("difb200_swiglu", p(fc1), p(act), 2, S_loc, self.ffn, 2 * self.ffn, 0, 0, stream)
         fc2 = ops.w8a8_linear(act, *self.lin["fc2"])

@@ -78,6 +78,28 @@ def test_plugin_rope_fusions_keep_the_bits(monkeypatch):
         assert np.array_equal(results[0][ids[key]], results[1][ids[key]])
 
 
+def test_plugin_norm_quant_fusion_saves_the_normalised_tensor_and_stays_in_the_bar(monkeypatch):
+    """RmsNormModulate -> QuantizeInt8Rows runs as one kernel in the plugin: the normalised tensors
+    are not resident any more, and the block output stays well inside the path's bf16 bar against
+    the plan with separate kernels (the row statistic is summed in another order, so single codes
+    may move by one)."""
+    from diffusion_compiler_b200 import plugin
+    rng = np.random.default_rng(12)
+    S, hidden, heads, dim, ffn, rotary = 400, 512, 4, 128, 1024, 96
+    p, ids, consts, inputs = blocks.synth_video_block(rng, S, hidden, heads, dim, ffn, rotary, _cpu_quantize)
+    results, resident = [], []
+    for fusion in ("1", "0"):
+        monkeypatch.setenv("DIFB200_NORM_FUSION", fusion)
+        ex = plugin.PluginExecutor(0)
+        prepared = ex.prepare(p, consts)
+        got, _ = prepared.run(inputs)
+        resident.append(int(prepared.compile_telemetry.resident_bytes))
+        ex.close()
+        results.append(ob.bf16_to_f32(got[ids["out"]]))
+    assert resident[1] - resident[0] >= 2 * S * hidden * 2  # two [S, hidden] bf16 tensors fewer
+    assert rel_l2(results[0], results[1]) <= 5e-4 and cosine(results[0], results[1]) >= 0.99999
+
+
 @pytest.mark.skipif(not ob.ref_available(), reason="reference build (oracle/_ref) not present")
 def test_mmdit_double_stream_block_through_plugin_matches_reference_executor():
     from diffusion_compiler_b200 import plugin
