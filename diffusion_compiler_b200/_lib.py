@@ -33,6 +33,8 @@ def lib() -> C.CDLL:
                                                  vp, vp, vp, vp, vp]
         L.difb200_rms_norm_modulate_quant.restype = C.c_int
         L.difb200_rms_norm_modulate_quant.argtypes = [vp, vp, vp, vp, u64, u64, f32, i32, f32, vp, vp, vp]
+        L.difb200_layer_norm_modulate_quant.restype = C.c_int
+        L.difb200_layer_norm_modulate_quant.argtypes = [vp, vp, vp, vp, vp, u64, u64, u64, f32, i32, f32, vp, vp, vp]
         L.difb200_quantize_weight_rows.restype = C.c_int
         L.difb200_quantize_weight_rows.argtypes = [vp, vp, u64, u64, i32, i32, vp, vp, vp]
         L.difb200_linear_int8_scaled.restype = C.c_int

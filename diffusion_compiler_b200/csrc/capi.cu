@@ -106,6 +106,21 @@ int difb200_rms_norm_modulate_quant(const void *x, const void *weight, const voi
                             static_cast<cudaStream_t>(stream), false, nullptr, &norm);
 }
 
+int difb200_layer_norm_modulate_quant(const void *x, const void *weight, const void *bias, const void *scale,
+                                      const void *shift, uint64_t rows, uint64_t columns, uint64_t rows_per_modulation,
+                                      float epsilon, int32_t implementation, float clip, int8_t *codes,
+                                      float *row_scales, void *stream) {
+  if (!x || !weight || !bias || !scale || !shift)
+    return fail(kInvalidArgument, "difb200_layer_norm_modulate_quant: null pointer");
+  if (rows_per_modulation == 0 || rows % rows_per_modulation != 0)
+    return fail(kInvalidArgument, "difb200_layer_norm_modulate_quant: rows must be a multiple of rows_per_modulation");
+  const void *parts[1] = {x};
+  const uint64_t widths[1] = {columns};
+  const NormPrologue norm{weight, scale, shift, epsilon, bias, rows_per_modulation};
+  return quantize_int8_rows(parts, widths, 1, rows, implementation, clip, nullptr, codes, row_scales, nullptr, nullptr,
+                            static_cast<cudaStream_t>(stream), false, nullptr, &norm);
+}
+
 int difb200_quantize_weight_rows(const void *weight, const void *input_scale, uint64_t rows, uint64_t columns,
                                  int32_t implementation, int32_t mse_scale, int8_t *codes, float *scales,
                                  void *stream) {

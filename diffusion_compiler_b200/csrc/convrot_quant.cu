@@ -48,6 +48,8 @@ struct QuantParams {
   const uint16_t *norm_scale;  // [rows, columns]; nullptr = no prologue
   const uint16_t *norm_shift;  // [rows, columns]
   float norm_eps;
+  const uint16_t *norm_bias;   // [columns]: LayerNormModulate (mean removed, weight and bias); nullptr = RMS
+  uint64_t norm_rows_per_mod;  // rows that share one row of scale / shift
 };
 
 // Fixed Rademacher diagonal of the signed variants (reference cpu_executor.cpp:183-189).
@@ -314,23 +316,45 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
           xs[16 + 2 * i] = __uint_as_float(wb[i] << 16);
           xs[16 + 2 * i + 1] = __uint_as_float(wb[i] & 0xffff0000u);
         }
-        float ss = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          ss = __fmaf_rn(xs[i], xs[i], ss);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-          ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+        const bool layer = p.norm_bias != nullptr;
         float *stat = red + parity * 2 * total_warps + total_warps;
-        if (lane == 0)
-          stat[warp] = ss;
-        row_barrier();
-        ss = 0.0f;
-        for (int w = 0; w < warps_per_row; ++w)
-          ss = __fadd_rn(ss, stat[slot * warps_per_row + w]);
+        auto row_sum = [&](float v, float *slots) { // warp tree, then the row's warps in order
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1)
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+          if (lane == 0)
+            slots[warp] = v;
+          row_barrier();
+          v = 0.0f;
+          for (int w = 0; w < warps_per_row; ++w)
+            v = __fadd_rn(v, slots[slot * warps_per_row + w]);
+          return v;
+        };
+        float mean = 0.0f, ss = 0.0f;
+        if (layer) {
+          // LayerNormModulate (cpu_executor.cpp:1108-1148): mean, then the centred second moment.
+          // The second sum uses the other parity's slots: they are free until the next row, which
+          // every warp of this row reaches only after the barriers of the maxima exchange below.
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            mean = __fadd_rn(mean, xs[i]);
+          mean = __fdiv_rn(row_sum(mean, stat), (float)p.columns);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float d = __fsub_rn(xs[i], mean);
+            if (i < 16 ? act_a : act_b)
+              ss = __fmaf_rn(d, d, ss);
+          }
+          ss = row_sum(ss, red + (parity ^ 1u) * 2 * total_warps + total_warps);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            ss = __fmaf_rn(xs[i], xs[i], ss);
+          ss = row_sum(ss, stat);
+        }
         const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)p.columns), p.norm_eps)));
         const uint32_t col = group_a * 256u + 16u * a;
-        const uint64_t at = (row_ok ? row : 0) * (uint64_t)p.columns + col;
+        const uint64_t at = ((row_ok ? row : 0) / p.norm_rows_per_mod) * (uint64_t)p.columns + col;
         const uint4 one = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
@@ -338,8 +362,11 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
           const uint4 *wp = reinterpret_cast<const uint4 *>(p.norm_weight + col + 256u * g);
           const uint4 *sp = reinterpret_cast<const uint4 *>(p.norm_scale + at + 256u * g);
           const uint4 *hp = reinterpret_cast<const uint4 *>(p.norm_shift + at + 256u * g);
+          const uint4 *bp = reinterpret_cast<const uint4 *>(p.norm_bias + col + 256u * g);
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
+            const uint4 bq = (act && layer) ? __ldg(bp + half) : zero;
+            const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
             const uint4 wq = (act && p.norm_weight) ? __ldg(wp + half) : one;
             const uint4 sq = act ? __ldg(sp + half) : zero, hq = act ? __ldg(hp + half) : zero;
             const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w}, sw[4] = {sq.x, sq.y, sq.z, sq.w},
@@ -353,8 +380,16 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
                 const float wv = __uint_as_float(k ? (ww[i] & 0xffff0000u) : (ww[i] << 16));
                 const float sv = __uint_as_float(k ? (sw[i] & 0xffff0000u) : (sw[i] << 16));
                 const float hv = __uint_as_float(k ? (hw[i] & 0xffff0000u) : (hw[i] << 16));
-                const float normalized = __fmul_rn(__fmul_rn(xs[e + k], inv), wv);
-                y[k] = __fadd_rn(__fmul_rn(normalized, __fadd_rn(1.0f, sv)), hv);
+                if (layer) { // intermediate bf16 roundings of the reference's LayerNormModulate
+                  const float bv = __uint_as_float(k ? (bw[i] & 0xffff0000u) : (bw[i] << 16));
+                  const float normalized = round_bf16(
+                      __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(xs[e + k], mean), inv), wv), bv));
+                  const float one_plus = round_bf16(__fadd_rn(1.0f, sv));
+                  y[k] = __fadd_rn(round_bf16(__fmul_rn(normalized, one_plus)), hv);
+                } else {
+                  const float normalized = __fmul_rn(__fmul_rn(xs[e + k], inv), wv);
+                  y[k] = __fadd_rn(__fmul_rn(normalized, __fadd_rn(1.0f, sv)), hv);
+                }
               }
               uint32_t packed;
               asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(y[1]), "f"(y[0]));
@@ -842,13 +877,16 @@ int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, ui
       return fail(kInvalidArgument, "QuantizeInt8Rows: norm prologue without scale / shift");
     if (implementation < 2 || implementation == 4 || implementation == 7 || part_count != 1 || rcodes ||
         ((reinterpret_cast<uintptr_t>(norm->scale) | reinterpret_cast<uintptr_t>(norm->shift) |
-          reinterpret_cast<uintptr_t>(norm->weight)) & 15))
+          reinterpret_cast<uintptr_t>(norm->weight) | reinterpret_cast<uintptr_t>(norm->bias)) & 15) ||
+        norm->rows_per_modulation == 0 || (norm->bias && !norm->weight))
       return fail(kUnsupported, "QuantizeInt8Rows: the norm prologue needs one input, a 256-wide ConvRot variant, no "
                                 "residual outputs and 16-byte aligned pointers");
     p.norm_weight = static_cast<const uint16_t *>(norm->weight);
     p.norm_scale = static_cast<const uint16_t *>(norm->scale);
     p.norm_shift = static_cast<const uint16_t *>(norm->shift);
     p.norm_eps = norm->epsilon;
+    p.norm_bias = static_cast<const uint16_t *>(norm->bias);
+    p.norm_rows_per_mod = norm->rows_per_modulation;
   }
   if (rows == 0)
     return kOk;

@@ -12,11 +12,14 @@ struct DeviceStatus;
 
 const std::string &last_error();
 
-// RmsNormModulate (explicit scale / shift layout, bf16) computed in front of the quantiser in the
-// same kernel: weight [columns] or null, scale / shift [rows, columns].
+// RmsNormModulate (explicit scale / shift layout) or, with a bias, LayerNormModulate computed in
+// front of the quantiser in the same kernel, all bf16: weight [columns] or null, bias [columns]
+// or null (null = RMS statistic), scale / shift [rows / rows_per_modulation, columns].
 struct NormPrologue {
   const void *weight, *scale, *shift;
   float epsilon;
+  const void *bias = nullptr;
+  uint64_t rows_per_modulation = 1;
 };
 
 int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, uint32_t part_count,

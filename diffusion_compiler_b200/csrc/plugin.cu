@@ -193,7 +193,7 @@ void plan(Executable &exe) {
     }
   }
 
-  // ---- RmsNormModulate (explicit scale / shift) -> QuantizeInt8Rows (256-wide ConvRot) ----
+  // ---- RmsNormModulate (explicit scale / shift) or LayerNormModulate -> QuantizeInt8Rows (256-wide ConvRot) ----
   // One kernel normalises, modulates, rotates and quantises; the normalised tensor is not
   // materialised. The row statistic is summed in another order than by the separate norm kernel
   // (both are parallel sums; the reference sums sequentially, cpu_executor.cpp:1241-1264), so a
@@ -203,13 +203,17 @@ void plan(Executable &exe) {
     for (size_t n = 0; n < p.ops.size(); ++n) {
       const ir::Op &norm = p.ops[n];
       size_t qi = 0;
-      if (norm.opcode != ir::RmsNormModulate || norm.u64(ir::ModulationLayout, 1) == 2 ||
-          !sole_consumer(norm.out[0], ir::QuantizeInt8Rows, qi))
+      const bool rms = norm.opcode == ir::RmsNormModulate && norm.u64(ir::ModulationLayout, 1) != 2;
+      const bool layer = norm.opcode == ir::LayerNormModulate && norm.in.size() == 5;
+      if (!(rms || layer) || !sole_consumer(norm.out[0], ir::QuantizeInt8Rows, qi))
         continue;
       const ir::Op &quant = p.ops[qi];
       const ir::Tensor &x = *p.tensor(norm.in[0]);
       const uint64_t impl = quant.u64(ir::Implementation, 1);
-      if (quant.in.size() != 1 || quant.out.size() != 2 || x.dtype != ir::BF16 || x.dims.size() != 2 ||
+      bool all_bf16 = true;
+      for (auto id : norm.in)
+        all_bf16 = all_bf16 && p.tensor(id)->dtype == ir::BF16;
+      if (quant.in.size() != 1 || quant.out.size() != 2 || !all_bf16 || (rms && x.dims.size() != 2) ||
           x.last() % 256 != 0 || !(impl == 2 || impl == 3 || impl == 5 || impl == 6))
         continue;
       exe.steps[qi].norm_step = (int)n;
@@ -462,8 +466,11 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
       if (st.norm_step >= 0) {
         const ir::Op &norm = *exe.steps[(size_t)st.norm_step].op;
         const bool weighted = norm.in.size() == 4;
-        const NormPrologue prologue{weighted ? D(norm.in[1]) : nullptr, D(norm.in[weighted ? 2 : 1]),
-                                    D(norm.in[weighted ? 3 : 2]), (float)norm.f64(ir::Epsilon, 1.0e-5)};
+        NormPrologue prologue{weighted ? D(norm.in[1]) : nullptr, D(norm.in[weighted ? 2 : 1]),
+                              D(norm.in[weighted ? 3 : 2]), (float)norm.f64(ir::Epsilon, 1.0e-5)};
+        if (norm.opcode == ir::LayerNormModulate)
+          prologue = NormPrologue{D(norm.in[1]), D(norm.in[3]), D(norm.in[4]), (float)norm.f64(ir::Epsilon, 1.0e-5),
+                                  D(norm.in[2]), T(norm.in[0]).rows() / T(norm.in[3]).rows()};
         const void *part = D(norm.in[0]);
         const uint64_t width = T(norm.in[0]).last();
         require(quantize_int8_rows(&part, &width, 1, T(norm.in[0]).rows(), (int)op.u64(ir::Implementation, 1),

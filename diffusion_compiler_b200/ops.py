@@ -94,6 +94,26 @@ def rms_norm_modulate_quant(x: torch.Tensor, weight: Optional[torch.Tensor], sca
     return codes, scales
 
 
+def layer_norm_modulate_quant(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, scale: torch.Tensor,
+                              shift: torch.Tensor, epsilon: float = 1e-5, implementation: int = 2,
+                              clip: float = 1.0):
+    """LayerNormModulate + QuantizeInt8Rows in one kernel: x bf16 [M, K], weight / bias bf16 [K],
+    scale / shift bf16 [M / r, K] (r rows of x share one modulation row) -> (codes i8 [M, K], row
+    scales f32 [M])."""
+    x = _require(x, torch.bfloat16, "x")
+    weight, bias = _require(weight, torch.bfloat16, "weight"), _require(bias, torch.bfloat16, "bias")
+    scale, shift = _require(scale, torch.bfloat16, "scale"), _require(shift, torch.bfloat16, "shift")
+    M, K = x.shape
+    if scale.shape != shift.shape or scale.shape[-1] != K or M % scale.shape[0] != 0:
+        raise ValueError("scale and shift must be [M / r, K]")
+    codes = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scales = torch.empty((M,), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().difb200_layer_norm_modulate_quant(_ptr(x), _ptr(weight), _ptr(bias), _ptr(scale), _ptr(shift),
+                                                             M, K, M // scale.shape[0], epsilon, implementation, clip,
+                                                             _ptr(codes), _ptr(scales), _stream()))
+    return codes, scales
+
+
 def weight_equalization(weight: torch.Tensor) -> torch.Tensor:
     """The offline packer's input-equalisation vector for a bf16 [N, K] weight (reference
     tools/difflux2sample.cpp:2967-2990): sqrt(column absmax / geometric mean of the column

@@ -76,6 +76,20 @@ DIFB200_EXPORT int difb200_rms_norm_modulate_quant(const void *x, const void *we
                                                    int8_t *codes, float *row_scales, void *stream);
 
 /*
+ * LayerNormModulate (src/runtime/cpu_executor.cpp:1108-1148: affine layer norm, then
+ * (1 + scale) * h + shift with the reference's intermediate bf16 roundings) and QuantizeInt8Rows
+ * (a 256-wide ConvRot variant, static clip) in one kernel. x: bf16 [rows, columns]; weight, bias:
+ * bf16 [columns]; scale, shift: bf16 [rows / rows_per_modulation, columns] (one modulation row per
+ * batch item). Mean and centred second moment are parallel sums, as in
+ * difb200_layer_norm_modulate.
+ */
+DIFB200_EXPORT int difb200_layer_norm_modulate_quant(const void *x, const void *weight, const void *bias,
+                                                     const void *scale, const void *shift, uint64_t rows,
+                                                     uint64_t columns, uint64_t rows_per_modulation,
+                                                     float epsilon, int32_t implementation, float clip,
+                                                     int8_t *codes, float *row_scales, void *stream);
+
+/*
  * Weight-side packing: the bf16 weight matrix [rows = N, columns = K] quantised row by row with
  * the same rotation and quantiser as the activations (clip 1), giving the I8 weight and the
  * per-output-channel scales that LinearInt8Scaled binds as constants. This is the encoder of the

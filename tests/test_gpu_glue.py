@@ -95,6 +95,46 @@ def test_layer_norm_modulate():
     _one_ulp(got, want, o)
 
 
+def test_layer_norm_modulate_quant_fused_in_the_plugin(monkeypatch):
+    """LayerNormModulate -> QuantizeInt8Rows, which the plugin's planner runs as one kernel, against
+    the reference executor's two ops and against the plugin's own two kernels: under 0.5 % of the
+    codes differ from the reference's, never by more than 1, scales within 1 %; against the two
+    kernels of this library a few codes in 10^5 at most."""
+    from diffusion_compiler_b200 import plugin
+    d, p = _program()
+    rng = np.random.default_rng(31)
+    x = p.add_tensor(d.DType.BF16, [2, S, HIDDEN], d.Role.Input)
+    w = p.add_tensor(d.DType.BF16, [HIDDEN], d.Role.Constant)
+    bias = p.add_tensor(d.DType.BF16, [HIDDEN], d.Role.Constant)
+    scale = p.add_tensor(d.DType.BF16, [2, 1, HIDDEN], d.Role.Input)
+    shift = p.add_tensor(d.DType.BF16, [2, 1, HIDDEN], d.Role.Input)
+    h = p.add_tensor(d.DType.BF16, [2, S, HIDDEN])
+    codes = p.add_tensor(d.DType.I8, [2, S, HIDDEN], d.Role.Output)
+    scales = p.add_tensor(d.DType.F32, [2 * S], d.Role.Output)
+    p.add_op(d.Opcode.LayerNormModulate, [x, w, bias, scale, shift], [h],
+             [d.Attribute.f64(d.AttrKey.Epsilon, 1e-6), d.Attribute.u64(d.AttrKey.BlockSize, 128)])
+    p.add_op(d.Opcode.QuantizeInt8Rows, [h], [codes, scales],
+             [d.Attribute.u64(d.AttrKey.BlockSize, 256), d.Attribute.u64(d.AttrKey.Implementation, 2)])
+    consts = {w: _bf(rng, [HIDDEN]), bias: _bf(rng, [HIDDEN], 0.1)}
+    inputs = {x: _bf(rng, [2, S, HIDDEN]), scale: _bf(rng, [2, 1, HIDDEN], 0.1), shift: _bf(rng, [2, 1, HIDDEN], 0.1)}
+    want, _ = ob.ref().run(p, {**consts, **inputs})
+    runs, resident = [], []
+    for fusion in ("1", "0"):
+        monkeypatch.setenv("DIFB200_NORM_FUSION", fusion)
+        ex = plugin.PluginExecutor(0)
+        prepared = ex.prepare(p, consts)
+        got, _ = prepared.run(inputs)
+        resident.append(int(prepared.compile_telemetry.resident_bytes))
+        ex.close()
+        runs.append(got)
+    assert resident[1] - resident[0] >= 2 * S * HIDDEN * 2  # the normalised tensor is not resident when fused
+    gc, wc = runs[0][codes].astype(np.int32), want[codes].astype(np.int32)
+    assert np.abs(gc - wc).max() <= 1 and np.mean(gc != wc) < 5e-3, (np.abs(gc - wc).max(), np.mean(gc != wc))
+    assert np.allclose(runs[0][scales], want[scales], rtol=1e-2)
+    own = runs[1][codes].astype(np.int32)
+    assert np.abs(gc - own).max() <= 1 and np.mean(gc != own) < 1e-3, np.mean(gc != own)
+
+
 def test_qk_norm_partial_rope():
     d, p = _program()
     rng = np.random.default_rng(4)
