@@ -204,7 +204,12 @@ void plan(Executable &exe) {
       const ir::Op &norm = p.ops[n];
       size_t qi = 0;
       const bool rms = norm.opcode == ir::RmsNormModulate && norm.u64(ir::ModulationLayout, 1) != 2;
-      const bool layer = norm.opcode == ir::LayerNormModulate && norm.in.size() == 5;
+      // LayerNormModulate has two row reductions and three more roundings per element: in the
+      // instruction-bound quantiser that costs more than the saved tensor above a few thousand
+      // rows (measured at 3072 columns: 45 -> 29 us at 1024 rows, 78 -> 85 us at 8192), so only
+      // short tensors are fused.
+      const bool layer = norm.opcode == ir::LayerNormModulate && norm.in.size() == 5 &&
+                         p.tensor(norm.in[0])->rows() <= 2048;
       if (!(rms || layer) || !sole_consumer(norm.out[0], ir::QuantizeInt8Rows, qi))
         continue;
       const ir::Op &quant = p.ops[qi];
