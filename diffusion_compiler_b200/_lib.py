@@ -28,6 +28,11 @@ def lib() -> C.CDLL:
         L.difb200_last_error.restype = C.c_char_p
         L.difb200_version.restype = C.c_int
         L.difb200_poll_status.restype = C.c_int
+        L.difb200_set_wait_limit_ns.restype = None
+        L.difb200_set_wait_limit_ns.argtypes = [u64]
+        L.difb200_test_withhold_gemm_load.restype = None
+        L.difb200_test_withhold_gemm_load.argtypes = [u32]
+        L.difb200_selftest_host.restype = C.c_int
         L.difb200_quantize_int8_rows.restype = C.c_int
         L.difb200_quantize_int8_rows.argtypes = [C.POINTER(vp), C.POINTER(u64), u32, u64, i32, f32, vp,
                                                  vp, vp, vp, vp, vp]

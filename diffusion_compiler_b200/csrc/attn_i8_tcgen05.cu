@@ -60,6 +60,7 @@ struct AttnParams {
   uint16_t *out;         // [B,S,H,128] bf16
   uint32_t B, Sq, Sk, H, KV, S_pad; // Sq query tokens, Sk key tokens (S_pad = Sk rounded up to 128)
   float scale_log2e;     // scale * log2(e)
+  unsigned long long wait_ns; // limit of every bounded wait
   DeviceStatus *status;
 };
 
@@ -156,6 +157,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   volatile uint32_t *abort_ptr = slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned long long wait_ns = p.wait_ns;
   const uint32_t q_blocks = (p.Sq + 255u) / 256u;
   const uint32_t qb = blockIdx.x % q_blocks;
   const uint32_t head = (blockIdx.x / q_blocks) % p.H;
@@ -225,7 +227,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t k_dst = stage_addr + s * kStageBytes, v_dst = k_dst + kKBytes,
                        t_dst = v_dst + kVBytes;
         const int32_t key0 = (int32_t)(i * kTile);
-        if (!ptx::mbar_wait_warp(k_empty + 8 * s, phase ^ 1u, abort_ptr)) {
+        if (!ptx::mbar_wait_warp(k_empty + 8 * s, phase ^ 1u, abort_ptr, wait_ns)) {
           give_up(0, i);
           break;
         }
@@ -233,7 +235,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           ptx::mbar_expect_tx(k_full + 8 * s, kKBytes);
           ptx::tma_load_4d(k_dst, &map_k, k_full + 8 * s, 0, (int32_t)kvh, key0, (int32_t)batch);
         }
-        if (!ptx::mbar_wait_warp(v_empty + 8 * s, phase ^ 1u, abort_ptr)) {
+        if (!ptx::mbar_wait_warp(v_empty + 8 * s, phase ^ 1u, abort_ptr, wait_ns)) {
           give_up(1, i);
           break;
         }
@@ -283,11 +285,11 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                           idesc_pv, k != 0 ? 1u : (g != 0u ? 1u : 0u));
         ptx::mma_commit(pv_done + 8 * t);
       };
-      if (!ptx::mbar_wait_warp(q_full, 0, abort_ptr)) {
+      if (!ptx::mbar_wait_warp(q_full, 0, abort_ptr, wait_ns)) {
         give_up(2, 0);
         ok = false;
       }
-      if (ok && (!ptx::mbar_wait_warp(k_full, 0, abort_ptr) || !ptx::mbar_wait_warp(v_full, 0, abort_ptr))) {
+      if (ok && (!ptx::mbar_wait_warp(k_full, 0, abort_ptr, wait_ns) || !ptx::mbar_wait_warp(v_full, 0, abort_ptr, wait_ns))) {
         give_up(2, 1);
         ok = false;
       }
@@ -310,14 +312,14 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // warps take the completion of that Q.K^T as their signal for the table, and this
         // stage's V was awaited the same way one stage earlier)
         if (h == 0u && more &&
-            (!ptx::mbar_wait_warp(k_full + 8 * st_n, phase_n, abort_ptr) ||
-             !ptx::mbar_wait_warp(v_full + 8 * st_n, phase_n, abort_ptr))) {
+            (!ptx::mbar_wait_warp(k_full + 8 * st_n, phase_n, abort_ptr, wait_ns) ||
+             !ptx::mbar_wait_warp(v_full + 8 * st_n, phase_n, abort_ptr, wait_ns))) {
           give_up(2, 5);
           break;
         }
 #pragma unroll
         for (uint32_t t = 0; t < 2; ++t) {
-          if (!ptx::mbar_wait_warp(p_full + 16 * t + 8 * h, use & 1u, abort_ptr)) {
+          if (!ptx::mbar_wait_warp(p_full + 16 * t + 8 * h, use & 1u, abort_ptr, wait_ns)) {
             give_up(2, 3 + t);
             ok = false;
             break;
@@ -364,7 +366,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1)
         kmax = fmaxf(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
-      if (!ptx::mbar_wait(q_full, 0)) {
+      if (!ptx::mbar_wait(q_full, 0, wait_ns)) {
         if (lane == 0)
           report(p.status, 9 + t, 0);
         *abort_ptr = 1;
@@ -396,7 +398,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       // The scores of this step. The stage's key table needs no wait of its own: it arrives on
       // the barrier of the V tile, which the MMA warp has seen complete before it issued the
       // Q.K^T whose completion is awaited here.
-      if (!ptx::mbar_wait_abortable(s_full + 16 * t + 8 * h, use & 1u, abort_ptr)) {
+      if (!ptx::mbar_wait_abortable(s_full + 16 * t + 8 * h, use & 1u, abort_ptr, wait_ns)) {
         if (!*abort_ptr && lane == 0)
           report(p.status, 3 + t, g);
         *abort_ptr = 1;
@@ -457,7 +459,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (__any_sync(0xffffffffu, grow)) {
           // rescale O (and l) by an exact power of two; needs P.V of the previous step finished
           // (grow implies an earlier step with a valid key, so g > 0)
-          if (!ptx::mbar_wait(pv_done + 8 * t, (g - 1u) & 1u)) {
+          if (!ptx::mbar_wait(pv_done + 8 * t, (g - 1u) & 1u, wait_ns)) {
             if (lane == 0)
               report(p.status, 5 + t, g);
             *abort_ptr = 1;
@@ -506,7 +508,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       ptx::mbar_arrive(p_full + 16 * t + 8 * h);
     }
     if (alive && n_kv > 0) {
-      if (!ptx::mbar_wait(o_done + 8 * t, 0)) {
+      if (!ptx::mbar_wait(o_done + 8 * t, 0, wait_ns)) {
         if (lane == 0)
           report(p.status, 7 + t, 0);
         *abort_ptr = 1;
@@ -605,12 +607,12 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
                                    CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
-  static std::once_flag once;
-  static cudaError_t attr_rc = cudaSuccess;
-  std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(attn_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-  });
-  if (int rc = check_cuda(attr_rc, "cudaFuncSetAttribute(attn_i8_kernel)"))
+  static const char attr_key = 0; // the opt-in belongs to the function in one context: once per device
+  if (int rc = current_device_once(&attr_key, [](void *, int *) -> int {
+        return check_cuda(cudaFuncSetAttribute(attn_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)kSmemBytes),
+                          "cudaFuncSetAttribute(attn_i8_kernel)");
+      }, nullptr, nullptr))
     return rc;
 
   float2 *table = static_cast<float2 *>(scratch);
@@ -636,6 +638,7 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
   p.KV = (uint32_t)KV;
   p.S_pad = s_pad;
   p.scale_log2e = scale * 1.4426950408889634f;
+  p.wait_ns = wait_limit_ns();
   p.status = status;
   const uint64_t grid = B * H * ((Sq + 255) / 256);
   attn_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);

@@ -83,6 +83,52 @@ int difb200_poll_status(void) {
   return poll_device_status("difb200_poll_status");
 }
 
+void difb200_set_wait_limit_ns(uint64_t nanoseconds) { set_wait_limit_ns(nanoseconds); }
+
+void difb200_test_withhold_gemm_load(uint32_t k_block) { withhold_next_gemm_load(k_block); }
+
+int difb200_selftest_host(void) {
+  // per_device_once: one initialisation per (key, device ordinal), failures are not cached
+  static const char key_a = 0, key_b = 0;
+  struct Counter {
+    int calls = 0, fail_first = 0;
+  };
+  auto init = [](void *arg, int *value) -> int {
+    Counter *c = static_cast<Counter *>(arg);
+    ++c->calls;
+    if (c->fail_first && c->calls == 1)
+      return kExecutionError;
+    *value = 100 + c->calls;
+    return kOk;
+  };
+  Counter a, b;
+  int v = 0;
+  // ordinals far above any real device, so nothing a real launch cached is touched
+  if (per_device_once(&key_a, 1000, init, &a, &v) != kOk || v != 101 || a.calls != 1)
+    return fail(kInternalError, "selftest: first use on a device did not initialise");
+  if (per_device_once(&key_a, 1000, init, &a, &v) != kOk || v != 101 || a.calls != 1)
+    return fail(kInternalError, "selftest: second use on the same device initialised again");
+  if (per_device_once(&key_a, 1001, init, &a, &v) != kOk || v != 102 || a.calls != 2)
+    return fail(kInternalError, "selftest: another device did not get its own initialisation");
+  b.fail_first = 1;
+  if (per_device_once(&key_b, 1000, init, &b, &v) == kOk)
+    return fail(kInternalError, "selftest: a failing initialisation was reported as success");
+  if (per_device_once(&key_b, 1000, init, &b, &v) != kOk || v != 102 || b.calls != 2)
+    return fail(kInternalError, "selftest: a failed initialisation was cached");
+  // the wait limit and the withheld-load test aid are plain host state
+  const unsigned long long before = wait_limit_ns();
+  set_wait_limit_ns(12345);
+  const bool limit_ok = wait_limit_ns() == 12345;
+  set_wait_limit_ns(0);
+  const bool default_ok = wait_limit_ns() == 1500ull * 1000ull * 1000ull;
+  set_wait_limit_ns(before);
+  withhold_next_gemm_load(3);
+  const bool armed = take_withheld_gemm_load() == 3u, disarmed = take_withheld_gemm_load() == 0xffffffffu;
+  if (!limit_ok || !default_ok || !armed || !disarmed)
+    return fail(kInternalError, "selftest: wait limit or withheld-load state misbehaves");
+  return kOk;
+}
+
 int difb200_quantize_int8_rows(const void *const *parts, const uint64_t *part_widths,
                                uint32_t part_count, uint64_t rows, int32_t implementation,
                                float clip, const float *clip_device, int8_t *codes, float *scales,

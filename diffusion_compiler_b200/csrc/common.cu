@@ -2,8 +2,11 @@
 // the per-device status words that kernels with bounded waits report through.
 #include "common.cuh"
 
+#include <atomic>
+#include <map>
 #include <mutex>
 #include <unordered_map>
+#include <utility>
 
 namespace difb200 {
 
@@ -12,7 +15,43 @@ thread_local std::string g_last_error;
 std::mutex g_mutex;
 std::unordered_map<int, DeviceStatus *> g_status_words;
 std::unordered_map<int, int> g_sm_counts;
+std::mutex g_once_mutex;
+std::map<std::pair<const void *, int>, int> g_once_values;
 } // namespace
+
+namespace {
+std::atomic<unsigned long long> g_wait_limit_ns{1500ull * 1000ull * 1000ull};
+std::atomic<uint32_t> g_withhold_kb{0xffffffffu};
+} // namespace
+
+unsigned long long wait_limit_ns() { return g_wait_limit_ns.load(); }
+void set_wait_limit_ns(unsigned long long ns) { g_wait_limit_ns.store(ns ? ns : 1500ull * 1000ull * 1000ull); }
+void withhold_next_gemm_load(uint32_t k_block) { g_withhold_kb.store(k_block); }
+uint32_t take_withheld_gemm_load() { return g_withhold_kb.exchange(0xffffffffu); }
+
+int per_device_once(const void *key, int device, int (*init)(void *arg, int *value), void *arg, int *value) {
+  std::lock_guard<std::mutex> lock(g_once_mutex);
+  const auto it = g_once_values.find({key, device});
+  if (it != g_once_values.end()) {
+    if (value)
+      *value = it->second;
+    return kOk;
+  }
+  int v = 0;
+  if (int rc = init(arg, &v))
+    return rc;
+  g_once_values[{key, device}] = v;
+  if (value)
+    *value = v;
+  return kOk;
+}
+
+int current_device_once(const void *key, int (*init)(void *arg, int *value), void *arg, int *value) {
+  int device = 0;
+  if (int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice"))
+    return rc;
+  return per_device_once(key, device, init, arg, value);
+}
 
 void set_last_error(const std::string &text) { g_last_error = text; }
 const std::string &last_error() { return g_last_error; }

@@ -26,6 +26,12 @@ int fail(int status, const std::string &text);
 int check_cuda(cudaError_t code, const char *what);
 int sm_count();
 
+// One-time set-up that is per device, not per process (function attributes and occupancy
+// figures belong to a context): `init` runs the first time `key` is seen with `device` and its
+// result value is cached; a failing `init` is not cached. Thread-safe.
+int per_device_once(const void *key, int device, int (*init)(void *arg, int *value), void *arg, int *value);
+int current_device_once(const void *key, int (*init)(void *arg, int *value), void *arg, int *value);
+
 // Device-side status words written by kernels whose bounded waits ran out. Index 0 is a
 // sticky flag, 1..3 describe where (kernel id, role, iteration).
 struct DeviceStatus {
@@ -34,6 +40,13 @@ struct DeviceStatus {
   unsigned int role;
   unsigned int detail;
 };
+// Limit of the kernels' bounded waits in nanoseconds (default 1.5 s), read at every launch.
+unsigned long long wait_limit_ns();
+void set_wait_limit_ns(unsigned long long ns); // 0 restores the default
+// Test aid for the give-up path: the next LinearInt8Scaled launch leaves out the loads of one
+// k-block. take_...() returns that k-block (0xffffffff = none) and disarms.
+void withhold_next_gemm_load(uint32_t k_block);
+uint32_t take_withheld_gemm_load();
 DeviceStatus *device_status_words();      // per-device, allocated once
 int poll_device_status(const char *what); // copies back, clears, maps to kExecutionError
 

@@ -79,7 +79,8 @@ __device__ __forceinline__ void bfly(uint64_t &x0, uint64_t &x1, uint64_t &x2, u
 __device__ __forceinline__ float absmax2(float m, uint64_t v) {
   float lo, hi;
   unpack2(v, lo, hi);
-  return fmaxf(fmaxf(m, fabsf(lo)), fabsf(hi));
+  asm("max.f32 %0, %0, %1, %2;" : "+f"(m) : "f"(fabsf(lo)), "f"(fabsf(hi))); // one three-input maximum
+  return m;
 }
 
 // Correctly rounded fp32 quotient a/b from y = RN(1/b): two Markstein refinements.
@@ -90,14 +91,13 @@ __device__ __forceinline__ uint64_t div2_exact(uint64_t a, uint64_t y, uint64_t 
   r = fma2(negb, q, a);
   return fma2(r, y, q);
 }
-// a and b are bf16 values (8 significant bits): no quotient of two such numbers lies within
-// 2^-17 (relative) of a bf16 rounding boundary unless it is an exact tie, and one refinement
-// reproduces an exactly representable quotient, so this is enough for bf16(a/b).
-__device__ __forceinline__ uint64_t div2_bf16(uint64_t a, uint64_t y, uint64_t negb) {
-  const uint64_t q = mul2(a, y);
-  const uint64_t r = fma2(negb, q, a);
-  return fma2(r, y, q);
-}
+// bf16(a / b) for bf16 values a and b (8 significant bits each, integers V and S in [128, 255]
+// times powers of two) needs no refinement at all: a rounding boundary of the quotient is M / 2^k
+// with M odd in [257, 511], and |V / S - M / 2^k| = |2^k V - M S| / (S 2^k) is either 0 -- which
+// would need the odd M > 255 to divide V <= 255, impossible -- or at least 2^-17 of the quotient,
+// while a * RN(1 / b) is within 2^-23 of it. So the plain product rounds to the same bf16 value
+// as the IEEE quotient, ties cannot occur, and a zero numerator gives zero.
+__device__ __forceinline__ uint64_t div2_bf16(uint64_t a, uint64_t y) { return mul2(a, y); }
 
 __device__ __forceinline__ uint64_t round_bf16_2(uint64_t v) {
   float lo, hi;
@@ -122,7 +122,7 @@ __device__ __forceinline__ void quantize_pair(uint64_t value, uint64_t y, uint64
     c0 = max(sat_s8(q0), -127);
     c1 = max(sat_s8(q1), -127);
   } else {
-    unpack2(round_bf16_2(div2_bf16(round_bf16_2(value), y, negb)), q0, q1);
+    unpack2(round_bf16_2(div2_bf16(round_bf16_2(value), y)), q0, q1);
     c0 = sat_s8(q0);
     c1 = sat_s8(q1);
   }

@@ -15,7 +15,7 @@
 // Two forms of the same kernel (template parameter CTAS):
 //   CTAS = 1: 128x256 tile per CTA, cta_group::1, 4 stages of 48 KB.
 //   CTAS = 2: a CTA pair (cluster of 2) computes a 256x256 tile with cta_group::2 MMAs: each CTA
-//             stages its 128 rows of A and only its 128 rows (half) of the B tile, 6 stages of
+//             stages its 128 rows of A and only its 128 rows (half) of the B tile, 5 stages of
 //             32 KB. This halves the B bytes every SM moves through shared memory per MAC -- at
 //             8192 INT8 MACs/clk/SM the 128x256 single-CTA tile needs 48 KB written plus 48 KB read
 //             per 512 clocks, which is what bounds the CTAS = 1 form. The leader CTA (cluster rank
@@ -112,8 +112,9 @@ struct GemmParams {
   int32_t *acc_out;
   uint32_t M, N, K;
   uint32_t epilogue;
-  uint32_t debug;     // measurement aid: 1 = issue no MMAs, 2 = issue no TMA loads (results are garbage)
   uint32_t tma_store; // 1: outputs leave through TMA stores (needs N % 8 == 0, aligned out)
+  uint32_t withhold_kb; // test aid: the loads of this k-block are never issued (0xffffffff = none)
+  unsigned long long wait_ns; // limit of every bounded wait
   DeviceStatus *status;
 };
 
@@ -162,7 +163,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t staging_base = smem_base + kStages * kStageBytes;
   const uint32_t scale_base = staging_base + Cfg<CTAS>::kStagingBytes;
   const uint32_t bar_base = scale_base + kScaleBytes;
-  // barrier layout (8 bytes each): full[4], empty[4], tmem_full[2], tmem_empty[2]; then a word
+  // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]; then a word
   // for the TMEM base address and a word for the abort flag.
   const uint32_t full_bar = bar_base, empty_bar = bar_base + 8 * kStages;
   const uint32_t tfull_bar = bar_base + 16 * kStages, tempty_bar = tfull_bar + 16;
@@ -172,7 +173,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile uint32_t *abort_ptr = slot_ptr + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool no_mma = (p.debug & 1u) != 0, no_tma = (p.debug & 2u) != 0; // measurement aids
+  const unsigned long long wait_ns = p.wait_ns;
   const uint32_t tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + kBN - 1) / kBN;
   const uint32_t num_tiles = tiles_m * tiles_n;
   const uint32_t k_blocks = (p.K + kBK - 1) / kBK;
@@ -227,7 +228,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int32_t m0 = (int32_t)((tile / tiles_n) * kTileM + cta_rank * kBM);
       const int32_t n0 = (int32_t)((tile % tiles_n) * kBN + cta_rank * Cfg<CTAS>::kBRows);
       for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-        if (!ptx::mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1u, abort_ptr)) {
+        if (!ptx::mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1u, abort_ptr, wait_ns)) {
           give_up(0, kb);
           ok = false;
           break;
@@ -235,11 +236,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
         const uint32_t bar = full_bar + 8 * stage;
         const int32_t k0 = (int32_t)(kb * kBK);
-        if (ptx::elect_one()) {
-          if (no_tma) {
-            if (cta_rank == 0)
-              ptx::mbar_arrive(bar);
-          } else if (CTAS == 2) {
+        if (kb == p.withhold_kb) {
+          // test aid: the bytes are announced but never loaded, so the consumer's wait on this
+          // stage runs out and the kernel leaves through its give-up path
+          if (cta_rank == 0 && ptx::elect_one())
+            ptx::mbar_expect_tx(bar, CTAS * kStageBytes);
+        } else if (ptx::elect_one()) {
+          if (CTAS == 2) {
             // A pair counts the bytes of both CTAs on the leader's barrier: the leader expects
             // them all, the peer's loads complete their bytes there (cta_group::2 form of the
             // load) and the peer itself never arrives.
@@ -278,14 +281,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       };
       for (uint32_t tile = unit; tile < num_tiles && ok; tile += units, ++local) {
         const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
-        if (!ptx::mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_ptr)) {
+        if (!ptx::mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_ptr, wait_ns)) {
           give_up(1, 0xffffu);
           break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-          if (!ptx::mbar_wait_warp(full_bar + 8 * stage, phase, abort_ptr)) {
+          if (!ptx::mbar_wait_warp(full_bar + 8 * stage, phase, abort_ptr, wait_ns)) {
             give_up(1, kb);
             ok = false;
             break;
@@ -295,17 +298,15 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint64_t a_desc = desc0 + (uint64_t)((stage * kStageBytes) >> 4);
           const uint64_t b_desc = a_desc + (uint64_t)(kABytes >> 4);
           if (ptx::elect_one()) {
-            if (!no_mma) {
 #pragma unroll
-              for (int k = 0; k < kBK / kUmmaK; ++k) {
-                const uint32_t accumulate = k != 0 ? 1u : (kb != 0u ? 1u : 0u);
-                if (CTAS == 2)
-                  ptx::mma_i8_ss_pair(d_tmem, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
-                                      idesc, accumulate);
-                else
-                  ptx::mma_i8_ss(d_tmem, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
-                                 idesc, accumulate);
-              }
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              const uint32_t accumulate = k != 0 ? 1u : (kb != 0u ? 1u : 0u);
+              if (CTAS == 2)
+                ptx::mma_i8_ss_pair(d_tmem, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
+                                    idesc, accumulate);
+              else
+                ptx::mma_i8_ss(d_tmem, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
+                               idesc, accumulate);
             }
             commit(empty_bar + 8 * stage); // frees the smem stage when these MMAs retire
           }
@@ -341,7 +342,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bs[c] = ((p.epilogue & kEpiBias) && n < p.N) ? bf16_bits_to_f32(__ldg(p.bias + n)) : 0.0f;
       }
       __syncwarp();
-      if (*abort_ptr || !ptx::mbar_wait(tfull_bar + 8 * acc, acc_phase)) {
+      if (*abort_ptr || !ptx::mbar_wait(tfull_bar + 8 * acc, acc_phase, wait_ns)) {
         if (!*abort_ptr && lane == 0)
           report_timeout(p.status, 2, tile);
         *abort_ptr = 1;
@@ -506,16 +507,18 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
       return rc;
   }
 
-  static std::once_flag once;
-  static cudaError_t attr_rc = cudaSuccess;
-  std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(gemm_i8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)smem_bytes<1>());
-    if (attr_rc == cudaSuccess)
-      attr_rc = cudaFuncSetAttribute(gemm_i8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem_bytes<2>());
-  });
-  if (int rc = check_cuda(attr_rc, "cudaFuncSetAttribute(gemm_i8_kernel)"))
+  // The dynamic shared-memory opt-in is an attribute of the function in one context, so it is
+  // made once per device (a process may hold plugin contexts on several GPUs).
+  static const char attr_key = 0;
+  if (int rc = current_device_once(&attr_key, [](void *, int *) -> int {
+        if (int rc = check_cuda(cudaFuncSetAttribute(gemm_i8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     (int)smem_bytes<1>()),
+                                "cudaFuncSetAttribute(gemm_i8_kernel<1>)"))
+          return rc;
+        return check_cuda(cudaFuncSetAttribute(gemm_i8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem_bytes<2>()),
+                          "cudaFuncSetAttribute(gemm_i8_kernel<2>)");
+      }, nullptr, nullptr))
     return rc;
 
   GemmParams p{};
@@ -529,8 +532,8 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   p.K = (uint32_t)K;
   p.epilogue = epilogue;
   p.tma_store = tma_store ? 1u : 0u;
-  if (const char *dbg = std::getenv("DIFB200_GEMM_DEBUG"))
-    p.debug = (uint32_t)std::strtoul(dbg, nullptr, 0);
+  p.withhold_kb = take_withheld_gemm_load();
+  p.wait_ns = wait_limit_ns();
   p.status = status;
   if (ctas == 2) {
     cudaLaunchConfig_t config{};
@@ -546,15 +549,19 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
     config.attrs = &attr;
     config.numAttrs = 1;
     // The kernel is persistent: launch exactly as many CTA pairs as can be resident at once
-    // (SM pairs are formed inside a GPC, so this can be fewer than SMs / 2).
-    static int resident_pairs = 0;
-    if (resident_pairs == 0) {
-      int n = 0;
-      if (int rc = check_cuda(cudaOccupancyMaxActiveClusters(&n, gemm_i8_kernel<2>, &config),
-                              "cudaOccupancyMaxActiveClusters"))
-        return rc;
-      resident_pairs = n > 0 ? n : 1;
-    }
+    // (SM pairs are formed inside a GPC, so this can be fewer than SMs / 2); a per-device figure.
+    static const char pairs_key = 0;
+    int resident_pairs = 0;
+    if (int rc = current_device_once(&pairs_key, [](void *arg, int *value) -> int {
+          int n = 0;
+          if (int rc = check_cuda(cudaOccupancyMaxActiveClusters(&n, gemm_i8_kernel<2>,
+                                                                 static_cast<cudaLaunchConfig_t *>(arg)),
+                                  "cudaOccupancyMaxActiveClusters"))
+            return rc;
+          *value = n > 0 ? n : 1;
+          return kOk;
+        }, &config, &resident_pairs))
+      return rc;
     uint64_t pairs = (uint64_t)resident_pairs;
     if (pairs > pair_tiles)
       pairs = pair_tiles;
@@ -566,21 +573,6 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   uint64_t grid = (uint64_t)sm_count();
   if (grid > tiles)
     grid = tiles;
-  if (std::getenv("DIFB200_GEMM_CLUSTER1")) { // measurement aid: single-CTA form launched as clusters of 2
-    cudaLaunchConfig_t config{};
-    config.gridDim = dim3((unsigned)(grid & ~1ull));
-    config.blockDim = dim3(kThreads);
-    config.dynamicSmemBytes = smem_bytes<1>();
-    config.stream = stream;
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    config.attrs = &attr;
-    config.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&config, gemm_i8_kernel<1>, map_a, map_b, map_c, p), "launch");
-  }
   gemm_i8_kernel<1><<<(unsigned)grid, kThreads, smem_bytes<1>(), stream>>>(map_a, map_b, map_c, p);
   return check_cuda(cudaGetLastError(), "gemm_i8_kernel launch");
 }

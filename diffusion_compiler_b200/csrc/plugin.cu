@@ -61,6 +61,7 @@ struct Step {
 
 struct Executable {
   Context *ctx = nullptr;
+  int device = 0;                   // ordinal of ctx's device (kept here: the destructor must not read ctx)
   ir::Program program;
   std::vector<void *> dev;          // device buffer per tensor (nullptr when never materialised)
   std::vector<uint8_t> owned;       // 0 where dev[i] aliases another tensor's buffer (Reshape)
@@ -72,8 +73,7 @@ struct Executable {
   bool constants_bound = false;     // v2: uploaded at compile
   std::vector<cudaEvent_t> uploaded, produced; // per tensor, made on first use by an overlapped execute
   ~Executable() {
-    if (ctx)
-      cudaSetDevice(ctx->device);
+    cudaSetDevice(device);
     for (cudaEvent_t e : uploaded)
       if (e)
         cudaEventDestroy(e);
@@ -87,6 +87,16 @@ struct Executable {
       cudaFree(attn_scratch);
     if (flag)
       cudaFree(flag);
+  }
+};
+
+struct EventPair { // two CUDA events that do not outlive their scope
+  cudaEvent_t a = nullptr, b = nullptr;
+  ~EventPair() {
+    if (a)
+      cudaEventDestroy(a);
+    if (b)
+      cudaEventDestroy(b);
   }
 };
 
@@ -810,14 +820,16 @@ dif_backend_status compile_common(dif_backend_context context, const uint8_t *di
       throw PluginError{1, "compile: null argument"};
     *executable = nullptr;
     require_cuda(cudaSetDevice(ctx->device), "cudaSetDevice");
-    cudaEvent_t e0, e1;
-    require_cuda(cudaEventCreate(&e0), "cudaEventCreate");
-    require_cuda(cudaEventCreate(&e1), "cudaEventCreate");
+    EventPair events; // destroyed on every way out, a failed compile included
+    require_cuda(cudaEventCreate(&events.a), "cudaEventCreate");
+    require_cuda(cudaEventCreate(&events.b), "cudaEventCreate");
+    const cudaEvent_t e0 = events.a, e1 = events.b;
     cudaEventRecord(e0, ctx->stream);
     size_t free_before = 0, total = 0;
     cudaMemGetInfo(&free_before, &total);
     auto exe = std::make_unique<Executable>();
     exe->ctx = ctx;
+    exe->device = ctx->device;
     std::string text;
     if (int rc = ir::decode(diffir, size, exe->program, text))
       throw PluginError{rc == 2 ? 2 : 4, "DiffIR: " + text};
@@ -843,8 +855,6 @@ dif_backend_status compile_common(dif_backend_context context, const uint8_t *di
     cudaEventSynchronize(e1);
     float ms = 0.0f;
     cudaEventElapsedTime(&ms, e0, e1);
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
     if (telemetry) {
       telemetry->preparation_milliseconds = ms;
       telemetry->resident_bytes = exe->resident_bytes;
@@ -915,15 +925,7 @@ dif_backend_status execute(dif_backend_executable executable, const dif_backend_
                                      cudaMemcpyDeviceToHost, stream),
                      "cudaMemcpyAsync(device to host)");
     };
-    struct Events { // timing pair, destroyed on every way out
-      cudaEvent_t a = nullptr, b = nullptr;
-      ~Events() {
-        if (a)
-          cudaEventDestroy(a);
-        if (b)
-          cudaEventDestroy(b);
-      }
-    } events;
+    EventPair events; // timing pair, destroyed on every way out
     require_cuda(cudaEventCreate(&events.a), "cudaEventCreate");
     require_cuda(cudaEventCreate(&events.b), "cudaEventCreate");
     const cudaEvent_t e0 = events.a, e1 = events.b;

@@ -38,9 +38,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kWaitNanoseconds of wall time (the global nanosecond timer is
-// read every 256 polls), far beyond any legitimate wait in these kernels, so that a protocol
-// error ends in a reported status within seconds instead of a hang.
+// Bounded wait: gives up after `limit_ns` of wall time (the global nanosecond timer is read
+// every 256 polls). The limit is a kernel parameter taken from wait_limit_ns() at launch; its
+// default, kWaitNanoseconds, is far beyond any legitimate wait in these kernels, so that a
+// protocol error ends in a reported status within seconds instead of a hang.
 constexpr unsigned long long kWaitNanoseconds = 1500ull * 1000ull * 1000ull;
 __device__ __forceinline__ unsigned long long global_timer() {
   unsigned long long t;
@@ -58,7 +59,7 @@ __device__ __forceinline__ bool elect_one() {
                : "=r"(elected));
   return elected != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
   for (int i = 0; i < 256; ++i)
     if (mbar_try_wait(bar, parity))
       return true;
@@ -67,13 +68,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity))
         return true;
-    if (global_timer() - start > kWaitNanoseconds)
+    if (global_timer() - start > limit_ns)
       return false;
   }
 }
 // Per-thread wait whose common case is a single try_wait; `abort_flag` (shared memory, set by
 // any role of the CTA that gave up) ends it early.
-__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                    unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity))
     return true;
   for (int i = 0; i < 512; ++i)
@@ -84,7 +86,7 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parit
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity))
         return true;
-    if (*abort_flag || global_timer() - start > kWaitNanoseconds)
+    if (*abort_flag || global_timer() - start > limit_ns)
       return false;
   }
 }
@@ -92,7 +94,8 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parit
 // the loop around it keeps uniform control flow and its state can live in uniform registers.
 // The common case is one try_wait and one vote. `abort_flag` (shared memory, set by any role of
 // the CTA that gave up) ends the wait early.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                               unsigned long long limit_ns) {
   if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity)))
     return true;
   bool ok = false;
@@ -103,7 +106,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     for (;;) {
       for (int i = 0; i < 256 && !ok; ++i)
         ok = mbar_try_wait(bar, parity);
-      if (ok || *abort_flag || global_timer() - start > kWaitNanoseconds)
+      if (ok || *abort_flag || global_timer() - start > limit_ns)
         break;
     }
   }

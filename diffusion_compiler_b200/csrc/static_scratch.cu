@@ -10,8 +10,15 @@
 // scales and the status words of the GEMM's bounded waits) in a fixed array that is part of
 // the library image.
 //
-// Cost and limits: every GPU that loads libdifb200.so holds kStaticScratchBytes (40 MiB) of
-// device memory from load until the process exits, whether or not this entry point is used.
+// Cost and limits: every GPU on which the library's device code is loaded holds
+// kStaticScratchBytes (40 MiB) of device memory until the process exits, whether or not this
+// entry point is used. With CUDA's default lazy module loading that memory is taken when the
+// module is first needed on a device, which for a host that only uses this entry point is its
+// first call there (with CUDA_MODULE_LOADING=EAGER it is taken when the library is loaded). A
+// host that wants every allocation behind it before it starts serving therefore makes one call
+// with M = 0 per device at start-up: that call resolves the array's address, launches nothing
+// and returns 0. The address is cached per device ordinal for the life of the process; after a
+// cudaDeviceReset the cache is stale and this entry point must not be used again in that process.
 // A call needs 256 + roundup(4*M, 256) + M*K bytes of it and is rejected with status 2 and a
 // clear message when that exceeds the array. All calls share the one array and it keeps what
 // the last call left there, so two calls whose kernels may overlap on the GPU (different
@@ -80,10 +87,13 @@ extern "C" int difb200_w8a8_linear_static(const void *x, const int8_t *w, const 
     if (int rc = check_cuda(cudaMemcpy(&host, base, sizeof(host), cudaMemcpyDeviceToHost),
                             "cudaMemcpy(status words)"))
       return rc;
-    if (host.flag != 0)
+    if (host.flag != 0) {
+      // clear the sticky words, so that the caller can go on after having seen the error once
+      cudaMemset(base, 0, sizeof(DeviceStatus));
       return fail(kExecutionError, "difb200_w8a8_linear_static: a bounded device-side wait ran out in "
                                    "the previous call (role " + std::to_string(host.role) + ", detail " +
                                    std::to_string(host.detail) + ")");
+    }
   }
   if (M == 0 || N == 0)
     return kOk;

@@ -62,6 +62,7 @@ class Opcode(IntEnum):
     QkNormPartialRope = 7
     Attention = 8
     BiasAdd = 10
+    SiLU = 16
     RmsNorm = 17
     Fill = 18
     Cast = 21
@@ -69,6 +70,7 @@ class Opcode(IntEnum):
     AffineLastDim = 29
     LayerNorm = 30
     Gelu = 49
+    Sigmoid = 50
     Reshape = 51
     BroadcastTo = 52
     Slice = 53

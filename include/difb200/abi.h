@@ -3,7 +3,7 @@
  * libdifb200.so. This header restates the interface of the reference's
  * include/dif/backend/abi.h (structure layouts, enum values and symbol names have to be
  * identical for the reference's loader, src/backend/plugin.cpp:60-117, to drive this library);
- * tests/test_abi_layout.py checks every size and offset against the reference header.
+ * tests/test_abi_and_symbols.py checks every size and offset against the reference header.
  *
  * Contract (reference abi.h:121-126, plugin.cpp:119-283):
  *   create(device_ordinal)            -> context (one CUDA device, one stream)
@@ -19,6 +19,8 @@
  *                                        copies Output-role tensors device->host
  *   errors                            -> status code + NUL-terminated text in error->data
  * All pointers in tensor views are host pointers borrowed for the duration of the call.
+ * Lifetimes: destroy every executable before the context it was compiled in (the reference's
+ * host does, src/backend/plugin.cpp:96-99,186-191); an executable runs on its context's streams.
  */
 #ifndef DIFB200_ABI_H
 #define DIFB200_ABI_H

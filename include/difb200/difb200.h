@@ -41,6 +41,28 @@ DIFB200_EXPORT int difb200_version(void);
 DIFB200_EXPORT int difb200_poll_status(void);
 
 /*
+ * Limit, in nanoseconds of wall time, after which a bounded device-side wait gives up (default
+ * 1.5 s; 0 restores the default). Read at every kernel launch of this process. A kernel whose
+ * wait ran out frees what it holds, returns, and leaves status 5 for difb200_poll_status (the
+ * plugin's execute reports it as DIF_BACKEND_EXECUTION_ERROR); the context stays usable.
+ */
+DIFB200_EXPORT void difb200_set_wait_limit_ns(uint64_t nanoseconds);
+
+/*
+ * Test aid, not for production use: the next difb200_linear_int8_scaled launch announces but
+ * never issues the loads of k-block `k_block` (K / 128 blocks per tile), so that the wait on
+ * that stage runs out and the give-up path can be exercised with a short wait limit. The
+ * result of that launch is undefined. Disarms itself after one launch.
+ */
+DIFB200_EXPORT void difb200_test_withhold_gemm_load(uint32_t k_block);
+
+/*
+ * Host-only self-check of the library's per-device bookkeeping (one-time set-up keyed by device
+ * ordinal, wait-limit state). Touches no GPU; returns 0 when the invariants hold.
+ */
+DIFB200_EXPORT int difb200_selftest_host(void);
+
+/*
  * Opcode QuantizeInt8Rows (67). Replaces the reference CPU op
  * src/runtime/cpu_executor.cpp:124-307 and its generated CUDA kernel
  * src/compiler/compiler.cpp:635-845 (semantics: include/dif/ir/ir.hpp:123-134,285-293;
@@ -225,9 +247,15 @@ DIFB200_EXPORT int difb200_w8a8_linear(const void *x, const int8_t *w, const flo
  * for hosts that planned their device memory up front or must not trigger an allocation while
  * they run a layer. A call needs 256 + roundup(4*M, 256) + M*K bytes; larger problems are
  * rejected with status 2. The first call on a device resolves the array's address (make that
- * first call outside any stream capture). All calls share the array: calls that can overlap on
- * the GPU race, so keep them on one stream or order them. check_previous != 0 first
- * synchronises `stream` and returns status 5 if a bounded wait ran out in the previous call.
+ * first call outside any stream capture); under CUDA's default lazy module loading it is also
+ * the moment the 40 MiB are taken on that device, so a host that wants no allocation while it
+ * serves calls once with M = 0 per device at start-up (nothing is launched, 0 is returned). The
+ * address is cached per device for the life of the process: do not use this entry point after a
+ * cudaDeviceReset. All calls share the array: calls that can overlap on the GPU race, so keep
+ * them on one stream or order them. check_previous != 0 first synchronises `stream` and returns
+ * status 5 (once; the words are cleared) if a bounded wait ran out in the previous call. Those
+ * status words live in the static array, not where difb200_poll_status looks: a call with
+ * M = 0 and check_previous != 0 is the poll of this entry point.
  */
 DIFB200_EXPORT int difb200_w8a8_linear_static(const void *x, const int8_t *w, const float *col_scales,
                                               const void *bias, uint32_t epilogue,

@@ -451,6 +451,8 @@ typedef struct {
   float scale;
   int32_t *acc_out;
   uint16_t *out;
+  uint64_t Sq;  /* query tokens per batch entry (== S for the DiffIR op, < S for a query sample) */
+  int fp32_p;   /* INT8 form only: keep P in fp32 (the reported middle tier) */
 } attn_ctx;
 
 static void attention_exact_body(void *vctx, int64_t begin, int64_t end) {
@@ -458,7 +460,7 @@ static void attention_exact_body(void *vctx, int64_t begin, int64_t end) {
   const uint16_t *q = (const uint16_t *)ctx->q, *k = (const uint16_t *)ctx->k,
                  *v = (const uint16_t *)ctx->v;
   const uint8_t *key_valid = ctx->key_valid;
-  const uint64_t S = ctx->S, H = ctx->H, KV = ctx->KV, D = ctx->D;
+  const uint64_t S = ctx->S, Sq = ctx->Sq, H = ctx->H, KV = ctx->KV, D = ctx->D;
   const float scale = ctx->scale;
   uint16_t *out = ctx->out;
   const uint64_t group = H / KV;
@@ -466,11 +468,11 @@ static void attention_exact_body(void *vctx, int64_t begin, int64_t end) {
     float *prob = (float *)malloc(sizeof(float) * (size_t)S);
     {
       for (int64_t bq = begin; bq < end; ++bq) {
-        const uint64_t b = (uint64_t)bq / S, query = (uint64_t)bq % S;
+        const uint64_t b = (uint64_t)bq / Sq, query = (uint64_t)bq % Sq;
         for (uint64_t head = 0; head < H; ++head) {
           const uint64_t kvh = head / group;
-          const uint16_t *qr = q + ((b * S + query) * H + head) * D;
-          uint16_t *orow = out + ((b * S + query) * H + head) * D;
+          const uint16_t *qr = q + ((b * Sq + query) * H + head) * D;
+          uint16_t *orow = out + ((b * Sq + query) * H + head) * D;
           float maximum = -INFINITY;
           for (uint64_t key = 0; key < S; ++key) {
             const uint16_t *kr = k + ((b * S + key) * KV + kvh) * D;
@@ -512,8 +514,19 @@ ORC_EXPORT void orc_attention_exact(const uint16_t *q, const uint16_t *k,
                                     uint64_t B, uint64_t S, uint64_t H,
                                     uint64_t KV, uint64_t D, float scale,
                                     uint16_t *out) {
-  attn_ctx ctx = {q, k, v, NULL, NULL, key_valid, B, S, H, KV, D, scale, NULL, out};
+  attn_ctx ctx = {q, k, v, NULL, NULL, key_valid, B, S, H, KV, D, scale, NULL, out, S, 0};
   parallel_for((int64_t)(B * S), attention_exact_body, &ctx);
+}
+
+/* The same op for a sample of queries: q/out [B,Sq,H,D] against all S keys (query rows are
+ * independent in cpu_executor.cpp:1853-1908, so a row computed here equals the row of the full op). */
+ORC_EXPORT void orc_attention_exact_rows(const uint16_t *q, const uint16_t *k,
+                                         const uint16_t *v, const uint8_t *key_valid,
+                                         uint64_t B, uint64_t Sq, uint64_t S, uint64_t H,
+                                         uint64_t KV, uint64_t D, float scale,
+                                         uint16_t *out) {
+  attn_ctx ctx = {q, k, v, NULL, NULL, key_valid, B, S, H, KV, D, scale, NULL, out, Sq, 0};
+  parallel_for((int64_t)(B * Sq), attention_exact_body, &ctx);
 }
 
 /*
@@ -547,7 +560,7 @@ static void attention_int8_body(void *vctx, int64_t begin, int64_t end) {
   const uint16_t *v = (const uint16_t *)ctx->v;
   const float *qs = ctx->qs, *ks = ctx->ks;
   const uint8_t *key_valid = ctx->key_valid;
-  const uint64_t S = ctx->S, H = ctx->H, KV = ctx->KV, D = ctx->D;
+  const uint64_t S = ctx->S, Sq = ctx->Sq, H = ctx->H, KV = ctx->KV, D = ctx->D;
   int32_t *acc_out = ctx->acc_out;
   uint16_t *out = ctx->out;
   const uint64_t group = H / KV;
@@ -557,12 +570,12 @@ static void attention_int8_body(void *vctx, int64_t begin, int64_t end) {
     float *o = (float *)malloc(sizeof(float) * (size_t)D);
     {
       for (int64_t bq = begin; bq < end; ++bq) {
-        const uint64_t b = (uint64_t)bq / S, query = (uint64_t)bq % S;
+        const uint64_t b = (uint64_t)bq / Sq, query = (uint64_t)bq % Sq;
         for (uint64_t head = 0; head < H; ++head) {
           const uint64_t kvh = head / group;
-          const int8_t *qr = q8 + ((b * S + query) * H + head) * D;
-          uint16_t *orow = out + ((b * S + query) * H + head) * D;
-          const float A = qs[(b * S + query) * H + head] * c;
+          const int8_t *qr = q8 + ((b * Sq + query) * H + head) * D;
+          uint16_t *orow = out + ((b * Sq + query) * H + head) * D;
+          const float A = qs[(b * Sq + query) * H + head] * c;
           float umax = -INFINITY;
           for (uint64_t key = 0; key < S; ++key) {
             const int8_t *kr = k8 + ((b * S + key) * KV + kvh) * D;
@@ -570,7 +583,7 @@ static void attention_int8_body(void *vctx, int64_t begin, int64_t end) {
             for (uint64_t d = 0; d < D; ++d)
               acc += (int32_t)qr[d] * (int32_t)kr[d];
             if (acc_out && b == 0 && head == 0)
-              acc_out[query * S + key] = acc;
+              acc_out[query * S + key] = acc; /* only from the entry point with Sq == S */
             uint32_t kbits;
             memcpy(&kbits, &ks[(b * S + key) * KV + kvh], 4);
             kbits = (kbits + 1U + ((kbits >> 2U) & 1U)) & ~3U;
@@ -596,7 +609,7 @@ static void attention_int8_body(void *vctx, int64_t begin, int64_t end) {
               continue;
             const float p = exp2f(fmaf(u[key], A, -m));
             denominator += p;
-            const float P = rbf(p);
+            const float P = ctx->fp32_p ? p : rbf(p);
             const uint16_t *vr = v + ((b * S + key) * KV + kvh) * D;
             for (uint64_t d = 0; d < D; ++d)
               o[d] += P * bf2f(vr[d]);
@@ -617,8 +630,22 @@ ORC_EXPORT void orc_attention_int8(const int8_t *q8, const float *qs,
                                    uint64_t B, uint64_t S, uint64_t H,
                                    uint64_t KV, uint64_t D, float scale,
                                    int32_t *acc_out, uint16_t *out) {
-  attn_ctx ctx = {q8, k8, v, qs, ks, key_valid, B, S, H, KV, D, scale, acc_out, out};
+  attn_ctx ctx = {q8, k8, v, qs, ks, key_valid, B, S, H, KV, D, scale, acc_out, out, S, 0};
   parallel_for((int64_t)(B * S), attention_int8_body, &ctx);
+}
+
+/* The same contract for a sample of queries (q8 / qs / out over Sq query tokens, keys and values
+ * over S tokens): the token-sharded form, and the way rows of very long sequences are checked.
+ * fp32_p != 0 keeps P unrounded: same quantisation, exact fp32 softmax weights -- the middle tier
+ * that separates the error of the bf16 P from the error of the INT8 codes. */
+ORC_EXPORT void orc_attention_int8_rows(const int8_t *q8, const float *qs,
+                                        const int8_t *k8, const float *ks,
+                                        const uint16_t *v, const uint8_t *key_valid,
+                                        uint64_t B, uint64_t Sq, uint64_t S, uint64_t H,
+                                        uint64_t KV, uint64_t D, float scale, int fp32_p,
+                                        uint16_t *out) {
+  attn_ctx ctx = {q8, k8, v, qs, ks, key_valid, B, S, H, KV, D, scale, NULL, out, Sq, fp32_p};
+  parallel_for((int64_t)(B * Sq), attention_int8_body, &ctx);
 }
 
 ORC_EXPORT int orc_version(void) { return 1; }

@@ -75,6 +75,11 @@ class _Orc:
         L.orc_attention_int8.restype = None
         L.orc_attention_int8.argtypes = [_p8, _pf, _p8, _pf, _pu16, _pu8] + [C.c_uint64] * 5 + \
                                         [C.c_float, _pi32, _pu16]
+        L.orc_attention_int8_rows.restype = None
+        L.orc_attention_int8_rows.argtypes = [_p8, _pf, _p8, _pf, _pu16, _pu8] + [C.c_uint64] * 6 + \
+                                             [C.c_float, C.c_int, _pu16]
+        L.orc_attention_exact_rows.restype = None
+        L.orc_attention_exact_rows.argtypes = [_pu16, _pu16, _pu16, _pu8] + [C.c_uint64] * 6 + [C.c_float, _pu16]
 
     def quantize_int8_rows(self, parts: Sequence[np.ndarray], implementation: int, clip: float = 1.0,
                            residual: bool = False):
@@ -193,6 +198,39 @@ class _Orc:
         self.lib.orc_attention_int8(_ptr(q8, _p8), _ptr(qs, _pf), _ptr(k8, _p8), _ptr(ks, _pf), _ptr(v, _pu16),
                                     _ptr(kvp, _pu8), B, S, H, KV, D, scale, _ptr(acc, _pi32), _ptr(out, _pu16))
         return (out, acc) if want_acc else out
+
+
+    def attention_int8_rows(self, q8, qs, k8, ks, v, key_valid=None, scale=None, fp32_p=False):
+        """INT8 attention of a query sample [B,Sq,H,D] against all keys [B,S,KV,D]; fp32_p keeps
+        the softmax weights unrounded (the reported middle tier)."""
+        q8 = np.ascontiguousarray(q8, np.int8)
+        k8 = np.ascontiguousarray(k8, np.int8)
+        qs = np.ascontiguousarray(qs, np.float32)
+        ks = np.ascontiguousarray(ks, np.float32)
+        v = np.ascontiguousarray(v, np.uint16)
+        B, Sq, H, D = q8.shape
+        S, KV = k8.shape[1], k8.shape[2]
+        scale = float(1.0 / np.sqrt(float(D))) if scale is None else scale
+        kvp = None if key_valid is None else np.ascontiguousarray(key_valid, np.uint8)
+        out = np.empty((B, Sq, H, D), np.uint16)
+        self.lib.orc_attention_int8_rows(_ptr(q8, _p8), _ptr(qs, _pf), _ptr(k8, _p8), _ptr(ks, _pf), _ptr(v, _pu16),
+                                         _ptr(kvp, _pu8), B, Sq, S, H, KV, D, scale, 1 if fp32_p else 0,
+                                         _ptr(out, _pu16))
+        return out
+
+    def attention_exact_rows(self, q, k, v, key_valid=None, scale=None):
+        """Exact Attention of a query sample [B,Sq,H,D] against all keys [B,S,KV,D]."""
+        q = np.ascontiguousarray(q, np.uint16)
+        k = np.ascontiguousarray(k, np.uint16)
+        v = np.ascontiguousarray(v, np.uint16)
+        B, Sq, H, D = q.shape
+        S, KV = k.shape[1], k.shape[2]
+        scale = float(1.0 / np.sqrt(float(D))) if scale is None else scale
+        kvp = None if key_valid is None else np.ascontiguousarray(key_valid, np.uint8)
+        out = np.empty_like(q)
+        self.lib.orc_attention_exact_rows(_ptr(q, _pu16), _ptr(k, _pu16), _ptr(v, _pu16), _ptr(kvp, _pu8),
+                                          B, Sq, S, H, KV, D, scale, _ptr(out, _pu16))
+        return out
 
 
 class _View(C.Structure):

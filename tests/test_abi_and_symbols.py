@@ -10,7 +10,16 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 INCLUDE = os.path.join(ROOT, "include")
-REF_ABI = "/root/reference/include/dif/backend/abi.h"
+
+
+def _reference_root():
+    """The reference checkout the oracle recipe builds from (its REF variable)."""
+    res = subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "print-ref"],
+                         capture_output=True, text=True)
+    return res.stdout.strip()
+
+
+REF_ABI = os.path.join(_reference_root(), "include", "dif", "backend", "abi.h")
 
 
 @pytest.fixture(scope="module")
@@ -48,6 +57,13 @@ def test_api_tables(lib):
         assert api.capabilities & 0b1010 == 0b1010  # BF16 | I8
         for field in ("create", "destroy", "compile", "destroy_executable", "execute"):
             assert C.cast(getattr(api, field), C.c_void_p).value
+
+
+def test_per_device_bookkeeping_selftest(lib):
+    """One-time kernel set-up (shared-memory opt-in, resident CTA pairs) is keyed by device
+    ordinal, a failed set-up is retried, and the wait-limit state round-trips: the library's
+    host-only self-check, which touches no GPU."""
+    assert lib.difb200_selftest_host() == 0, lib.difb200_last_error().decode()
 
 
 def test_create_without_gpu_fails_loudly(lib):

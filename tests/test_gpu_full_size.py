@@ -109,3 +109,67 @@ def test_attention_full_sequence_head_sample(ops):
     b = ob.bf16_to_f32(want)
     assert np.isfinite(a).all()
     assert rel_l2(a, b) <= 2e-3 and cosine(a, b) >= 0.9999, (rel_l2(a, b), cosine(a, b))
+
+
+def _attention_row_sample(ops, B, Sq, Sk, H, KV, masked_tail, heads, n_rows, seed):
+    """Runs the kernel on the whole problem and checks a sample of query rows of `heads` (which
+    must share one kv head) against the three tiers: the kernel's contract on the same codes
+    (gated at the path's bf16 bar), the same codes with fp32 softmax weights (reported) and the
+    reference's exact Attention (gated at the reference's own cosine bar). Sq < Sk is the
+    token-sharded form (attention is not causal, so where the queries sit in the sequence does not
+    enter)."""
+    import torch
+    torch.manual_seed(seed)
+    D = 128
+    rms = lambda t: (t.float() / t.float().pow(2).mean(-1, keepdim=True).add(1e-6).sqrt()).to(torch.bfloat16)
+    q = rms(torch.randn(B, Sq, H, D, device="cuda"))
+    k = rms(torch.randn(B, Sk, KV, D, device="cuda"))
+    v = torch.randn(B, Sk, KV, D, device="cuda").to(torch.bfloat16)
+    valid = None
+    if masked_tail:
+        valid = torch.ones(B, Sk, dtype=torch.uint8, device="cuda")
+        valid[:, -masked_tail:] = 0
+    q8, qs = ops.quantize_int8_rows([q.view(-1, D)], 1)
+    k8, ks = ops.quantize_int8_rows([k.view(-1, D)], 1)
+    q8, k8 = q8.view(B, Sq, H, D), k8.view(B, Sk, KV, D)
+    out = ops.attention_int8(q8, qs, k8, ks, v, valid)
+    torch.cuda.synchronize()
+    ops.poll_status()
+    kv = heads[0] // (H // KV)
+    assert all(h // (H // KV) == kv for h in heads)
+    b = B - 1
+    rows = _sample_rows(np.random.default_rng(seed), Sq, n_rows)
+    ridx = torch.from_numpy(rows).cuda()
+    n = lambda t: np.ascontiguousarray(t.cpu().numpy())
+    q8_s = n(q8[b:b + 1][:, ridx][:, :, heads])
+    qs_s = n(qs.view(B, Sq, H)[b:b + 1][:, ridx][:, :, heads]).reshape(-1)
+    k8_s, ks_s = n(k8[b:b + 1, :, kv:kv + 1]), n(ks.view(B, Sk, KV)[b:b + 1, :, kv:kv + 1]).reshape(-1)
+    v_s = from_torch_bf16(v[b:b + 1, :, kv:kv + 1].contiguous())
+    valid_s = None if valid is None else n(valid[b:b + 1])
+    ob.orc().lib.orc_set_threads(8)
+    got = ob.bf16_to_f32(from_torch_bf16(out[b:b + 1][:, ridx][:, :, heads].contiguous()))
+    t1 = ob.bf16_to_f32(ob.orc().attention_int8_rows(q8_s, qs_s, k8_s, ks_s, v_s, valid_s))
+    t2 = ob.bf16_to_f32(ob.orc().attention_int8_rows(q8_s, qs_s, k8_s, ks_s, v_s, valid_s, fp32_p=True))
+    exact = ob.bf16_to_f32(ob.orc().attention_exact_rows(
+        from_torch_bf16(q[b:b + 1][:, ridx][:, :, heads].contiguous()),
+        from_torch_bf16(k[b:b + 1, :, kv:kv + 1].contiguous()), v_s, valid_s))
+    tiers = {"t1_rel_l2": rel_l2(got, t1), "t1_cosine": cosine(got, t1), "t2_rel_l2": rel_l2(got, t2),
+             "t3_rel_l2": rel_l2(got, exact), "t3_cosine": cosine(got, exact)}
+    print("attention tiers B=%d Sq=%d Sk=%d H=%d KV=%d: %s" % (B, Sq, Sk, H, KV, tiers))
+    assert np.isfinite(got).all()
+    assert tiers["t1_rel_l2"] <= 2e-3 and tiers["t1_cosine"] >= 0.9999, tiers
+    assert tiers["t3_cosine"] >= 0.9999, tiers
+    return tiers
+
+
+def test_attention_dense_benchmark_shape_row_sample(ops):
+    """Benchmark configuration 2, dense variant (B=2, S=4608, 24 query and 24 kv heads)."""
+    _attention_row_sample(ops, 2, 4608, 4608, 24, 24, 0, heads=[17], n_rows=96, seed=21)
+
+
+def test_attention_video_sequence_query_shard_row_sample(ops):
+    """The video block's attention as one of eight token shards sees it: 4159 local queries
+    against the 33272 keys of the whole sequence (Sq < Sk), 24 heads, the last 40 keys masked as
+    the padding of an uneven split would be; rows of two heads against the three tiers."""
+    for head in (0, 23):
+        _attention_row_sample(ops, 1, 4159, 33272, 24, 24, 40, heads=[head], n_rows=40, seed=33 + head)

@@ -155,12 +155,11 @@ def test_linear_int8_scaled_bit_exact(ops, gemm_form, M, K, N):
     ops.poll_status()
 
 
-def test_w8a8_linear_end_to_end_config0(ops):
-    """BASELINE config 0: M=1024, K=N=3072, H256ConvRot activations, bias; GPU quant + GEMM chained."""
+def test_w8a8_linear_end_to_end_single_layer(ops):
+    """The single-layer benchmark case (M=1024, K=N=3072, H256ConvRot activations, bias): GPU quant + GEMM chained."""
     import torch
     rng = np.random.default_rng(0)
     ob.orc().lib.orc_set_threads(8)
-    M = K = N = None
     M, K, N = 1024, 3072, 3072
     x = activations(rng, M, K)
     w8, ws = _weights(rng, N, K, 2)

@@ -37,10 +37,17 @@ def test_static_scratch_linear_matches_caller_scratch_twice():
         bias = to_torch_bf16(bf16_normal(rng, (N,), 0.01))
         want = ops.w8a8_linear(x, w8, ws, bias=bias, gelu=gelu)
         got = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = _call_static(lib, x, w8, ws, bias, gelu, got, check_previous=call)
         assert rc == 0, lib.difb200_last_error().decode()
         torch.cuda.synchronize()
+        if call > 0:  # the array's address is resolved by now: a call must not change free memory
+            assert torch.cuda.mem_get_info()[0] == free_before, "the static entry point allocated device memory"
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), "call %d differs" % call
+    # M = 0 with check_previous is the poll of this entry point: nothing is launched, 0 is returned
+    empty = torch.empty(0, 1024, dtype=torch.bfloat16, device="cuda")
+    assert _call_static(lib, empty, w8, ws, None, False, empty, check_previous=1) == 0
 
 
 def test_static_scratch_rejects_oversize():
