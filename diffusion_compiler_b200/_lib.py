@@ -52,6 +52,24 @@ def lib() -> C.CDLL:
         L.difb200_attention_int8_scratch_bytes.argtypes = [u64, u64, u64]
         L.difb200_attention_int8.restype = C.c_int
         L.difb200_attention_int8.argtypes = [vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, u64, f32, vp, u64, vp, vp]
+        L.difb200_attention_int8_state_bytes.restype = u64
+        L.difb200_attention_int8_state_bytes.argtypes = [u64, u64, u64]
+        L.difb200_attention_int8_chunk.restype = C.c_int
+        L.difb200_attention_int8_chunk.argtypes = [vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, u64, f32, vp, u64,
+                                                   vp, C.POINTER(u32), i32, i32, vp, vp]
+        pu8, pu64, pi32, pu32 = C.POINTER(C.c_uint8), C.POINTER(u64), C.POINTER(i32), C.POINTER(u32)
+        for name, args in (
+                ("difb200_world_unique_id", [pu8]),
+                ("difb200_world_rendezvous", [C.c_char_p, i32, i32, pu8, u32]),
+                ("difb200_world_create", [pu8, i32, i32, C.POINTER(vp)]),
+                ("difb200_world_destroy", [vp]),
+                ("difb200_world_exchange", [vp, i32, C.POINTER(vp), pu64, i32, vp]),
+                ("difb200_sharded_attention", [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, f32, vp, u64, vp, vp,
+                                               vp]),
+                ("difb200_world_plan", [i32, i32, u32, pi32, i32, pu32, pi32, pi32, i32, pi32]),
+                ("difb200_world_selftest_fake", [i32, i32, u32])):
+            getattr(L, name).restype = C.c_int
+            getattr(L, name).argtypes = args
         L.difb200_attention_scratch_bytes.restype = u64
         L.difb200_attention_scratch_bytes.argtypes = [u64, u64, u64, u64]
         L.difb200_attention.restype = C.c_int

@@ -35,7 +35,15 @@
 // Tensor memory (512 columns): per query tile two score buffers of 64 columns (INT32; the bf16 P
 // of a step overwrites the first 32 columns of its buffer and is the TMEM A operand of P.V),
 // then O0 | O1 (fp32, 128 columns each).
+//
+// Chunked form (the token-sharded block, where keys arrive from other GPUs one slice at a time):
+// a launch covers up to two ranges of 128-key tiles and may carry the unnormalised state of every
+// query row -- m, l and the fp32 output accumulator -- in from an earlier launch and out to a
+// later one. Every m is an integer, so moving a row from one m to a larger one multiplies l, O
+// and every p by an exact power of two: a sequence of launches over disjoint key ranges gives the
+// single launch's result up to the order of the fp32 sums.
 #include "common.cuh"
+#include "ops.h"
 #include "ptx.cuh"
 
 #include <mutex>
@@ -62,6 +70,11 @@ struct AttnParams {
   float scale_log2e;     // scale * log2(e)
   unsigned long long wait_ns; // limit of every bounded wait
   DeviceStatus *status;
+  // key tiles of this launch: [tile_begin[0], +tile_count[0]) then [tile_begin[1], +tile_count[1])
+  uint32_t tile_begin[2], tile_count[2];
+  float *o_state;        // [B,Sq,H,128] fp32 unnormalised outputs carried between launches
+  float2 *ml_state;      // [B,Sq,H] (m, l) carried between launches
+  uint32_t carry_in, carry_out;
 };
 
 __device__ __forceinline__ void report(DeviceStatus *status, uint32_t role, uint32_t detail) {
@@ -84,11 +97,14 @@ __device__ __forceinline__ void report(DeviceStatus *status, uint32_t role, uint
 // One block of 128 threads per (batch, kv head, key tile), one thread per key.
 __global__ void __launch_bounds__(128)
 key_table_kernel(const int8_t *k8, const float *ks, const uint8_t *key_valid, float *table,
-                 float *tile_bound, uint32_t S, uint32_t KV, uint32_t S_pad) {
-  const uint32_t tiles = S_pad / kTile;
-  const uint32_t tile = blockIdx.x % tiles;
-  const uint32_t kvh = (blockIdx.x / tiles) % KV;
-  const uint32_t b = blockIdx.x / (tiles * KV);
+                 float *tile_bound, uint32_t S, uint32_t KV, uint32_t S_pad, uint32_t begin0, uint32_t count0,
+                 uint32_t begin1, uint32_t count1) {
+  const uint32_t tiles = S_pad / kTile;     // tiles of the whole key axis (table layout)
+  const uint32_t mine = count0 + count1;    // tiles this launch covers
+  const uint32_t local = blockIdx.x % mine;
+  const uint32_t tile = local < count0 ? begin0 + local : begin1 + (local - count0);
+  const uint32_t kvh = (blockIdx.x / mine) % KV;
+  const uint32_t b = blockIdx.x / (mine * KV);
   const uint32_t j = tile * kTile + threadIdx.x;
   float k22 = 0.0f, bias = -INFINITY, bound = 0.0f;
   if (j < S && (key_valid == nullptr || key_valid[(uint64_t)b * S + j] != 0)) {
@@ -164,8 +180,11 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const uint32_t batch = blockIdx.x / (q_blocks * p.H);
   const uint32_t kvh = head / (p.H / p.KV);
   const uint32_t q0 = qb * 256u;
-  const uint32_t n_kv = (p.Sk + kTile - 1) / kTile;
+  const uint32_t n_kv = p.tile_count[0] + p.tile_count[1];
   const uint32_t n_steps = 2u * n_kv;               // 64-key steps
+  auto key_tile = [&](uint32_t i) {                 // i-th key tile of this launch -> tile of the key axis
+    return i < p.tile_count[0] ? p.tile_begin[0] + i : p.tile_begin[1] + (i - p.tile_count[0]);
+  };
   auto score_col = [](uint32_t t, uint32_t b) { return t * 128u + b * 64u; }; // TMEM column of a score buffer
 
   if (threadIdx.x == 0) {
@@ -226,7 +245,8 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       for (uint32_t i = 0; i < n_kv; ++i) {
         const uint32_t k_dst = stage_addr + s * kStageBytes, v_dst = k_dst + kKBytes,
                        t_dst = v_dst + kVBytes;
-        const int32_t key0 = (int32_t)(i * kTile);
+        const uint32_t tile = key_tile(i);
+        const int32_t key0 = (int32_t)(tile * kTile);
         if (!ptx::mbar_wait_warp(k_empty + 8 * s, phase ^ 1u, abort_ptr, wait_ns)) {
           give_up(0, i);
           break;
@@ -245,7 +265,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           ptx::tma_load_4d(v_dst + kVBytes / 2, &map_v, v_full + 8 * s, 64, (int32_t)kvh, key0,
                            (int32_t)batch);
           asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-                           "r"(t_dst), "l"(reinterpret_cast<uint64_t>(table + (uint64_t)i * kTile)),
+                           "r"(t_dst), "l"(reinterpret_cast<uint64_t>(table + (uint64_t)tile * kTile)),
                        "r"(kKsBytes), "r"(v_full + 8 * s)
                        : "memory");
         }
@@ -282,7 +302,7 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           ptx::mma_f16_ts(tmem + 256u + t * 128u, tmem + score_col(t, h) + 8u * k, b + (uint64_t)(128 * k),
-                          idesc_pv, k != 0 ? 1u : (g != 0u ? 1u : 0u));
+                          idesc_pv, k != 0 ? 1u : ((g != 0u || p.carry_in) ? 1u : 0u));
         ptx::mma_commit(pv_done + 8 * t);
       };
       if (!ptx::mbar_wait_warp(q_full, 0, abort_ptr, wait_ns)) {
@@ -360,9 +380,9 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     bool fixed_max = false;
     {
       float kmax = 0.0f;
-      const float *bounds = p.tile_bound + ((uint64_t)batch * p.KV + kvh) * n_kv;
+      const float *bounds = p.tile_bound + ((uint64_t)batch * p.KV + kvh) * (p.S_pad / kTile);
       for (uint32_t i = lane; i < n_kv; i += 32)
-        kmax = fmaxf(kmax, __ldg(bounds + i));
+        kmax = fmaxf(kmax, __ldg(bounds + key_tile(i)));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1)
         kmax = fmaxf(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
@@ -387,9 +407,39 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       const float bound = __fmul_rn(__fmul_rn(A, __fsqrt_rn((float)n2)), kmax);
       const float m_fixed = ceilf(__fadd_rn(bound, 0.001f));
-      fixed_max = __all_sync(0xffffffffu, m_fixed <= 60.0f);
-      if (fixed_max)
-        m_run = m_fixed;
+      // State carried in from the launch over the previous key ranges. m only ever grows, and
+      // the fixed form may use any integer that is at least its bound: the larger of the carried m
+      // and this launch's bound serves both, the carried l and O move to it by an exact power of
+      // two, and the running form simply goes on from the carried m.
+      float m_prev = -INFINITY;
+      if (p.carry_in && row_ok) {
+        const float2 ml = __ldg(p.ml_state + ((uint64_t)batch * p.Sq + (q0 + t * 128u + row_in_tile)) * p.H + head);
+        m_prev = ml.x;
+        l = ml.y;
+      }
+      const float m_both = fmaxf(m_prev, m_fixed);
+      fixed_max = __all_sync(0xffffffffu, m_both <= 60.0f);
+      m_run = fixed_max ? m_both : m_prev;
+      if (p.carry_in) {
+        const float factor = (fixed_max && m_prev != -INFINITY) ? ex2(m_prev - m_run) : (fixed_max ? 0.0f : 1.0f);
+        l *= factor;
+        const float4 *src = reinterpret_cast<const float4 *>(
+            p.o_state + (((uint64_t)batch * p.Sq + (q0 + t * 128u + row_in_tile)) * p.H + head) * kTile);
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const float4 x = row_ok ? __ldg(src + 8 * c + v) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            o[4 * v] = __float_as_uint(x.x * factor);
+            o[4 * v + 1] = __float_as_uint(x.y * factor);
+            o[4 * v + 2] = __float_as_uint(x.z * factor);
+            o[4 * v + 3] = __float_as_uint(x.w * factor);
+          }
+          ptx::tmem_st_32x32(o_tmem + 32u * c, o);
+        }
+        ptx::tmem_st_wait(); // published to the MMA warp with the arrive behind the first P
+      }
     }
     const uint64_t A2 = pack2(A, A);
     for (uint32_t g = 0; g < n_steps && alive; ++g) {
@@ -515,12 +565,22 @@ attn_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       } else {
         ptx::tc_fence_after();
         uint16_t *dst = p.out + (((uint64_t)batch * p.Sq + qrow) * p.H + head) * kTile;
+        if (p.carry_out && row_ok)
+          p.ml_state[((uint64_t)batch * p.Sq + qrow) * p.H + head] = make_float2(m_run, l);
+        float4 *carry = reinterpret_cast<float4 *>(p.o_state + (((uint64_t)batch * p.Sq + qrow) * p.H + head) * kTile);
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
           ptx::tmem_ld_32x32(o_tmem + 32u * c, o);
           ptx::tmem_ld_wait();
-          if (row_ok) {
+          if (p.carry_out) {
+            if (row_ok) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                carry[8 * c + v] = make_float4(__uint_as_float(o[4 * v]), __uint_as_float(o[4 * v + 1]),
+                                               __uint_as_float(o[4 * v + 2]), __uint_as_float(o[4 * v + 3]));
+            }
+          } else if (row_ok) {
             uint32_t w[16];
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
@@ -554,10 +614,14 @@ size_t attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV) {
   return (size_t)(B * KV * s_pad * sizeof(float2) + ((B * KV * (s_pad / kTile) * sizeof(float) + 15) & ~15ull));
 }
 
+size_t attention_int8_state_bytes(uint64_t B, uint64_t Sq, uint64_t H) {
+  return (size_t)(B * Sq * H * (kTile * sizeof(float) + sizeof(float2)));
+}
+
 int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks, const void *v_bf16,
                    const uint8_t *key_valid, uint64_t B, uint64_t Sq, uint64_t S, uint64_t H, uint64_t KV,
                    uint64_t D, float scale, void *scratch, size_t scratch_bytes, void *out_bf16,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const AttentionChunk *chunk) {
   // S is the number of key/value tokens from here on; Sq the number of query tokens.
   if (!q8 || !qs || !k8 || !ks || !v_bf16 || !out_bf16 || !scratch)
     return fail(kInvalidArgument, "Attention(INT8): null pointer");
@@ -581,6 +645,20 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
   if (!status)
     return fail(kOutOfMemory, "Attention(INT8): cannot allocate device status words");
   const uint32_t s_pad = (uint32_t)((S + kTile - 1) / kTile * kTile);
+  const uint32_t all_tiles = s_pad / kTile;
+  uint32_t begin[2] = {0, 0}, count[2] = {all_tiles, 0};
+  if (chunk) {
+    for (int i = 0; i < 2; ++i) {
+      begin[i] = chunk->tile_begin[i];
+      count[i] = chunk->tile_count[i];
+      if ((uint64_t)begin[i] + count[i] > all_tiles)
+        return fail(kInvalidArgument, "Attention(INT8): key tile range beyond the key axis");
+    }
+    if (count[0] + count[1] == 0)
+      return fail(kInvalidArgument, "Attention(INT8): a launch needs at least one key tile");
+    if ((chunk->carry_in || chunk->carry_out) && (!chunk->state || (reinterpret_cast<uintptr_t>(chunk->state) & 15)))
+      return fail(kInvalidArgument, "Attention(INT8): carried state needs a 16-byte aligned state buffer");
+  }
 
   CUtensorMap map_q, map_k, map_v;
   {
@@ -618,11 +696,12 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
   float2 *table = static_cast<float2 *>(scratch);
   float *tile_bound = reinterpret_cast<float *>(table + B * KV * s_pad);
   {
-    const uint64_t blocks = B * KV * (s_pad / kTile);
+    const uint64_t blocks = B * KV * (count[0] + count[1]);
     if (blocks > 0x7fffffffull)
       return fail(kUnsupported, "Attention(INT8): problem too large");
     key_table_kernel<<<(unsigned)blocks, 128, 0, stream>>>(k8, ks, key_valid, reinterpret_cast<float *>(table),
-                                                           tile_bound, (uint32_t)S, (uint32_t)KV, s_pad);
+                                                           tile_bound, (uint32_t)S, (uint32_t)KV, s_pad, begin[0],
+                                                           count[0], begin[1], count[1]);
     if (int rc = check_cuda(cudaGetLastError(), "key_table_kernel launch"))
       return rc;
   }
@@ -640,6 +719,17 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
   p.scale_log2e = scale * 1.4426950408889634f;
   p.wait_ns = wait_limit_ns();
   p.status = status;
+  for (int i = 0; i < 2; ++i) {
+    p.tile_begin[i] = begin[i];
+    p.tile_count[i] = count[i];
+  }
+  if (chunk && (chunk->carry_in || chunk->carry_out)) {
+    // state buffer: fp32 outputs [B,Sq,H,128], then (m, l) per row
+    p.o_state = static_cast<float *>(chunk->state);
+    p.ml_state = reinterpret_cast<float2 *>(p.o_state + B * Sq * H * kTile);
+    p.carry_in = chunk->carry_in ? 1u : 0u;
+    p.carry_out = chunk->carry_out ? 1u : 0u;
+  }
   const uint64_t grid = B * H * ((Sq + 255) / 256);
   attn_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
   return check_cuda(cudaGetLastError(), "attn_i8_kernel launch");

@@ -4,6 +4,11 @@
 #include "common.cuh"
 #include "glue.h"
 #include "ops.h"
+#include "world.h"
+
+#include <string>
+#include <thread>
+#include <vector>
 
 using namespace difb200;
 
@@ -196,6 +201,150 @@ int difb200_attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, 
                            uint64_t scratch_bytes, void *out, void *stream) {
   return attention_int8(q8, qs, k8, ks, v, key_valid, B, Sq, Sk, H, KV, D, scale, scratch, scratch_bytes, out,
                         static_cast<cudaStream_t>(stream));
+}
+
+uint64_t difb200_attention_int8_state_bytes(uint64_t B, uint64_t Sq, uint64_t H) {
+  return attention_int8_state_bytes(B, Sq, H);
+}
+
+int difb200_attention_int8_chunk(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
+                                 const void *v, const uint8_t *key_valid, uint64_t B, uint64_t Sq, uint64_t Sk,
+                                 uint64_t H, uint64_t KV, uint64_t D, float scale, void *scratch,
+                                 uint64_t scratch_bytes, void *out, const uint32_t *tile_ranges,
+                                 int32_t carry_in, int32_t carry_out, void *state, void *stream) {
+  if (!tile_ranges)
+    return fail(kInvalidArgument, "difb200_attention_int8_chunk: null tile ranges");
+  AttentionChunk chunk{};
+  chunk.tile_begin[0] = tile_ranges[0];
+  chunk.tile_count[0] = tile_ranges[1];
+  chunk.tile_begin[1] = tile_ranges[2];
+  chunk.tile_count[1] = tile_ranges[3];
+  chunk.carry_in = carry_in != 0;
+  chunk.carry_out = carry_out != 0;
+  chunk.state = state;
+  return attention_int8(q8, qs, k8, ks, v, key_valid, B, Sq, Sk, H, KV, D, scale, scratch, scratch_bytes, out,
+                        static_cast<cudaStream_t>(stream), &chunk);
+}
+
+// ---- multi-GPU world ----
+int difb200_world_unique_id(uint8_t *id128) {
+  if (!id128)
+    return fail(kInvalidArgument, "difb200_world_unique_id: null pointer");
+  return world_unique_id(id128);
+}
+
+int difb200_world_create(const uint8_t *id128, int32_t rank, int32_t size, void **world) {
+  if (!world)
+    return fail(kInvalidArgument, "difb200_world_create: null pointer");
+  World *w = nullptr;
+  const int rc = world_create(id128, rank, size, &w);
+  *world = w;
+  return rc;
+}
+
+int difb200_world_destroy(void *world) {
+  delete static_cast<World *>(world);
+  return kOk;
+}
+
+int difb200_world_rendezvous(const char *directory, int32_t rank, int32_t size, uint8_t *id128, uint32_t timeout_ms) {
+  if (!directory)
+    return fail(kInvalidArgument, "difb200_world_rendezvous: null directory");
+  return world_rendezvous(directory, rank, size, id128, timeout_ms);
+}
+
+int difb200_world_exchange(void *world, int32_t which, void *const *buffers, const uint64_t *slice_bytes,
+                           int32_t count, void *producer_stream) {
+  return world_exchange_class(static_cast<World *>(world), which, buffers, slice_bytes, count,
+                              static_cast<cudaStream_t>(producer_stream));
+}
+
+int difb200_sharded_attention(void *world, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
+                              const void *v, const uint8_t *key_valid, uint64_t Sq, uint64_t slice_tokens, uint64_t H,
+                              uint64_t KV, float scale, void *scratch, uint64_t scratch_bytes, void *state, void *out,
+                              void *stream) {
+  return sharded_attention(static_cast<World *>(world), q8, qs, k8, ks, v, key_valid, Sq, slice_tokens, H, KV, scale,
+                           scratch, scratch_bytes, state, out, static_cast<cudaStream_t>(stream));
+}
+
+int difb200_world_plan(int32_t rank, int32_t size, uint32_t tiles_per_slice, const int32_t *group_sizes,
+                       int32_t group_count, uint32_t *tile_ranges, int32_t *first_step, int32_t *step_count,
+                       int32_t capacity, int32_t *launches) {
+  if (!tile_ranges || !first_step || !step_count || !launches || (group_count > 0 && !group_sizes))
+    return fail(kInvalidArgument, "difb200_world_plan: null pointer");
+  std::vector<int> groups(group_sizes, group_sizes + (group_count > 0 ? group_count : 0));
+  std::vector<LaunchPlan> plans;
+  if (!plan_launches(rank, size, tiles_per_slice, groups, plans))
+    return fail(kInvalidArgument, "difb200_world_plan: the group sizes must be positive and sum to the world size");
+  if ((int)plans.size() > capacity)
+    return fail(kInvalidArgument, "difb200_world_plan: output arrays are too small");
+  *launches = (int32_t)plans.size();
+  for (size_t i = 0; i < plans.size(); ++i) {
+    tile_ranges[4 * i] = plans[i].tile_begin[0];
+    tile_ranges[4 * i + 1] = plans[i].tile_count[0];
+    tile_ranges[4 * i + 2] = plans[i].tile_begin[1];
+    tile_ranges[4 * i + 3] = plans[i].tile_count[1];
+    first_step[i] = plans[i].steps.front();
+    step_count[i] = (int32_t)plans[i].steps.size();
+  }
+  return kOk;
+}
+
+int difb200_world_selftest_fake(int32_t size, int32_t missing_rank, uint32_t timeout_ms) {
+  // `size` ranks as threads of this process exchange two host buffers (different slice sizes)
+  // through the host-memory transport with the schedule the GPUs use. With missing_rank >= 0 that
+  // rank never shows up: every other rank must come back with an execution error by the deadline.
+  if (size < 1 || size > 64)
+    return fail(kInvalidArgument, "selftest: 1..64 ranks");
+  FakeFabric *fabric = fake_fabric_create(size, timeout_ms);
+  const uint64_t slices[2] = {96, 40};
+  std::vector<int> status((size_t)size, -1);
+  std::vector<std::string> text((size_t)size);
+  std::vector<std::vector<unsigned char>> a((size_t)size), b((size_t)size);
+  auto fill = [](int rank, int buffer, uint64_t i) { return (unsigned char)(17 * rank + 5 * buffer + i); };
+  std::vector<std::thread> threads;
+  for (int r = 0; r < size; ++r) {
+    if (r == missing_rank)
+      continue;
+    threads.emplace_back([&, r] {
+      World world;
+      world.rank = r;
+      world.size = size;
+      world.transport = fake_transport(fabric, r);
+      a[(size_t)r].assign((size_t)(size * slices[0]), 0);
+      b[(size_t)r].assign((size_t)(size * slices[1]), 0);
+      for (uint64_t i = 0; i < slices[0]; ++i)
+        a[(size_t)r][(size_t)(r * slices[0] + i)] = fill(r, 0, i);
+      for (uint64_t i = 0; i < slices[1]; ++i)
+        b[(size_t)r][(size_t)(r * slices[1] + i)] = fill(r, 1, i);
+      void *buffers[2] = {a[(size_t)r].data(), b[(size_t)r].data()};
+      status[(size_t)r] = world_exchange(&world, buffers, slices, 2, nullptr, nullptr);
+      text[(size_t)r] = last_error();
+    });
+  }
+  for (auto &t : threads)
+    t.join();
+  fake_fabric_destroy(fabric);
+  for (int r = 0; r < size; ++r) {
+    if (r == missing_rank)
+      continue;
+    if (missing_rank >= 0) {
+      if (status[(size_t)r] != kExecutionError)
+        return fail(kInternalError, "selftest: rank " + std::to_string(r) + " did not report the missing rank");
+      continue;
+    }
+    if (status[(size_t)r] != kOk)
+      return fail(kInternalError, "selftest: rank " + std::to_string(r) + " failed: " + text[(size_t)r]);
+    for (int src = 0; src < size; ++src) {
+      for (uint64_t i = 0; i < slices[0]; ++i)
+        if (a[(size_t)r][(size_t)(src * slices[0] + i)] != fill(src, 0, i))
+          return fail(kInternalError, "selftest: wrong bytes in the first buffer");
+      for (uint64_t i = 0; i < slices[1]; ++i)
+        if (b[(size_t)r][(size_t)(src * slices[1] + i)] != fill(src, 1, i))
+          return fail(kInternalError, "selftest: wrong bytes in the second buffer");
+    }
+  }
+  return kOk;
 }
 
 uint64_t difb200_attention_scratch_bytes(uint64_t B, uint64_t S, uint64_t H, uint64_t KV) {

@@ -42,10 +42,21 @@ int w8a8_linear(const void *x_bf16, const int8_t *w, const float *col_scales, co
 
 // INT8 attention on already quantised Q/K (QuantizeInt8Rows Direct per token-head) and bf16 V.
 size_t attention_int8_scratch_bytes(uint64_t B, uint64_t S, uint64_t KV);
+// One launch of a chunked attention: it covers the key tiles (128 keys each) [tile_begin[i],
+// tile_begin[i] + tile_count[i]) for i = 0, 1 and may take the unnormalised state of every query
+// row (m, l, fp32 outputs) from `state` and / or leave it there instead of writing `out`.
+// A sequence of launches over disjoint tile ranges, the first without carry_in and the last
+// without carry_out, gives the single launch's result up to the order of the fp32 sums.
+struct AttentionChunk {
+  uint32_t tile_begin[2], tile_count[2];
+  bool carry_in, carry_out;
+  void *state; // attention_int8_state_bytes(B, Sq, H) bytes, 16-byte aligned
+};
+size_t attention_int8_state_bytes(uint64_t B, uint64_t Sq, uint64_t H);
 int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const float *ks, const void *v_bf16,
                    const uint8_t *key_valid, uint64_t B, uint64_t Sq, uint64_t Sk, uint64_t H, uint64_t KV,
                    uint64_t D, float scale, void *scratch, size_t scratch_bytes, void *out_bf16,
-                   cudaStream_t stream);
+                   cudaStream_t stream, const AttentionChunk *chunk = nullptr);
 
 // DiffIR Attention on bf16 q/k/v in its INT8 lowering: Direct quantisation of q and k per
 // token-head, then attention_int8. Scratch holds the codes, scales and the key table.

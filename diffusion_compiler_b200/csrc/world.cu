@@ -1,0 +1,434 @@
+// Multi-GPU world: NCCL communicator (the library is resolved at run time, so a single-GPU host
+// needs no NCCL), the ring exchange of the key / value slices, the launch plan of the chunked
+// attention, a bounded rendezvous, and a host-memory transport for CPU tests. See world.h.
+#include "world.h"
+
+#include "common.cuh"
+#include "ops.h"
+
+#include <dlfcn.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <condition_variable>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <deque>
+#include <map>
+#include <mutex>
+#include <thread>
+
+namespace difb200 {
+
+// ---- launch plan ------------------------------------------------------------------------------
+bool plan_launches(int rank, int size, uint32_t tiles_per_slice, std::vector<int> group_sizes,
+                   std::vector<LaunchPlan> &out) {
+  out.clear();
+  if (size < 1 || rank < 0 || rank >= size)
+    return false;
+  if (group_sizes.empty()) {
+    group_sizes.push_back(1);
+    if (size > 1 && size <= 4) {
+      group_sizes.push_back(size - 1);
+    } else if (size > 4) {
+      group_sizes.push_back((size - 1) / 2);
+      group_sizes.push_back(size - 1 - (size - 1) / 2);
+    }
+  }
+  int total = 0;
+  for (int g : group_sizes) {
+    if (g <= 0)
+      return false;
+    total += g;
+  }
+  if (total != size)
+    return false;
+  int first = 0; // first ring step of the group
+  for (int g : group_sizes) {
+    LaunchPlan plan{};
+    for (int s = first; s < first + g; ++s)
+      plan.steps.push_back(s);
+    // steps first .. first + g - 1 bring the slices of ranks rank - first, rank - first - 1, ...:
+    // the slices [rank - first - g + 1, rank - first] modulo size, i.e. one or two runs of tiles
+    const int low = ((rank - first - g + 1) % size + size) % size;
+    const int run0 = low + g <= size ? g : size - low; // slices before the wrap
+    plan.tile_begin[0] = (uint32_t)low * tiles_per_slice;
+    plan.tile_count[0] = (uint32_t)run0 * tiles_per_slice;
+    plan.tile_begin[1] = 0;
+    plan.tile_count[1] = (uint32_t)(g - run0) * tiles_per_slice;
+    out.push_back(plan);
+    first += g;
+  }
+  return true;
+}
+
+// ---- NCCL, resolved with dlopen ---------------------------------------------------------------
+namespace {
+
+struct NcclUniqueId {
+  char internal[128];
+};
+typedef struct ncclComm *NcclComm;
+
+struct NcclApi {
+  int (*GetUniqueId)(NcclUniqueId *) = nullptr;
+  int (*CommInitRank)(NcclComm *, int, NcclUniqueId, int) = nullptr;
+  int (*CommDestroy)(NcclComm) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
+  int (*Send)(const void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+  int (*Recv)(void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+  const char *(*GetErrorString)(int) = nullptr;
+  bool ok = false;
+  std::string error;
+};
+
+const NcclApi &nccl() {
+  static NcclApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char *name = std::getenv("DIFB200_NCCL_LIBRARY");
+    void *handle = dlopen(name && name[0] ? name : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!handle) {
+      api.error = std::string("cannot load NCCL (libnccl.so.2; set DIFB200_NCCL_LIBRARY): ") + dlerror();
+      return;
+    }
+    auto sym = [&](const char *symbol) { return dlsym(handle, symbol); };
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+    api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+    api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+    api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+    api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.GroupStart && api.GroupEnd && api.Send &&
+             api.Recv && api.GetErrorString;
+    if (!api.ok)
+      api.error = "the NCCL library lacks a required symbol";
+  });
+  return api;
+}
+
+int check_nccl(int rc, const char *what) {
+  if (rc == 0)
+    return kOk;
+  return fail(kExecutionError, std::string(what) + ": NCCL error " + std::to_string(rc) + " (" +
+                                   nccl().GetErrorString(rc) + ")");
+}
+
+class NcclTransport : public Transport {
+public:
+  NcclComm comm = nullptr;
+  ~NcclTransport() override {
+    if (comm)
+      nccl().CommDestroy(comm);
+  }
+  int group_start() override { return check_nccl(nccl().GroupStart(), "ncclGroupStart"); }
+  int send(const void *data, size_t bytes, int peer, cudaStream_t stream) override {
+    return check_nccl(nccl().Send(data, bytes, 0 /* ncclInt8 */, peer, comm, stream), "ncclSend");
+  }
+  int recv(void *data, size_t bytes, int peer, cudaStream_t stream) override {
+    return check_nccl(nccl().Recv(data, bytes, 0 /* ncclInt8 */, peer, comm, stream), "ncclRecv");
+  }
+  int group_end() override { return check_nccl(nccl().GroupEnd(), "ncclGroupEnd"); }
+  bool on_device() const override { return true; }
+};
+
+} // namespace
+
+World::~World() {
+  delete transport;
+  for (auto &events : landed)
+    for (cudaEvent_t e : events)
+      if (e)
+        cudaEventDestroy(e);
+  if (ready)
+    cudaEventDestroy(ready);
+  if (comm_stream)
+    cudaStreamDestroy(comm_stream);
+}
+
+int world_unique_id(uint8_t id[128]) {
+  if (!nccl().ok)
+    return fail(kUnsupported, nccl().error);
+  NcclUniqueId uid;
+  if (int rc = check_nccl(nccl().GetUniqueId(&uid), "ncclGetUniqueId"))
+    return rc;
+  std::memcpy(id, uid.internal, 128);
+  return kOk;
+}
+
+int world_create(const uint8_t id[128], int rank, int size, World **out) {
+  if (!out || !id || size < 1 || rank < 0 || rank >= size)
+    return fail(kInvalidArgument, "world: bad rank or size");
+  *out = nullptr;
+  if (!nccl().ok)
+    return fail(kUnsupported, nccl().error);
+  World *world = new World();
+  world->rank = rank;
+  world->size = size;
+  if (int rc = check_cuda(cudaGetDevice(&world->device), "cudaGetDevice")) {
+    delete world;
+    return rc;
+  }
+  int least = 0, greatest = 0;
+  cudaDeviceGetStreamPriorityRange(&least, &greatest);
+  int rc = check_cuda(cudaStreamCreateWithPriority(&world->comm_stream, cudaStreamNonBlocking, greatest),
+                      "cudaStreamCreateWithPriority");
+  if (!rc)
+    rc = check_cuda(cudaEventCreateWithFlags(&world->ready, cudaEventDisableTiming), "cudaEventCreate");
+  if (!rc) {
+    NcclTransport *transport = new NcclTransport();
+    world->transport = transport;
+    NcclUniqueId uid;
+    std::memcpy(uid.internal, id, 128);
+    rc = check_nccl(nccl().CommInitRank(&transport->comm, size, uid, rank), "ncclCommInitRank");
+  }
+  if (rc) {
+    delete world;
+    return rc;
+  }
+  *out = world;
+  return kOk;
+}
+
+// ---- rendezvous -------------------------------------------------------------------------------
+int world_rendezvous(const std::string &directory, int rank, int size, uint8_t id[128], uint32_t timeout_ms) {
+  if (directory.empty() || size < 1 || rank < 0 || rank >= size || !id)
+    return fail(kInvalidArgument, "world rendezvous: bad arguments");
+  auto path = [&](int r) { return directory + "/rank_" + std::to_string(r); };
+  {
+    const std::string temp = path(rank) + ".writing";
+    FILE *f = std::fopen(temp.c_str(), "wb");
+    if (!f)
+      return fail(kExecutionError, "world rendezvous: cannot write into " + directory);
+    const size_t written = std::fwrite(id, 1, 128, f); // only rank 0's content is read
+    std::fclose(f);
+    if (written != 128 || std::rename(temp.c_str(), path(rank).c_str()) != 0)
+      return fail(kExecutionError, "world rendezvous: cannot publish " + path(rank));
+  }
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (;;) {
+    int missing = -1;
+    for (int r = 0; r < size; ++r) {
+      struct stat st;
+      if (stat(path(r).c_str(), &st) != 0 || st.st_size != 128) {
+        missing = r;
+        break;
+      }
+    }
+    if (missing < 0)
+      break;
+    if (std::chrono::steady_clock::now() >= deadline)
+      return fail(kExecutionError, "world rendezvous: rank " + std::to_string(missing) + " of " +
+                                       std::to_string(size) + " did not arrive within " +
+                                       std::to_string(timeout_ms) + " ms; not entering the communicator set-up");
+    std::this_thread::sleep_for(std::chrono::milliseconds(2));
+  }
+  if (rank != 0) {
+    FILE *f = std::fopen(path(0).c_str(), "rb");
+    if (!f || std::fread(id, 1, 128, f) != 128) {
+      if (f)
+        std::fclose(f);
+      return fail(kExecutionError, "world rendezvous: cannot read the communicator id");
+    }
+    std::fclose(f);
+  }
+  return kOk;
+}
+
+int world_from_environment(World **out) {
+  *out = nullptr;
+  const char *size_text = std::getenv("DIFB200_WORLD_SIZE");
+  const int size = size_text ? std::atoi(size_text) : 1;
+  if (size <= 1)
+    return kOk;
+  const char *rank_text = std::getenv("DIFB200_WORLD_RANK"), *dir = std::getenv("DIFB200_WORLD_DIR");
+  if (!rank_text || !dir)
+    return fail(kInvalidArgument, "DIFB200_WORLD_SIZE > 1 needs DIFB200_WORLD_RANK and DIFB200_WORLD_DIR");
+  const int rank = std::atoi(rank_text);
+  const char *timeout_text = std::getenv("DIFB200_WORLD_TIMEOUT_MS");
+  const uint32_t timeout_ms = timeout_text ? (uint32_t)std::strtoul(timeout_text, nullptr, 10) : 60000u;
+  uint8_t id[128] = {0};
+  if (rank == 0)
+    if (int rc = world_unique_id(id))
+      return rc;
+  if (int rc = world_rendezvous(dir, rank, size, id, timeout_ms))
+    return rc;
+  return world_create(id, rank, size, out);
+}
+
+// ---- exchange ---------------------------------------------------------------------------------
+int world_exchange(World *world, void *const *buffers, const uint64_t *slice_bytes, int count,
+                   cudaStream_t producer, cudaEvent_t *events) {
+  if (!world || !world->transport || count < 1 || !buffers || !slice_bytes)
+    return fail(kInvalidArgument, "world exchange: bad arguments");
+  if (world->size == 1)
+    return kOk;
+  Transport &t = *world->transport;
+  cudaStream_t stream = world->comm_stream;
+  if (t.on_device()) {
+    if (int rc = check_cuda(cudaEventRecord(world->ready, producer), "cudaEventRecord(slice ready)"))
+      return rc;
+    if (int rc = check_cuda(cudaStreamWaitEvent(stream, world->ready, 0), "cudaStreamWaitEvent(slice ready)"))
+      return rc;
+  }
+  for (int s = 1; s < world->size; ++s) {
+    const RingStep step = ring_step(world->rank, world->size, s);
+    if (int rc = t.group_start())
+      return rc;
+    for (int i = 0; i < count; ++i) {
+      char *base = static_cast<char *>(buffers[i]);
+      if (int rc = t.send(base + (uint64_t)world->rank * slice_bytes[i], (size_t)slice_bytes[i], step.send_to, stream))
+        return rc;
+      if (int rc = t.recv(base + (uint64_t)step.recv_from * slice_bytes[i], (size_t)slice_bytes[i], step.recv_from,
+                          stream))
+        return rc;
+    }
+    if (int rc = t.group_end())
+      return rc;
+    if (events && events[s - 1] && t.on_device())
+      if (int rc = check_cuda(cudaEventRecord(events[s - 1], stream), "cudaEventRecord(step landed)"))
+        return rc;
+  }
+  return kOk;
+}
+
+int world_exchange_class(World *world, int which, void *const *buffers, const uint64_t *slice_bytes, int count,
+                         cudaStream_t producer) {
+  if (!world || which < 0 || which > 1)
+    return fail(kInvalidArgument, "world exchange: bad class");
+  auto &events = world->landed[which];
+  while ((int)events.size() < world->size - 1) {
+    cudaEvent_t e = nullptr;
+    if (int rc = check_cuda(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate"))
+      return rc;
+    events.push_back(e);
+  }
+  return world_exchange(world, buffers, slice_bytes, count, producer, events.data());
+}
+
+namespace {
+std::vector<int> groups_from_environment() {
+  // DIFB200_ATTENTION_GROUPS="1,3,4": how many ring steps each attention launch covers
+  std::vector<int> groups;
+  if (const char *text = std::getenv("DIFB200_ATTENTION_GROUPS")) {
+    int value = 0;
+    bool digits = false;
+    for (const char *c = text;; ++c) {
+      if (*c >= '0' && *c <= '9') {
+        value = value * 10 + (*c - '0');
+        digits = true;
+      } else {
+        if (digits)
+          groups.push_back(value);
+        value = 0;
+        digits = false;
+        if (!*c)
+          break;
+      }
+    }
+  }
+  return groups;
+}
+} // namespace
+
+int sharded_attention(World *world, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
+                      const void *v_bf16, const uint8_t *key_valid, uint64_t Sq, uint64_t slice_tokens, uint64_t H,
+                      uint64_t KV, float scale, void *scratch, size_t scratch_bytes, void *state, void *out_bf16,
+                      cudaStream_t stream) {
+  const int size = world ? world->size : 1, rank = world ? world->rank : 0;
+  if (slice_tokens == 0 || slice_tokens % 128 != 0)
+    return fail(kInvalidArgument, "sharded attention: the slice length must be a positive multiple of 128");
+  std::vector<LaunchPlan> launches;
+  std::vector<int> groups = groups_from_environment();
+  if (!plan_launches(rank, size, (uint32_t)(slice_tokens / 128), groups, launches)) {
+    groups.clear(); // a malformed override falls back to the default grouping
+    plan_launches(rank, size, (uint32_t)(slice_tokens / 128), groups, launches);
+  }
+  if (launches.size() > 1 && !state)
+    return fail(kInvalidArgument, "sharded attention: several launches need a state buffer");
+  const uint64_t keys = (uint64_t)size * slice_tokens;
+  for (size_t i = 0; i < launches.size(); ++i) {
+    const LaunchPlan &plan = launches[i];
+    for (int step : plan.steps) {
+      if (step == 0)
+        continue; // the own slice: written on `stream` itself
+      for (int which = 0; which < 2; ++which) {
+        if ((int)world->landed[which].size() < step)
+          return fail(kInvalidArgument, "sharded attention: the exchange of the gather buffers was not enqueued");
+        if (int rc = check_cuda(cudaStreamWaitEvent(stream, world->landed[which][(size_t)step - 1], 0),
+                                "cudaStreamWaitEvent(slice landed)"))
+          return rc;
+      }
+    }
+    AttentionChunk chunk{};
+    for (int r = 0; r < 2; ++r) {
+      chunk.tile_begin[r] = plan.tile_begin[r];
+      chunk.tile_count[r] = plan.tile_count[r];
+    }
+    chunk.carry_in = i > 0;
+    chunk.carry_out = i + 1 < launches.size();
+    chunk.state = state;
+    if (int rc = attention_int8(q8, qs, k8, ks, v_bf16, key_valid, 1, Sq, keys, H, KV, 128, scale, scratch,
+                                scratch_bytes, out_bf16, stream, &chunk))
+      return rc;
+  }
+  return kOk;
+}
+
+// ---- host-memory transport for tests ----------------------------------------------------------
+struct FakeFabric {
+  int size;
+  uint32_t timeout_ms;
+  std::mutex mutex;
+  std::condition_variable arrived;
+  std::map<std::pair<int, int>, std::deque<std::vector<char>>> mail; // (from, to) -> messages in order
+};
+
+namespace {
+class FakeTransport : public Transport {
+public:
+  FakeFabric *fabric;
+  int rank;
+  FakeTransport(FakeFabric *f, int r) : fabric(f), rank(r) {}
+  int group_start() override { return kOk; }
+  int group_end() override { return kOk; }
+  bool on_device() const override { return false; }
+  int send(const void *data, size_t bytes, int peer, cudaStream_t) override {
+    if (peer < 0 || peer >= fabric->size)
+      return fail(kInvalidArgument, "fake transport: bad peer");
+    std::lock_guard<std::mutex> lock(fabric->mutex);
+    const char *p = static_cast<const char *>(data);
+    fabric->mail[{rank, peer}].emplace_back(p, p + bytes);
+    fabric->arrived.notify_all();
+    return kOk;
+  }
+  int recv(void *data, size_t bytes, int peer, cudaStream_t) override {
+    std::unique_lock<std::mutex> lock(fabric->mutex);
+    auto &queue = fabric->mail[{peer, rank}];
+    if (!fabric->arrived.wait_for(lock, std::chrono::milliseconds(fabric->timeout_ms), [&] { return !queue.empty(); }))
+      return fail(kExecutionError, "fake transport: rank " + std::to_string(peer) + " sent nothing to rank " +
+                                       std::to_string(rank) + " within the deadline");
+    if (queue.front().size() != bytes)
+      return fail(kExecutionError, "fake transport: message size mismatch");
+    std::memcpy(data, queue.front().data(), bytes);
+    queue.pop_front();
+    return kOk;
+  }
+};
+} // namespace
+
+FakeFabric *fake_fabric_create(int size, uint32_t timeout_ms) {
+  FakeFabric *f = new FakeFabric();
+  f->size = size;
+  f->timeout_ms = timeout_ms;
+  return f;
+}
+void fake_fabric_destroy(FakeFabric *fabric) { delete fabric; }
+Transport *fake_transport(FakeFabric *fabric, int rank) { return new FakeTransport(fabric, rank); }
+
+} // namespace difb200

@@ -1,0 +1,114 @@
+// The multi-GPU world of the token-sharded block: one process per GPU, one NCCL communicator,
+// and the schedule by which the key / value slices of all ranks reach every rank.
+//
+// The reference runs on one device per executor (reference include/dif/runtime/executor.hpp:683)
+// and has no communication layer; this is the sequence-partitioned form of its video block
+// (graph: reference tools/difc.cpp:261-345). Rank r owns a contiguous slice of the tokens.
+// Everything but attention is row-local. Before attention every rank needs the INT8 key codes,
+// their per-token-head scales and the bf16 values of all tokens: each rank keeps full-length
+// gather buffers whose own slice its producer kernels write directly, and the slices travel in
+// size - 1 ring-shifted steps (step s: send the own slice to rank + s, receive the slice of
+// rank - s; every GPU sends and receives one slice per step, which NVSwitch serves at full
+// bandwidth). Attention starts on the own slice while the others are in flight and takes the
+// arrived slices in a few launches that carry the softmax state (attention_int8 with an
+// AttentionChunk); launches are ordered behind the steps they need by CUDA events only: no
+// kernel ever waits on a flag that another kernel or another GPU writes.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+namespace difb200 {
+
+// Point-to-point transport of one rank. The schedule above is written against this interface so
+// that it also runs among CPU threads over a host-memory transport (how it is tested without GPUs).
+class Transport {
+public:
+  virtual ~Transport() {}
+  virtual int group_start() = 0;
+  virtual int send(const void *data, size_t bytes, int peer, cudaStream_t stream) = 0;
+  virtual int recv(void *data, size_t bytes, int peer, cudaStream_t stream) = 0;
+  virtual int group_end() = 0;
+  virtual bool on_device() const = 0; // false: host memory, calls complete before they return
+};
+
+struct RingStep {
+  int send_to, recv_from;
+};
+inline RingStep ring_step(int rank, int size, int step) {
+  return RingStep{(rank + step) % size, ((rank - step) % size + size) % size};
+}
+
+// One attention launch of the chunked form: which ring steps must have landed before it, and the
+// (at most two) ranges of 128-key tiles it covers. Step 0 is the rank's own slice.
+struct LaunchPlan {
+  std::vector<int> steps;
+  uint32_t tile_begin[2], tile_count[2];
+};
+// `group_sizes` partitions the steps 0 .. size - 1 in order (e.g. {1, 3, 4} at 8 ranks); an empty
+// vector selects the default (own slice first; the rest in one launch up to 4 ranks, in two from 5).
+// Returns false when the sizes do not sum to `size` or contain a zero.
+bool plan_launches(int rank, int size, uint32_t tiles_per_slice, std::vector<int> group_sizes,
+                   std::vector<LaunchPlan> &out);
+
+class World {
+public:
+  int rank = 0, size = 1, device = 0;
+  Transport *transport = nullptr;       // owned
+  cudaStream_t comm_stream = nullptr;   // the exchange runs here, at the highest priority
+  cudaEvent_t ready = nullptr;          // producer stream -> communication stream
+  // landed[c][s - 1]: slice of rank - s has arrived in the buffers of exchange class c
+  // (0 = values, 1 = key codes and scales); recorded by world_exchange_class
+  std::vector<cudaEvent_t> landed[2];
+  ~World();
+};
+
+// Rendezvous of `size` processes through a directory all of them can reach, bounded by
+// `timeout_ms`: every rank leaves a file, rank 0 also the 128-byte communicator id (`id` in for
+// rank 0, out for the others), and every rank waits until all files are there. Returns
+// kExecutionError with text when a rank is missing at the deadline, so that no rank enters the
+// (unbounded) communicator set-up alone.
+int world_rendezvous(const std::string &directory, int rank, int size, uint8_t id[128], uint32_t timeout_ms);
+
+int world_unique_id(uint8_t id[128]);
+// Communicator on the current device (blocks until all ranks have called it).
+int world_create(const uint8_t id[128], int rank, int size, World **out);
+// World from the environment of this process: DIFB200_WORLD_SIZE (absent or 1: *out = nullptr),
+// DIFB200_WORLD_RANK, DIFB200_WORLD_DIR (rendezvous directory), DIFB200_WORLD_TIMEOUT_MS (60000).
+int world_from_environment(World **out);
+
+// Ring exchange of gather buffers. buffers[i] holds size * slice_bytes[i] bytes; this rank's slice
+// is final once everything enqueued on `producer` so far has run. The size - 1 steps are enqueued
+// on the communication stream; events[s - 1] (caller-owned, may be null) is recorded when the
+// slice of rank - s has landed in every buffer of this call.
+int world_exchange(World *world, void *const *buffers, const uint64_t *slice_bytes, int count,
+                   cudaStream_t producer, cudaEvent_t *events);
+
+// The same exchange with the world's own events of class `which` (0 = values, 1 = keys).
+int world_exchange_class(World *world, int which, void *const *buffers, const uint64_t *slice_bytes, int count,
+                         cudaStream_t producer);
+
+// Attention of this rank's queries over the keys and values of all ranks, as the launches of
+// `plan_launches` on `stream`: each launch first waits (CUDA events) for the ring steps whose
+// slices it reads. Gather buffers: k8 [size * slice_tokens, KV, 128] int8, ks [size * slice_tokens,
+// KV] f32, v [size * slice_tokens, KV, 128] bf16 with slice_tokens a multiple of 128; key_valid
+// [size * slice_tokens] marks real tokens (slice padding is 0); the exchanges of both classes must
+// have been enqueued. `world` may be null (one rank: a single launch over the own slice).
+// scratch: attention_int8_scratch_bytes(1, size * slice_tokens, KV); state:
+// attention_int8_state_bytes(1, Sq, H) (unused with one launch).
+int sharded_attention(World *world, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
+                      const void *v_bf16, const uint8_t *key_valid, uint64_t Sq, uint64_t slice_tokens, uint64_t H,
+                      uint64_t KV, float scale, void *scratch, size_t scratch_bytes, void *state, void *out_bf16,
+                      cudaStream_t stream);
+
+// Host-memory transport among the threads of one process, for tests: `size` mailboxes, every
+// recv waits at most timeout_ms for its matching send.
+struct FakeFabric;
+FakeFabric *fake_fabric_create(int size, uint32_t timeout_ms);
+void fake_fabric_destroy(FakeFabric *fabric);
+Transport *fake_transport(FakeFabric *fabric, int rank);
+
+} // namespace difb200

@@ -244,6 +244,43 @@ def attention_int8(q8: torch.Tensor, qs: torch.Tensor, k8: torch.Tensor, ks: tor
     return out
 
 
+def attention_int8_chunked(q8: torch.Tensor, qs: torch.Tensor, k8: torch.Tensor, ks: torch.Tensor, v: torch.Tensor,
+                           tile_groups: Sequence[Sequence[Tuple[int, int]]], key_valid: Optional[torch.Tensor] = None,
+                           scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """attention_int8 as a sequence of launches, one per entry of ``tile_groups``; an entry is one or
+    two (first tile, tile count) ranges of 128-key tiles. The unnormalised state of every query row
+    is carried from launch to launch; the last launch writes the bf16 result. The groups must
+    cover every key tile exactly once (the token-sharded block launches one group per set of
+    key / value slices that have arrived)."""
+    q8 = _require(q8, torch.int8, "q8")
+    k8 = _require(k8, torch.int8, "k8")
+    qs, ks = _require(qs, torch.float32, "qs"), _require(ks, torch.float32, "ks")
+    v = _require(v, torch.bfloat16, "v")
+    B, Sq, H, D = (int(d) for d in q8.shape)
+    Sk, KV = int(k8.shape[1]), int(k8.shape[2])
+    if key_valid is not None:
+        key_valid = key_valid.to(torch.uint8).contiguous()
+    if scale is None:
+        scale = 1.0 / (D ** 0.5)
+    if out is None:
+        out = torch.empty((B, Sq, H, D), dtype=torch.bfloat16, device=q8.device)
+    L = _lib.lib()
+    scratch = torch.empty(int(L.difb200_attention_int8_scratch_bytes(B, Sk, KV)), dtype=torch.uint8, device=q8.device)
+    state = torch.empty(int(L.difb200_attention_int8_state_bytes(B, Sq, H)), dtype=torch.uint8, device=q8.device)
+    groups = [list(g) for g in tile_groups]
+    with torch.cuda.device(q8.device):
+        for i, group in enumerate(groups):
+            if not 1 <= len(group) <= 2:
+                raise ValueError("a launch covers one or two tile ranges")
+            flat = [int(x) for r in group for x in r] + [0, 0] * (2 - len(group))
+            ranges = (C.c_uint32 * 4)(*flat)
+            _lib.check(L.difb200_attention_int8_chunk(_ptr(q8), _ptr(qs), _ptr(k8), _ptr(ks), _ptr(v), _ptr(key_valid),
+                                                      B, Sq, Sk, H, KV, D, float(scale), _ptr(scratch), scratch.numel(),
+                                                      _ptr(out), ranges, 1 if i > 0 else 0,
+                                                      1 if i + 1 < len(groups) else 0, _ptr(state), _stream()))
+    return out
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, key_valid: Optional[torch.Tensor] = None,
               scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
               scratch: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -170,6 +170,83 @@ DIFB200_EXPORT int difb200_attention_int8(const int8_t *q8, const float *qs, con
                                           uint64_t scratch_bytes, void *out, void *stream);
 
 /*
+ * One launch of a chunked difb200_attention_int8 (no counterpart in the reference, which runs
+ * on one device: include/dif/runtime/executor.hpp:683). It is the form the token-sharded block
+ * uses: keys and values arrive from other GPUs one slice at a time, and attention over the
+ * slices that are already here runs while the rest is in flight.
+ *   tile_ranges = {begin0, count0, begin1, count1}: the launch covers the 128-key tiles
+ *   [begin0, begin0 + count0) and [begin1, begin1 + count1) of the key axis (Sk rounded up to 128).
+ *   carry_in != 0: start from the state an earlier launch left in `state`; carry_out != 0: leave
+ *   the state there instead of writing `out`. state: difb200_attention_int8_state_bytes(B,Sq,H)
+ *   bytes, 16-byte aligned (per query row: m, l and 128 unnormalised fp32 outputs).
+ * A sequence of launches over disjoint tile ranges -- the first without carry_in, the last
+ * without carry_out, all on one stream or ordered by events -- gives the result of the single
+ * launch over all tiles up to the order of the fp32 sums (every m is an integer, so moving a row
+ * to a larger m is an exact scaling by a power of two).
+ */
+DIFB200_EXPORT uint64_t difb200_attention_int8_state_bytes(uint64_t B, uint64_t Sq, uint64_t H);
+DIFB200_EXPORT int difb200_attention_int8_chunk(const int8_t *q8, const float *qs, const int8_t *k8,
+                                                const float *ks, const void *v, const uint8_t *key_valid,
+                                                uint64_t B, uint64_t Sq, uint64_t Sk, uint64_t H,
+                                                uint64_t KV, uint64_t D, float scale, void *scratch,
+                                                uint64_t scratch_bytes, void *out,
+                                                const uint32_t *tile_ranges, int32_t carry_in,
+                                                int32_t carry_out, void *state, void *stream);
+
+/*
+ * The multi-GPU world of the token-sharded block (no counterpart in the reference, which runs one
+ * device per executor: include/dif/runtime/executor.hpp:683). One process per GPU; rank r owns a
+ * contiguous slice of the tokens; weights are replicated; the only exchange per block is that of
+ * the INT8 key codes, their scales and the bf16 values, over NCCL (the NCCL library is resolved
+ * with dlopen when a world is created: libnccl.so.2 or DIFB200_NCCL_LIBRARY).
+ *   difb200_world_unique_id     rank 0 makes the 128-byte communicator id, which the host hands to
+ *                               the other ranks by any means it has
+ *   difb200_world_rendezvous    optional bounded meeting point in a directory shared by the ranks
+ *                               (fresh per job): every rank checks in, rank 0 leaves the id, all wait
+ *                               at most timeout_ms and get status 5 if a rank is missing, so that no
+ *                               rank enters the unbounded communicator set-up alone
+ *   difb200_world_create        communicator + a high-priority communication stream on the current
+ *                               device; blocks until every rank has called it
+ *   difb200_world_exchange      ring exchange of `count` gather buffers of class `which` (0 = values,
+ *                               1 = key codes and scales): buffers[i] holds size * slice_bytes[i] bytes
+ *                               and this rank's slice is final once the work enqueued on
+ *                               producer_stream so far has run. Step s of size - 1 sends the own slice
+ *                               to rank + s and receives that of rank - s; nothing is waited for here
+ *   difb200_sharded_attention   this rank's queries q8 [Sq,H,128] / qs against the gather buffers k8
+ *                               [size * slice_tokens, KV, 128], ks, v (slice_tokens a multiple of 128,
+ *                               key_valid [size * slice_tokens] marks real tokens): a few launches of
+ *                               difb200_attention_int8_chunk, the own slice first, each ordered behind
+ *                               the ring steps it reads by CUDA events (DIFB200_ATTENTION_GROUPS="1,3,4"
+ *                               sets how many steps each launch takes). world may be NULL (one rank)
+ *   difb200_world_plan          the launch plan itself (host only): tile ranges, first ring step and
+ *                               number of steps of every launch
+ * A rank that is lost while an exchange is in flight is not detected here (NCCL has no deadline of
+ * its own); hosts that need that put a heartbeat in front of every step.
+ */
+DIFB200_EXPORT int difb200_world_unique_id(uint8_t *id128);
+DIFB200_EXPORT int difb200_world_rendezvous(const char *directory, int32_t rank, int32_t size, uint8_t *id128,
+                                            uint32_t timeout_ms);
+DIFB200_EXPORT int difb200_world_create(const uint8_t *id128, int32_t rank, int32_t size, void **world);
+DIFB200_EXPORT int difb200_world_destroy(void *world);
+DIFB200_EXPORT int difb200_world_exchange(void *world, int32_t which, void *const *buffers,
+                                          const uint64_t *slice_bytes, int32_t count, void *producer_stream);
+DIFB200_EXPORT int difb200_sharded_attention(void *world, const int8_t *q8, const float *qs, const int8_t *k8,
+                                             const float *ks, const void *v, const uint8_t *key_valid,
+                                             uint64_t Sq, uint64_t slice_tokens, uint64_t H, uint64_t KV,
+                                             float scale, void *scratch, uint64_t scratch_bytes, void *state,
+                                             void *out, void *stream);
+DIFB200_EXPORT int difb200_world_plan(int32_t rank, int32_t size, uint32_t tiles_per_slice,
+                                      const int32_t *group_sizes, int32_t group_count, uint32_t *tile_ranges,
+                                      int32_t *first_step, int32_t *step_count, int32_t capacity,
+                                      int32_t *launches);
+/*
+ * Host-only check of the exchange schedule: `size` ranks as threads of the calling process run
+ * it over a host-memory transport and compare every gathered byte. With missing_rank >= 0 that
+ * rank never joins and every other rank must return an execution error within timeout_ms.
+ */
+DIFB200_EXPORT int difb200_world_selftest_fake(int32_t size, int32_t missing_rank, uint32_t timeout_ms);
+
+/*
  * Opcode Attention (8) on bf16 q [B,S,H,128], k/v [B,S,KV,128] in its INT8 lowering: q and k
  * are quantised per token-head (QuantizeInt8Rows Direct) into scratch, then
  * difb200_attention_int8 runs. scratch: difb200_attention_scratch_bytes(B,S,H,KV) bytes.

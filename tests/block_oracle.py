@@ -1,22 +1,28 @@
-"""Block-level oracle with the INT8 attention contract in place of exact attention (test
-infrastructure).
+"""Splitting a DiT block program at its Attention op (test infrastructure).
 
-The reference CPU executor evaluates Attention exactly whatever its Implementation attribute says
-(reference tests/exact_stream_attention_tests.cpp:87-88), while this backend runs the INT8
-lowering, whose result sits about 5e-3 to 9e-3 (rel-L2) from the exact one by construction (Q and
-K are INT8 codes). Behind the attention every W8A8 linear re-quantises its input, which turns any
-small input difference into a difference of the size of its own quantisation noise, so at the
-benchmark widths a block output differs from the exact-attention block by more than the 2e-3 bar
-although every operator is within it.
+Why blocks are checked in parts. The reference CPU executor evaluates Attention exactly whatever
+its Implementation attribute says (reference tests/exact_stream_attention_tests.cpp:87-88), while
+this backend runs the INT8 lowering, whose output sits about 5e-3 to 1e-2 (rel-L2) from the exact
+one by construction (Q and K are INT8 codes) and about 3e-4 to 7e-4 from its own CPU contract (the
+tensor core accumulates P.V in another order and precision than a sequential fp32 loop). Behind
+the attention every W8A8 linear re-quantises its input, and a quantiser turns a small input
+difference d into an output difference of about sqrt(d * step): codes that sit near a rounding
+boundary flip. At the benchmark widths (gain of a 3072-wide N(0, 0.02) projection about 1.1) a
+3e-4 difference at the attention output is 3e-3 to 4e-3 at the block output; the same holds for the
+reference itself when its attention output is perturbed that much (see
+test_reference_block_amplifies_a_small_attention_difference in tests/test_oracle_golden.py). So
+a whole block cannot meet 2e-3 against an executor with another attention, although every
+operator does.
 
-To check all other operators of a block at the tight bar, this module runs the reference executor
-on the part of the program before the Attention op, evaluates the attention with
-``orc_attention_int8`` (the CPU statement of the kernel's contract on the reference's own
-QuantizeInt8Rows(Direct) codes), and runs the reference executor on the rest. Programs with exactly
-one Attention without a bias input are supported."""
+Hence: ``split`` cuts a program with exactly one unbiased Attention into the part before it (its
+outputs are the attention operands and everything the second part reads) and the part behind it
+(the attention result becomes an input). Each part runs through the plugin and through the
+reference executor on identical inputs and is compared at the tight bar; the attention operator
+has its own tiers; the whole block is compared at the reference's own bar for an INT8 attention
+route (cosine >= 0.9999, reference tests/owned_attention_tests.cpp:122-157)."""
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, List, Tuple
 
 import numpy as np
 
@@ -24,62 +30,64 @@ import oracle_bridge as ob
 from diffusion_compiler_b200 import diffir as d
 
 
-def _copy_tensors(p):
-    return [d.TensorDesc(t.id, t.dtype, t.roles, list(t.dims)) for t in p.tensors]
+def _sub_program(p: d.Program, ops, make_outputs, final) -> Tuple[d.Program, set]:
+    q = d.Program()
+    used = {t for op in ops for t in list(op.inputs) + list(op.outputs)}
+    produced = {o for op in ops for o in op.outputs}
+    for t in p.tensors:
+        if t.id not in used:
+            continue
+        t = d.TensorDesc(t.id, t.dtype, t.roles, list(t.dims))
+        if t.id in produced:
+            t.roles = int(d.Role.Output) if (t.id in make_outputs or t.id in final) else 0
+        elif not (t.has_role(d.Role.Input) or t.has_role(d.Role.Constant)):
+            t.roles = int(d.Role.Input)
+        q.tensors.append(t)
+    q.operations = list(ops)
+    return q, used
 
 
-def reference_with_int8_attention(p: d.Program, bound: Dict[int, np.ndarray]) -> Dict[int, np.ndarray]:
-    """Outputs of ``p`` as the reference executor computes them, except that the single Attention
-    op is evaluated by the INT8 contract. ``bound`` holds inputs and constants by tensor id."""
+def split(p: d.Program):
+    """(pre program, post program, attention op, ids carried from pre to post)."""
     at = [i for i, op in enumerate(p.operations) if op.opcode == d.Opcode.Attention]
     assert len(at) == 1 and len(p.operations[at[0]].inputs) == 3, "one unbiased Attention expected"
     att = p.operations[at[0]]
     pre_ops, post_ops = p.operations[:at[0]], p.operations[at[0] + 1:]
     made_pre = {o for op in pre_ops for o in op.outputs}
     used_post = {i for op in post_ops for i in op.inputs}
-    carried = (made_pre & used_post) | set(att.inputs)
+    carried = sorted((made_pre & used_post) | set(att.inputs))
     final = {t.id for t in p.with_role(d.Role.Output)}
+    pre, _ = _sub_program(p, pre_ops, set(carried), final)
+    post, _ = _sub_program(p, post_ops, set(), final)
+    return pre, post, att, carried
 
-    def sub_program(ops, extra_outputs, extra_inputs):
-        q = d.Program()
-        used = {t for op in ops for t in list(op.inputs) + list(op.outputs)}
-        for t in _copy_tensors(p):
-            if t.id not in used:
-                continue
-            produced_here = any(t.id in op.outputs for op in ops)
-            if t.id in extra_inputs and not produced_here:
-                t.roles = int(d.Role.Input)
-            elif t.id in extra_outputs and produced_here:
-                t.roles |= int(d.Role.Output)
-            elif not produced_here and not (t.has_role(d.Role.Input) or t.has_role(d.Role.Constant)):
-                t.roles = int(d.Role.Input)
-            elif produced_here and t.has_role(d.Role.Output) and t.id not in final:
-                t.roles = 0
-            q.tensors.append(t)
-        q.operations = list(ops)
-        return q, used
 
-    pre, pre_used = sub_program(pre_ops, carried, set())
-    pre_out, _ = ob.ref().run(pre, {k: v for k, v in bound.items() if k in pre_used})
-    q, k, v = (pre_out[t] for t in att.inputs)
-    qd = p.tensor(att.inputs[0]).dims
-    batched = len(qd) == 4
-    B, S, H, D = (qd if batched else [1] + list(qd))
-    KV = p.tensor(att.inputs[1]).dims[-2]
-    scale = None
-    for a in att.attributes:
-        if a.key == d.AttrKey.AttentionScale:
-            scale = float(np.array([a.bits], np.uint64).view(np.float64)[0])
-    q8, qs = ob.orc().quantize_int8_rows([q.reshape(-1, D)], 1)
-    k8, ks = ob.orc().quantize_int8_rows([k.reshape(-1, D)], 1)
-    attn = ob.orc().attention_int8(q8.reshape(B, S, H, D), qs, k8.reshape(B, S, KV, D), ks,
-                                   np.ascontiguousarray(v).reshape(B, S, KV, D), None, scale)
-    post, post_used = sub_program(post_ops, set(), carried | set(att.outputs))
-    feed = {k_: v_ for k_, v_ in bound.items() if k_ in post_used}
-    for t in carried:
-        if t in post_used:
-            feed[t] = pre_out[t]
-    feed[att.outputs[0]] = attn.reshape(p.tensor(att.outputs[0]).dims)
-    out, _ = ob.ref().run(post, feed)
-    out.update({t: pre_out[t] for t in final if t in pre_out})
+def feed_for(program: d.Program, *sources: Dict[int, np.ndarray]) -> Dict[int, np.ndarray]:
+    """The Input- and Constant-role tensors of ``program`` picked from the given dictionaries."""
+    out = {}
+    for t in program.tensors:
+        if t.has_role(d.Role.Input) or t.has_role(d.Role.Constant):
+            for s in sources:
+                if t.id in s:
+                    out[t.id] = s[t.id]
+                    break
+            else:
+                raise KeyError("no value for tensor %d" % t.id)
+    return out
+
+
+def constants_of(program: d.Program, consts: Dict[int, np.ndarray]) -> Dict[int, np.ndarray]:
+    return {t.id: consts[t.id] for t in program.tensors if t.has_role(d.Role.Constant)}
+
+
+def inputs_of(program: d.Program, *sources: Dict[int, np.ndarray]) -> Dict[int, np.ndarray]:
+    out = {}
+    for t in program.tensors:
+        if t.has_role(d.Role.Input):
+            for s in sources:
+                if t.id in s:
+                    out[t.id] = s[t.id]
+                    break
+            else:
+                raise KeyError("no value for input tensor %d" % t.id)
     return out

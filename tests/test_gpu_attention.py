@@ -107,3 +107,45 @@ def test_attention_repeatable(ops):
     b = ops.attention(to_torch_bf16(q), to_torch_bf16(k), to_torch_bf16(v))
     torch.cuda.synchronize()
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("B,Sq,Sk,H,KV,masked,q_gain", [(1, 300, 1100, 4, 2, True, 1.0), (2, 256, 640, 2, 2, False, 1.0),
+                                                        (1, 200, 900, 2, 1, True, 6.0)])
+def test_attention_chunked_launches_match_the_single_launch(ops, B, Sq, Sk, H, KV, masked, q_gain):
+    """The chunked form (keys taken in several launches that carry m, l and the fp32 outputs of
+    every query row) against the single launch over all keys: in ring order as the token-sharded
+    block consumes slices (own slice first, then the others, one group wrapping around the end of
+    the key axis), also with the running-maximum path (q_gain 6). Powers of two scale exactly, so
+    only the order of the fp32 sums may differ: rel-L2 <= 1e-4 here, far inside the path's bar."""
+    import torch
+    rng = np.random.default_rng(300 + Sk)
+    q, _, _ = _qkv(rng, B, Sq, H, KV)
+    _, k, v = _qkv(rng, B, Sk, H, KV)
+    if q_gain != 1.0:
+        q = ob.f32_to_bf16(ob.bf16_to_f32(q) * np.float32(q_gain))
+    valid = None
+    if masked:
+        valid = np.ones((B, Sk), np.uint8)
+        valid[:, 250:260] = 0          # a padded slice tail in the middle of the key axis
+        valid[:, Sk - 37:] = 0
+    q8, qs = ob.orc().quantize_int8_rows([q.reshape(-1, 128)], 1)
+    k8, ks = ob.orc().quantize_int8_rows([k.reshape(-1, 128)], 1)
+    t = lambda a: torch.from_numpy(a).cuda()
+    args = (t(q8.reshape(B, Sq, H, 128)), t(qs), t(k8.reshape(B, Sk, KV, 128)), t(ks), to_torch_bf16(v))
+    tv = None if valid is None else t(valid)
+    whole = ops.attention_int8(*args, tv)
+    tiles = (Sk + 127) // 128
+    own = 2 if tiles > 3 else 1  # "this rank's slice" starts at tile `own`
+    groups = [[(own, 1)], [(own + 1, tiles - own - 1), (0, 1)], [(1, own - 1)]] if own == 2 else \
+             [[(own, 1)], [(own + 1, tiles - own - 1), (0, 1)]]
+    groups = [[r for r in g if r[1] > 0] for g in groups]
+    groups = [g for g in groups if g]
+    parts = ops.attention_int8_chunked(*args, groups, tv)
+    same_order = ops.attention_int8_chunked(*args, [[(0, 1)], [(1, tiles - 1)]], tv) if tiles > 1 else whole
+    torch.cuda.synchronize()
+    ops.poll_status()
+    a, b, c = (ob.bf16_to_f32(from_torch_bf16(x)) for x in (parts, whole, same_order))
+    assert np.isfinite(a).all()
+    assert rel_l2(a, b) <= 1e-4 and cosine(a, b) >= 0.999999, (rel_l2(a, b), cosine(a, b))
+    # same tile order as the single launch: the carried state continues the very same sums
+    assert np.array_equal(from_torch_bf16(same_order), from_torch_bf16(whole)) or rel_l2(c, b) <= 1e-5
