@@ -3,16 +3,20 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (N=1 and every N): the DiT projection set of one 1024x1024 image at batch 2 (CFG),
-M = 2 x 4608 tokens per GPU, all W8A8 `int8-convrot` (QuantizeInt8Rows H256ConvRot +
-LinearInt8Scaled + BiasAdd [+ Gelu]): fused QKV 3072->9216, out-proj 3072->3072, MLP up
-3072->12288 (GELU-tanh) and MLP down 12288->3072. One step = one pass over all four. With
-N > 1 every rank runs its own batch (tokens are sharded, weights replicated, no collective on
-the data path): weak scaling. The metric is INT8 TOPS = 2*M*N*K summed over the projections,
-divided by the step time (quantisation kernels included in the time, not in the op count).
+Headline workload (every N): the video DiT block of benchmark configuration 4 -- 21 x 30 x 52 latent
+tokens + 512 text tokens = 33272 tokens, hidden 3072, 24 heads of 128, FFN 8192 (SwiGLU), 3-axis
+RoPE over 96 of the 128 head dimensions, every Linear W8A8 `int8-convrot`, INT8 attention -- as ONE
+DiffIR program through the backend plugin C-ABI. One step = one pass over the block. With N > 1
+the tokens are sharded over the N GPUs (strong scaling: the total work is fixed): every rank runs
+the same program on its slice through its own plugin context, and the plugin exchanges the INT8
+key codes, their scales and the bf16 values over NCCL inside the library. The metric is
+tokens per second of the whole job.
 
-Prints ONE JSON line on rank 0. Synthetic data: seeded N(0,1) bf16 activations with 32 outlier
-channels x16, N(0,0.02) weights quantised by the same ConvRot transform, N(0,0.01) bias.
+`value`: device time of the timed passes of execute() (inputs already in HBM), max over ranks.
+`e2e`: the same call per step with the per-rank inputs in pinned HOST memory and the output read
+back, wall clock, copies inside the timed region. Prints ONE JSON line on rank 0. Synthetic data:
+seeded N(0,1) bf16 activations, N(0,0.02) weights quantised by the same ConvRot transform,
+modulation from one conditioning vector through a random linear map.
 """
 from __future__ import annotations
 
@@ -21,13 +25,14 @@ import json
 import os
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-PROJECTIONS = [  # name, K, N, gelu
+PROJECTIONS = [  # benchmark configuration 1: name, K, N, gelu
     ("qkv", 3072, 9216, False),
     ("out_proj", 3072, 3072, False),
     ("mlp_up", 3072, 12288, True),
@@ -35,6 +40,9 @@ PROJECTIONS = [  # name, K, N, gelu
 ]
 M_TOKENS = 2 * 4608
 H256_CONVROT = 2
+VIDEO = dict(tokens=21 * 30 * 52 + 512, hidden=3072, heads=24, dim=128, ffn=8192, rotary=96)
+NOMINAL_INT8_TOPS, NOMINAL_BF16_TFLOPS = 4500.0, 2250.0
+OP_ATTENTION, OP_LINEAR_I8, OP_QUANT = 8, 68, 67
 
 
 def measured_peaks():
@@ -54,7 +62,7 @@ def recorded_traffic(kernel: str, operand_bytes: float, output_bytes: float):
     The committed ncu capture holds dram__bytes_read/write of one launch on a small case together
     with that case's operand and output bytes; reads scale with the operand bytes (every operand
     byte is fetched once) and writes with the output bytes, so the figure returned is the capture
-    scaled to the average launch of this benchmark (operand_bytes / output_bytes per launch)."""
+    scaled to the launch measured here."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
     try:
         with open(path) as f:
@@ -66,7 +74,7 @@ def recorded_traffic(kernel: str, operand_bytes: float, output_bytes: float):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -87,6 +95,7 @@ class ClockSampler:
             self.thread.start()
         except Exception:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -118,7 +127,204 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
 
 
-def synth_inputs(torch, device, seed: int):
+# ---------------------------------------------------------------------------------------------
+# the video block through the plugin
+# ---------------------------------------------------------------------------------------------
+
+def video_block_weights(device, seed=4):
+    """Seeded weights of the block, the same on every rank: {name: (codes, scales)} and tables."""
+    import numpy as np
+    from diffusion_compiler_b200 import blocks
+    rng = np.random.default_rng(seed)
+    quantize = blocks.gpu_weight_quantizer(str(device))
+    h, f = VIDEO["hidden"], VIDEO["ffn"]
+    shapes = {"q": (h, h), "k": (h, h), "v": (h, h), "o": (h, h), "fc1": (2 * f, h), "fc2": (h, f)}
+    return {name: quantize(blocks.random_bf16(rng, shape, 0.02)) for name, shape in shapes.items()}
+
+
+def video_block_slice(weights, positions, lo, hi, seed_rows=100):
+    """(program, ids, constants) of the block for the token rows [lo, hi) of a sequence whose
+    (t, h, w) positions are `positions`: the per-rank program of the token-sharded run, or the
+    whole block for lo = 0, hi = S."""
+    import numpy as np
+    from diffusion_compiler_b200 import blocks
+    v = VIDEO
+    p, ids = blocks.video_block_program(hi - lo, v["hidden"], v["heads"], v["dim"], v["ffn"], v["rotary"])
+    consts = {}
+    for name, (w, cs, b, N, K) in ids["linears"].items():
+        consts[w], consts[cs] = weights[name]
+    one_h = blocks.f32_to_bf16(np.ones(v["hidden"], np.float32))
+    one_d = blocks.f32_to_bf16(np.ones(v["dim"], np.float32))
+    consts[ids["norm1"]], consts[ids["norm2"]] = one_h, one_h.copy()
+    consts[ids["q_norm"]], consts[ids["k_norm"]] = one_d, one_d.copy()
+    cosv, sinv = blocks.rope_tables_3axis(positions, v["rotary"])
+    consts[ids["cos"]], consts[ids["sin"]] = np.ascontiguousarray(cosv[lo:hi]), np.ascontiguousarray(sinv[lo:hi])
+    return p, ids, consts
+
+
+def video_block_inputs(torch, ids, tokens, lo, hi, seed=7):
+    """Pinned host inputs of the rows [lo, hi): x and the six modulation tensors (each row of a
+    modulation tensor is the same vector, from one conditioning vector through a random linear map).
+    Every rank derives its rows from the same seeded full-sequence tensors."""
+    import numpy as np
+    g = torch.Generator().manual_seed(seed)
+    hidden = VIDEO["hidden"]
+    cond = torch.randn(64, generator=g)
+    inputs, keep = {}, []
+    x_rows = torch.empty(hi - lo, hidden, dtype=torch.bfloat16).pin_memory()
+    # rows are generated in blocks of 1024 tokens so that a slice equals the same rows of the whole
+    block = 1024
+    for first in range(0, tokens, block):
+        if first + block <= lo or first >= hi:
+            continue
+        gb = torch.Generator().manual_seed(seed * 100003 + first)
+        rows = torch.randn(min(block, tokens - first), hidden, generator=gb).to(torch.bfloat16)
+        a, b = max(first, lo), min(first + rows.shape[0], hi)
+        if a < b:
+            x_rows[a - lo:b - lo] = rows[a - first:b - first]
+    keep.append(x_rows)
+    inputs[ids["x"]] = x_rows.view(torch.int16).numpy().view(np.uint16)
+    for m in ids["mods"]:
+        proj = torch.randn(hidden, 64, generator=g) * 0.02
+        vec = (proj @ cond).to(torch.bfloat16)
+        t = vec[None, :].expand(hi - lo, hidden).contiguous().pin_memory()
+        keep.append(t)
+        inputs[m] = t.view(torch.int16).numpy().view(np.uint16)
+    return inputs, keep
+
+
+def pinned_output(torch, program, tid):
+    import numpy as np
+    t = torch.empty(tuple(program.tensor(tid).dims), dtype=torch.int16).pin_memory()
+    return t, t.numpy().view(np.uint16)
+
+
+def video_block_parity(torch, dist, device_index, rank, world, weights):
+    """Sharded against unsharded on real NCCL ranks: a reduced sequence (a 4 x 6 x 21 grid + 101 text
+    tokens = 605 tokens, uneven over the ranks) at the block's true widths. Every rank runs its slice
+    of ONE seeded input through its world context; rank 0 also runs the whole sequence through a
+    single-GPU context and compares: the attention output (the only operator that sees other ranks'
+    data; only the order of its fp32 sums may differ) and the block output (behind the attention
+    every W8A8 linear re-quantises, which amplifies that to a few 1e-4)."""
+    import numpy as np
+    from diffusion_compiler_b200 import blocks, diffir, plugin
+    from diffusion_compiler_b200.sequence_shard import ShardPlan
+    tokens = 4 * 6 * 21 + 101
+    positions = blocks.video_positions(grid=(4, 6, 21), text_tokens=101)
+    plan = ShardPlan.make(tokens, world)
+    lo, hi = plan.bounds(rank)
+
+    def run(executor, lo, hi):
+        p, ids, consts = video_block_slice(weights, positions, lo, hi)
+        att = [op for op in p.operations if op.opcode == diffir.Opcode.Attention][0]
+        p.tensor(att.outputs[0]).roles |= int(diffir.Role.Output)
+        inputs, keep = video_block_inputs(torch, ids, tokens, lo, hi, seed=11)
+        prepared = executor.prepare(p, consts)
+        out, _ = prepared.run(inputs)
+        prepared.close()
+        return out[ids["out"]], out[att.outputs[0]]
+
+    sharded = plugin.PluginExecutor(device_index)  # joins the world named by the environment
+    out_rows, attn_rows = run(sharded, lo, hi)
+    sharded.close()
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (out_rows, attn_rows))
+    if rank != 0:
+        return None
+    saved = os.environ.pop("DIFB200_WORLD_SIZE")
+    try:
+        single = plugin.PluginExecutor(device_index)
+        whole_out, whole_attn = run(single, 0, tokens)
+        single.close()
+    finally:
+        os.environ["DIFB200_WORLD_SIZE"] = saved
+    f32 = lambda a: (a.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+    def compare(parts, whole):
+        got = np.concatenate(parts, axis=0)
+        a, b = f32(got).ravel(), f32(whole).ravel()
+        return {"rel_l2": float(np.sqrt(np.sum((a - b) ** 2) / np.sum(b ** 2))),
+                "cosine": float(np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b))),
+                "bit_identical": bool(np.array_equal(got, whole))}
+    res = {"tokens": tokens, "ranks": world, "tokens_per_rank": [plan.local_tokens(r) for r in range(world)],
+           "attention": compare([g[1] for g in gathered], whole_attn),
+           "block": compare([g[0] for g in gathered], whole_out)}
+    res["ok"] = bool(res["attention"]["rel_l2"] <= 1e-4 and res["block"]["rel_l2"] <= 1e-3
+                     and res["block"]["cosine"] >= 0.9999)
+    return res
+
+
+def run_video_block(torch, dist, args, rank, local_rank, world, device, barrier, reduce_max):
+    """The headline: device-timed passes, end-to-end steps, per-opcode times of the timed passes."""
+    from diffusion_compiler_b200 import _lib, blocks, plugin
+    from diffusion_compiler_b200.sequence_shard import ShardPlan
+    S = VIDEO["tokens"]
+    weights = video_block_weights(device)
+    parity = video_block_parity(torch, dist, local_rank, rank, world, weights) if world > 1 else None
+    plan = ShardPlan.make(S, world)
+    lo, hi = plan.bounds(rank)
+    positions = blocks.video_positions()
+    p, ids, consts = video_block_slice(weights, positions, lo, hi)
+    inputs, keep = video_block_inputs(torch, ids, S, lo, hi)
+    out_t, out_np = pinned_output(torch, p, ids["out"])
+    outputs = {ids["out"]: out_np}
+    executor = plugin.PluginExecutor(local_rank)
+    prepared = executor.prepare(p, consts)
+    del weights
+    prepared.run(inputs, warmups=1, iterations=1, outputs=outputs)  # first-use set-up of every kernel
+    prepared.profile()
+    lib = _lib.lib()
+    # --- timed region: W warm-up passes, then K timed passes inside one execute() ---
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    if rank == 0:
+        time.sleep(0.3)
+    barrier()
+    launches_before = int(lib.difb200_launch_count())
+    t0 = time.perf_counter()
+    _, tel = prepared.run(inputs, warmups=max(args.warmup, 3), iterations=args.steps, outputs=outputs)
+    barrier()
+    wall_s = time.perf_counter() - t0
+    passes = max(args.warmup, 3) + args.steps  # the counter also saw the warm-up passes of the call
+    launches = (int(lib.difb200_launch_count()) - launches_before) * args.steps // passes
+    clocks = sampler.stop() if sampler else None
+    profile = prepared.profile()
+    ms_per_step = reduce_max(tel.mean_milliseconds)
+    # --- end to end: one execute() per step, pinned host inputs in, output back ---
+    n_e2e = max(3, min(args.steps, 10))
+    prepared.run(inputs, outputs=outputs)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        prepared.run(inputs, outputs=outputs)
+    barrier()
+    e2e_ms = reduce_max((time.perf_counter() - t0) * 1e3 / n_e2e)
+    h2d = sum(a.nbytes for a in inputs.values())
+    d2h = out_np.nbytes
+    # --- sustained: the same pass for about two seconds, with the clocks it runs at ---
+    sustained = None
+    if world == 1 and not args.no_extras:
+        n = max(10, int(2200.0 / max(ms_per_step, 1e-3)))
+        s2 = ClockSampler(local_rank).start()
+        time.sleep(0.2)
+        _, tel2 = prepared.run(inputs, warmups=0, iterations=n, outputs=outputs)
+        c2 = s2.stop()
+        sustained = {"passes": n, "ms_per_step": tel2.mean_milliseconds,
+                     "tokens_per_s": S / (tel2.mean_milliseconds * 1e-3), "sm_mhz_median": c2["sm_mhz"],
+                     "ms_times_mhz": (tel2.mean_milliseconds * c2["sm_mhz"]) if c2["sm_mhz"] else None,
+                     "reasons": c2["reasons"]}
+    resident = int(prepared.compile_telemetry.resident_bytes)
+    prepared.close()
+    executor.close()
+    return {"S": S, "plan": plan, "ms_per_step": ms_per_step, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": d2h,
+            "launches": launches, "clocks": clocks, "profile": profile, "parity": parity, "sustained": sustained,
+            "resident_bytes": resident, "operations": len(p.operations), "timed_wall_s": wall_s}
+
+
+# ---------------------------------------------------------------------------------------------
+# further configurations, reported beside the headline
+# ---------------------------------------------------------------------------------------------
+
+def synth_projection_set(torch, device, seed: int):
     """Seeded synthetic activations / weights / biases of the projection set, on `device`."""
     from diffusion_compiler_b200 import ops
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -129,17 +335,15 @@ def synth_inputs(torch, device, seed: int):
         x[:, chans] *= 16.0
         w = (torch.randn(N, K, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
         b = (torch.randn(N, generator=g, dtype=torch.float32) * 0.01).to(torch.bfloat16)
-        x_host = x.to(torch.bfloat16).pin_memory()
         w8, ws = ops.quantize_int8_rows([w.to(device)], H256_CONVROT)  # offline weight-side ConvRot
-        layers.append({"name": name, "K": K, "N": N, "gelu": gelu, "x_host": x_host,
-                       "x": x_host.to(device, non_blocking=True), "w8": w8, "ws": ws, "bias": b.to(device),
-                       "codes": torch.empty(M_TOKENS, K, dtype=torch.int8, device=device),
+        layers.append({"name": name, "K": K, "N": N, "gelu": gelu, "x": x.to(torch.bfloat16).to(device),
+                       "w8": w8, "ws": ws, "bias": b.to(device),
                        "out": torch.empty(M_TOKENS, N, dtype=torch.bfloat16, device=device)})
     torch.cuda.synchronize(device)
     return layers
 
 
-def run_step(ops, layers, events=None):
+def run_projection_step(ops, layers, events=None):
     for i, L in enumerate(layers):
         if events is not None:
             events[i][0].record()
@@ -151,62 +355,107 @@ def run_step(ops, layers, events=None):
             events[i][2].record()
 
 
-def plugin_e2e(torch, layers, device_index, steps, barrier):
-    """Times execute() of the plugin on the projection-set program with pinned host buffers."""
-    import numpy as np
-    from diffusion_compiler_b200 import diffir, plugin
-    p = diffir.Program()
-    consts, inputs, outputs = {}, {}, {}
-    for L in layers:
-        K, N = L["K"], L["N"]
-        x = p.add_tensor(diffir.DType.BF16, [M_TOKENS, K], diffir.Role.Input)
-        codes = p.add_tensor(diffir.DType.I8, [M_TOKENS, K])
-        row = p.add_tensor(diffir.DType.F32, [M_TOKENS])
-        w = p.add_tensor(diffir.DType.I8, [N, K], diffir.Role.Constant)
-        cs = p.add_tensor(diffir.DType.F32, [N], diffir.Role.Constant)
-        b = p.add_tensor(diffir.DType.BF16, [N], diffir.Role.Constant)
-        y = p.add_tensor(diffir.DType.BF16, [M_TOKENS, N])
-        yb = p.add_tensor(diffir.DType.BF16, [M_TOKENS, N], diffir.Role.Internal if L["gelu"] else diffir.Role.Output)
-        p.add_op(diffir.Opcode.QuantizeInt8Rows, [x], [codes, row],
-                 [diffir.Attribute.u64(diffir.AttrKey.BlockSize, 256),
-                  diffir.Attribute.u64(diffir.AttrKey.Implementation, H256_CONVROT)])
-        p.add_op(diffir.Opcode.LinearInt8Scaled, [codes, w, row, cs], [y])
-        p.add_op(diffir.Opcode.BiasAdd, [y, b], [yb])
-        out_id = yb
-        if L["gelu"]:
-            out_id = p.add_tensor(diffir.DType.BF16, [M_TOKENS, N], diffir.Role.Output)
-            p.add_op(diffir.Opcode.Gelu, [yb], [out_id], [diffir.Attribute.u64(diffir.AttrKey.Approximation, 1)])
-        consts[w] = L["w8"].cpu().numpy()
-        consts[cs] = L["ws"].cpu().numpy()
-        consts[b] = L["bias"].view(torch.int16).cpu().numpy().view(np.uint16)
-        inputs[x] = L["x_host"].view(torch.int16).numpy().view(np.uint16)          # pinned
-        host_out = torch.empty((M_TOKENS, N), dtype=torch.int16).pin_memory()
-        outputs[out_id] = host_out.numpy().view(np.uint16)                        # pinned
-    ex = plugin.PluginExecutor(device_index)
-    prepared = ex.prepare(p, consts)
-    prepared.run(inputs, warmups=1, iterations=1, outputs=outputs)
-    barrier()
-    t0 = time.perf_counter()
-    device_ms = 0.0
-    for _ in range(steps):
-        _, tel = prepared.run(inputs, warmups=0, iterations=1, outputs=outputs)
-        device_ms += tel.mean_milliseconds
-    wall_ms = (time.perf_counter() - t0) * 1e3 / steps
-    barrier()
-    h2d = sum(a.nbytes for a in inputs.values())
-    d2h = sum(a.nbytes for a in outputs.values())
-    prepared.close()
-    ex.close()
-    return wall_ms, h2d, d2h, device_ms / steps
+def projection_set_extra(torch, ops, device, local_rank, peaks, i8_peak, steps=20):
+    """Benchmark configuration 1 (M = 2 x 4608 tokens; QKV 3072->9216, out 3072->3072, MLP up
+    3072->12288 + GELU, MLP down 12288->3072): INT8 TOPS of the step, the GEMM against the tensor
+    rooflines, the ConvRot quantiser against the HBM roofline, and the same step looped for two
+    seconds with the clocks it runs at."""
+    layers = synth_projection_set(torch, device, seed=0)
+    total_ops = sum(2.0 * M_TOKENS * N * K for _, K, N, _ in PROJECTIONS)
+    for _ in range(5):
+        run_projection_step(ops, layers)
+    torch.cuda.synchronize()
+    events = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in layers] for _ in range(steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for s in range(steps):
+        run_projection_step(ops, layers, events[s])
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    gemm_ms = sum(ev[1].elapsed_time(ev[2]) for s in events for ev in s) / steps
+    quant_ms = sum(ev[0].elapsed_time(ev[1]) for s in events for ev in s) / steps
+    gemm_tops = total_ops / (gemm_ms * 1e-3) / 1e12
+    quant_bytes = sum(3.0 * M_TOKENS * K + 4.0 * M_TOKENS for _, K, _, _ in PROJECTIONS)
+    n = max(50, int(2200.0 / ms))
+    sampler = ClockSampler(local_rank).start()
+    time.sleep(0.2)
+    start.record()
+    for _ in range(n):
+        run_projection_step(ops, layers)
+    stop.record()
+    torch.cuda.synchronize()
+    sus_ms = start.elapsed_time(stop) / n
+    clocks = sampler.stop()
+    ops.poll_status()
+    return {
+        "workload": "DiT projection set (benchmark configuration 1), M=9216",
+        "ms_per_step": ms, "int8_tops": total_ops / (ms * 1e-3) / 1e12,
+        "roofline_gemm": {"bound": "tensor", "kernel": "gemm_i8_kernel (tcgen05 kind::i8)", "achieved": gemm_tops,
+                          "unit": "TOP/s", "peak_i8_measured": i8_peak,
+                          "frac_of_measured_i8_peak": (gemm_tops / i8_peak["tops"]) if i8_peak else None,
+                          "frac_of_2x_bf16_burst": gemm_tops / (2.0 * peaks["bf16_tflops"]),
+                          "frac_of_2x_bf16_sustained": gemm_tops / (2.0 * peaks["bf16_tflops_sustained"]),
+                          "frac_of_nominal_4500": gemm_tops / NOMINAL_INT8_TOPS,
+                          "traffic": recorded_traffic(
+                              "gemm_i8_kernel",
+                              sum(M_TOKENS * K + N * K for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS),
+                              sum(2.0 * M_TOKENS * N for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS))},
+        "roofline_quant": {"bound": "hbm", "kernel": "convrot_quant_kernel",
+                           "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                           "frac": quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                           "peak_source": "%s copy bandwidth" % peaks["source"],
+                           "traffic": recorded_traffic(
+                               "convrot_quant_kernel",
+                               sum(2.0 * M_TOKENS * K for _, K, _, _ in PROJECTIONS) / len(PROJECTIONS),
+                               sum(M_TOKENS * K + 4.0 * M_TOKENS for _, K, _, _ in PROJECTIONS) / len(PROJECTIONS))},
+        "sustained": {"steps": n, "ms_per_step": sus_ms, "int8_tops": total_ops / (sus_ms * 1e-3) / 1e12,
+                      "sm_mhz_median": clocks["sm_mhz"], "reasons": clocks["reasons"],
+                      "ms_times_mhz": (sus_ms * clocks["sm_mhz"]) if clocks["sm_mhz"] else None},
+    }
 
 
-def attention_extra(torch, ops, device):
-    """Benchmark configuration 2: INT8 attention, B=2 H=24 S=4608 D=128; dense and GQA(8)+key mask."""
+def attention_tiers(torch, ops, q, k, v, q8, qs, k8, ks, valid, out, heads):
+    """The three accuracy tiers of the INT8 attention on `heads` of batch entry 0, from fp32 torch
+    restatements on the GPU (the CPU oracle runs the same tiers in tests/): T1 against the kernel's
+    own contract on the same codes (22-bit key scales, integer maximum, bf16 P, unrounded sum), T2
+    against fp32 softmax weights on the same codes, T3 against exact attention on the bf16 inputs."""
+    B, S, H, D = q.shape
+    KV = k.shape[2]
+    scale = 1.0 / (D ** 0.5)
+    res = {"t1_rel_l2": [], "t2_rel_l2": [], "t3_rel_l2": [], "t3_cosine": []}
+    for h in heads:
+        kvh = h // (H // KV)
+        keep = slice(None) if valid is None else valid[0].bool()
+        got = out[0, :, h].float()
+        qf, kf, vf = q[0, :, h].float(), k[0, :, kvh].float()[keep], v[0, :, kvh].float()[keep]
+        exact = torch.softmax((qf @ kf.t()) * scale, dim=-1) @ vf
+        acc = (q8[0, :, h].float() @ k8[0, :, kvh].float()[keep].t())  # exact: |acc| < 2^24
+        bits = ks.view(B, -1, KV)[0, :, kvh][keep].contiguous().view(torch.int32)
+        k22 = ((bits + 1 + ((bits >> 2) & 1)) & ~3).view(torch.float32)
+        u = acc * k22[None, :]
+        A = (qs.view(B, S, H)[0, :, h] * (scale * 1.4426950408889634))[:, None]
+        m = torch.ceil((u * A).amax(dim=1, keepdim=True))
+        p = torch.exp2(u * A - m)
+        t2 = (p @ vf) / p.sum(1, keepdim=True)
+        t1 = (p.to(torch.bfloat16).float() @ vf) / p.sum(1, keepdim=True)
+        rel = lambda a, b: float((a - b).double().norm() / b.double().norm())
+        res["t1_rel_l2"].append(rel(got, t1.to(torch.bfloat16).float()))
+        res["t2_rel_l2"].append(rel(got, t2))
+        res["t3_rel_l2"].append(rel(got, exact))
+        res["t3_cosine"].append(float(torch.nn.functional.cosine_similarity(got.double().ravel(), exact.double().ravel(),
+                                                                            dim=0)))
+    return {k_: max(v_) if "rel" in k_ else min(v_) for k_, v_ in res.items()}
+
+
+def attention_extra(torch, ops, device, peaks, i8_peak):
+    """Benchmark configuration 2: INT8 attention, B=2 H=24 S=4608 D=128; dense and GQA(8)+key mask; plus
+    the attention of the video block on its own (S = 33272)."""
     res = []
-    for KV, masked in ((24, False), (8, True)):
-        B, S, H, D = 2, 4608, 24, 128
+    rms = lambda t: (t.float() / t.float().pow(2).mean(-1, keepdim=True).add(1e-6).sqrt()).to(torch.bfloat16)
+    for B, S, H, KV, masked in ((2, 4608, 24, 24, False), (2, 4608, 24, 8, True), (1, VIDEO["tokens"], 24, 24, False)):
+        D = 128
         g = torch.Generator(device=device).manual_seed(2)
-        rms = lambda t: (t.float() / t.float().pow(2).mean(-1, keepdim=True).add(1e-6).sqrt()).to(torch.bfloat16)
         q = rms(torch.randn(B, S, H, D, device=device, generator=g, dtype=torch.float32))
         k = rms(torch.randn(B, S, KV, D, device=device, generator=g, dtype=torch.float32))
         v = torch.randn(B, S, KV, D, device=device, generator=g, dtype=torch.float32).to(torch.bfloat16)
@@ -221,7 +470,7 @@ def attention_extra(torch, ops, device):
         out = torch.empty_like(q)
         for _ in range(3):
             ops.attention_int8(q8, qs, k8, ks, v, valid, out=out)
-        n = 10
+        n = 10 if S < 10000 else 4
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
         ev[0].record()
         for i in range(n):
@@ -230,9 +479,16 @@ def attention_extra(torch, ops, device):
         torch.cuda.synchronize()
         ms = sum(ev[i].elapsed_time(ev[i + 1]) for i in range(n)) / n
         half = 2.0 * B * H * S * sk * D
-        t_ideal_ms = (half / 4500e12 + half / 2250e12) * 1e3
-        res.append({"kv_heads": KV, "key_mask": masked, "ms": ms, "tops_qk_plus_pv": 2 * half / (ms * 1e-3) / 1e12,
-                    "t_ideal_over_t_nominal": t_ideal_ms / ms})
+        t_nominal = (half / (NOMINAL_INT8_TOPS * 1e12) + half / (NOMINAL_BF16_TFLOPS * 1e12)) * 1e3
+        entry = {"B": B, "S": S, "heads": H, "kv_heads": KV, "key_mask": masked, "ms": ms,
+                 "tops_qk_plus_pv": 2 * half / (ms * 1e-3) / 1e12, "t_ideal_over_t_nominal": t_nominal / ms}
+        if i8_peak:
+            t_meas = (half / (i8_peak["tops"] * 1e12) + half / (peaks["bf16_tflops"] * 1e12)) * 1e3
+            entry["t_ideal_over_t_measured_peaks"] = t_meas / ms
+        if S < 10000:
+            entry["tiers"] = attention_tiers(torch, ops, q, k, v, q8, qs, k8, ks, valid, out, heads=[0, H - 1])
+        res.append(entry)
+        del q, k, v, q8, k8, out
     return res
 
 
@@ -246,65 +502,37 @@ def mmdit_block_extra(torch, device_index):
                                                       blocks.gpu_weight_quantizer("cuda:%d" % device_index))
     ex = plugin.PluginExecutor(device_index)
     prepared = ex.prepare(p, consts)
-    t0 = time.perf_counter()
     _, tel = prepared.run(inputs, warmups=2, iterations=5)
-    wall = time.perf_counter() - t0
     tokens = 2 * (4096 + 512)
     res = {"tokens": tokens, "device_ms": tel.mean_milliseconds, "tokens_per_s": tokens / (tel.mean_milliseconds * 1e-3),
-           "operations": len(p.operations), "resident_gb": prepared.compile_telemetry.resident_bytes / 1e9,
-           "execute_wall_s_7_passes_with_copies": wall}
+           "operations": len(p.operations), "resident_gb": prepared.compile_telemetry.resident_bytes / 1e9}
     prepared.close()
     ex.close()
     return res
 
 
-def video_block_extra(torch, device, rank, world, dist, iters=5):
-    """Benchmark configuration 4: the video DiT block, 33272 tokens sharded along tokens over `world` GPUs,
-    all-gather of quantised K (+scales) and bf16 V over NCCL. Strong scaling."""
-    import numpy as np
-    from diffusion_compiler_b200 import blocks
-    from diffusion_compiler_b200.sequence_shard import GatherBuffers, ShardPlan, VideoBlock
-    S, hidden, heads, dim, ffn, rotary = 21 * 30 * 52 + 512, 3072, 24, 128, 8192, 96
-    rng = np.random.default_rng(4)  # same weights on every rank
-    quantize = blocks.gpu_weight_quantizer(str(device))
-    linears = {}
-    for name, (N, K) in (("q", (hidden, hidden)), ("k", (hidden, hidden)), ("v", (hidden, hidden)),
-                         ("o", (hidden, hidden)), ("fc1", (2 * ffn, hidden)), ("fc2", (hidden, ffn))):
-        linears[name] = quantize(blocks.random_bf16(rng, (N, K), 0.02))
-    cosv, sinv = blocks.rope_tables_3axis(blocks.video_positions(), rotary)
-    one_h, one_d = blocks.f32_to_bf16(np.ones(hidden, np.float32)), blocks.f32_to_bf16(np.ones(dim, np.float32))
-    block = VideoBlock({"norm1": one_h, "norm2": one_h, "q_norm": one_d, "k_norm": one_d, "cos": cosv, "sin": sinv,
-                        "linears": linears}, hidden, heads, dim, ffn, rotary, device)
-    plan = ShardPlan.make(S, world)
-    lo, hi = plan.bounds(rank)
-    g = torch.Generator(device=device).manual_seed(100 + rank)
-    x = torch.randn(hi - lo, hidden, device=device, generator=g, dtype=torch.float32).to(torch.bfloat16)
-    mods = [(torch.randn(1, hidden, device=device, generator=g, dtype=torch.float32) * 0.1).to(torch.bfloat16)
-            .expand(hi - lo, hidden).contiguous() for _ in range(6)]
-    gb = GatherBuffers(plan, rank, heads, dim, device)
-    for _ in range(2):
-        block.forward(x, mods, plan, rank, gb=gb)
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    events = {}
-    for _ in range(iters):
-        block.forward(x, mods, plan, rank, gb=gb, events=events)
-    torch.cuda.synchronize()
-    names = ["start", "pre_attention", "gathered", "attention", "end"]
-    seg = {b: sum(events[a][i].elapsed_time(events[b][i]) for i in range(iters)) / iters
-           for a, b in zip(names[:-1], names[1:])}
-    total = sum(events["start"][i].elapsed_time(events["end"][i]) for i in range(iters)) / iters
-    t = torch.tensor([total, seg["pre_attention"], seg["gathered"], seg["attention"], seg["end"]],
-                     dtype=torch.float64, device=device)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total = float(t[0])
-    gather_bytes = (world - 1) * plan.slice_len * heads * (dim + 4 + 2 * dim)
-    return {"tokens": S, "ms_per_block": total, "tokens_per_s": S / (total * 1e-3), "scaling": "strong",
-            "ms_pre_attention": float(t[1]), "ms_all_gather": float(t[2]), "ms_attention": float(t[3]),
-            "ms_post_attention": float(t[4]), "all_gather_bytes_received_per_rank": gather_bytes,
-            "tokens_per_rank": plan.slice_len}
+def measure_i8_peak(torch, local_rank):
+    """tcgen05.mma kind::i8 issue rate with operands resident in shared memory (both instruction
+    forms of the GEMM), with the SM clock sampled while it runs."""
+    import ctypes as C
+    from diffusion_compiler_b200 import _lib
+    lib = _lib.lib()
+    best = None
+    for form in (1, 2):
+        tops, ms = C.c_double(0.0), C.c_double(0.0)
+        sampler = ClockSampler(local_rank).start()
+        time.sleep(0.15)
+        rc = 0
+        for _ in range(6):  # ~20 launches of half a millisecond: long enough for a clock sample or two
+            rc = rc or lib.difb200_measure_i8_mma_peak(form, 8192, C.byref(tops), C.byref(ms), None)
+        clocks = sampler.stop()
+        if rc != 0:
+            continue
+        entry = {"tops": tops.value, "form": "cta_group::%d, M%d N256 K32" % (form, 128 * form), "ms": ms.value,
+                 "sm_mhz_median": clocks["sm_mhz"]}
+        if best is None or entry["tops"] > best["tops"]:
+            best = entry
+    return best
 
 
 def small_case(name: str):
@@ -317,9 +545,17 @@ def small_case(name: str):
         res = mmdit_block_extra(torch, 0)
         print("case mmdit_block done: %.2f ms" % res["device_ms"])
         return
-    if name == "video_block":  # three forwards of the 33272-token block on one GPU (launch lists only)
-        res = video_block_extra(torch, torch.device("cuda:0"), 0, 1, None, iters=1)
-        print("case video_block done: %.2f ms" % res["ms_per_block"])
+    if name == "video_block":  # three passes of the 33272-token block on one GPU (launch lists only)
+        from diffusion_compiler_b200 import blocks, plugin
+        weights = video_block_weights(torch.device("cuda:0"))
+        p, ids, consts = video_block_slice(weights, blocks.video_positions(), 0, VIDEO["tokens"])
+        inputs, keep = video_block_inputs(torch, ids, VIDEO["tokens"], 0, VIDEO["tokens"])
+        ex = plugin.PluginExecutor(0)
+        prepared = ex.prepare(p, consts)
+        _, tel = prepared.run(inputs, warmups=1, iterations=2)
+        print("case video_block done: %.2f ms" % tel.mean_milliseconds)
+        prepared.close()
+        ex.close()
         return
     if name == "gemm":    # the QKV projection of the step: 36 x 36 pair tiles of 256x256, 227 MB
         M, N, K = M_TOKENS, 9216, 3072
@@ -349,50 +585,93 @@ def small_case(name: str):
     print("case %s done" % name)
 
 
-def cpu_reference_sample(threads: int, rows_per_thread: int):
-    """Times the reference CPU executor (oracle/_ref) -- or, where it was not built, the C
-    restatement -- on a row sample of the same four projections, `threads` host threads."""
+# ---------------------------------------------------------------------------------------------
+# the reference's CPU executor on the same block (the CPU baseline and the reference arm)
+# ---------------------------------------------------------------------------------------------
+
+def cpu_reference_block(threads: int, rows: int = 128, attn_tokens: int = 768):
+    """Times the reference CPU executor (oracle/_ref; where it was not built, the C restatement) on a
+    bounded sample of the video block, `threads` host threads, and extrapolates to the 33272-token
+    block. The executor is single-threaded and rows / heads are independent, so every thread runs
+    its own copy of the sample. Sample 1: the whole block program at the true widths on `rows`
+    tokens (its attention is negligible at that length): time per token of everything that grows
+    linearly. Sample 2: an Attention op of one head over `attn_tokens` tokens: time per (query, key,
+    head). Full block = S * t_token + S^2 * 24 * t_pair, divided over the threads."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import numpy as np
     import oracle_bridge as ob
     from concurrent.futures import ThreadPoolExecutor
-    from diffusion_compiler_b200 import diffir
-    rng = np.random.default_rng(0)
+    from diffusion_compiler_b200 import blocks, diffir
     kind = "reference" if ob.ref_available() else "port"
-    jobs = []
-    total_ops = 0.0
-    for name, K, N, gelu in PROJECTIONS:
-        w8 = rng.integers(-127, 128, size=(N, K), dtype=np.int8)
-        ws = (rng.random(N, dtype=np.float32) * 1e-3 + 1e-4).astype(np.float32)
-        bias = ob.f32_to_bf16((rng.standard_normal(N) * 0.01).astype(np.float32))
-        x = ob.f32_to_bf16(rng.standard_normal((rows_per_thread, K)).astype(np.float32))
-        jobs.append((K, N, gelu, x, w8, ws, bias))
-        total_ops += 2.0 * rows_per_thread * N * K * threads
+    v = VIDEO
+    rng = np.random.default_rng(0)
+    # weights need not be ConvRot images of anything for timing: random codes, plausible scales
+    fake = lambda w_bits: (rng.integers(-127, 128, size=w_bits.shape, dtype=np.int8),
+                           (rng.random(w_bits.shape[0], dtype=np.float32) * 1e-3 + 1e-4).astype(np.float32))
+    if kind == "reference":
+        p, ids, consts, inputs = blocks.synth_video_block(rng, rows, v["hidden"], v["heads"], v["dim"], v["ffn"],
+                                                          v["rotary"], fake)
+        bound = {**consts, **inputs}
+        ap = diffir.attention_program(1, attn_tokens, 1, 1, 128, masked=False)
+        a_ids = ap["ids"]
+        a_bound = {a_ids[n]: blocks.random_bf16(rng, (1, attn_tokens, 1, 128), 1.0) for n in ("q", "k", "v")}
 
-    def work(_):
-        for K, N, gelu, x, w8, ws, bias in jobs:
-            if kind == "reference":
-                pr = diffir.w8a8_linear_program(rows_per_thread, K, N, H256_CONVROT, bias=True, gelu=gelu)
-                ids = pr["ids"]
-                ob.ref().run(pr["program"], {ids["x"]: x, ids["weight"]: w8, ids["col_scales"]: ws,
-                                             ids["bias"]: bias})
-            else:
-                c, s = ob.orc().quantize_int8_rows([x], H256_CONVROT)
-                y = ob.orc().bias_add(ob.orc().linear_int8_scaled(c, w8, s, ws), bias)
-                if gelu:
-                    ob.orc().gelu_tanh(y)
+        def block(_):
+            ob.ref().run(p, bound)
 
-    t0 = time.perf_counter()
-    with ThreadPoolExecutor(max_workers=threads) as pool:
-        list(pool.map(work, range(threads)))
-    dt = time.perf_counter() - t0
-    return {"value": total_ops / dt / 1e12, "unit": "TOPS", "cores": threads, "kind": kind,
-            "sample": "%d rows per thread x %d threads of the same 4 projections (full weights), %.1f s"
-                      % (rows_per_thread, threads, dt)}, dt
+        def attention(_):
+            ob.ref().run(ap["program"], a_bound)
+    else:
+        x = blocks.random_bf16(rng, (rows, v["hidden"]), 1.0)
+        shapes = [(v["hidden"], v["hidden"])] * 4 + [(2 * v["ffn"], v["hidden"]), (v["hidden"], v["ffn"])]
+        mats = [fake(np.zeros((n, k), np.uint16)) for n, k in shapes]
+        qkv = blocks.random_bf16(rng, (1, attn_tokens, 1, 128), 1.0)
+
+        def block(_):
+            for (w8, ws), (n, k) in zip(mats, shapes):
+                xin = x if k == v["hidden"] else blocks.random_bf16(rng, (rows, k), 1.0)
+                c, s = ob.orc().quantize_int8_rows([xin], H256_CONVROT)
+                ob.orc().linear_int8_scaled(c, w8, s, ws)
+
+        def attention(_):
+            ob.orc().attention_exact(qkv, qkv, qkv)
+
+    def timed(fn):
+        t0 = time.perf_counter()
+        with ThreadPoolExecutor(max_workers=threads) as pool:
+            list(pool.map(fn, range(threads)))
+        return time.perf_counter() - t0
+
+    t_block = timed(block)
+    t_attn = timed(attention)
+    S = v["tokens"]
+    t_token = t_block / rows                       # seconds per token and thread
+    t_pair = t_attn / (attn_tokens * attn_tokens)  # seconds per (query, key, head) and thread
+    full_s = (S * t_token + float(S) * S * v["heads"] * t_pair) / threads
+    return {"value": S / full_s, "unit": "tokens/s", "cores": threads, "kind": kind,
+            "sample": "%d threads, each: the block at true widths on %d tokens (%.1f s) and Attention of one head "
+                      "on %d tokens (%.1f s); extrapolated as S*t_token + S^2*24*t_pair over the threads"
+                      % (threads, rows, t_block, attn_tokens, t_attn),
+            "sample_seconds": t_block + t_attn, "extrapolated_full_block_seconds": full_s,
+            "seconds_per_token_linear_part": t_token, "seconds_per_query_key_head": t_pair}
 
 
 def emit_json_line(fd: int, line: dict) -> None:
     os.write(fd, (json.dumps(line) + "\n").encode())
+
+
+def workload_config(world: int):
+    v = VIDEO
+    return {"workload": "video DiT block (benchmark configuration 4): %d tokens (21x30x52 latent + 512 text), hidden "
+                        "%d, %d heads x %d, FFN %d SwiGLU, 3-axis RoPE over %d dims, W8A8 int8-convrot linears, INT8 "
+                        "attention; one DiffIR program through the backend plugin"
+                        % (v["tokens"], v["hidden"], v["heads"], v["dim"], v["ffn"], v["rotary"]),
+            "tokens": v["tokens"],
+            "parallelism": "tokens sharded over %d GPU(s), weights replicated, K codes / K scales / V exchanged over "
+                           "NCCL in ring steps, attention starts on the local slice" % world,
+            "quantization": "H256ConvRot activations + per-channel INT8 weights; Q and K per token-head INT8, V bf16",
+            "l2": "one pass streams ~6 GB of activations and weights per GPU at N=1 (0.9 GB at N=8), larger than the "
+                  "126 MB L2; no flush"}
 
 
 def main():
@@ -408,19 +687,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-extras", action="store_true", help="skip the attention / block configs")
+    ap.add_argument("--no-extras", action="store_true", help="skip the projection-set / attention / MMDiT configs")
     ap.add_argument("--case", choices=["gemm", "quant", "attention", "video_block", "mmdit_block"],
                     help="run 3 launches of one kernel on a small case and exit (the command profiled with ncu)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    total_ops = sum(2.0 * M_TOKENS * N * K for _, K, N, _ in PROJECTIONS)
-    config = {"workload": "DiT projection set (benchmark configuration 1): M=2x4608 tokens per GPU, W8A8 int8-convrot "
-                          "QKV 3072->9216, out 3072->3072, MLP up 3072->12288 +GELU, MLP down 12288->3072",
-              "tokens_per_gpu": M_TOKENS, "quantization": "H256ConvRot activations + per-channel INT8 weights",
-              "parallelism": "token-sharded x%d, weights replicated" % max(world, args.gpus),
-              "l2": "inputs+weights+outputs of one step are ~1.1 GB, larger than the 126 MB L2; no flush"}
+    config = workload_config(max(world, 1))
 
     if args.case:
         small_case(args.case)
@@ -429,23 +703,25 @@ def main():
         if rank != 0:
             return
         threads = os.cpu_count() or 1
-        rows = 256
-        steps = max(1, min(args.steps, 3))
-        vals = []
+        steps = max(1, min(args.steps, 2))
+        runs = []
         for _ in range(min(args.warmup, 1)):
-            cpu_reference_sample(threads, 8)
+            cpu_reference_block(threads, rows=8, attn_tokens=128)
+        t0 = time.perf_counter()
         for _ in range(steps):
-            res, dt = cpu_reference_sample(threads, rows)
-            vals.append(res)
-        best = max(vals, key=lambda r: r["value"])
-        ms = total_ops / (best["value"] * 1e12) * 1e3
-        line = {"impl": "reference", "metric": "int8_tops_w8a8_projection_set", "value": best["value"],
-                "unit": "TOPS", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
-                "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            runs.append(cpu_reference_block(threads))
+        measured_ms = (time.perf_counter() - t0) * 1e3 / steps
+        best = max(runs, key=lambda r: r["value"])
+        line = {"impl": "reference", "metric": "video_dit_block_tokens_per_s", "value": best["value"],
+                "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+                "ms_per_step": measured_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int8", "data": "synthetic", "config": config, "cpu_baseline": best,
-                "e2e": {"value": best["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                "note": "reference CPU executor on host cores; ms_per_step is the full-workload time "
-                        "extrapolated from the row sample"}
+                "e2e": {"value": best["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "extrapolated_full_block_ms": best["extrapolated_full_block_seconds"] * 1e3,
+                "note": "reference CPU executor on all host threads. A step of this arm is the bounded sample named in "
+                        "cpu_baseline.sample, and ms_per_step is its measured wall time; value is the tokens/s of the "
+                        "full 33272-token block extrapolated from the sample (the full block is tens of core-hours on "
+                        "the CPU executor, dominated by exact attention)"}
         sys.stdout.flush()
         emit_json_line(json_fd, line)
         return
@@ -457,113 +733,102 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     dist = None
+    os.environ["DIFB200_PROFILE"] = "1"
     if world > 1:
+        # torch.distributed is the benchmark's own plumbing (barriers, the max over ranks, handing
+        # out the rendezvous directory, collecting the parity slices); the block's exchange runs on
+        # the communicator inside the library
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    layers = synth_inputs(torch, device, seed=rank)
+        box = [tempfile.mkdtemp(prefix="difb200_world_") if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        os.environ.update(DIFB200_WORLD_SIZE=str(world), DIFB200_WORLD_RANK=str(rank), DIFB200_WORLD_DIR=box[0])
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        run_step(ops, layers)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    # --- timed region: K steps, device-resident inputs ---
-    gemm_events = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)]
-                    for _ in layers] for _ in range(args.steps)]
-    barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for s in range(args.steps):
-        run_step(ops, layers, gemm_events[s])
-    stop.record()
-    barrier()
-    elapsed_ms = start.elapsed_time(stop)
+    def reduce_max(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    peaks = measured_peaks()
+    i8_peak = measure_i8_peak(torch, local_rank) if rank == 0 else None
+    block = run_video_block(torch, dist, args, rank, local_rank, world, device, barrier, reduce_max)
     ops.poll_status()
-    # --- end-to-end: the reference-facing call. The same four projections as ONE DiffIR program
-    # through the backend plugin C-ABI (dif_backend_get_v2: compile once, then execute per step)
-    # with pinned HOST buffers: every step copies the activations in and the bf16 outputs out. ---
-    e2e_ms, h2d, d2h, e2e_device_ms = plugin_e2e(torch, layers, local_rank, max(3, min(args.steps, 10)), barrier)
-    clocks = sampler.stop() if rank == 0 else None
-
-    t = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = float(t[0]), float(t[1])
-    ms_per_step = elapsed_ms / args.steps
-    value = world * total_ops / (ms_per_step * 1e-3) / 1e12
-
+    S, ms = block["S"], block["ms_per_step"]
+    line = None
     if rank == 0:
-        peaks = measured_peaks()
-        # dominant kernel: the tcgen05 GEMM. achieved = algorithmic 2*M*N*K per launch / launch time
-        gemm_ms = quant_ms_total = 0.0
-        for s in range(args.steps):
-            for ev in gemm_events[s]:
-                quant_ms_total += ev[0].elapsed_time(ev[1])
-                gemm_ms += ev[1].elapsed_time(ev[2])
-        gemm_tops = args.steps * total_ops / (gemm_ms * 1e-3) / 1e12
-        int8_peak = 2.0 * peaks["bf16_tflops"]
-        quant_bytes = sum(3.0 * M_TOKENS * K + 4.0 * M_TOKENS for _, K, _, _ in PROJECTIONS)
-        quant_ms = quant_ms_total / args.steps
-        line = {
-            "metric": "int8_tops_w8a8_projection_set", "value": value, "unit": "TOPS", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
-            "data": "synthetic", "config": config,
-            "e2e": {"value": world * total_ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "kernel_stream_ms_per_step": e2e_device_ms,
-                    "path": "backend plugin C-ABI (dif_backend_get_v2 execute): pinned host activations in, "
-                            "4x(QuantizeInt8Rows+LinearInt8Scaled+BiasAdd[+Gelu]) on device, bf16 outputs to pinned host; "
-                            "uploads, kernels and downloads overlap on three streams inside execute"},
-            "gpu_launches": args.steps * 2 * len(layers),
-            "roofline": {"bound": "tensor", "kernel": "gemm_i8_kernel (tcgen05 kind::i8)",
-                         "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s", "frac": gemm_tops / int8_peak,
-                         "peak_source": "2 x %s bf16 burst TFLOP/s (INT8 dense = 2x bf16 on B200); nominal 4500"
-                                        % peaks["source"],
-                         "frac_of_nominal_4500": gemm_tops / 4500.0,
-                         "frac_of_2x_sustained_bf16": gemm_tops / (2.0 * peaks["bf16_tflops_sustained"]),
-                         "traffic": recorded_traffic(
-                             "gemm_i8_kernel",
-                             sum(M_TOKENS * K + N * K for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS),
-                             sum(2.0 * M_TOKENS * N for _, K, N, _ in PROJECTIONS) / len(PROJECTIONS)),
-                         "traffic_note": "bytes per launch: ncu capture of the QKV launch (M=9216 N=9216 K=3072) scaled by "
-                                         "operand and output bytes to the average of the 4 launches of a step"},
-            "roofline_quant": {"bound": "hbm", "kernel": "convrot_quant_kernel",
-                               "achieved": quant_bytes / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
-                               "unit": "GB/s", "frac": quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                               "note": "CUDA events around the 4 quantize launches of every step",
-                               "traffic": recorded_traffic(
-                                   "convrot_quant_kernel",
-                                   sum(2.0 * M_TOKENS * K for _, K, _, _ in PROJECTIONS) / len(PROJECTIONS),
-                                   sum(M_TOKENS * K + 4.0 * M_TOKENS for _, K, _, _ in PROJECTIONS) / len(PROJECTIONS))},
-            "clocks": clocks,
+        prof = block["profile"]
+        per_step = lambda op: (prof[op][0] / args.steps, prof[op][1] // args.steps) if op in prof else (None, 0)
+        attn_ms, attn_steps = per_step(OP_ATTENTION)
+        gemm_ms, gemm_steps = per_step(OP_LINEAR_I8)
+        quant_ms, _ = per_step(OP_QUANT)
+        local = block["plan"].local_tokens(0)
+        half = 2.0 * VIDEO["heads"] * local * S * VIDEO["dim"]   # QK^T (int8) or P.V (bf16) ops on this rank
+        i8 = i8_peak["tops"] if i8_peak else 2.0 * peaks["bf16_tflops"]
+        t_meas = (half / (i8 * 1e12) + half / (peaks["bf16_tflops"] * 1e12)) * 1e3
+        t_nom = (half / (NOMINAL_INT8_TOPS * 1e12) + half / (NOMINAL_BF16_TFLOPS * 1e12)) * 1e3
+        gemm_ops = 2.0 * local * sum(n * k for n, k in ((3072, 3072),) * 4 + ((16384, 3072), (3072, 8192)))
+        roofline = {
+            "bound": "tensor", "kernel": "attn_i8_kernel (tcgen05 kind::i8 QK^T + kind::f16 P.V, 70 % of the step)",
+            "achieved": (2.0 * half / (attn_ms * 1e-3) / 1e12) if attn_ms else None,
+            "peak": 2.0 * half / (t_meas * 1e-3) / 1e12, "unit": "TOP/s",
+            "frac": (t_meas / attn_ms) if attn_ms else None,
+            "frac_of_nominal": (t_nom / attn_ms) if attn_ms else None,
+            "peak_source": "harmonic mix of the two precisions: QK^T at the %s INT8 MMA rate (%.0f TOPS), P.V at the "
+                           "%s bf16 burst figure (%.0f TFLOP/s); frac = t_ideal / t"
+                           % ("measured" if i8_peak else "2 x bf16", i8, peaks["source"], peaks["bf16_tflops"]),
+            "ms_per_launch": attn_ms, "launches_per_step": attn_steps,
+            "note": "attention step of the timed passes, CUDA events on the plugin's kernel stream (key table "
+                    "kernel included; with N > 1 also the waits for slices still in flight)",
+            "traffic": recorded_traffic("attn_i8_kernel",
+                                        local * VIDEO["heads"] * 128.0 + S * VIDEO["heads"] * (128.0 + 256.0 + 8.0),
+                                        2.0 * local * VIDEO["heads"] * 128.0),
         }
+        line = {
+            "metric": "video_dit_block_tokens_per_s", "value": S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": config,
+            "e2e": {"value": S / (block["e2e_ms"] * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": block["h2d"],
+                    "d2h_bytes_per_step": block["d2h"], "ms_per_step": block["e2e_ms"],
+                    "path": "backend plugin C-ABI (dif_backend_get_v2 execute), one call per step and rank: x and the six "
+                            "full-shape modulation tensors of the rank's token slice from pinned host memory, the block "
+                            "on the device (NCCL exchange inside the library), the output slice back to pinned host "
+                            "memory; bytes are per rank"},
+            "gpu_launches": block["launches"],
+            "roofline": roofline,
+            "step_breakdown_ms": {"attention": attn_ms, "w8a8_gemms": gemm_ms, "convrot_quantisers": quant_ms,
+                                  "gemm_tops": (gemm_ops / (gemm_ms * 1e-3) / 1e12) if gemm_ms else None,
+                                  "everything_else": (ms - (attn_ms or 0) - (gemm_ms or 0) - (quant_ms or 0))},
+            "peak_i8_measured": i8_peak,
+            "clocks": block["clocks"],
+            "plugin": {"operations": block["operations"], "resident_gb": block["resident_bytes"] / 1e9},
+        }
+        if block["parity"] is not None:
+            line["parity"] = block["parity"]
+        if block["sustained"] is not None:
+            line["sustained"] = block["sustained"]
         if world == 1 and not args.no_cpu_baseline:
-            threads = os.cpu_count() or 1
-            res, _ = cpu_reference_sample(threads, 512)
-            line["cpu_baseline"] = res
-    extras = {}
-    if not args.no_extras:
+            line["cpu_baseline"] = cpu_reference_block(os.cpu_count() or 1)
+    if not args.no_extras and rank == 0 and world == 1:
         # the further benchmark configurations, reported beside the headline (not part of `value`)
-        extras["video_block"] = video_block_extra(torch, device, rank, world, dist)
-        if rank == 0:
-            extras["attention"] = attention_extra(torch, ops, device)
-            if world == 1:
-                extras["mmdit_block"] = mmdit_block_extra(torch, local_rank)
+        line["projection_set"] = projection_set_extra(torch, ops, device, local_rank, peaks, i8_peak)
+        line["attention"] = attention_extra(torch, ops, device, peaks, i8_peak)
+        line["mmdit_block"] = mmdit_block_extra(torch, local_rank)
         ops.poll_status()
     if rank == 0:
-        line.update(extras)
         sys.stdout.flush()
         emit_json_line(json_fd, line)
+    bad_parity = bool(block["parity"] is not None and not block["parity"]["ok"])
     if dist is not None:
+        dist.barrier()
         dist.destroy_process_group()
+    if bad_parity:
+        raise SystemExit("the token-sharded block differs from the unsharded one beyond the bar: %s" % block["parity"])
 
 
 if __name__ == "__main__":

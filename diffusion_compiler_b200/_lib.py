@@ -28,6 +28,7 @@ def lib() -> C.CDLL:
         L.difb200_last_error.restype = C.c_char_p
         L.difb200_version.restype = C.c_int
         L.difb200_poll_status.restype = C.c_int
+        L.difb200_launch_count.restype = u64
         L.difb200_set_wait_limit_ns.restype = None
         L.difb200_set_wait_limit_ns.argtypes = [u64]
         L.difb200_test_withhold_gemm_load.restype = None
@@ -70,6 +71,11 @@ def lib() -> C.CDLL:
                 ("difb200_world_selftest_fake", [i32, i32, u32])):
             getattr(L, name).restype = C.c_int
             getattr(L, name).argtypes = args
+        L.difb200_measure_i8_mma_peak.restype = C.c_int
+        L.difb200_measure_i8_mma_peak.argtypes = [i32, u32, C.POINTER(C.c_double), C.POINTER(C.c_double), vp]
+        L.difb200_executable_profile.restype = C.c_int
+        L.difb200_executable_profile.argtypes = [vp, C.POINTER(u32), C.POINTER(C.c_double), C.POINTER(u64), u32,
+                                                 C.POINTER(u32)]
         L.difb200_attention_scratch_bytes.restype = u64
         L.difb200_attention_scratch_bytes.argtypes = [u64, u64, u64, u64]
         L.difb200_attention.restype = C.c_int

@@ -702,7 +702,7 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
     key_table_kernel<<<(unsigned)blocks, 128, 0, stream>>>(k8, ks, key_valid, reinterpret_cast<float *>(table),
                                                            tile_bound, (uint32_t)S, (uint32_t)KV, s_pad, begin[0],
                                                            count[0], begin[1], count[1]);
-    if (int rc = check_cuda(cudaGetLastError(), "key_table_kernel launch"))
+    if (int rc = launched(cudaGetLastError(), "key_table_kernel launch"))
       return rc;
   }
   AttnParams p{};
@@ -732,7 +732,7 @@ int attention_int8(const int8_t *q8, const float *qs, const int8_t *k8, const fl
   }
   const uint64_t grid = B * H * ((Sq + 255) / 256);
   attn_i8_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
-  return check_cuda(cudaGetLastError(), "attn_i8_kernel launch");
+  return launched(cudaGetLastError(), "attn_i8_kernel launch");
 }
 
 } // namespace difb200

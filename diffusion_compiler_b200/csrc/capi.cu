@@ -80,7 +80,9 @@ extern "C" {
 
 const char *difb200_last_error(void) { return last_error().c_str(); }
 
-int difb200_version(void) { return 1; }
+int difb200_version(void) { return 2; }
+
+uint64_t difb200_launch_count(void) { return launch_count(); }
 
 int difb200_poll_status(void) {
   if (int rc = check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"))

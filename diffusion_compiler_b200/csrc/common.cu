@@ -69,6 +69,16 @@ int check_cuda(cudaError_t code, const char *what) {
   return fail(code == cudaErrorMemoryAllocation ? kOutOfMemory : kExecutionError, text);
 }
 
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+}
+int launched(cudaError_t code, const char *what) {
+  if (code == cudaSuccess)
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  return check_cuda(code, what);
+}
+unsigned long long launch_count() { return g_launches.load(); }
+
 int sm_count() {
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess)

@@ -24,6 +24,9 @@ enum Status : int {
 void set_last_error(const std::string &text);
 int fail(int status, const std::string &text);
 int check_cuda(cudaError_t code, const char *what);
+// check_cuda for the status of a kernel launch; counts the launches of this process (launch_count).
+int launched(cudaError_t code, const char *what);
+unsigned long long launch_count();
 int sm_count();
 
 // One-time set-up that is per device, not per process (function attributes and occupancy

@@ -819,7 +819,7 @@ int launch_convrot_impl(const QuantParams &p, cudaStream_t stream) {
   if (grid > batches)
     grid = batches;
   kernel<<<(unsigned)grid, threads, smem, stream>>>(p, warps_per_row, rows_per_cta);
-  return check_cuda(cudaGetLastError(), "convrot_quant_kernel launch");
+  return launched(cudaGetLastError(), "convrot_quant_kernel launch");
 }
 
 template <bool SIGNED, bool F32, bool H4096>
@@ -911,7 +911,7 @@ int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, ui
       direct_quant_kernel<true><<<(unsigned)blocks, threads, 0, stream>>>(p);
     else
       direct_quant_kernel<false><<<(unsigned)blocks, threads, 0, stream>>>(p);
-    return check_cuda(cudaGetLastError(), "direct_quant_kernel launch");
+    return launched(cudaGetLastError(), "direct_quant_kernel launch");
   }
   if (implementation < 2 || implementation > 7)
     return fail(kInvalidArgument, "QuantizeInt8Rows: unknown implementation");

@@ -566,7 +566,7 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
     if (pairs > pair_tiles)
       pairs = pair_tiles;
     config.gridDim = dim3((unsigned)(2 * pairs));
-    return check_cuda(cudaLaunchKernelEx(&config, gemm_i8_kernel<2>, map_a, map_b, map_c, p),
+    return launched(cudaLaunchKernelEx(&config, gemm_i8_kernel<2>, map_a, map_b, map_c, p),
                       "gemm_i8_kernel<2> launch");
   }
   const uint64_t tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
@@ -574,7 +574,7 @@ int linear_int8_scaled(const int8_t *x, const int8_t *w, const float *row_scales
   if (grid > tiles)
     grid = tiles;
   gemm_i8_kernel<1><<<(unsigned)grid, kThreads, smem_bytes<1>(), stream>>>(map_a, map_b, map_c, p);
-  return check_cuda(cudaGetLastError(), "gemm_i8_kernel launch");
+  return launched(cudaGetLastError(), "gemm_i8_kernel launch");
 }
 
 } // namespace difb200

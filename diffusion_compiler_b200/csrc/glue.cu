@@ -345,7 +345,7 @@ __global__ void k_linear(const void *x, const void *w, const void *bias, void *o
   }
 }
 
-int done(const char *what) { return check_cuda(cudaGetLastError(), what); }
+int done(const char *what) { return launched(cudaGetLastError(), what); }
 
 } // namespace
 

@@ -359,7 +359,7 @@ inline unsigned blocks_for(uint64_t n, int threads) {
   const uint64_t cap = (uint64_t)sm_count() * 32;
   return (unsigned)(b < 1 ? 1 : (b > cap ? cap : b));
 }
-int done(const char *what) { return check_cuda(cudaGetLastError(), what); }
+int done(const char *what) { return launched(cudaGetLastError(), what); }
 
 } // namespace
 

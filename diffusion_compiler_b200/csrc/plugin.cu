@@ -12,13 +12,28 @@
 // of the reference's INT8 route (src/runtime/cuda_executor.cpp:8422-8423, 3388-3391). The
 // environment variable DIFB200_INT8_ATTENTION=0 turns the lowering off; an Attention that is not
 // admitted is reported as unsupported (there is no exact-attention kernel and no CPU path here).
+//
+// Token-sharded execution. With DIFB200_WORLD_SIZE > 1 in the environment (plus DIFB200_WORLD_RANK
+// and DIFB200_WORLD_DIR, see world.h) create() joins an NCCL world of one process per GPU. Every
+// rank then compiles and executes the SAME program on ITS slice of the tokens (the program's token
+// count is the slice length; weights are replicated as constants), and an Attention op attends from
+// the local queries to the keys and values of all ranks: K codes, K scales and V are produced
+// straight into this rank's slice of full-length gather buffers, exchanged in ring steps on a
+// communication stream as soon as their producers are enqueued (the steps in front of the attention
+// are reordered so that the V and K chains run before the Q chain), and attention runs as a few
+// launches, the own slice first, each behind the ring steps it reads. The reference has no such
+// mode (one device per executor, include/dif/runtime/executor.hpp:683); a single-process host
+// drives one rank exactly as before.
 #include "difb200/abi.h"
+#include "difb200/difb200.h"
 
 #include "common.cuh"
 #include "diffir.h"
 #include "glue.h"
 #include "ops.h"
+#include "world.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -33,6 +48,7 @@ namespace {
 
 struct Context {
   int device = 0;
+  World *world = nullptr;           // token-sharded mode: the NCCL world this context is a rank of
   cudaStream_t stream = nullptr;    // kernels
   cudaStream_t h2d = nullptr;       // uploads of an overlapped execute
   cudaStream_t d2h = nullptr;       // downloads of an overlapped execute
@@ -57,6 +73,22 @@ struct Step {
   bool q_quantised = false, k_quantised = false;
   // QuantizeInt8Rows that also runs the RmsNormModulate (explicit scale / shift) producing its input
   int norm_step = -1;
+  // token-sharded mode: Attention over the gathered keys / values (index into Executable::sharded);
+  // steps after which this rank's V / K slice is final and its ring exchange starts
+  int sharded = -1, exchange_v_for = -1, exchange_k_for = -1;
+};
+
+// Gather buffers and geometry of one token-sharded Attention.
+struct Sharded {
+  size_t step = 0;
+  uint64_t tokens = 0, slice_tokens = 0, heads = 0, kv_heads = 0;
+  int8_t *k8 = nullptr, *q8 = nullptr;   // k8 [size * slice_tokens, KV, 128]; q8 [tokens, H, 128]
+  float *ks = nullptr, *qs = nullptr;
+  void *v = nullptr;                     // bf16 [size * slice_tokens, KV, 128]
+  uint8_t *valid = nullptr;              // [size * slice_tokens]
+  void *scratch = nullptr, *state = nullptr;
+  size_t scratch_bytes = 0;
+  int v_root = -1;                       // tensor whose buffer IS this rank's V slice (-1: V is copied in)
 };
 
 struct Executable {
@@ -66,14 +98,25 @@ struct Executable {
   std::vector<void *> dev;          // device buffer per tensor (nullptr when never materialised)
   std::vector<uint8_t> owned;       // 0 where dev[i] aliases another tensor's buffer (Reshape)
   std::vector<Step> steps;
+  std::vector<size_t> order;        // execution order of the steps (program order unless token-sharded)
+  std::vector<Sharded> sharded;
+  std::vector<void *> world_buffers; // device allocations of the token-sharded mode
   void *attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
   unsigned int *flag = nullptr;     // device flag for data-dependent argument errors
   uint64_t resident_bytes = 0;
   bool constants_bound = false;     // v2: uploaded at compile
   std::vector<cudaEvent_t> uploaded, produced; // per tensor, made on first use by an overlapped execute
+  // DIFB200_PROFILE=1: CUDA events in front of every step of the timed passes; the time between two
+  // of them on the kernel stream is summed per opcode (difb200_executable_profile reads and clears)
+  bool profile = false, profile_pass = false;
+  std::vector<cudaEvent_t> profile_events;
+  std::vector<uint32_t> profile_opcodes;        // opcode of the step that follows event i of this pass
+  std::map<uint32_t, std::pair<double, uint64_t>> profile_sum;
   ~Executable() {
     cudaSetDevice(device);
+    for (cudaEvent_t e : profile_events)
+      cudaEventDestroy(e);
     for (cudaEvent_t e : uploaded)
       if (e)
         cudaEventDestroy(e);
@@ -83,6 +126,8 @@ struct Executable {
     for (size_t i = 0; i < dev.size(); ++i)
       if (dev[i] && (i >= owned.size() || owned[i]))
         cudaFree(dev[i]);
+    for (void *b : world_buffers)
+      cudaFree(b);
     if (attn_scratch)
       cudaFree(attn_scratch);
     if (flag)
@@ -351,6 +396,162 @@ void plan(Executable &exe) {
   }
 }
 
+
+// ---- token-sharded mode: which Attention ops gather their keys / values over the world, when the
+// ring exchanges start, and the order in which the steps in front of an attention run ----
+void plan_world(Executable &exe) {
+  const ir::Program &p = exe.program;
+  exe.order.resize(exe.steps.size());
+  for (size_t i = 0; i < exe.order.size(); ++i)
+    exe.order[i] = i;
+  World *world = exe.ctx->world;
+  if (!world || world->size <= 1)
+    return;
+  std::map<uint32_t, size_t> producer;
+  for (size_t i = 0; i < p.ops.size(); ++i)
+    for (auto id : p.ops[i].out)
+      producer[id] = i;
+  size_t window_begin = 0; // steps before this index keep their place (they belong to an earlier attention)
+  for (size_t a = 0; a < p.ops.size(); ++a) {
+    const ir::Op &att = p.ops[a];
+    Step &st = exe.steps[a];
+    if (att.opcode != ir::Attention || st.skip)
+      continue;
+    const ir::Tensor &q = *p.tensor(att.in[0]);
+    const bool batched = q.dims.size() == 4;
+    if ((batched && q.dims[0] != 1) || st.mask_tensor >= 0 || att.in.size() != 3)
+      throw PluginError{2, "Attention (op " + std::to_string(att.id) + "): the token-sharded mode covers one "
+                               "sequence per program (no batch axis above 1) without a key mask"};
+    Sharded sh;
+    sh.step = a;
+    sh.tokens = q.dims[batched ? 1 : 0];
+    sh.heads = q.dims[batched ? 2 : 1];
+    sh.kv_heads = att.u64(ir::KvHeads, sh.heads);
+    const int index = (int)exe.sharded.size();
+    st.sharded = index;
+    // K: final after the last QkNormPartialRope part that writes its codes; else at the attention itself
+    if (st.k_quantised) {
+      int last = -1;
+      for (size_t r = 0; r < a; ++r)
+        if (exe.steps[r].rope_attention == (int)a && exe.steps[r].rope_role == 1)
+          last = (int)r;
+      if (last >= 0)
+        exe.steps[(size_t)last].exchange_k_for = index;
+    }
+    // V: the buffer of the tensor behind the chain of aliasing Reshapes becomes this rank's slice
+    uint32_t v_id = att.in[2];
+    for (;;) {
+      const auto it = producer.find(v_id);
+      if (it == producer.end() || !exe.steps[it->second].alias)
+        break;
+      v_id = p.ops[it->second].in[0];
+    }
+    const ir::Tensor &v_root = *p.tensor(v_id);
+    if (!v_root.has(ir::Input) && !v_root.has(ir::Constant) && producer.count(v_id)) {
+      const int root = p.index_of(v_id);
+      for (size_t k = 0; k < a; ++k) {
+        const Step &cand = exe.steps[k];
+        const bool writes = !cand.skip && (cand.out_tensor == root ||
+                                           std::find(cand.op->out.begin(), cand.op->out.end(), v_id) != cand.op->out.end());
+        if (writes) {
+          sh.v_root = root;
+          exe.steps[k].exchange_v_for = index;
+        }
+      }
+    }
+    exe.sharded.push_back(sh);
+
+    // Order of the steps in [window_begin, a): whatever several operands need first, then the V
+    // chain, the K chain, the Q chain, then steps the attention does not depend on. Each class
+    // keeps its program order, so every step still runs after the steps it reads from.
+    std::vector<unsigned> klass(a, 0u);
+    for (unsigned operand = 0; operand < 3; ++operand) {
+      std::vector<uint32_t> todo{att.in[operand]};
+      while (!todo.empty()) {
+        const uint32_t id = todo.back();
+        todo.pop_back();
+        const auto it = producer.find(id);
+        if (it == producer.end() || it->second >= a || (klass[it->second] & (1u << operand)))
+          continue;
+        klass[it->second] |= 1u << operand;
+        for (auto in : p.ops[it->second].in)
+          todo.push_back(in);
+      }
+    }
+    auto rank_of = [&](size_t i) {
+      switch (klass[i]) {
+      case 4u: return 1; // V only (operand index 2)
+      case 2u: return 2; // K only
+      case 1u: return 3; // Q only
+      case 0u: return 4; // not needed by this attention
+      default: return 0; // shared by several operands
+      }
+    };
+    std::stable_sort(exe.order.begin() + (long)window_begin, exe.order.begin() + (long)a,
+                     [&](size_t x, size_t y) { return rank_of(x) < rank_of(y); });
+    window_begin = a + 1;
+  }
+}
+
+// Token-sharded mode: the ranks agree on a common padded slice length, then every sharded
+// Attention gets its gather buffers (zeroed once: padding rows must stay finite, a masked key still
+// multiplies its value row by zero), the validity mask of the gathered key axis, the local query
+// codes, the key table scratch and the state carried between attention launches.
+void allocate_world(Executable &exe) {
+  World *world = exe.ctx->world;
+  if (exe.sharded.empty() || !world)
+    return;
+  const uint64_t size = (uint64_t)world->size;
+  auto device_alloc = [&](size_t bytes, bool zero) {
+    void *ptr = nullptr;
+    require_cuda(cudaMalloc(&ptr, bytes ? bytes : 16), "cudaMalloc(token-sharded attention)");
+    exe.world_buffers.push_back(ptr);
+    exe.resident_bytes += bytes;
+    if (zero)
+      require_cuda(cudaMemsetAsync(ptr, 0, bytes ? bytes : 16, exe.ctx->stream), "cudaMemsetAsync");
+    return ptr;
+  };
+  for (Sharded &sh : exe.sharded) {
+    // every rank's token count, through the world's own exchange
+    uint64_t *counts = static_cast<uint64_t *>(device_alloc(size * sizeof(uint64_t), true));
+    require_cuda(cudaMemcpyAsync(counts + world->rank, &sh.tokens, sizeof(uint64_t), cudaMemcpyHostToDevice,
+                                 exe.ctx->stream),
+                 "cudaMemcpyAsync(token count)");
+    void *buffers[1] = {counts};
+    const uint64_t slice[1] = {sizeof(uint64_t)};
+    require(world_exchange(world, buffers, slice, 1, exe.ctx->stream, nullptr));
+    require_cuda(cudaStreamSynchronize(world->comm_stream), "cudaStreamSynchronize(token counts)");
+    std::vector<uint64_t> tokens(size);
+    require_cuda(cudaMemcpy(tokens.data(), counts, size * sizeof(uint64_t), cudaMemcpyDeviceToHost),
+                 "cudaMemcpy(token counts)");
+    uint64_t longest = 0;
+    for (uint64_t t : tokens)
+      longest = t > longest ? t : longest;
+    sh.slice_tokens = (longest + 127) / 128 * 128;
+    const uint64_t keys = size * sh.slice_tokens, KV = sh.kv_heads;
+    sh.k8 = static_cast<int8_t *>(device_alloc(keys * KV * 128, true));
+    sh.ks = static_cast<float *>(device_alloc(keys * KV * sizeof(float), true));
+    sh.v = device_alloc(keys * KV * 256, true);
+    sh.q8 = static_cast<int8_t *>(device_alloc(sh.tokens * sh.heads * 128, false));
+    sh.qs = static_cast<float *>(device_alloc(sh.tokens * sh.heads * sizeof(float), false));
+    sh.scratch_bytes = attention_int8_scratch_bytes(1, keys, KV);
+    sh.scratch = device_alloc(sh.scratch_bytes, false);
+    sh.state = device_alloc(attention_int8_state_bytes(1, sh.tokens, sh.heads), false);
+    std::vector<uint8_t> valid(keys, 0);
+    for (uint64_t r = 0; r < size; ++r)
+      for (uint64_t t = 0; t < tokens[r]; ++t)
+        valid[r * sh.slice_tokens + t] = 1;
+    sh.valid = static_cast<uint8_t *>(device_alloc(keys, false));
+    require_cuda(cudaMemcpyAsync(sh.valid, valid.data(), keys, cudaMemcpyHostToDevice, exe.ctx->stream),
+                 "cudaMemcpyAsync(key validity)");
+    require_cuda(cudaStreamSynchronize(exe.ctx->stream), "cudaStreamSynchronize");
+    if (sh.v_root >= 0) {
+      exe.dev[(size_t)sh.v_root] = static_cast<char *>(sh.v) + (uint64_t)world->rank * sh.slice_tokens * KV * 256;
+      exe.owned[(size_t)sh.v_root] = 0;
+    }
+  }
+}
+
 void allocate(Executable &exe) {
   const ir::Program &p = exe.program;
   exe.dev.assign(p.tensors.size(), nullptr);
@@ -400,6 +601,9 @@ void allocate(Executable &exe) {
     if (st.alias)
       aliased[(size_t)p.index_of(st.op->out[0])] = true;
   exe.owned.assign(p.tensors.size(), 1);
+  for (const Sharded &sh : exe.sharded) // lives inside the gather buffer (allocate_world)
+    if (sh.v_root >= 0)
+      aliased[(size_t)sh.v_root] = true;
   for (size_t i = 0; i < p.tensors.size(); ++i) {
     if (!needed[i] || aliased[i])
       continue;
@@ -407,6 +611,7 @@ void allocate(Executable &exe) {
     require_cuda(cudaMalloc(&exe.dev[i], bytes ? bytes : 16), "cudaMalloc(tensor)");
     exe.resident_bytes += bytes;
   }
+  allocate_world(exe);
   for (const Step &st : exe.steps) // program order: a chain of reshapes resolves front to back
     if (st.alias) {
       const size_t out = (size_t)p.index_of(st.op->out[0]);
@@ -415,7 +620,7 @@ void allocate(Executable &exe) {
     }
   size_t scratch = 0;
   for (const Step &st : exe.steps) {
-    if (st.skip || st.op->opcode != ir::Attention)
+    if (st.skip || st.op->opcode != ir::Attention || st.sharded >= 0)
       continue;
     const ir::Tensor &q = *p.tensor(st.op->in[0]);
     const bool batched = q.dims.size() == 4;
@@ -441,6 +646,30 @@ struct Overlap {
   std::vector<int> finished_outputs;
 };
 
+// DIFB200_PROFILE: an event on the kernel stream in front of the next step (opcode 0 closes a pass).
+void profile_mark(Executable &exe, uint32_t opcode) {
+  const size_t at = exe.profile_opcodes.size();
+  if (at >= exe.profile_events.size()) {
+    cudaEvent_t e = nullptr;
+    require_cuda(cudaEventCreate(&e), "cudaEventCreate(profile)");
+    exe.profile_events.push_back(e);
+  }
+  require_cuda(cudaEventRecord(exe.profile_events[at], exe.ctx->stream), "cudaEventRecord(profile)");
+  exe.profile_opcodes.push_back(opcode);
+}
+// After the pass has finished on the device: add the spans to the per-opcode sums.
+void profile_collect(Executable &exe) {
+  for (size_t i = 0; i + 1 < exe.profile_opcodes.size(); ++i) {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, exe.profile_events[i], exe.profile_events[i + 1]) == cudaSuccess) {
+      auto &sum = exe.profile_sum[exe.profile_opcodes[i]];
+      sum.first += ms;
+      sum.second += 1;
+    }
+  }
+  exe.profile_opcodes.clear();
+}
+
 // ---- one pass over the program ---------------------------------------------------------------
 void run_steps(Executable &exe, Overlap *overlap = nullptr) {
   const ir::Program &p = exe.program;
@@ -453,10 +682,43 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
       overlap->upload_pending[(size_t)idx] = 0;
     }
   };
-  for (size_t step_index = 0; step_index <= exe.steps.size(); ++step_index) {
-    if (overlap && step_index > 0) {
+  World *world = exe.ctx->world;
+  // token-sharded mode: this rank's slice of a gather buffer is final, its ring exchange starts
+  auto exchange = [&](const Sharded &sh, int which) {
+    const uint64_t KV = sh.kv_heads, rows = sh.slice_tokens;
+    if (which == 0) {
+      void *buffers[1] = {sh.v};
+      const uint64_t bytes[1] = {rows * KV * 256};
+      require(world_exchange_class(world, 0, buffers, bytes, 1, s));
+    } else {
+      void *buffers[2] = {sh.k8, sh.ks};
+      const uint64_t bytes[2] = {rows * KV * 128, rows * KV * sizeof(float)};
+      require(world_exchange_class(world, 1, buffers, bytes, 2, s));
+    }
+  };
+  // where the INT8 operands of an Attention live: its scratch buffer, or (token-sharded) the local
+  // query buffers and this rank's slice of the gathered key buffers
+  auto operands_of = [&](size_t attention_step) {
+    const Step &at = exe.steps[attention_step];
+    const ir::Tensor &q = T(at.op->in[0]);
+    const bool batched = q.dims.size() == 4;
+    const uint64_t B = batched ? q.dims[0] : 1, S = q.dims[batched ? 1 : 0], H = q.dims[batched ? 2 : 1];
+    if (at.sharded < 0)
+      return attention_scratch_layout(exe.attn_scratch, B, S, H, at.op->u64(ir::KvHeads, H));
+    const Sharded &sh = exe.sharded[(size_t)at.sharded];
+    const uint64_t first = (uint64_t)world->rank * sh.slice_tokens * sh.kv_heads;
+    AttentionScratch l{};
+    l.q8 = sh.q8;
+    l.qs = sh.qs;
+    l.k8 = sh.k8 + first * 128;
+    l.ks = sh.ks + first;
+    l.rest = sh.scratch;
+    return l;
+  };
+  for (size_t position = 0; position <= exe.order.size(); ++position) {
+    if (overlap && position > 0) {
       // every Output tensor the previous op (run, fused away or skipped) lists is final now
-      for (auto id : exe.steps[step_index - 1].op->out) {
+      for (auto id : exe.steps[exe.order[position - 1]].op->out) {
         const int idx = p.index_of(id);
         if (idx >= 0 && p.tensors[(size_t)idx].has(ir::Output) && exe.dev[(size_t)idx]) {
           require_cuda(cudaEventRecord(exe.produced[(size_t)idx], s), "cudaEventRecord(output)");
@@ -464,9 +726,9 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
         }
       }
     }
-    if (step_index == exe.steps.size())
+    if (position == exe.order.size())
       break;
-    const Step &st = exe.steps[step_index];
+    const Step &st = exe.steps[exe.order[position]];
     if (overlap) {
       for (auto id : st.op->in)
         await_upload(p.index_of(id));
@@ -476,6 +738,8 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
     if (st.skip)
       continue;
     const ir::Op &op = *st.op;
+    if (exe.profile_pass)
+      profile_mark(exe, op.opcode);
     switch (op.opcode) {
     case ir::QuantizeInt8Rows: {
       if (st.norm_step >= 0) {
@@ -525,6 +789,35 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
       const uint64_t B = batched ? q.dims[0] : 1, S = q.dims[batched ? 1 : 0], H = q.dims[batched ? 2 : 1];
       const uint64_t KV = op.u64(ir::KvHeads, H);
       const float scale = (float)op.f64(ir::AttentionScale, 1.0 / std::sqrt((double)q.last()));
+      if (st.sharded >= 0) {
+        const Sharded &sh = exe.sharded[(size_t)st.sharded];
+        const AttentionScratch l = operands_of(exe.order[position]);
+        const uint64_t width[1] = {128};
+        if (!st.q_quantised) {
+          const void *part[1] = {D(op.in[0])};
+          require(quantize_int8_rows(part, width, 1, S * H, 1, 1.0f, nullptr, l.q8, l.qs, nullptr, nullptr, s));
+        }
+        if (!st.k_quantised) {
+          const void *part[1] = {D(op.in[1])};
+          require(quantize_int8_rows(part, width, 1, S * KV, 1, 1.0f, nullptr, l.k8, l.ks, nullptr, nullptr, s));
+        }
+        if (sh.v_root < 0) // V was not produced in place: copy this rank's rows into its slice
+          require_cuda(cudaMemcpyAsync(static_cast<char *>(sh.v) + (uint64_t)world->rank * sh.slice_tokens * KV * 256,
+                                       D(op.in[2]), (size_t)(S * KV * 256), cudaMemcpyDeviceToDevice, s),
+                       "cudaMemcpyAsync(values into the gather buffer)");
+        bool v_started = false, k_started = false; // exchanges a producer step has already started
+        for (const Step &other : exe.steps) {
+          v_started = v_started || other.exchange_v_for == st.sharded;
+          k_started = k_started || other.exchange_k_for == st.sharded;
+        }
+        if (!v_started)
+          exchange(sh, 0);
+        if (!k_started)
+          exchange(sh, 1);
+        require(sharded_attention(world, l.q8, l.qs, sh.k8, sh.ks, sh.v, sh.valid, S, sh.slice_tokens, H, KV, scale,
+                                  sh.scratch, sh.scratch_bytes, sh.state, D(op.out[0]), s));
+        break;
+      }
       require(attention_bf16_via_int8(st.q_quantised ? nullptr : D(op.in[0]), st.k_quantised ? nullptr : D(op.in[1]),
                                       D(op.in[2]),
                                       st.mask_tensor >= 0 ? static_cast<const uint8_t *>(exe.dev[(size_t)st.mask_tensor])
@@ -610,11 +903,7 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
       int8_t *codes = nullptr;
       float *scales = nullptr;
       if (st.rope_attention >= 0) {
-        const ir::Op &att = *exe.steps[(size_t)st.rope_attention].op;
-        const ir::Tensor &q = T(att.in[0]);
-        const bool batched = q.dims.size() == 4;
-        const uint64_t B = batched ? q.dims[0] : 1, S = q.dims[batched ? 1 : 0], H = q.dims[batched ? 2 : 1];
-        const AttentionScratch l = attention_scratch_layout(exe.attn_scratch, B, S, H, att.u64(ir::KvHeads, H));
+        const AttentionScratch l = operands_of((size_t)st.rope_attention);
         codes = st.rope_role == 0 ? l.q8 : l.k8;
         scales = st.rope_role == 0 ? l.qs : l.ks;
         layout.out_seq = st.rope_out_seq;
@@ -729,6 +1018,10 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
     default:
       throw PluginError{2, std::string("unsupported opcode ") + ir::opcode_name(op.opcode)};
     }
+    if (st.exchange_v_for >= 0)
+      exchange(exe.sharded[(size_t)st.exchange_v_for], 0);
+    if (st.exchange_k_for >= 0)
+      exchange(exe.sharded[(size_t)st.exchange_k_for], 1);
   }
 }
 
@@ -773,8 +1066,17 @@ dif_backend_status create(int32_t device_ordinal, dif_backend_context *context, 
     require_cuda(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate");
     require_cuda(cudaStreamCreateWithFlags(&ctx->h2d, cudaStreamNonBlocking), "cudaStreamCreate");
     require_cuda(cudaStreamCreateWithFlags(&ctx->d2h, cudaStreamNonBlocking), "cudaStreamCreate");
-    std::snprintf(ctx->device_name, sizeof(ctx->device_name), "%.200s (difb200 sm_100a, int8-attention %s)",
-                  prop.name, int8_attention_enabled() ? "on" : "off");
+    // token-sharded mode: join the world the environment describes (bounded rendezvous, then NCCL)
+    World *world = nullptr;
+    require(world_from_environment(&world));
+    ctx->world = world;
+    if (world)
+      std::snprintf(ctx->device_name, sizeof(ctx->device_name),
+                    "%.180s (difb200 sm_100a, int8-attention %s, token-sharded rank %d of %d)", prop.name,
+                    int8_attention_enabled() ? "on" : "off", world->rank, world->size);
+    else
+      std::snprintf(ctx->device_name, sizeof(ctx->device_name), "%.200s (difb200 sm_100a, int8-attention %s)",
+                    prop.name, int8_attention_enabled() ? "on" : "off");
     *context = ctx.release();
   });
 }
@@ -784,6 +1086,7 @@ void destroy(dif_backend_context context) {
   if (!ctx)
     return;
   cudaSetDevice(ctx->device);
+  delete ctx->world; // the communicator and its stream go first
   if (ctx->stream)
     cudaStreamDestroy(ctx->stream);
   if (ctx->h2d)
@@ -830,10 +1133,13 @@ dif_backend_status compile_common(dif_backend_context context, const uint8_t *di
     auto exe = std::make_unique<Executable>();
     exe->ctx = ctx;
     exe->device = ctx->device;
+    if (const char *v = std::getenv("DIFB200_PROFILE"))
+      exe->profile = v[0] == '1';
     std::string text;
     if (int rc = ir::decode(diffir, size, exe->program, text))
       throw PluginError{rc == 2 ? 2 : 4, "DiffIR: " + text};
     plan(*exe);
+    plan_world(*exe);
     allocate(*exe);
     if (v2) {
       size_t expected = 0;
@@ -1012,9 +1318,14 @@ dif_backend_status execute(dif_backend_executable executable, const dif_backend_
         run_steps(*exe);
       for (uint32_t it = 0; it < options->iterations; ++it) {
         cudaEventRecord(e0, ctx->stream);
+        exe->profile_pass = exe->profile;
         run_steps(*exe);
+        if (exe->profile_pass)
+          profile_mark(*exe, 0);
+        exe->profile_pass = false;
         cudaEventRecord(e1, ctx->stream);
         require_cuda(cudaEventSynchronize(e1), "cudaEventSynchronize");
+        profile_collect(*exe);
         float ms = 0.0f;
         cudaEventElapsedTime(&ms, e0, e1);
         sum += ms;
@@ -1056,6 +1367,26 @@ const dif_backend_api_v2 kApiV2 = {sizeof(dif_backend_api_v2), DIF_BACKEND_ABI_V
 
 } // namespace
 } // namespace difb200
+
+extern "C" int difb200_executable_profile(void *executable, uint32_t *opcodes, double *milliseconds, uint64_t *steps,
+                                          uint32_t capacity, uint32_t *count) {
+  using namespace difb200;
+  Executable *exe = static_cast<Executable *>(executable);
+  if (!exe || !opcodes || !milliseconds || !steps || !count)
+    return fail(kInvalidArgument, "difb200_executable_profile: null pointer");
+  uint32_t n = 0;
+  for (const auto &entry : exe->profile_sum) {
+    if (n == capacity)
+      break;
+    opcodes[n] = entry.first;
+    milliseconds[n] = entry.second.first;
+    steps[n] = entry.second.second;
+    ++n;
+  }
+  *count = n;
+  exe->profile_sum.clear();
+  return kOk;
+}
 
 extern "C" {
 const dif_backend_api_v1 *dif_backend_get_v1(void) { return &difb200::kApiV1; }

@@ -10,6 +10,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <atomic>
 #include <chrono>
 #include <condition_variable>
 #include <cstdio>
@@ -196,10 +197,13 @@ int world_create(const uint8_t id[128], int rank, int size, World **out) {
 }
 
 // ---- rendezvous -------------------------------------------------------------------------------
-int world_rendezvous(const std::string &directory, int rank, int size, uint8_t id[128], uint32_t timeout_ms) {
+int world_rendezvous(const std::string &directory, int rank, int size, uint8_t id[128], uint32_t timeout_ms,
+                     uint32_t generation) {
   if (directory.empty() || size < 1 || rank < 0 || rank >= size || !id)
     return fail(kInvalidArgument, "world rendezvous: bad arguments");
-  auto path = [&](int r) { return directory + "/rank_" + std::to_string(r); };
+  auto path = [&](int r) {
+    return directory + "/world_" + std::to_string(generation) + "_rank_" + std::to_string(r);
+  };
   {
     const std::string temp = path(rank) + ".writing";
     FILE *f = std::fopen(temp.c_str(), "wb");
@@ -256,7 +260,11 @@ int world_from_environment(World **out) {
   if (rank == 0)
     if (int rc = world_unique_id(id))
       return rc;
-  if (int rc = world_rendezvous(dir, rank, size, id, timeout_ms))
+  // A process may join several worlds one after another (one per plugin context): the n-th world
+  // of every rank meets under the n-th name, so the files of an earlier world are never mistaken
+  // for this one's. Every rank has to create its worlds in the same order.
+  static std::atomic<uint32_t> generation{0};
+  if (int rc = world_rendezvous(dir, rank, size, id, timeout_ms, generation.fetch_add(1)))
     return rc;
   return world_create(id, rank, size, out);
 }

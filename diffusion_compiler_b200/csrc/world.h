@@ -70,8 +70,10 @@ public:
 // `timeout_ms`: every rank leaves a file, rank 0 also the 128-byte communicator id (`id` in for
 // rank 0, out for the others), and every rank waits until all files are there. Returns
 // kExecutionError with text when a rank is missing at the deadline, so that no rank enters the
-// (unbounded) communicator set-up alone.
-int world_rendezvous(const std::string &directory, int rank, int size, uint8_t id[128], uint32_t timeout_ms);
+// (unbounded) communicator set-up alone. `generation` tells apart the worlds that meet in one
+// directory one after another (the file names carry it).
+int world_rendezvous(const std::string &directory, int rank, int size, uint8_t id[128], uint32_t timeout_ms,
+                     uint32_t generation = 0);
 
 int world_unique_id(uint8_t id[128]);
 // Communicator on the current device (blocks until all ranks have called it).

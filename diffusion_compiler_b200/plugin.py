@@ -139,6 +139,15 @@ class PreparedExecution:
             raise BackendError(rc, buf.value.decode(errors="replace"))
         return outputs, telemetry
 
+    def profile(self) -> Dict[int, tuple]:
+        """{opcode: (milliseconds, steps)} summed over the timed passes since the last call; filled only
+        when DIFB200_PROFILE=1 was in the environment at prepare() (difb200_executable_profile)."""
+        from . import _lib
+        cap = 64
+        opcodes, ms, steps, n = (C.c_uint32 * cap)(), (C.c_double * cap)(), (C.c_uint64 * cap)(), C.c_uint32(0)
+        _lib.check(_lib.lib().difb200_executable_profile(self._handle, opcodes, ms, steps, cap, C.byref(n)))
+        return {int(opcodes[i]): (float(ms[i]), int(steps[i])) for i in range(n.value)}
+
     def close(self):
         if self._handle:
             self._executor.api.destroy_executable(self._handle)

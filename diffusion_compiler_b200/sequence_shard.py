@@ -1,20 +1,19 @@
-"""Token-sharded execution of the video DiT block on 1/2/4/8 GPUs (one process per GPU).
+"""Token partition of the video DiT block and a device-API harness of its sharded form.
 
 The reference has no multi-GPU layer (one device per Executor, reference
-``include/dif/runtime/executor.hpp:683``); this is the sequence-partitioned form of the block that
-``blocks.video_block_program`` describes. Rank r owns a contiguous slice of the tokens. Weights,
-norm weights and RoPE tables are replicated. Everything except attention is row-local, so every
-op runs on the local slice; the one exchange step per block is an all-gather along tokens of the
-INT8 key codes, their per-token-head scales and the bf16 values. Queries stay local and each rank
-attends from its own queries to all keys (``ops.attention_int8`` with Sq < Sk); nothing is reduced
-afterwards.
+``include/dif/runtime/executor.hpp:683``); the sequence-partitioned form of the block that
+``blocks.video_block_program`` describes lives in the native library: with ``DIFB200_WORLD_SIZE``
+set, every rank's plugin context runs the block program on its token slice and exchanges the INT8
+key codes, their per-token-head scales and the bf16 values over its own NCCL communicator
+(``csrc/world.cu``, ``csrc/plugin.cu``). Rank r owns a contiguous slice of the tokens; weights,
+norm weights and RoPE tables are replicated; everything except attention is row-local; queries
+stay local and each rank attends from its own queries to all keys; nothing is reduced afterwards.
 
-The K quantiser and the V projection write straight into this rank's slice of the gather
-buffers (no staging copy), and the collective is an in-place ``all_gather_into_tensor`` over
-NCCL/NVLink. Slices are padded to a common length; padded keys are masked.
-
-The shard arithmetic and the gather work on CPU tensors with the gloo backend too, which is how
-the N > 1 path is tested without GPUs.
+This module holds the partition arithmetic (``ShardPlan``) that the benchmark and the tests share
+with that mode, and ``VideoBlock``: the same block issued kernel by kernel through the device API
+on one GPU, with the gather buffers laid out as a rank of a larger world would see them. Tests
+use it to emulate the ranks of a world one after another on a single GPU (slices copied between
+per-rank buffers in place of the exchange) and to check the CUDA-graph replay of the block.
 """
 from __future__ import annotations
 
@@ -77,21 +76,6 @@ class GatherBuffers:
         lo = self.rank * self.plan.slice_len
         return t[lo: lo + self.plan.slice_len]
 
-    def all_gather(self, group=None, names=("k8", "ks", "v"), async_op: bool = False):
-        """In-place all-gather of the named buffers (each rank contributes its slice). With
-        ``async_op`` the collectives are only enqueued and the work handles are returned; their
-        ``wait()`` makes the current stream wait for them."""
-        import torch.distributed as dist
-        works = []
-        if self.plan.world == 1:
-            return works
-        for name in names:
-            t = getattr(self, name)
-            w = dist.all_gather_into_tensor(t, self.local(t), group=group, async_op=async_op)
-            if async_op:
-                works.append(w)
-        return works
-
 
 class VideoBlock:
     """Device-resident weights of one video block and its (optionally token-sharded) forward.
@@ -116,7 +100,6 @@ class VideoBlock:
         self.lin = {name: (torch.from_numpy(w).to(device), torch.from_numpy(s).to(device))
                     for name, (w, s) in tensors["linears"].items()}
         self._scratch = None
-        self._comm_stream = None
         self._graphs = {}
         self._valid = {}
 
@@ -193,14 +176,13 @@ class VideoBlock:
         self._glue("difb200_residual_gate", p(r1), p(fc2), p(mods[5]), p(out), 2, S_loc, hid, S_loc, stream)
         return out
 
-    def forward(self, x: torch.Tensor, mods: List[torch.Tensor], plan: ShardPlan, rank: int, group=None,
+    def forward(self, x: torch.Tensor, mods: List[torch.Tensor], plan: ShardPlan, rank: int,
                 gb: Optional[GatherBuffers] = None, events: Optional[dict] = None,
                 graphs: bool = False) -> torch.Tensor:
-        """x and the six modulation tensors are this rank's [S_local, hidden] slices. With
-        ``graphs`` the kernels of the block are replayed from four CUDA graphs (V part, K part,
-        Q part, attention + rest; the collectives stay outside), captured on the first call for
-        these very tensors: a rank's share of a block is short enough at 8 GPUs for the launch
-        overhead of ~20 kernels to show."""
+        """The block on one GPU (``plan.world`` == 1, or the local part of an emulated rank whose
+        gather buffers the caller has filled). x and the six modulation tensors are [S_local,
+        hidden]. With ``graphs`` the kernels of the block are replayed from four CUDA graphs (V
+        part, K part, Q part, attention + rest), captured on the first call for these very tensors."""
         def mark(name):
             if events is not None:
                 ev = torch.cuda.Event(enable_timing=True)
@@ -210,67 +192,33 @@ class VideoBlock:
         if gb is None:
             gb = GatherBuffers(plan, rank, self.heads, self.dim, self.device)
         if graphs:
-            return self._forward_graphed(x, mods, plan, rank, group, gb, mark)
+            return self._forward_graphed(x, mods, plan, rank, gb, mark)
         mark("start")
-        works = []
-        if plan.world > 1:
-            # The V all-gather runs under the K and Q work, the K all-gather under the Q work:
-            # each is enqueued on a side stream as soon as its producer has been enqueued.
-            launch = self._gather_launcher(gb, group, works)
-            q8, qs = self.pre_attention(x, mods, plan, rank, gb, on_v_ready=lambda: launch(("v",)),
-                                        on_k_ready=lambda: launch(("k8", "ks")))
-        else:
-            q8, qs = self.pre_attention(x, mods, plan, rank, gb)
+        q8, qs = self.pre_attention(x, mods, plan, rank, gb)
         mark("pre_attention")
-        for w in works:
-            w.wait()  # the main stream waits for the collectives
-        mark("gathered")
         attn = self.attend(q8, qs, plan, gb)
         mark("attention")
         out = self.post_attention(x, attn, mods)
         mark("end")
         return out
 
-    def _gather_launcher(self, gb: GatherBuffers, group, works: list):
-        if self._comm_stream is None:
-            self._comm_stream = torch.cuda.Stream(device=self.device)
-        main = torch.cuda.current_stream()
-
-        def launch(names):
-            ready = torch.cuda.Event()
-            ready.record(main)
-            with torch.cuda.stream(self._comm_stream):
-                self._comm_stream.wait_event(ready)
-                works.extend(gb.all_gather(group, names=names, async_op=True))
-        return launch
-
-    def _forward_graphed(self, x, mods, plan, rank, group, gb, mark):
+    def _forward_graphed(self, x, mods, plan, rank, gb, mark):
         key = (x.data_ptr(), tuple(m.data_ptr() for m in mods), gb.k8.data_ptr(), plan.tokens, plan.world, rank)
         state = self._graphs.get(key)
         if state is None:
             state = self._capture(x, mods, plan, rank, gb)
             self._graphs[key] = state
         mark("start")
-        works = []
-        launch = self._gather_launcher(gb, group, works) if plan.world > 1 else None
         state["v"].replay()
-        if launch:
-            launch(("v",))
         state["k"].replay()
-        if launch:
-            launch(("k8", "ks"))
         state["q"].replay()
         mark("pre_attention")
-        for w in works:
-            w.wait()
-        mark("gathered")
         state["rest"].replay()
         mark("end")
         return state["out"]
 
     def _capture(self, x, mods, plan, rank, gb):
-        """Records the four kernel sequences of this block for these very tensors (every rank
-        does this in its first graphed call, so the warm-up pass with its collectives lines up).
+        """Records the four kernel sequences of this block for these very tensors.
         pre_attention reports the end of its V and K parts through callbacks: a capture ends and
         the next begins inside them. The returned output tensor is overwritten by every replay."""
         self.forward(x, mods, plan, rank, gb=gb)  # lazy allocations and one-time set-up, outside a capture

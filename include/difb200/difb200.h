@@ -32,6 +32,8 @@ extern "C" {
 
 DIFB200_EXPORT const char *difb200_last_error(void);
 DIFB200_EXPORT int difb200_version(void);
+/* Kernels of this library launched by this process so far (every entry point and the plugin count). */
+DIFB200_EXPORT uint64_t difb200_launch_count(void);
 
 /*
  * Reads and clears the device-side status words. Kernels with bounded waits (mbarrier spins)
@@ -339,6 +341,27 @@ DIFB200_EXPORT int difb200_w8a8_linear_static(const void *x, const int8_t *w, co
                                               int32_t implementation, float clip, uint64_t M,
                                               uint64_t N, uint64_t K, void *out,
                                               int32_t check_previous, void *stream);
+
+/*
+ * Measured INT8 tensor-core peak of the current device: one launch in which every SM (form 1) or
+ * every resident CTA pair (form 2, cta_group::2) issues `mma_per_issuer` tcgen05.mma kind::i8
+ * instructions of M128 (256) x N256 x K32 back to back on operands that stay in shared memory.
+ * Best of three timed launches (CUDA events); *tops = 2 * MACs / time. Synchronises `stream`.
+ * 8192 MMAs take about half a millisecond.
+ */
+DIFB200_EXPORT int difb200_measure_i8_mma_peak(int32_t ctas_per_mma, uint32_t mma_per_issuer, double *tops,
+                                               double *milliseconds, void *stream);
+
+/*
+ * Per-opcode device time of a plugin executable (a dif_backend_executable of this library). With
+ * DIFB200_PROFILE=1 in the environment at compile, execute() records a CUDA event on its kernel
+ * stream in front of every step of its timed passes; this call returns, per DiffIR opcode, the
+ * summed time between consecutive events and the number of steps, and clears the sums. It is how
+ * the benchmark times the dominant kernel inside the timed region (the reference reports per-op
+ * times from CUDA events the same way: src/runtime/cuda_executor.cpp:11139-11153).
+ */
+DIFB200_EXPORT int difb200_executable_profile(void *executable, uint32_t *opcodes, double *milliseconds,
+                                              uint64_t *steps, uint32_t capacity, uint32_t *count);
 
 #ifdef __cplusplus
 }
