@@ -71,6 +71,22 @@ def lib() -> C.CDLL:
                 ("difb200_world_selftest_fake", [i32, i32, u32])):
             getattr(L, name).restype = C.c_int
             getattr(L, name).argtypes = args
+        pcs = C.POINTER(C.c_char_p)
+        for name, args in (
+                ("difb200_cache_open", [C.c_char_p, C.POINTER(vp)]),
+                ("difb200_cache_close", [vp]),
+                ("difb200_cache_tensor", [vp, C.c_char_p, C.POINTER(u32), C.POINTER(u32), C.POINTER(u64),
+                                          C.POINTER(vp), C.POINTER(u64)]),
+                ("difb200_cache_write", [C.c_char_p, u32, pcs, C.POINTER(u32), C.POINTER(u32), C.POINTER(u64),
+                                         C.POINTER(vp)]),
+                ("difb200_program_fingerprint", [C.c_char_p, u64, C.POINTER(C.c_uint8)]),
+                ("difb200_cvr1_check", [C.POINTER(u32), C.c_char_p, u64, u32]),
+                ("difb200_build_convrot_cache", [C.c_char_p, C.c_char_p, u64, u32, C.POINTER(u32), C.POINTER(vp),
+                                                 C.POINTER(u64), C.POINTER(u64), C.POINTER(C.c_uint8), vp])):
+            getattr(L, name).restype = C.c_int
+            getattr(L, name).argtypes = args
+        L.difb200_cvr1_identity.restype = None
+        L.difb200_cvr1_identity.argtypes = [u32, C.POINTER(C.c_uint8), C.POINTER(C.c_uint8), C.POINTER(u32)]
         L.difb200_measure_i8_mma_peak.restype = C.c_int
         L.difb200_measure_i8_mma_peak.argtypes = [i32, u32, C.POINTER(C.c_double), C.POINTER(C.c_double), vp]
         L.difb200_executable_profile.restype = C.c_int

@@ -343,6 +343,46 @@ DIFB200_EXPORT int difb200_w8a8_linear_static(const void *x, const int8_t *w, co
                                               int32_t check_previous, void *stream);
 
 /*
+ * ConvRot INT8 weight caches, the files the reference keeps quantised Linear weights in (host side
+ * except for the builder). Container: SafeTensors exactly as the reference reads and writes it
+ * (src/weights/safetensors.cpp). Forms: per-projection pairs "weight" I8 [N,K] + "scale" F32 [N]
+ * (tools/difflux2sample.cpp:3079-3091) and the generic cache "linear.<weight tensor id>.weight" /
+ * ".scale" with the identity record "__meta__.convrot_int8" I32[20] = {0x31525643 "CVR1", 1, 256,
+ * projection count, 8 words of the program fingerprint, 8 words of the source index digest}
+ * (src/runtime/cuda_executor.cpp:4266-4364, tools/difh3convrot.cpp:51,208-231).
+ *   difb200_cache_open / _tensor / _close   read a file; `data` points into memory owned by the
+ *                                           handle (valid until close); dtype is the DiffIR code
+ *                                           (0 for a "__meta__." tensor of another type)
+ *   difb200_cache_write                     write tensors (dims8: 8 entries per tensor) under
+ *                                           "<path>.building", then rename; refuses to run over an
+ *                                           unfinished file of that name
+ *   difb200_program_fingerprint             SHA-256 of DIFIR bytes without their trailing digest
+ *                                           (src/ir/codec.cpp:494-497)
+ *   difb200_cvr1_identity / _check          make the identity record; check magic, version, group,
+ *                                           fingerprint (diffir may be NULL) and projection count
+ *   difb200_build_convrot_cache             quantise `count` bf16 [rows, columns] HOST weight matrices
+ *                                           on the current GPU (H256ConvRot rows, clip 1: the encoder of
+ *                                           tools/difh3convrot.cpp:364-446) and write the generic cache
+ */
+DIFB200_EXPORT int difb200_cache_open(const char *path, void **cache);
+DIFB200_EXPORT int difb200_cache_close(void *cache);
+DIFB200_EXPORT int difb200_cache_tensor(void *cache, const char *name, uint32_t *dtype, uint32_t *rank,
+                                        uint64_t *dims8, const void **data, uint64_t *bytes);
+DIFB200_EXPORT int difb200_cache_write(const char *path, uint32_t count, const char *const *names,
+                                       const uint32_t *dtypes, const uint32_t *ranks, const uint64_t *dims8,
+                                       const void *const *data);
+DIFB200_EXPORT int difb200_program_fingerprint(const uint8_t *diffir, uint64_t size, uint8_t *digest32);
+DIFB200_EXPORT void difb200_cvr1_identity(uint32_t projections, const uint8_t *program_digest32,
+                                          const uint8_t *index_digest32, uint32_t *identity20);
+DIFB200_EXPORT int difb200_cvr1_check(const uint32_t *identity20, const uint8_t *diffir, uint64_t size,
+                                      uint32_t projections);
+DIFB200_EXPORT int difb200_build_convrot_cache(const char *path, const uint8_t *diffir, uint64_t diffir_size,
+                                               uint32_t count, const uint32_t *weight_ids,
+                                               const void *const *host_weights_bf16, const uint64_t *rows,
+                                               const uint64_t *columns, const uint8_t *index_digest32,
+                                               void *stream);
+
+/*
  * Measured INT8 tensor-core peak of the current device: one launch in which every SM (form 1) or
  * every resident CTA pair (form 2, cta_group::2) issues `mma_per_issuer` tcgen05.mma kind::i8
  * instructions of M128 (256) x N256 x K32 back to back on operands that stay in shared memory.

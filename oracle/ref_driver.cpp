@@ -149,3 +149,68 @@ difref_encode_check(const uint8_t *diffir, size_t n, char *err, size_t errcap) {
 }
 
 }
+
+// ---- the reference's own SafeTensors reader / writer and program fingerprint, for the cache
+// interoperability tests (src/weights/safetensors.cpp, src/ir/codec.cpp:494-497) ----
+#include "dif/weights/safetensors.hpp"
+
+extern "C" {
+
+__attribute__((visibility("default"))) int
+difref_fingerprint(const uint8_t *diffir, size_t n, uint8_t *digest32, char *err, size_t errcap) {
+  try {
+    const auto program = dif::ir::decode(std::span<const uint8_t>(diffir, n));
+    const auto digest = dif::ir::fingerprint(program);
+    std::memcpy(digest32, digest.data(), 32);
+    return 0;
+  } catch (const std::exception &e) {
+    set_error(err, errcap, e.what());
+    return 1;
+  }
+}
+
+// Writes `count` tensors with the reference's SafeTensorWriter. dims holds 8 entries per tensor.
+__attribute__((visibility("default"))) int
+difref_write_safetensors(const char *path, size_t count, const char *const *names, const uint32_t *dtypes,
+                         const uint32_t *ranks, const uint64_t *dims, const void *const *data,
+                         const uint64_t *byte_counts, char *err, size_t errcap) {
+  try {
+    std::vector<dif::weights::SafeTensorWriteSpec> specs;
+    for (size_t i = 0; i < count; ++i)
+      specs.push_back({names[i], static_cast<dif::ir::DType>(dtypes[i]),
+                       std::vector<std::uint64_t>(dims + 8 * i, dims + 8 * i + ranks[i])});
+    dif::weights::SafeTensorWriter writer(path, specs);
+    for (size_t i = 0; i < count; ++i)
+      writer.append(names[i], std::span<const std::uint8_t>(static_cast<const std::uint8_t *>(data[i]),
+                                                            static_cast<size_t>(byte_counts[i])));
+    (void)writer.finish();
+    return 0;
+  } catch (const std::exception &e) {
+    set_error(err, errcap, e.what());
+    return 1;
+  }
+}
+
+// Reads one tensor with the reference's reader; returns its description and copies its bytes.
+__attribute__((visibility("default"))) int
+difref_read_safetensor(const char *path, const char *name, uint32_t *dtype, uint32_t *rank, uint64_t *dims8,
+                       void *out, uint64_t capacity, uint64_t *byte_count, char *err, size_t errcap) {
+  try {
+    const auto file = dif::weights::read_safetensors(path);
+    const auto tensor = dif::weights::map_safetensor(file, name);
+    *dtype = static_cast<uint32_t>(tensor.dtype);
+    *rank = static_cast<uint32_t>(tensor.dims.size());
+    for (size_t i = 0; i < tensor.dims.size() && i < 8; ++i)
+      dims8[i] = tensor.dims[i];
+    *byte_count = tensor.byte_size();
+    if (tensor.byte_size() > capacity)
+      throw std::runtime_error("output buffer too small");
+    std::memcpy(out, tensor.data(), tensor.byte_size());
+    return 0;
+  } catch (const std::exception &e) {
+    set_error(err, errcap, e.what());
+    return 1;
+  }
+}
+
+}
