@@ -93,6 +93,27 @@ int sm_count() {
   return count;
 }
 
+void *device_scratch(size_t bytes) {
+  static std::unordered_map<int, std::pair<void *, size_t>> areas;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess)
+    return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto &area = areas[device];
+  if (area.second >= bytes && area.first)
+    return area.first;
+  if (area.first)
+    cudaFree(area.first); // waits for everything that may still read the old area
+  area = {nullptr, 0};
+  const size_t rounded = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
+  if (cudaMalloc(&area.first, rounded) != cudaSuccess) {
+    area.first = nullptr;
+    return nullptr;
+  }
+  area.second = rounded;
+  return area.first;
+}
+
 DeviceStatus *device_status_words() {
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess)

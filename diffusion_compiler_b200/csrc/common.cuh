@@ -50,6 +50,9 @@ void set_wait_limit_ns(unsigned long long ns); // 0 restores the default
 // k-block. take_...() returns that k-block (0xffffffff = none) and disarms.
 void withhold_next_gemm_load(uint32_t k_block);
 uint32_t take_withheld_gemm_load();
+// Per-device scratch that only grows (reallocated, which synchronises the device, when a call
+// needs more than any call before it): small work areas whose size follows the row count.
+void *device_scratch(size_t bytes);
 DeviceStatus *device_status_words();      // per-device, allocated once
 int poll_device_status(const char *what); // copies back, clears, maps to kExecutionError
 

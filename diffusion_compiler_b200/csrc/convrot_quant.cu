@@ -50,6 +50,7 @@ struct QuantParams {
   float norm_eps;
   const uint16_t *norm_bias;   // [columns]: LayerNormModulate (mean removed, weight and bias); nullptr = RMS
   uint64_t norm_rows_per_mod;  // rows that share one row of scale / shift
+  const float2 *norm_stats;    // per row (mean, inverse deviation) in the reference's order, or nullptr
 };
 
 // Fixed Rademacher diagonal of the signed variants (reference cpu_executor.cpp:183-189).
@@ -330,8 +331,13 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
             v = __fadd_rn(v, slots[slot * warps_per_row + w]);
           return v;
         };
-        float mean = 0.0f, ss = 0.0f;
-        if (layer) {
+        float mean = 0.0f, ss = 0.0f, inv = 0.0f;
+        if (p.norm_stats) {
+          // the statistic in the reference's sequential order, from glue::row_stats_sequential
+          const float2 st = __ldg(p.norm_stats + (row_ok ? row : 0));
+          mean = st.x;
+          inv = st.y;
+        } else if (layer) {
           // LayerNormModulate (cpu_executor.cpp:1108-1148): mean, then the centred second moment.
           // The second sum uses the other parity's slots: they are free until the next row, which
           // every warp of this row reaches only after the barriers of the maxima exchange below.
@@ -352,7 +358,8 @@ convrot_quant_kernel(const QuantParams p, const int warps_per_row, const int row
             ss = __fmaf_rn(xs[i], xs[i], ss);
           ss = row_sum(ss, stat);
         }
-        const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)p.columns), p.norm_eps)));
+        if (!p.norm_stats)
+          inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)p.columns), p.norm_eps)));
         const uint32_t col = group_a * 256u + 16u * a;
         const uint64_t at = ((row_ok ? row : 0) / p.norm_rows_per_mod) * (uint64_t)p.columns + col;
         const uint4 one = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), zero = make_uint4(0, 0, 0, 0);
@@ -887,6 +894,12 @@ int quantize_int8_rows(const void *const *parts, const uint64_t *part_widths, ui
     p.norm_eps = norm->epsilon;
     p.norm_bias = static_cast<const uint16_t *>(norm->bias);
     p.norm_rows_per_mod = norm->rows_per_modulation;
+    if (rows > 0) { // the row statistic in the reference's order, by its own kernel in front
+      int rc = 0;
+      if (glue::row_stats_sequential(parts[0], rows, columns, norm->epsilon, norm->bias != nullptr, &p.norm_stats,
+                                     stream, &rc) && rc)
+        return rc;
+    }
   }
   if (rows == 0)
     return kOk;

@@ -103,7 +103,7 @@ __global__ void k_fill(void *o, uint32_t dt, uint64_t n, float value) {
 }
 // ---- RmsNorm (1051-1075): one warp per row ----
 __global__ void k_rms_norm(const void *x, const void *w, void *o, uint32_t dt, uint64_t rows, uint64_t cols,
-                           float eps, float weight_offset) {
+                           float eps, float weight_offset, const float2 *stats) {
   const int lane = threadIdx.x & 31;
   const uint64_t warp = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const uint64_t nwarps = (uint64_t)gridDim.x * (blockDim.x >> 5);
@@ -114,7 +114,8 @@ __global__ void k_rms_norm(const void *x, const void *w, void *o, uint32_t dt, u
       sum = __fmaf_rn(v, v, sum);
     }
     sum = warp_sum(sum);
-    const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(sum, (float)cols), eps)));
+    // with `stats` the statistic comes in the reference's sequential order (bit-exact outputs)
+    const float inv = stats ? stats[r].y : __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(sum, (float)cols), eps)));
     for (uint64_t c = lane; c < cols; c += 32)
       st(o, dt, r * cols + c,
          __fmul_rn(__fmul_rn(ld(x, dt, r * cols + c), inv), __fadd_rn(ld(w, dt, c), weight_offset)));
@@ -372,7 +373,13 @@ int fill(void *o, uint32_t dt, uint64_t n, float value, cudaStream_t s) {
 }
 int rms_norm(const void *x, const void *w, void *o, uint32_t dt, uint64_t rows, uint64_t cols, float eps,
              float weight_offset, cudaStream_t s) {
-  k_rms_norm<<<row_blocks(rows), 256, 0, s>>>(x, w, o, dt, rows, cols, eps, weight_offset);
+  const float2 *stats = nullptr;
+  if (dt == 2) { // bf16 rows: the statistic in the reference's own order, by its own kernel
+    int rc = 0;
+    if (row_stats_sequential(x, rows, cols, eps, false, &stats, s, &rc) && rc)
+      return rc;
+  }
+  k_rms_norm<<<row_blocks(rows), 256, 0, s>>>(x, w, o, dt, rows, cols, eps, weight_offset, stats);
   return done("k_rms_norm");
 }
 int layer_norm_modulate(const void *x, const void *w, const void *b, const void *scale, const void *shift, void *o,

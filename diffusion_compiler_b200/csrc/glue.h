@@ -46,6 +46,15 @@ int mask_to_bias(const uint8_t *mask, void *o, uint32_t dt, uint64_t B, uint64_t
 int linear(const void *x, const void *w, const void *bias, void *o, uint32_t dt, uint64_t M, uint64_t N, uint64_t K,
            cudaStream_t s);
 
+// Row statistics of a bf16 [rows, cols] tensor in the reference's own order (one sequential fp32
+// chain per row, cpu_executor.cpp:1051-1062, 1119-1129, 1250-1256), so that a normalisation built on
+// them has the reference's bits: stats[r] = (0, 1 / sqrt(sum x^2 / cols + eps)) or, with `layer`,
+// (mean, 1 / sqrt(sum (x - mean)^2 / cols + eps)). *stats points into per-device scratch that the
+// next call of this function reuses. False (nothing launched) when cols is not a multiple of 64,
+// x is not 16-byte aligned or DIFB200_EXACT_NORM=0 asks for the parallel sums.
+bool row_stats_sequential(const void *x, uint64_t rows, uint64_t cols, float eps, bool layer, const float2 **stats,
+                          cudaStream_t s, int *rc);
+
 // bf16 fast paths (glue_fast.cu). Each returns false when dtype, widths or alignment are not
 // covered (nothing launched; the caller runs the generic kernel), else true with the launch
 // status in *rc.

@@ -8,6 +8,8 @@
 
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace difb200 {
 namespace glue {
 namespace {
@@ -73,13 +75,85 @@ k_swiglu_bf16(const uint4 *x, uint4 *o, uint64_t rows, uint64_t width8, uint64_t
   }
 }
 
+
+// ---- row statistics in the reference's sequential order ----
+// The reference sums a row's squares (or values, then squared deviations) in one fp32 chain, column
+// by column (cpu_executor.cpp:1051-1062 RmsNorm, 1119-1129 LayerNormModulate, 1250-1256
+// RmsNormModulate). A parallel sum differs from that chain in the last bit of about one row in
+// three, which flips one bf16 output in a few thousand -- and every ConvRot quantiser behind the
+// norm amplifies such a flip across its 256-wide group. So the statistic is computed here in the
+// reference's order: one lane per row walks its row sequentially. A warp owns 32 rows and moves them
+// through shared memory 64 columns at a time (coalesced 128-byte loads, rows 9 x 16 bytes apart so
+// that lanes read their own rows without bank conflicts); the loads of the next 64 columns are in
+// flight while the chain of the current ones runs. Squares of bf16 values are exact in fp32, so the
+// fused multiply-add equals the reference's multiply followed by add; the deviations of the layer
+// form are not, and get the two roundings.
+constexpr int kStatCols = 64, kStatPitch = 9; // uint4 per row in shared memory (8 + 1 pad)
+
+template <bool LAYER>
+__global__ void __launch_bounds__(256)
+k_row_stats_sequential(const uint4 *x, float2 *stats, uint64_t rows, uint32_t cols, float eps) {
+  __shared__ uint4 tile[8][32 * kStatPitch];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t cols8 = cols >> 3, chunks = cols / kStatCols;
+  uint4 *mine = tile[warp];
+  for (uint64_t row0 = ((uint64_t)blockIdx.x * 8 + warp) * 32; row0 < rows; row0 += (uint64_t)gridDim.x * 256) {
+    const uint64_t row = row0 + lane;
+    // lane l fetches, for j = 0..7, the 16 bytes (row0 + 4 j + l / 8, chunk column l % 8)
+    auto fetch = [&](uint32_t chunk, uint4 (&v)[8]) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint64_t r = row0 + 4 * j + (lane >> 3);
+        v[j] = r < rows ? __ldg(x + r * cols8 + chunk * (kStatCols / 8) + (lane & 7)) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    float mean = 0.0f, acc = 0.0f;
+#pragma unroll 1
+    for (int pass = LAYER ? 0 : 1; pass < 2; ++pass) {
+      acc = 0.0f;
+      uint4 next[8];
+      fetch(0, next);
+#pragma unroll 1
+      for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          mine[(4 * j + (lane >> 3)) * kStatPitch + (lane & 7)] = next[j];
+        if (chunk + 1 < chunks)
+          fetch(chunk + 1, next);
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float f[8];
+          unpack8(mine[lane * kStatPitch + c], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            if (pass == 0) {
+              acc = __fadd_rn(acc, f[e]);
+            } else if (LAYER) {
+              const float d = __fsub_rn(f[e], mean);
+              acc = __fadd_rn(acc, __fmul_rn(d, d));
+            } else {
+              acc = __fmaf_rn(f[e], f[e], acc);
+            }
+          }
+        }
+      }
+      if (pass == 0)
+        mean = __fdiv_rn(acc, (float)cols);
+    }
+    if (row < rows)
+      stats[row] = make_float2(mean, __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(acc, (float)cols), eps))));
+  }
+}
+
 // ---- RmsNormModulate, explicit scale / shift (cpu_executor.cpp:1241-1264) ----
 // One warp per row; lane l owns the 8-element groups l, l + 32, ... CHUNKS > 0: the row has
 // CHUNKS * 256 columns and stays in registers; CHUNKS == 0: any multiple of 256, read twice.
 template <int CHUNKS>
 __global__ void __launch_bounds__(256)
 k_rms_norm_modulate_bf16(const uint4 *x, const uint4 *w, const uint4 *a, const uint4 *b, uint4 *o, uint64_t rows,
-                         uint32_t cols, float eps) {
+                         uint32_t cols, float eps, const float2 *stats) {
   const int lane = threadIdx.x & 31;
   const uint64_t warp = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const uint64_t nwarps = (uint64_t)gridDim.x * (blockDim.x >> 5);
@@ -100,7 +174,9 @@ k_rms_norm_modulate_bf16(const uint4 *x, const uint4 *w, const uint4 *a, const u
         sum = __fmaf_rn(f[e], f[e], sum);
     }
     sum = warp_sum(sum);
-    const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(sum, (float)cols), eps)));
+    // `stats`: the statistic in the reference's sequential order (row_stats_sequential), which
+    // makes every output bit the reference's; else the warp's parallel sum (last bit may differ)
+    const float inv = stats ? stats[r].y : __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(sum, (float)cols), eps)));
 #pragma unroll
     for (uint32_t k = 0; k < chunks; ++k) {
       const uint32_t c = lane + 32u * k;
@@ -125,7 +201,8 @@ k_rms_norm_modulate_bf16(const uint4 *x, const uint4 *w, const uint4 *a, const u
 template <int CHUNKS>
 __global__ void __launch_bounds__(256)
 k_layer_norm_modulate_bf16(const uint4 *x, const uint4 *w, const uint4 *b, const uint4 *scale, const uint4 *shift,
-                           uint4 *o, uint64_t rows, uint32_t cols, uint64_t rows_per_mod, float eps) {
+                           uint4 *o, uint64_t rows, uint32_t cols, uint64_t rows_per_mod, float eps,
+                           const float2 *stats) {
   const int lane = threadIdx.x & 31;
   const uint64_t warp = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const uint64_t nwarps = (uint64_t)gridDim.x * (blockDim.x >> 5);
@@ -145,7 +222,7 @@ k_layer_norm_modulate_bf16(const uint4 *x, const uint4 *w, const uint4 *b, const
       for (int e = 0; e < 8; ++e)
         mean += f[e];
     }
-    mean = __fdiv_rn(warp_sum(mean), (float)cols);
+    mean = stats ? stats[r].x : __fdiv_rn(warp_sum(mean), (float)cols);
     float var = 0.0f;
 #pragma unroll
     for (uint32_t k = 0; k < chunks; ++k) {
@@ -158,7 +235,7 @@ k_layer_norm_modulate_bf16(const uint4 *x, const uint4 *w, const uint4 *b, const
       }
     }
     var = warp_sum(var);
-    const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(var, (float)cols), eps)));
+    const float inv = stats ? stats[r].y : __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(var, (float)cols), eps)));
     const uint64_t mrow = (r / rows_per_mod) * cols8;
 #pragma unroll
     for (uint32_t k = 0; k < chunks; ++k) {
@@ -385,6 +462,34 @@ bool swiglu_fast(const void *x, void *o, uint32_t dt, uint64_t rows, uint64_t wi
   return true;
 }
 
+bool row_stats_sequential(const void *x, uint64_t rows, uint64_t cols, float eps, bool layer, const float2 **stats,
+                          cudaStream_t s, int *rc) {
+  *stats = nullptr;
+  *rc = 0;
+  if (const char *v = std::getenv("DIFB200_EXACT_NORM"))
+    if (v[0] == '0')
+      return false;
+  if (rows == 0 || cols == 0 || cols % kStatCols != 0 || cols > 0xffffff00ull || !aligned16(x))
+    return false;
+  float2 *area = static_cast<float2 *>(device_scratch(rows * sizeof(float2)));
+  if (!area) {
+    *rc = fail(kOutOfMemory, "cannot allocate the row statistics scratch");
+    return true;
+  }
+  uint64_t blocks = (rows + 255) / 256;
+  const uint64_t cap = (uint64_t)sm_count() * 4;
+  blocks = blocks > cap ? cap : blocks;
+  if (layer)
+    k_row_stats_sequential<true><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4 *>(x), area, rows,
+                                                                  (uint32_t)cols, eps);
+  else
+    k_row_stats_sequential<false><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4 *>(x), area, rows,
+                                                                   (uint32_t)cols, eps);
+  *rc = done("k_row_stats_sequential");
+  *stats = area;
+  return true;
+}
+
 bool rms_norm_modulate_fast(const void *x, const void *w, const void *a, const void *b, void *o, uint32_t dt,
                             uint64_t rows, uint64_t cols, float eps, cudaStream_t s, int *rc) {
   if (dt != 2 || cols == 0 || cols % 256 != 0 || cols > 0xffffff00ull || !aligned16(x) || (w && !aligned16(w)) ||
@@ -395,12 +500,15 @@ bool rms_norm_modulate_fast(const void *x, const void *w, const void *a, const v
   blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
   const auto X = static_cast<const uint4 *>(x), W = static_cast<const uint4 *>(w), A = static_cast<const uint4 *>(a),
              B = static_cast<const uint4 *>(b);
+  const float2 *stats = nullptr;
+  if (row_stats_sequential(x, rows, cols, eps, false, &stats, s, rc) && *rc)
+    return true;
   if (cols == 3072)
     k_rms_norm_modulate_bf16<12><<<(unsigned)blocks, 256, 0, s>>>(X, W, A, B, static_cast<uint4 *>(o), rows,
-                                                                  (uint32_t)cols, eps);
+                                                                  (uint32_t)cols, eps, stats);
   else
     k_rms_norm_modulate_bf16<0><<<(unsigned)blocks, 256, 0, s>>>(X, W, A, B, static_cast<uint4 *>(o), rows,
-                                                                 (uint32_t)cols, eps);
+                                                                 (uint32_t)cols, eps, stats);
   *rc = done("k_rms_norm_modulate_bf16");
   return true;
 }
@@ -416,12 +524,15 @@ bool layer_norm_modulate_fast(const void *x, const void *w, const void *b, const
   blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
   const auto X = static_cast<const uint4 *>(x), W = static_cast<const uint4 *>(w), B = static_cast<const uint4 *>(b),
              SC = static_cast<const uint4 *>(scale), SH = static_cast<const uint4 *>(shift);
+  const float2 *stats = nullptr;
+  if (row_stats_sequential(x, rows, cols, eps, true, &stats, s, rc) && *rc)
+    return true;
   if (cols == 3072)
     k_layer_norm_modulate_bf16<12><<<(unsigned)blocks, 256, 0, s>>>(X, W, B, SC, SH, static_cast<uint4 *>(o), rows,
-                                                                    (uint32_t)cols, rows_per_mod, eps);
+                                                                    (uint32_t)cols, rows_per_mod, eps, stats);
   else
     k_layer_norm_modulate_bf16<0><<<(unsigned)blocks, 256, 0, s>>>(X, W, B, SC, SH, static_cast<uint4 *>(o), rows,
-                                                                   (uint32_t)cols, rows_per_mod, eps);
+                                                                   (uint32_t)cols, rows_per_mod, eps, stats);
   *rc = done("k_layer_norm_modulate_bf16");
   return true;
 }
