@@ -83,49 +83,60 @@ k_swiglu_bf16(const uint4 *x, uint4 *o, uint64_t rows, uint64_t width8, uint64_t
 // three, which flips one bf16 output in a few thousand -- and every ConvRot quantiser behind the
 // norm amplifies such a flip across its 256-wide group. So the statistic is computed here in the
 // reference's order: one lane per row walks its row sequentially. A warp owns 32 rows and moves them
-// through shared memory 64 columns at a time (coalesced 128-byte loads, rows 9 x 16 bytes apart so
-// that lanes read their own rows without bank conflicts); the loads of the next 64 columns are in
-// flight while the chain of the current ones runs. Squares of bf16 values are exact in fp32, so the
+// through shared memory 64 columns at a time (asynchronous 16-byte copies in coalesced 128-byte
+// runs, rows 9 x 16 bytes apart so that lanes read their own rows without bank conflicts), four
+// chunks deep: the memory latency of a chunk hides under the chains of the three before it.
+// Squares of bf16 values are exact in fp32, so the
 // fused multiply-add equals the reference's multiply followed by add; the deviations of the layer
 // form are not, and get the two roundings.
 constexpr int kStatCols = 64, kStatPitch = 9; // uint4 per row in shared memory (8 + 1 pad)
+constexpr int kStatStages = 4, kStatWarps = 2;  // chunks in flight per warp (hides the HBM latency), warps per CTA
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
+  // 16 bytes global -> shared, asynchronously; zero-filled when the row does not exist
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0) : "memory");
+}
 
 template <bool LAYER>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(32 * kStatWarps)
 k_row_stats_sequential(const uint4 *x, float2 *stats, uint64_t rows, uint32_t cols, float eps) {
-  __shared__ uint4 tile[8][32 * kStatPitch];
+  __shared__ uint4 tile[kStatWarps][kStatStages][32 * kStatPitch];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t cols8 = cols >> 3, chunks = cols / kStatCols;
-  uint4 *mine = tile[warp];
-  for (uint64_t row0 = ((uint64_t)blockIdx.x * 8 + warp) * 32; row0 < rows; row0 += (uint64_t)gridDim.x * 256) {
+  for (uint64_t row0 = ((uint64_t)blockIdx.x * kStatWarps + warp) * 32; row0 < rows;
+       row0 += (uint64_t)gridDim.x * kStatWarps * 32) {
     const uint64_t row = row0 + lane;
-    // lane l fetches, for j = 0..7, the 16 bytes (row0 + 4 j + l / 8, chunk column l % 8)
-    auto fetch = [&](uint32_t chunk, uint4 (&v)[8]) {
+    // lane l copies, for j = 0..7, the 16 bytes (row0 + 4 j + l / 8, chunk column l % 8) of a chunk
+    auto issue = [&](uint32_t chunk) {
+      if (chunk < chunks) {
+        uint4 *stage = tile[warp][chunk % kStatStages];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint64_t r = row0 + 4 * j + (lane >> 3);
-        v[j] = r < rows ? __ldg(x + r * cols8 + chunk * (kStatCols / 8) + (lane & 7)) : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < 8; ++j) {
+          const uint64_t r = row0 + 4 * j + (lane >> 3);
+          const bool valid = r < rows;
+          cp_async16(smem_u32(stage + (4 * j + (lane >> 3)) * kStatPitch + (lane & 7)),
+                     x + (valid ? r : 0) * cols8 + chunk * (kStatCols / 8) + (lane & 7), valid);
+        }
       }
+      asm volatile("cp.async.commit_group;" ::: "memory"); // one group per chunk slot, also when empty
     };
     float mean = 0.0f, acc = 0.0f;
 #pragma unroll 1
     for (int pass = LAYER ? 0 : 1; pass < 2; ++pass) {
       acc = 0.0f;
-      uint4 next[8];
-      fetch(0, next);
+      __syncwarp();
+      for (uint32_t c = 0; c < (uint32_t)kStatStages - 1; ++c)
+        issue(c);
 #pragma unroll 1
       for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          mine[(4 * j + (lane >> 3)) * kStatPitch + (lane & 7)] = next[j];
-        if (chunk + 1 < chunks)
-          fetch(chunk + 1, next);
-        __syncwarp();
+        issue(chunk + kStatStages - 1);              // its stage was read during chunk - 1
+        asm volatile("cp.async.wait_group %0;" ::"n"(kStatStages - 1) : "memory");
+        __syncwarp();                                // every lane's copies of this chunk have landed
+        const uint4 *stage = tile[warp][chunk % kStatStages];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           float f[8];
-          unpack8(mine[lane * kStatPitch + c], f);
+          unpack8(stage[lane * kStatPitch + c], f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             if (pass == 0) {
@@ -138,7 +149,9 @@ k_row_stats_sequential(const uint4 *x, float2 *stats, uint64_t rows, uint32_t co
             }
           }
         }
+        __syncwarp();                                // before a later copy overwrites this stage
       }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
       if (pass == 0)
         mean = __fdiv_rn(acc, (float)cols);
     }
@@ -476,15 +489,15 @@ bool row_stats_sequential(const void *x, uint64_t rows, uint64_t cols, float eps
     *rc = fail(kOutOfMemory, "cannot allocate the row statistics scratch");
     return true;
   }
-  uint64_t blocks = (rows + 255) / 256;
-  const uint64_t cap = (uint64_t)sm_count() * 4;
+  uint64_t blocks = (rows + 32 * kStatWarps - 1) / (32 * kStatWarps);
+  const uint64_t cap = (uint64_t)sm_count() * 6; // 37 KB of shared memory per CTA: six resident per SM
   blocks = blocks > cap ? cap : blocks;
   if (layer)
-    k_row_stats_sequential<true><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4 *>(x), area, rows,
-                                                                  (uint32_t)cols, eps);
+    k_row_stats_sequential<true><<<(unsigned)blocks, 32 * kStatWarps, 0, s>>>(static_cast<const uint4 *>(x), area,
+                                                                              rows, (uint32_t)cols, eps);
   else
-    k_row_stats_sequential<false><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4 *>(x), area, rows,
-                                                                   (uint32_t)cols, eps);
+    k_row_stats_sequential<false><<<(unsigned)blocks, 32 * kStatWarps, 0, s>>>(static_cast<const uint4 *>(x), area,
+                                                                               rows, (uint32_t)cols, eps);
   *rc = done("k_row_stats_sequential");
   *stats = area;
   return true;
