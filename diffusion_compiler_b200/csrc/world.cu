@@ -24,20 +24,53 @@
 namespace difb200 {
 
 // ---- launch plan ------------------------------------------------------------------------------
+std::vector<int> default_groups(int size) {
+  std::vector<int> groups{1};
+  if (size > 1 && size <= 4) {
+    groups.push_back(size - 1);
+  } else if (size > 4) {
+    groups.push_back((size - 1) / 2);
+    groups.push_back(size - 1 - (size - 1) / 2);
+  }
+  return groups;
+}
+
+std::vector<int> launch_groups(int size) {
+  // DIFB200_ATTENTION_GROUPS="1,3,4": how many ring steps (the own slice is step 0) each attention
+  // launch covers; a list that is malformed or does not sum to the world size is ignored
+  std::vector<int> groups;
+  if (const char *text = std::getenv("DIFB200_ATTENTION_GROUPS")) {
+    int value = 0, total = 0;
+    bool digits = false, ok = true;
+    for (const char *c = text;; ++c) {
+      if (*c >= '0' && *c <= '9') {
+        value = value * 10 + (*c - '0');
+        digits = true;
+      } else {
+        if (digits) {
+          groups.push_back(value);
+          total += value;
+          ok = ok && value > 0;
+        }
+        value = 0;
+        digits = false;
+        if (!*c)
+          break;
+      }
+    }
+    if (!ok || total != size)
+      groups.clear();
+  }
+  return groups.empty() ? default_groups(size) : groups;
+}
+
 bool plan_launches(int rank, int size, uint32_t tiles_per_slice, std::vector<int> group_sizes,
                    std::vector<LaunchPlan> &out) {
   out.clear();
   if (size < 1 || rank < 0 || rank >= size)
     return false;
-  if (group_sizes.empty()) {
-    group_sizes.push_back(1);
-    if (size > 1 && size <= 4) {
-      group_sizes.push_back(size - 1);
-    } else if (size > 4) {
-      group_sizes.push_back((size - 1) / 2);
-      group_sizes.push_back(size - 1 - (size - 1) / 2);
-    }
-  }
+  if (group_sizes.empty())
+    group_sizes = default_groups(size);
   int total = 0;
   for (int g : group_sizes) {
     if (g <= 0)
@@ -284,23 +317,35 @@ int world_exchange(World *world, void *const *buffers, const uint64_t *slice_byt
     if (int rc = check_cuda(cudaStreamWaitEvent(stream, world->ready, 0), "cudaStreamWaitEvent(slice ready)"))
       return rc;
   }
-  for (int s = 1; s < world->size; ++s) {
-    const RingStep step = ring_step(world->rank, world->size, s);
+  // The ring steps go out in the groups in which the attention launches consume them (one
+  // grouped NCCL call per launch: its peers are served concurrently); all steps of a group share
+  // the moment they are marked as landed.
+  const std::vector<int> groups = launch_groups(world->size);
+  int first = 0;
+  for (int g : groups) {
+    const int begin = first == 0 ? 1 : first, end = first + g; // step 0 is the own slice
+    first = end;
+    if (begin >= end)
+      continue;
     if (int rc = t.group_start())
       return rc;
-    for (int i = 0; i < count; ++i) {
-      char *base = static_cast<char *>(buffers[i]);
-      if (int rc = t.send(base + (uint64_t)world->rank * slice_bytes[i], (size_t)slice_bytes[i], step.send_to, stream))
-        return rc;
-      if (int rc = t.recv(base + (uint64_t)step.recv_from * slice_bytes[i], (size_t)slice_bytes[i], step.recv_from,
-                          stream))
-        return rc;
+    for (int s = begin; s < end; ++s) {
+      const RingStep step = ring_step(world->rank, world->size, s);
+      for (int i = 0; i < count; ++i) {
+        char *base = static_cast<char *>(buffers[i]);
+        if (int rc = t.send(base + (uint64_t)world->rank * slice_bytes[i], (size_t)slice_bytes[i], step.send_to, stream))
+          return rc;
+        if (int rc = t.recv(base + (uint64_t)step.recv_from * slice_bytes[i], (size_t)slice_bytes[i], step.recv_from,
+                            stream))
+          return rc;
+      }
     }
     if (int rc = t.group_end())
       return rc;
-    if (events && events[s - 1] && t.on_device())
-      if (int rc = check_cuda(cudaEventRecord(events[s - 1], stream), "cudaEventRecord(step landed)"))
-        return rc;
+    for (int s = begin; s < end; ++s)
+      if (events && events[s - 1] && t.on_device())
+        if (int rc = check_cuda(cudaEventRecord(events[s - 1], stream), "cudaEventRecord(step landed)"))
+          return rc;
   }
   return kOk;
 }
@@ -319,31 +364,6 @@ int world_exchange_class(World *world, int which, void *const *buffers, const ui
   return world_exchange(world, buffers, slice_bytes, count, producer, events.data());
 }
 
-namespace {
-std::vector<int> groups_from_environment() {
-  // DIFB200_ATTENTION_GROUPS="1,3,4": how many ring steps each attention launch covers
-  std::vector<int> groups;
-  if (const char *text = std::getenv("DIFB200_ATTENTION_GROUPS")) {
-    int value = 0;
-    bool digits = false;
-    for (const char *c = text;; ++c) {
-      if (*c >= '0' && *c <= '9') {
-        value = value * 10 + (*c - '0');
-        digits = true;
-      } else {
-        if (digits)
-          groups.push_back(value);
-        value = 0;
-        digits = false;
-        if (!*c)
-          break;
-      }
-    }
-  }
-  return groups;
-}
-} // namespace
-
 int sharded_attention(World *world, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
                       const void *v_bf16, const uint8_t *key_valid, uint64_t Sq, uint64_t slice_tokens, uint64_t H,
                       uint64_t KV, float scale, void *scratch, size_t scratch_bytes, void *state, void *out_bf16,
@@ -352,11 +372,8 @@ int sharded_attention(World *world, const int8_t *q8, const float *qs, const int
   if (slice_tokens == 0 || slice_tokens % 128 != 0)
     return fail(kInvalidArgument, "sharded attention: the slice length must be a positive multiple of 128");
   std::vector<LaunchPlan> launches;
-  std::vector<int> groups = groups_from_environment();
-  if (!plan_launches(rank, size, (uint32_t)(slice_tokens / 128), groups, launches)) {
-    groups.clear(); // a malformed override falls back to the default grouping
-    plan_launches(rank, size, (uint32_t)(slice_tokens / 128), groups, launches);
-  }
+  if (!plan_launches(rank, size, (uint32_t)(slice_tokens / 128), launch_groups(size), launches))
+    return fail(kInternalError, "sharded attention: no launch plan");
   if (launches.size() > 1 && !state)
     return fail(kInvalidArgument, "sharded attention: several launches need a state buffer");
   const uint64_t keys = (uint64_t)size * slice_tokens;

@@ -53,6 +53,9 @@ struct LaunchPlan {
 // Returns false when the sizes do not sum to `size` or contain a zero.
 bool plan_launches(int rank, int size, uint32_t tiles_per_slice, std::vector<int> group_sizes,
                    std::vector<LaunchPlan> &out);
+std::vector<int> default_groups(int size);
+// The grouping in force: DIFB200_ATTENTION_GROUPS when it is well-formed for `size`, else the default.
+std::vector<int> launch_groups(int size);
 
 class World {
 public:
@@ -84,8 +87,9 @@ int world_from_environment(World **out);
 
 // Ring exchange of gather buffers. buffers[i] holds size * slice_bytes[i] bytes; this rank's slice
 // is final once everything enqueued on `producer` so far has run. The size - 1 steps are enqueued
-// on the communication stream; events[s - 1] (caller-owned, may be null) is recorded when the
-// slice of rank - s has landed in every buffer of this call.
+// on the communication stream, one grouped transport call per attention launch group
+// (launch_groups); events[s - 1] (caller-owned, may be null) is recorded when the group of step s,
+// and with it the slice of rank - s, has landed in every buffer of this call.
 int world_exchange(World *world, void *const *buffers, const uint64_t *slice_bytes, int count,
                    cudaStream_t producer, cudaEvent_t *events);
 
