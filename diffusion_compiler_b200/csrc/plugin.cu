@@ -100,7 +100,7 @@ struct Executable {
   std::vector<Step> steps;
   std::vector<size_t> order;        // execution order of the steps (program order unless token-sharded)
   std::vector<Sharded> sharded;
-  std::vector<void *> world_buffers; // device allocations of the token-sharded mode
+  std::vector<void *> world_buffers; // device allocations beyond one per tensor (shared blocks, token-sharded mode)
   void *attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
   unsigned int *flag = nullptr;     // device flag for data-dependent argument errors
@@ -554,13 +554,34 @@ void allocate_world(Executable &exe) {
 
 void allocate(Executable &exe) {
   const ir::Program &p = exe.program;
-  exe.dev.assign(p.tensors.size(), nullptr);
-  // tensors produced only by skipped ops are never materialised
-  std::vector<bool> needed(p.tensors.size(), false);
-  for (size_t i = 0; i < p.tensors.size(); ++i)
+  const size_t n = p.tensors.size();
+  exe.dev.assign(n, nullptr);
+  // Reshape outputs share the buffer of their input: every tensor belongs to the group of its root
+  std::vector<size_t> root(n);
+  for (size_t i = 0; i < n; ++i)
+    root[i] = i;
+  for (const Step &st : exe.steps)
+    if (st.alias)
+      root[(size_t)p.index_of(st.op->out[0])] = root[(size_t)p.index_of(st.op->in[0])];
+  std::vector<size_t> position(exe.steps.size(), 0); // when a step runs (exe.order)
+  for (size_t k = 0; k < exe.order.size(); ++k)
+    position[exe.order[k]] = k;
+  // tensors produced only by skipped ops are never materialised; for the others, the first and
+  // the last step that touches their buffer
+  const size_t never = ~(size_t)0;
+  std::vector<bool> needed(n, false);
+  std::vector<size_t> first(n, never), last(n, 0);
+  for (size_t i = 0; i < n; ++i)
     if (p.tensors[i].has(ir::Input) || p.tensors[i].has(ir::Constant) || p.tensors[i].has(ir::Output))
       needed[i] = true;
-  for (const Step &st : exe.steps) {
+  for (size_t step = 0; step < exe.steps.size(); ++step) {
+    const Step &st = exe.steps[step];
+    auto touch = [&](int tensor) {
+      needed[(size_t)tensor] = true;
+      const size_t r = root[(size_t)tensor], at = position[step];
+      first[r] = first[r] == never || at < first[r] ? at : first[r];
+      last[r] = at > last[r] ? at : last[r];
+    };
     if (st.alias)
       needed[(size_t)p.index_of(st.op->in[0])] = true;
     if (st.skip)
@@ -573,43 +594,92 @@ void allocate(Executable &exe) {
                                              (st.k_quantised && k == 1)))
         continue;
       if (st.op->opcode == ir::QkNormPartialRope && st.rope_source >= 0 && k == 0) {
-        needed[(size_t)st.rope_source] = true;
+        touch(st.rope_source);
         continue;
       }
       if (st.op->opcode == ir::QuantizeInt8Rows && st.norm_step >= 0) { // reads the norm's inputs instead
         for (auto nid : exe.steps[(size_t)st.norm_step].op->in)
-          needed[(size_t)p.index_of(nid)] = true;
+          touch(p.index_of(nid));
         continue;
       }
-      needed[(size_t)p.index_of(id)] = true;
+      touch(p.index_of(id));
     }
     if (st.op->opcode == ir::LinearInt8Scaled) {
-      needed[(size_t)st.out_tensor] = true;
+      touch(st.out_tensor);
       if (st.bias_tensor >= 0)
-        needed[(size_t)st.bias_tensor] = true;
+        touch(st.bias_tensor);
     } else if (st.op->opcode == ir::QkNormPartialRope && st.rope_attention >= 0) {
       // writes INT8 codes into the attention scratch buffer, no bf16 tensor
     } else {
       for (auto id : st.op->out)
-        needed[(size_t)p.index_of(id)] = true;
+        touch(p.index_of(id));
     }
     if (st.mask_tensor >= 0)
-      needed[(size_t)st.mask_tensor] = true;
+      touch(st.mask_tensor);
   }
-  std::vector<bool> aliased(p.tensors.size(), false);
+  std::vector<bool> aliased(n, false);
   for (const Step &st : exe.steps)
     if (st.alias)
       aliased[(size_t)p.index_of(st.op->out[0])] = true;
-  exe.owned.assign(p.tensors.size(), 1);
+  exe.owned.assign(n, 1);
   for (const Sharded &sh : exe.sharded) // lives inside the gather buffer (allocate_world)
     if (sh.v_root >= 0)
       aliased[(size_t)sh.v_root] = true;
-  for (size_t i = 0; i < p.tensors.size(); ++i) {
+  // Internal tensors whose lifetimes do not overlap share device memory: a sweep over the step
+  // positions takes a block for every tensor at its first step (the smallest free block that holds
+  // it without wasting more than its size again, else a new allocation) and returns the blocks of
+  // the tensors whose last step this was. A block freed by a step is never handed to an output of
+  // the same step, so no kernel runs in place. Inputs, Outputs, Constants and every group with such
+  // a member keep buffers of their own (copies on other streams touch them).
+  // DIFB200_BUFFER_REUSE=0 gives every tensor its own allocation.
+  const char *reuse_env = std::getenv("DIFB200_BUFFER_REUSE");
+  const bool reuse = !(reuse_env && reuse_env[0] == '0');
+  std::vector<bool> pinned(n, false);
+  for (size_t i = 0; i < n; ++i)
+    if (p.tensors[i].has(ir::Input) || p.tensors[i].has(ir::Constant) || p.tensors[i].has(ir::Output))
+      pinned[root[i]] = true;
+  std::vector<std::vector<size_t>> born(exe.order.size()), dying(exe.order.size());
+  for (size_t i = 0; i < n; ++i) {
     if (!needed[i] || aliased[i])
       continue;
     const size_t bytes = (size_t)p.tensors[i].bytes();
-    require_cuda(cudaMalloc(&exe.dev[i], bytes ? bytes : 16), "cudaMalloc(tensor)");
-    exe.resident_bytes += bytes;
+    if (!reuse || pinned[i] || first[i] == never) {
+      require_cuda(cudaMalloc(&exe.dev[i], bytes ? bytes : 16), "cudaMalloc(tensor)");
+      exe.resident_bytes += bytes;
+    } else {
+      born[first[i]].push_back(i);
+      dying[last[i]].push_back(i);
+    }
+  }
+  struct Block {
+    void *ptr;
+    size_t bytes;
+  };
+  std::vector<Block> free_blocks;
+  std::vector<Block> block_of(n, Block{nullptr, 0});
+  for (size_t k = 0; k < exe.order.size(); ++k) {
+    for (size_t i : born[k]) {
+      const size_t bytes = (size_t)p.tensors[i].bytes() ? (size_t)p.tensors[i].bytes() : 16;
+      size_t best = free_blocks.size();
+      for (size_t b = 0; b < free_blocks.size(); ++b)
+        if (free_blocks[b].bytes >= bytes && free_blocks[b].bytes <= 2 * bytes &&
+            (best == free_blocks.size() || free_blocks[b].bytes < free_blocks[best].bytes))
+          best = b;
+      if (best < free_blocks.size()) {
+        block_of[i] = free_blocks[best];
+        free_blocks.erase(free_blocks.begin() + (long)best);
+      } else {
+        void *ptr = nullptr;
+        require_cuda(cudaMalloc(&ptr, bytes), "cudaMalloc(tensor)");
+        exe.world_buffers.push_back(ptr); // freed with the executable
+        exe.resident_bytes += bytes;
+        block_of[i] = Block{ptr, bytes};
+      }
+      exe.dev[i] = block_of[i].ptr;
+      exe.owned[i] = 0;
+    }
+    for (size_t i : dying[k])
+      free_blocks.push_back(block_of[i]);
   }
   allocate_world(exe);
   for (const Step &st : exe.steps) // program order: a chain of reshapes resolves front to back

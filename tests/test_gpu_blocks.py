@@ -88,6 +88,7 @@ def test_plugin_norm_quant_fusion_saves_the_normalised_tensor_and_stays_in_the_b
     S, hidden, heads, dim, ffn, rotary = 400, 512, 4, 128, 1024, 96
     p, ids, consts, inputs = blocks.synth_video_block(rng, S, hidden, heads, dim, ffn, rotary, _cpu_quantize)
     results, resident = [], []
+    monkeypatch.setenv("DIFB200_BUFFER_REUSE", "0")  # residency per tensor, so that the saved tensors show
     for fusion in ("1", "0"):
         monkeypatch.setenv("DIFB200_NORM_FUSION", fusion)
         ex = plugin.PluginExecutor(0)
@@ -98,6 +99,31 @@ def test_plugin_norm_quant_fusion_saves_the_normalised_tensor_and_stays_in_the_b
         results.append(ob.bf16_to_f32(got[ids["out"]]))
     assert resident[1] - resident[0] >= 2 * S * hidden * 2  # two [S, hidden] bf16 tensors fewer
     assert rel_l2(results[0], results[1]) <= 5e-4 and cosine(results[0], results[1]) >= 0.99999
+
+
+def test_plugin_buffer_reuse_keeps_the_bits_and_saves_memory(monkeypatch):
+    """Internal tensors whose lifetimes do not overlap share device memory (the plugin's default):
+    the same bits as with one allocation per tensor and fewer resident bytes,
+    also when the same executable runs several passes."""
+    from diffusion_compiler_b200 import plugin
+    rng = np.random.default_rng(16)
+    p, ids, consts, inputs = blocks.synth_mmdit_block(rng, batch=2, grid=(8, 8), text_tokens=24, hidden=512, heads=4,
+                                                     mlp=1024, quantize=_cpu_quantize)
+    results, resident = [], []
+    for reuse in ("1", "0"):
+        monkeypatch.setenv("DIFB200_BUFFER_REUSE", reuse)
+        ex = plugin.PluginExecutor(0)
+        prepared = ex.prepare(p, consts)
+        got, _ = prepared.run(inputs, warmups=1, iterations=2)
+        again, _ = prepared.run(inputs)
+        resident.append(int(prepared.compile_telemetry.resident_bytes))
+        ex.close()
+        for key in ("image_out", "text_out"):
+            assert np.array_equal(got[ids[key]], again[ids[key]])
+        results.append(got)
+    for key in ("image_out", "text_out"):
+        assert np.array_equal(results[0][ids[key]], results[1][ids[key]])
+    assert resident[0] < resident[1], resident
 
 
 @pytest.mark.skipif(not ob.ref_available(), reason="reference build (oracle/_ref) not present")

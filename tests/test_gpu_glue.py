@@ -121,6 +121,7 @@ def test_layer_norm_modulate_quant_fused_in_the_plugin(monkeypatch):
     inputs = {x: _bf(rng, [2, S, HIDDEN]), scale: _bf(rng, [2, 1, HIDDEN], 0.1), shift: _bf(rng, [2, 1, HIDDEN], 0.1)}
     want, _ = ob.ref().run(p, {**consts, **inputs})
     runs, resident = [], []
+    monkeypatch.setenv("DIFB200_BUFFER_REUSE", "0")  # residency per tensor, so that the saved tensor shows
     for fusion in ("1", "0"):
         monkeypatch.setenv("DIFB200_NORM_FUSION", fusion)
         ex = plugin.PluginExecutor(0)
