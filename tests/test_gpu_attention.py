@@ -149,3 +149,41 @@ def test_attention_chunked_launches_match_the_single_launch(ops, B, Sq, Sk, H, K
     assert rel_l2(a, b) <= 1e-4 and cosine(a, b) >= 0.999999, (rel_l2(a, b), cosine(a, b))
     # same tile order as the single launch: the carried state continues the very same sums
     assert np.array_equal(from_torch_bf16(same_order), from_torch_bf16(whole)) or rel_l2(c, b) <= 1e-5
+
+
+@pytest.mark.parametrize("size", [2, 4, 8])
+def test_attention_launch_plans_of_every_rank_match_the_single_launch(ops, size):
+    """The launch plan the token-sharded mode uses (difb200_world_plan: the own slice first, the other
+    slices in the groups their ring steps arrive in, ranges that wrap around the end of the key
+    axis) for every rank of a world of 2, 4 and 8, on one GPU: each rank's queries against the whole
+    gathered key axis in its planned launches must equal the single launch over all keys."""
+    import ctypes as C
+    import torch
+    from diffusion_compiler_b200 import _lib
+    lib = _lib.lib()
+    rng = np.random.default_rng(500 + size)
+    H, KV, slice_tokens, local = 2, 2, 256, 200      # slices padded to 2 key tiles, 200 real tokens each
+    Sk = size * slice_tokens
+    _, k, v = _qkv(rng, 1, Sk, H, KV)
+    valid = np.zeros((1, Sk), np.uint8)
+    for r in range(size):
+        valid[0, r * slice_tokens:r * slice_tokens + local] = 1
+    k8, ks = ob.orc().quantize_int8_rows([k.reshape(-1, 128)], 1)
+    t = lambda a: torch.from_numpy(a).cuda()
+    keys = (t(k8.reshape(1, Sk, KV, 128)), t(ks), to_torch_bf16(v))
+    for rank in range(size):
+        q, _, _ = _qkv(rng, 1, local, H, KV)
+        q8, qs = ob.orc().quantize_int8_rows([q.reshape(-1, 128)], 1)
+        cap = 16
+        ranges, first, count, n = (C.c_uint32 * (4 * cap))(), (C.c_int32 * cap)(), (C.c_int32 * cap)(), C.c_int32(0)
+        assert lib.difb200_world_plan(rank, size, slice_tokens // 128, (C.c_int32 * 1)(), 0, ranges, first, count, cap,
+                                      C.byref(n)) == 0
+        groups = [[(ranges[4 * i], ranges[4 * i + 1])] + ([(ranges[4 * i + 2], ranges[4 * i + 3])] if ranges[4 * i + 3] else [])
+                  for i in range(n.value)]
+        args = (t(q8.reshape(1, local, H, 128)), t(qs)) + keys
+        whole = ops.attention_int8(*args, t(valid))
+        parts = ops.attention_int8_chunked(*args, groups, t(valid))
+        torch.cuda.synchronize()
+        a, b = (ob.bf16_to_f32(from_torch_bf16(x)) for x in (parts, whole))
+        assert np.isfinite(a).all() and rel_l2(a, b) <= 1e-4, (size, rank, rel_l2(a, b))
+    ops.poll_status()
