@@ -214,12 +214,18 @@ def video_block_parity(torch, dist, device_index, rank, world, weights):
     plan = ShardPlan.make(tokens, world)
     lo, hi = plan.bounds(rank)
 
+    exchange = []
+
     def run(executor, lo, hi):
         p, ids, consts = video_block_slice(weights, positions, lo, hi)
         att = [op for op in p.operations if op.opcode == diffir.Opcode.Attention][0]
         p.tensor(att.outputs[0]).roles |= int(diffir.Role.Output)
-        inputs, keep = video_block_inputs(torch, ids, tokens, lo, hi, seed=11)
         prepared = executor.prepare(p, consts)
+        exchange.append(prepared.exchange())
+        # other inputs first, several passes: the compared pass must not see a slice of an earlier one
+        other, keep_other = video_block_inputs(torch, ids, tokens, lo, hi, seed=12)
+        prepared.run(other, warmups=1, iterations=2)
+        inputs, keep = video_block_inputs(torch, ids, tokens, lo, hi, seed=11)
         out, _ = prepared.run(inputs)
         prepared.close()
         return out[ids["out"]], out[att.outputs[0]]
@@ -247,11 +253,14 @@ def video_block_parity(torch, dist, device_index, rank, world, weights):
                 "cosine": float(np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b))),
                 "bit_identical": bool(np.array_equal(got, whole))}
     res = {"tokens": tokens, "ranks": world, "tokens_per_rank": [plan.local_tokens(r) for r in range(world)],
+           "exchange": exchange[0],
            "attention": compare([g[1] for g in gathered], whole_attn),
            "block": compare([g[0] for g in gathered], whole_out)}
-    # attention: only the order of fp32 sums differs (1e-4 is generous); block: the quantisers behind the
-    # attention turn that difference into one about thirty times larger, still inside the path's bar
-    res["ok"] = bool(res["attention"]["rel_l2"] <= 1e-4 and res["block"]["rel_l2"] <= 2e-3
+    # attention: only the order of the tensor cores' fp32 sums differs, which moves about one bf16 output
+    # in a thousand by one step (3e-5 .. 1e-4 measured); block: the quantisers behind the attention turn
+    # a difference d into about sqrt(d * step), the same amplification the block shows between exact and
+    # INT8 attention (4e-3 at full width), hence that bar
+    res["ok"] = bool(res["attention"]["rel_l2"] <= 3e-4 and res["block"]["rel_l2"] <= 4e-3
                      and res["block"]["cosine"] >= 0.9999)
     return res
 
@@ -273,6 +282,7 @@ def run_video_block(torch, dist, args, rank, local_rank, world, device, barrier,
     executor = plugin.PluginExecutor(local_rank)
     prepared = executor.prepare(p, consts)
     del weights
+    exchange = prepared.exchange()
     prepared.run(inputs, warmups=1, iterations=1, outputs=outputs)  # first-use set-up of every kernel
     prepared.profile()
     lib = _lib.lib()
@@ -319,7 +329,8 @@ def run_video_block(torch, dist, args, rank, local_rank, world, device, barrier,
     executor.close()
     return {"S": S, "plan": plan, "ms_per_step": ms_per_step, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": d2h,
             "launches": launches, "clocks": clocks, "profile": profile, "parity": parity, "sustained": sustained,
-            "resident_bytes": resident, "operations": len(p.operations), "timed_wall_s": wall_s}
+            "resident_bytes": resident, "operations": len(p.operations), "timed_wall_s": wall_s,
+            "exchange": exchange}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -662,15 +673,23 @@ def emit_json_line(fd: int, line: dict) -> None:
     os.write(fd, (json.dumps(line) + "\n").encode())
 
 
-def workload_config(world: int):
+EXCHANGE_TEXT = {
+    "none": "one rank, nothing is exchanged",
+    "direct": "K codes / K scales / V pushed into the peers' gather blocks by copy-engine copies over NVLink "
+              "(blocks mapped with CUDA IPC, set up over NCCL), ordered by sequence flags",
+    "nccl": "K codes / K scales / V exchanged over NCCL send / receive in ring steps"}
+
+
+def workload_config(world: int, exchange: str = "none"):
     v = VIDEO
     return {"workload": "video DiT block (benchmark configuration 4): %d tokens (21x30x52 latent + 512 text), hidden "
                         "%d, %d heads x %d, FFN %d SwiGLU, 3-axis RoPE over %d dims, W8A8 int8-convrot linears, INT8 "
                         "attention; one DiffIR program through the backend plugin"
                         % (v["tokens"], v["hidden"], v["heads"], v["dim"], v["ffn"], v["rotary"]),
             "tokens": v["tokens"],
-            "parallelism": "tokens sharded over %d GPU(s), weights replicated, K codes / K scales / V exchanged over "
-                           "NCCL in ring steps, attention starts on the local slice" % world,
+            "parallelism": "tokens sharded over %d GPU(s), weights replicated; %s; attention starts on the local "
+                           "slice" % (world, EXCHANGE_TEXT[exchange]),
+            "exchange": exchange,
             "quantization": "H256ConvRot activations + per-channel INT8 weights; Q and K per token-head INT8, V bf16",
             "l2": "one pass streams ~6 GB of activations and weights per GPU at N=1 (0.9 GB at N=8), larger than the "
                   "126 MB L2; no flush"}
@@ -762,6 +781,7 @@ def main():
     block = run_video_block(torch, dist, args, rank, local_rank, world, device, barrier, reduce_max)
     ops.poll_status()
     S, ms = block["S"], block["ms_per_step"]
+    config = workload_config(max(world, 1), block["exchange"])
     line = None
     if rank == 0:
         prof = block["profile"]

@@ -65,8 +65,12 @@ def lib() -> C.CDLL:
                 ("difb200_world_create", [pu8, i32, i32, C.POINTER(vp)]),
                 ("difb200_world_destroy", [vp]),
                 ("difb200_world_exchange", [vp, i32, C.POINTER(vp), pu64, i32, vp]),
-                ("difb200_sharded_attention", [vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, f32, vp, u64, vp, vp,
-                                               vp]),
+                ("difb200_world_bind", [vp, u64, vp, C.POINTER(vp), C.POINTER(vp), pi32]),
+                ("difb200_world_unbind", [vp, vp]),
+                ("difb200_world_push", [vp, vp, i32, pu64, pu64, i32, vp]),
+                ("difb200_world_selftest_flags", [u64, i32]),
+                ("difb200_sharded_attention", [vp, vp, vp, vp, vp, vp, vp, vp, u64, u64, u64, u64, f32, vp, u64, vp,
+                                               vp, vp]),
                 ("difb200_world_plan", [i32, i32, u32, pi32, i32, pu32, pi32, pi32, i32, pi32]),
                 ("difb200_world_selftest_fake", [i32, i32, u32])):
             getattr(L, name).restype = C.c_int
@@ -92,6 +96,8 @@ def lib() -> C.CDLL:
         L.difb200_executable_profile.restype = C.c_int
         L.difb200_executable_profile.argtypes = [vp, C.POINTER(u32), C.POINTER(C.c_double), C.POINTER(u64), u32,
                                                  C.POINTER(u32)]
+        L.difb200_executable_exchange.restype = C.c_int
+        L.difb200_executable_exchange.argtypes = [vp]
         L.difb200_attention_scratch_bytes.restype = u64
         L.difb200_attention_scratch_bytes.argtypes = [u64, u64, u64, u64]
         L.difb200_attention.restype = C.c_int

@@ -80,7 +80,7 @@ extern "C" {
 
 const char *difb200_last_error(void) { return last_error().c_str(); }
 
-int difb200_version(void) { return 2; }
+int difb200_version(void) { return 3; }
 
 uint64_t difb200_launch_count(void) { return launch_count(); }
 
@@ -261,12 +261,37 @@ int difb200_world_exchange(void *world, int32_t which, void *const *buffers, con
                               static_cast<cudaStream_t>(producer_stream));
 }
 
-int difb200_sharded_attention(void *world, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
-                              const void *v, const uint8_t *key_valid, uint64_t Sq, uint64_t slice_tokens, uint64_t H,
-                              uint64_t KV, float scale, void *scratch, uint64_t scratch_bytes, void *state, void *out,
-                              void *stream) {
-  return sharded_attention(static_cast<World *>(world), q8, qs, k8, ks, v, key_valid, Sq, slice_tokens, H, KV, scale,
-                           scratch, scratch_bytes, state, out, static_cast<cudaStream_t>(stream));
+int difb200_world_bind(void *world, uint64_t payload_bytes, void *stream, void **binding, void **block,
+                       int32_t *direct) {
+  if (!binding || !block || !direct)
+    return fail(kInvalidArgument, "difb200_world_bind: null pointer");
+  PeerBinding *b = nullptr;
+  const int rc = world_bind(static_cast<World *>(world), (size_t)payload_bytes, static_cast<cudaStream_t>(stream), &b);
+  *binding = b;
+  *block = b ? b->block : nullptr;
+  *direct = b && b->direct ? 1 : 0;
+  return rc;
+}
+
+int difb200_world_unbind(void *world, void *binding) {
+  return world_unbind(static_cast<World *>(world), static_cast<PeerBinding *>(binding));
+}
+
+int difb200_world_push(void *world, void *binding, int32_t which, const uint64_t *offsets, const uint64_t *slice_bytes,
+                       int32_t count, void *producer_stream) {
+  return world_push(static_cast<World *>(world), static_cast<PeerBinding *>(binding), which, offsets, slice_bytes, count,
+                    static_cast<cudaStream_t>(producer_stream));
+}
+
+int difb200_world_selftest_flags(uint64_t limit_ns, int32_t set) { return world_selftest_flags(limit_ns, set != 0); }
+
+int difb200_sharded_attention(void *world, void *binding, const int8_t *q8, const float *qs, const int8_t *k8,
+                              const float *ks, const void *v, const uint8_t *key_valid, uint64_t Sq,
+                              uint64_t slice_tokens, uint64_t H, uint64_t KV, float scale, void *scratch,
+                              uint64_t scratch_bytes, void *state, void *out, void *stream) {
+  return sharded_attention(static_cast<World *>(world), static_cast<PeerBinding *>(binding), q8, qs, k8, ks, v,
+                           key_valid, Sq, slice_tokens, H, KV, scale, scratch, scratch_bytes, state, out,
+                           static_cast<cudaStream_t>(stream));
 }
 
 int difb200_world_plan(int32_t rank, int32_t size, uint32_t tiles_per_slice, const int32_t *group_sizes,

@@ -49,6 +49,7 @@ namespace {
 struct Context {
   int device = 0;
   World *world = nullptr;           // token-sharded mode: the NCCL world this context is a rank of
+  std::shared_ptr<bool> world_alive = std::make_shared<bool>(false); // read by executables that outlive the context
   cudaStream_t stream = nullptr;    // kernels
   cudaStream_t h2d = nullptr;       // uploads of an overlapped execute
   cudaStream_t d2h = nullptr;       // downloads of an overlapped execute
@@ -89,6 +90,8 @@ struct Sharded {
   void *scratch = nullptr, *state = nullptr;
   size_t scratch_bytes = 0;
   int v_root = -1;                       // tensor whose buffer IS this rank's V slice (-1: V is copied in)
+  PeerBinding *binding = nullptr;        // the gather block holding v, k8, ks (mapped into the peers when direct)
+  uint64_t at_v = 0, at_k8 = 0, at_ks = 0; // their offsets in the block
 };
 
 struct Executable {
@@ -100,6 +103,8 @@ struct Executable {
   std::vector<Step> steps;
   std::vector<size_t> order;        // execution order of the steps (program order unless token-sharded)
   std::vector<Sharded> sharded;
+  World *world = nullptr;           // ctx->world, valid while *world_alive
+  std::shared_ptr<bool> world_alive;
   std::vector<void *> world_buffers; // device allocations beyond one per tensor (shared blocks, token-sharded mode)
   void *attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
@@ -126,6 +131,9 @@ struct Executable {
     for (size_t i = 0; i < dev.size(); ++i)
       if (dev[i] && (i >= owned.size() || owned[i]))
         cudaFree(dev[i]);
+    for (Sharded &sh : sharded) // collective among the ranks while the world lives
+      if (sh.binding)
+        world_unbind(world_alive && *world_alive ? world : nullptr, sh.binding);
     for (void *b : world_buffers)
       cudaFree(b);
     if (attn_scratch)
@@ -513,25 +521,24 @@ void allocate_world(Executable &exe) {
   };
   for (Sharded &sh : exe.sharded) {
     // every rank's token count, through the world's own exchange
-    uint64_t *counts = static_cast<uint64_t *>(device_alloc(size * sizeof(uint64_t), true));
-    require_cuda(cudaMemcpyAsync(counts + world->rank, &sh.tokens, sizeof(uint64_t), cudaMemcpyHostToDevice,
-                                 exe.ctx->stream),
-                 "cudaMemcpyAsync(token count)");
-    void *buffers[1] = {counts};
-    const uint64_t slice[1] = {sizeof(uint64_t)};
-    require(world_exchange(world, buffers, slice, 1, exe.ctx->stream, nullptr));
-    require_cuda(cudaStreamSynchronize(world->comm_stream), "cudaStreamSynchronize(token counts)");
     std::vector<uint64_t> tokens(size);
-    require_cuda(cudaMemcpy(tokens.data(), counts, size * sizeof(uint64_t), cudaMemcpyDeviceToHost),
-                 "cudaMemcpy(token counts)");
+    require(world_all_gather_host(world, &sh.tokens, tokens.data(), sizeof(uint64_t), exe.ctx->stream));
     uint64_t longest = 0;
     for (uint64_t t : tokens)
       longest = t > longest ? t : longest;
     sh.slice_tokens = (longest + 127) / 128 * 128;
     const uint64_t keys = size * sh.slice_tokens, KV = sh.kv_heads;
-    sh.k8 = static_cast<int8_t *>(device_alloc(keys * KV * 128, true));
-    sh.ks = static_cast<float *>(device_alloc(keys * KV * sizeof(float), true));
-    sh.v = device_alloc(keys * KV * 256, true);
+    // one block for the three gather buffers: with the direct exchange the peers map it as a whole
+    auto aligned = [](uint64_t bytes) { return (bytes + 255) / 256 * 256; };
+    sh.at_v = 0;
+    sh.at_k8 = sh.at_v + aligned(keys * KV * 256);
+    sh.at_ks = sh.at_k8 + aligned(keys * KV * 128);
+    require(world_bind(world, (size_t)(sh.at_ks + aligned(keys * KV * sizeof(float))), exe.ctx->stream, &sh.binding));
+    exe.resident_bytes += sh.binding->block_bytes;
+    char *block = static_cast<char *>(sh.binding->block);
+    sh.v = block + sh.at_v;
+    sh.k8 = reinterpret_cast<int8_t *>(block + sh.at_k8);
+    sh.ks = reinterpret_cast<float *>(block + sh.at_ks);
     sh.q8 = static_cast<int8_t *>(device_alloc(sh.tokens * sh.heads * 128, false));
     sh.qs = static_cast<float *>(device_alloc(sh.tokens * sh.heads * sizeof(float), false));
     sh.scratch_bytes = attention_int8_scratch_bytes(1, keys, KV);
@@ -756,14 +763,17 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
   // token-sharded mode: this rank's slice of a gather buffer is final, its ring exchange starts
   auto exchange = [&](const Sharded &sh, int which) {
     const uint64_t KV = sh.kv_heads, rows = sh.slice_tokens;
+    const bool direct = sh.binding && sh.binding->direct;
     if (which == 0) {
       void *buffers[1] = {sh.v};
-      const uint64_t bytes[1] = {rows * KV * 256};
-      require(world_exchange_class(world, 0, buffers, bytes, 1, s));
+      const uint64_t bytes[1] = {rows * KV * 256}, at[1] = {sh.at_v};
+      require(direct ? world_push(world, sh.binding, 0, at, bytes, 1, s)
+                     : world_exchange_class(world, 0, buffers, bytes, 1, s));
     } else {
       void *buffers[2] = {sh.k8, sh.ks};
-      const uint64_t bytes[2] = {rows * KV * 128, rows * KV * sizeof(float)};
-      require(world_exchange_class(world, 1, buffers, bytes, 2, s));
+      const uint64_t bytes[2] = {rows * KV * 128, rows * KV * sizeof(float)}, at[2] = {sh.at_k8, sh.at_ks};
+      require(direct ? world_push(world, sh.binding, 1, at, bytes, 2, s)
+                     : world_exchange_class(world, 1, buffers, bytes, 2, s));
     }
   };
   // where the INT8 operands of an Attention live: its scratch buffer, or (token-sharded) the local
@@ -884,7 +894,7 @@ void run_steps(Executable &exe, Overlap *overlap = nullptr) {
           exchange(sh, 0);
         if (!k_started)
           exchange(sh, 1);
-        require(sharded_attention(world, l.q8, l.qs, sh.k8, sh.ks, sh.v, sh.valid, S, sh.slice_tokens, H, KV, scale,
+        require(sharded_attention(world, sh.binding, l.q8, l.qs, sh.k8, sh.ks, sh.v, sh.valid, S, sh.slice_tokens, H, KV, scale,
                                   sh.scratch, sh.scratch_bytes, sh.state, D(op.out[0]), s));
         break;
       }
@@ -1140,6 +1150,7 @@ dif_backend_status create(int32_t device_ordinal, dif_backend_context *context, 
     World *world = nullptr;
     require(world_from_environment(&world));
     ctx->world = world;
+    *ctx->world_alive = world != nullptr;
     if (world)
       std::snprintf(ctx->device_name, sizeof(ctx->device_name),
                     "%.180s (difb200 sm_100a, int8-attention %s, token-sharded rank %d of %d)", prop.name,
@@ -1156,6 +1167,7 @@ void destroy(dif_backend_context context) {
   if (!ctx)
     return;
   cudaSetDevice(ctx->device);
+  *ctx->world_alive = false;
   delete ctx->world; // the communicator and its stream go first
   if (ctx->stream)
     cudaStreamDestroy(ctx->stream);
@@ -1203,6 +1215,8 @@ dif_backend_status compile_common(dif_backend_context context, const uint8_t *di
     auto exe = std::make_unique<Executable>();
     exe->ctx = ctx;
     exe->device = ctx->device;
+    exe->world = ctx->world;
+    exe->world_alive = ctx->world_alive;
     if (const char *v = std::getenv("DIFB200_PROFILE"))
       exe->profile = v[0] == '1';
     std::string text;
@@ -1456,6 +1470,20 @@ extern "C" int difb200_executable_profile(void *executable, uint32_t *opcodes, d
   *count = n;
   exe->profile_sum.clear();
   return kOk;
+}
+
+extern "C" int difb200_executable_exchange(void *executable) {
+  using namespace difb200;
+  const Executable *exe = static_cast<const Executable *>(executable);
+  if (!exe || exe->sharded.empty())
+    return 0;
+  for (const Sharded &sh : exe->sharded)
+    if (!sh.binding || !sh.binding->direct) {
+      if (sh.binding && !sh.binding->note.empty())
+        fail(kOk, sh.binding->note); // the reason, for difb200_last_error()
+      return 1;
+    }
+  return 2;
 }
 
 extern "C" {

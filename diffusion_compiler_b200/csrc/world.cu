@@ -299,7 +299,10 @@ int world_from_environment(World **out) {
   static std::atomic<uint32_t> generation{0};
   if (int rc = world_rendezvous(dir, rank, size, id, timeout_ms, generation.fetch_add(1)))
     return rc;
-  return world_create(id, rank, size, out);
+  if (int rc = world_create(id, rank, size, out))
+    return rc;
+  (*out)->wait_ns = (unsigned long long)(timeout_ms ? timeout_ms : 1u) * 1000ull * 1000ull;
+  return kOk;
 }
 
 // ---- exchange ---------------------------------------------------------------------------------
@@ -364,7 +367,324 @@ int world_exchange_class(World *world, int which, void *const *buffers, const ui
   return world_exchange(world, buffers, slice_bytes, count, producer, events.data());
 }
 
-int sharded_attention(World *world, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
+// ---- direct exchange: peer-mapped gather blocks, copy-engine pushes, sequence flags -------------
+namespace {
+
+struct FlagList {
+  uint32_t *flag[2 * kMaxDirectWorld];
+  uint32_t value[2 * kMaxDirectWorld];
+  int count;
+};
+
+// One thread per flag: waits until the word has reached its value (the words only grow; the
+// comparison is wrap-safe) or `limit_ns` has passed, which is reported in the device status words
+// (kernel 5; role = index in the list, detail = the value seen last) and ends the wait.
+__global__ void wait_flags_kernel(FlagList list, unsigned long long limit_ns, DeviceStatus *status) {
+  const int i = (int)threadIdx.x;
+  if (i >= list.count)
+    return;
+  const uint32_t *flag = list.flag[i];
+  const uint32_t want = list.value[i];
+  unsigned long long start = 0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+  for (;;) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if ((int32_t)(seen - want) >= 0)
+      break;
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - start > limit_ns) {
+      if (atomicExch(&status->flag, 1u) == 0u) {
+        status->kernel = 5u;
+        status->role = (unsigned)i;
+        status->detail = seen;
+      }
+      break;
+    }
+    __nanosleep(200);
+  }
+  __threadfence_system();
+}
+
+// One thread per flag: everything this stream did before is visible before the word is.
+__global__ void set_flags_kernel(FlagList list) {
+  const int i = (int)threadIdx.x;
+  if (i >= list.count)
+    return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(list.flag[i]), "r"(list.value[i]) : "memory");
+}
+
+int wait_flags(const FlagList &list, unsigned long long limit_ns, cudaStream_t stream) {
+  if (list.count == 0)
+    return kOk;
+  DeviceStatus *status = device_status_words();
+  if (!status)
+    return fail(kInternalError, "device status words are unavailable");
+  wait_flags_kernel<<<1, 2 * kMaxDirectWorld, 0, stream>>>(list, limit_ns, status);
+  return launched(cudaGetLastError(), "wait_flags_kernel");
+}
+
+int set_flags(const FlagList &list, cudaStream_t stream) {
+  if (list.count == 0)
+    return kOk;
+  set_flags_kernel<<<1, 2 * kMaxDirectWorld, 0, stream>>>(list);
+  return launched(cudaGetLastError(), "set_flags_kernel");
+}
+
+struct BindRecord {
+  cudaIpcMemHandle_t handle;
+  int32_t ok;
+  char gpu[16]; // the device's UUID: two ranks on one GPU must not wait for each other's kernels
+};
+
+// before an attention launch: the slices of its ring steps, both classes, carry this pass's number
+int await_slices(World *world, PeerBinding *binding, const LaunchPlan &plan, cudaStream_t stream) {
+  FlagList list{};
+  ExchangeFlags *own = binding->flags(world->rank);
+  for (int step : plan.steps) {
+    if (step == 0)
+      continue;
+    const int source = ring_step(world->rank, world->size, step).recv_from;
+    for (int which = 0; which < 2; ++which) {
+      if (binding->pushes[which] == 0)
+        return fail(kInvalidArgument, "sharded attention: the exchange of the gather buffers was not enqueued");
+      list.flag[list.count] = &own->arrived[which][source];
+      list.value[list.count] = binding->pushes[which];
+      ++list.count;
+    }
+  }
+  return wait_flags(list, world->wait_ns, stream);
+}
+
+// behind the last attention launch of a pass: the own slice may be overwritten once the pushes
+// have read it, and every peer learns that its slice here has been read
+int release_slices(World *world, PeerBinding *binding, cudaStream_t stream) {
+  if (int rc = check_cuda(cudaStreamWaitEvent(stream, binding->pushed, 0), "cudaStreamWaitEvent(slices pushed)"))
+    return rc;
+  ++binding->passes;
+  FlagList list{};
+  for (int r = 0; r < world->size; ++r) {
+    if (r == world->rank)
+      continue;
+    list.flag[list.count] = &binding->flags(r)->consumed[world->rank];
+    list.value[list.count] = binding->passes;
+    ++list.count;
+  }
+  return set_flags(list, stream);
+}
+
+} // namespace
+
+int world_all_gather_host(World *world, const void *mine, void *all, size_t bytes, cudaStream_t stream) {
+  if (!world || !mine || !all || bytes == 0)
+    return fail(kInvalidArgument, "world all-gather: bad arguments");
+  const size_t size = (size_t)world->size;
+  if (!world->transport->on_device()) { // host transport (tests): the buffers are host memory
+    std::memcpy(static_cast<char *>(all) + (size_t)world->rank * bytes, mine, bytes);
+    void *buffers[1] = {all};
+    const uint64_t slice[1] = {bytes};
+    return world_exchange(world, buffers, slice, 1, stream, nullptr);
+  }
+  char *device = nullptr;
+  if (int rc = check_cuda(cudaMalloc(&device, size * bytes), "cudaMalloc(all-gather)"))
+    return rc;
+  int rc = check_cuda(cudaMemcpyAsync(device + (size_t)world->rank * bytes, mine, bytes, cudaMemcpyHostToDevice, stream),
+                      "cudaMemcpyAsync(all-gather)");
+  void *buffers[1] = {device};
+  const uint64_t slice[1] = {bytes};
+  if (!rc)
+    rc = world_exchange(world, buffers, slice, 1, stream, nullptr);
+  if (!rc)
+    rc = check_cuda(cudaStreamSynchronize(world->comm_stream), "cudaStreamSynchronize(all-gather)");
+  if (!rc)
+    rc = check_cuda(cudaMemcpy(all, device, size * bytes, cudaMemcpyDeviceToHost), "cudaMemcpy(all-gather)");
+  cudaFree(device);
+  return rc;
+}
+
+int world_bind(World *world, size_t payload_bytes, cudaStream_t stream, PeerBinding **out) {
+  if (!world || !out)
+    return fail(kInvalidArgument, "world bind: bad arguments");
+  *out = nullptr;
+  PeerBinding *b = new PeerBinding();
+  b->payload_bytes = (payload_bytes + 255) / 256 * 256;
+  // a block of its own mapping granule, so that the exported handle covers exactly this block
+  const size_t granule = 2u << 20;
+  b->block_bytes = (b->payload_bytes + sizeof(ExchangeFlags) + granule - 1) / granule * granule;
+  b->peer.assign((size_t)world->size, nullptr);
+  b->checked.assign((size_t)world->size, 0u);
+  int rc = check_cuda(cudaMalloc(&b->block, b->block_bytes), "cudaMalloc(gather block)");
+  if (!rc)
+    rc = check_cuda(cudaMemsetAsync(b->block, 0, b->block_bytes, stream), "cudaMemsetAsync(gather block)");
+  if (!rc) // zero before any peer can learn the handle: a push must never be wiped
+    rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize(gather block)");
+  if (!rc)
+    rc = check_cuda(cudaEventCreateWithFlags(&b->pushed, cudaEventDisableTiming), "cudaEventCreate");
+  if (rc) {
+    if (b->block)
+      cudaFree(b->block);
+    delete b;
+    return rc;
+  }
+  b->peer[(size_t)world->rank] = static_cast<char *>(b->block);
+  *out = b;
+  if (world->size == 1)
+    return kOk;
+  const char *mode = std::getenv("DIFB200_EXCHANGE");
+  const bool wanted = !(mode && std::strcmp(mode, "nccl") == 0) && world->size <= kMaxDirectWorld &&
+                      world->transport->on_device();
+  // round 1: every rank's handle; round 2: whether every rank could map every handle
+  std::vector<BindRecord> records((size_t)world->size);
+  BindRecord mine{};
+  {
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, world->device) == cudaSuccess)
+      std::memcpy(mine.gpu, prop.uuid.bytes, 16);
+    else
+      cudaGetLastError();
+  }
+  if (wanted) {
+    mine.ok = cudaIpcGetMemHandle(&mine.handle, b->block) == cudaSuccess ? 1 : 0;
+    if (!mine.ok)
+      cudaGetLastError();
+  }
+  if (int rc2 = world_all_gather_host(world, &mine, records.data(), sizeof(BindRecord), stream))
+    return rc2;
+  bool all_exported = true, shared_gpu = false;
+  for (size_t r = 0; r < records.size(); ++r) {
+    all_exported = all_exported && records[r].ok == 1;
+    for (size_t o = 0; o < r; ++o)
+      shared_gpu = shared_gpu || std::memcmp(records[r].gpu, records[o].gpu, 16) == 0;
+  }
+  all_exported = all_exported && !shared_gpu;
+  int32_t mapped = all_exported ? 1 : 0;
+  if (all_exported) {
+    for (int r = 0; r < world->size && mapped; ++r) {
+      if (r == world->rank)
+        continue;
+      void *ptr = nullptr;
+      if (cudaIpcOpenMemHandle(&ptr, records[(size_t)r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        mapped = 0;
+      } else {
+        b->peer[(size_t)r] = static_cast<char *>(ptr);
+      }
+    }
+  }
+  std::vector<int32_t> everyone((size_t)world->size, 0);
+  if (int rc2 = world_all_gather_host(world, &mapped, everyone.data(), sizeof(int32_t), stream))
+    return rc2;
+  bool all_mapped = true;
+  for (int32_t m : everyone)
+    all_mapped = all_mapped && m == 1;
+  if (all_mapped) {
+    b->direct = true;
+    return kOk;
+  }
+  for (int r = 0; r < world->size; ++r)
+    if (r != world->rank && b->peer[(size_t)r]) {
+      cudaIpcCloseMemHandle(b->peer[(size_t)r]);
+      b->peer[(size_t)r] = nullptr;
+    }
+  b->note = !wanted ? "direct exchange not requested or not possible for this world"
+                    : (shared_gpu ? "two ranks share a GPU"
+                       : !all_exported ? "a rank could not export its gather block (CUDA IPC)"
+                                     : "a rank could not map a peer's gather block (CUDA IPC, peer access)");
+  return kOk;
+}
+
+int world_unbind(World *world, PeerBinding *b) {
+  if (!b)
+    return kOk;
+  int rc = kOk;
+  if (b->direct) {
+    // own pushes and flag stores are done; then nobody touches a block that is about to go
+    rc = check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize(unbind)");
+    for (char *mapped : b->peer)
+      if (mapped && mapped != b->block)
+        cudaIpcCloseMemHandle(mapped);
+    if (world) { // (a world that is gone already: the caller broke the order of destruction; no barrier then)
+      int32_t here = 1;
+      std::vector<int32_t> everyone((size_t)world->size, 0);
+      const int rc2 = world_all_gather_host(world, &here, everyone.data(), sizeof(int32_t), world->comm_stream);
+      rc = rc ? rc : rc2;
+    }
+  }
+  if (b->pushed)
+    cudaEventDestroy(b->pushed);
+  if (b->block)
+    cudaFree(b->block);
+  delete b;
+  return rc;
+}
+
+int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets, const uint64_t *slice_bytes, int count,
+               cudaStream_t producer) {
+  if (!world || !b || !b->direct || which < 0 || which > 1 || count < 1 || !offsets || !slice_bytes)
+    return fail(kInvalidArgument, "world push: bad arguments");
+  for (int i = 0; i < count; ++i)
+    if (offsets[i] + (uint64_t)world->size * slice_bytes[i] > b->payload_bytes)
+      return fail(kInvalidArgument, "world push: a buffer does not fit the gather block");
+  cudaStream_t stream = world->comm_stream;
+  if (int rc = check_cuda(cudaEventRecord(world->ready, producer), "cudaEventRecord(slice ready)"))
+    return rc;
+  if (int rc = check_cuda(cudaStreamWaitEvent(stream, world->ready, 0), "cudaStreamWaitEvent(slice ready)"))
+    return rc;
+  const uint32_t pass = ++b->pushes[which];
+  for (int s = 1; s < world->size; ++s) {
+    const int peer = ring_step(world->rank, world->size, s).send_to;
+    if (b->checked[(size_t)peer] < pass) {
+      b->checked[(size_t)peer] = pass;
+      if (pass > 1) { // the peer's attention of the previous pass has read what this push overwrites
+        FlagList list{};
+        list.flag[0] = &b->flags(world->rank)->consumed[peer];
+        list.value[0] = pass - 1;
+        list.count = 1;
+        if (int rc = wait_flags(list, world->wait_ns, stream))
+          return rc;
+      }
+    }
+    for (int i = 0; i < count; ++i) {
+      const uint64_t at = offsets[i] + (uint64_t)world->rank * slice_bytes[i];
+      if (int rc = check_cuda(cudaMemcpyAsync(b->peer[(size_t)peer] + at, static_cast<char *>(b->block) + at,
+                                              (size_t)slice_bytes[i], cudaMemcpyDeviceToDevice, stream),
+                              "cudaMemcpyAsync(slice to peer)"))
+        return rc;
+    }
+    FlagList list{};
+    list.flag[0] = &b->flags(peer)->arrived[which][world->rank];
+    list.value[0] = pass;
+    list.count = 1;
+    if (int rc = set_flags(list, stream))
+      return rc;
+  }
+  return check_cuda(cudaEventRecord(b->pushed, stream), "cudaEventRecord(slices pushed)");
+}
+
+int world_selftest_flags(unsigned long long limit_ns, bool set) {
+  uint32_t *word = nullptr;
+  if (int rc = check_cuda(cudaMalloc(&word, 256), "cudaMalloc(flag)"))
+    return rc;
+  int rc = check_cuda(cudaMemset(word, 0, 256), "cudaMemset(flag)");
+  FlagList list{};
+  list.flag[0] = word;
+  list.value[0] = 7;
+  list.count = 1;
+  if (!rc && set)
+    rc = set_flags(list, nullptr);
+  if (!rc)
+    rc = wait_flags(list, limit_ns, nullptr);
+  if (!rc)
+    rc = poll_device_status("flag self-test");
+  else
+    cudaDeviceSynchronize();
+  cudaFree(word);
+  return rc;
+}
+
+int sharded_attention(World *world, PeerBinding *binding, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
                       const void *v_bf16, const uint8_t *key_valid, uint64_t Sq, uint64_t slice_tokens, uint64_t H,
                       uint64_t KV, float scale, void *scratch, size_t scratch_bytes, void *state, void *out_bf16,
                       cudaStream_t stream) {
@@ -377,10 +697,15 @@ int sharded_attention(World *world, const int8_t *q8, const float *qs, const int
   if (launches.size() > 1 && !state)
     return fail(kInvalidArgument, "sharded attention: several launches need a state buffer");
   const uint64_t keys = (uint64_t)size * slice_tokens;
+  const bool direct = binding && binding->direct && size > 1;
   for (size_t i = 0; i < launches.size(); ++i) {
     const LaunchPlan &plan = launches[i];
+    if (direct) {
+      if (int rc = await_slices(world, binding, plan, stream))
+        return rc;
+    }
     for (int step : plan.steps) {
-      if (step == 0)
+      if (step == 0 || direct)
         continue; // the own slice: written on `stream` itself
       for (int which = 0; which < 2; ++which) {
         if ((int)world->landed[which].size() < step)
@@ -402,6 +727,8 @@ int sharded_attention(World *world, const int8_t *q8, const float *qs, const int
                                 scratch_bytes, out_bf16, stream, &chunk))
       return rc;
   }
+  if (direct)
+    return release_slices(world, binding, stream);
   return kOk;
 }
 

@@ -11,8 +11,17 @@
 // rank - s; every GPU sends and receives one slice per step, which NVSwitch serves at full
 // bandwidth). Attention starts on the own slice while the others are in flight and takes the
 // arrived slices in a few launches that carry the softmax state (attention_int8 with an
-// AttentionChunk); launches are ordered behind the steps they need by CUDA events only: no
-// kernel ever waits on a flag that another kernel or another GPU writes.
+// AttentionChunk).
+//
+// Two ways to move the slices. (1) Direct (the default where it can be set up): the gather block
+// of every rank is mapped into every other rank (CUDA IPC over NVLink), and a rank PUSHES its
+// slice into the peers' blocks with copy-engine copies on its communication stream, each followed
+// by a one-word sequence number written into the peer's flag area; an attention launch is
+// preceded by a one-CTA kernel that waits (bounded, see World::wait_ns) until the flags of the
+// slices it reads carry the number of this pass. No SM and no rendezvous between the two sides is
+// involved in a transfer, so transfers neither compete with the attention and GEMM CTAs for SMs
+// nor couple the ranks' kernel schedules. (2) NCCL send / receive pairs, one grouped call per
+// launch group, ordered by CUDA events; this is also what bootstraps (1).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -66,8 +75,51 @@ public:
   // landed[c][s - 1]: slice of rank - s has arrived in the buffers of exchange class c
   // (0 = values, 1 = key codes and scales); recorded by world_exchange_class
   std::vector<cudaEvent_t> landed[2];
+  // limit of the waits for another rank's flag (direct exchange), DIFB200_WORLD_TIMEOUT_MS
+  unsigned long long wait_ns = 60ull * 1000ull * 1000ull * 1000ull;
   ~World();
 };
+
+// Every rank's `bytes` bytes, in rank order, into `all` (host memory; blocks until they are there).
+int world_all_gather_host(World *world, const void *mine, void *all, size_t bytes, cudaStream_t stream);
+
+// ---- direct exchange --------------------------------------------------------------------------
+constexpr int kMaxDirectWorld = 16;
+// Flag area at the end of every gather block; all words count passes (1, 2, ...) and only grow.
+struct ExchangeFlags {
+  uint32_t arrived[2][kMaxDirectWorld]; // [class][source rank]: that rank's slice of pass n is here
+  uint32_t consumed[kMaxDirectWorld];   // [reader rank]: that rank's attention of pass n has read MY slice there
+  uint32_t reserved[16];
+};
+// One gather block (the buffers of one sharded attention, at the same offsets on every rank).
+struct PeerBinding {
+  bool direct = false;       // false: the block is plain device memory and the slices travel by NCCL
+  std::string note;          // why not direct
+  void *block = nullptr;     // own block: payload, then ExchangeFlags
+  size_t payload_bytes = 0, block_bytes = 0;
+  std::vector<char *> peer;  // peer[r]: the block of rank r as mapped here ([rank] = block)
+  uint32_t pushes[2] = {0, 0}; // exchanges enqueued so far, per class
+  uint32_t passes = 0;         // attention passes enqueued so far
+  std::vector<uint32_t> checked; // [peer]: the pass up to which the communication stream has waited for `consumed`
+  cudaEvent_t pushed = nullptr;  // communication stream: every push enqueued so far has read the own slice
+  ExchangeFlags *flags(int r) const { return reinterpret_cast<ExchangeFlags *>(peer[(size_t)r] + payload_bytes); }
+};
+// Collective: allocates a zeroed block of `payload_bytes` (+ flags) on every rank and, unless
+// DIFB200_EXCHANGE=nccl, maps the peers' blocks; `direct` is the same on all ranks (one rank that
+// cannot export or map makes all of them use NCCL, `note` says why).
+int world_bind(World *world, size_t payload_bytes, cudaStream_t stream, PeerBinding **out);
+// Collective: waits for this device's work, unmaps the peers, waits for all ranks, frees the block.
+int world_unbind(World *world, PeerBinding *binding);
+// Direct form of world_exchange_class: pushes this rank's slice of `count` buffers (at `offsets`
+// in the block, `slice_bytes` per rank) to every peer, in ring order, once `producer` has run what
+// is enqueued so far; before the first push of a pass to a peer the communication stream waits
+// until that peer's attention of the previous pass has read the slice it is about to overwrite.
+int world_push(World *world, PeerBinding *binding, int which, const uint64_t *offsets, const uint64_t *slice_bytes,
+               int count, cudaStream_t producer);
+// Test of the flag kernels on one device: a wait for a flag that is set beforehand (`set` true:
+// returns kOk) or that nothing sets (`set` false: the wait gives up after `limit_ns` and the
+// status poll returns kExecutionError); the context stays usable either way.
+int world_selftest_flags(unsigned long long limit_ns, bool set);
 
 // Rendezvous of `size` processes through a directory all of them can reach, bounded by
 // `timeout_ms`: every rank leaves a file, rank 0 also the 128-byte communicator id (`id` in for
@@ -105,7 +157,8 @@ int world_exchange_class(World *world, int which, void *const *buffers, const ui
 // have been enqueued. `world` may be null (one rank: a single launch over the own slice).
 // scratch: attention_int8_scratch_bytes(1, size * slice_tokens, KV); state:
 // attention_int8_state_bytes(1, Sq, H) (unused with one launch).
-int sharded_attention(World *world, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
+// `binding` (may be null: NCCL events) selects the direct exchange's flags as the ordering.
+int sharded_attention(World *world, PeerBinding *binding, const int8_t *q8, const float *qs, const int8_t *k8, const float *ks,
                       const void *v_bf16, const uint8_t *key_valid, uint64_t Sq, uint64_t slice_tokens, uint64_t H,
                       uint64_t KV, float scale, void *scratch, size_t scratch_bytes, void *state, void *out_bf16,
                       cudaStream_t stream);

@@ -148,6 +148,12 @@ class PreparedExecution:
         _lib.check(_lib.lib().difb200_executable_profile(self._handle, opcodes, ms, steps, cap, C.byref(n)))
         return {int(opcodes[i]): (float(ms[i]), int(steps[i])) for i in range(n.value)}
 
+    def exchange(self) -> str:
+        """How a token-sharded executable moves its slices: "none" (one rank), "nccl" or "direct"
+        (difb200_executable_exchange)."""
+        from . import _lib
+        return ("none", "nccl", "direct")[int(_lib.lib().difb200_executable_exchange(self._handle))]
+
     def close(self):
         if self._handle:
             self._executor.api.destroy_executable(self._handle)

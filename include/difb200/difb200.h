@@ -199,8 +199,10 @@ DIFB200_EXPORT int difb200_attention_int8_chunk(const int8_t *q8, const float *q
  * The multi-GPU world of the token-sharded block (no counterpart in the reference, which runs one
  * device per executor: include/dif/runtime/executor.hpp:683). One process per GPU; rank r owns a
  * contiguous slice of the tokens; weights are replicated; the only exchange per block is that of
- * the INT8 key codes, their scales and the bf16 values, over NCCL (the NCCL library is resolved
- * with dlopen when a world is created: libnccl.so.2 or DIFB200_NCCL_LIBRARY).
+ * the INT8 key codes, their scales and the bf16 values: pushed into the peers' gather blocks by
+ * copy-engine copies over NVLink where the blocks can be mapped into each other (CUDA IPC; the
+ * default), else sent and received with NCCL, which also bootstraps the mapping (the NCCL library
+ * is resolved with dlopen when a world is created: libnccl.so.2 or DIFB200_NCCL_LIBRARY).
  *   difb200_world_unique_id     rank 0 makes the 128-byte communicator id, which the host hands to
  *                               the other ranks by any means it has
  *   difb200_world_rendezvous    optional bounded meeting point in a directory shared by the ranks
@@ -214,16 +216,35 @@ DIFB200_EXPORT int difb200_attention_int8_chunk(const int8_t *q8, const float *q
  *                               and this rank's slice is final once the work enqueued on
  *                               producer_stream so far has run. Step s of size - 1 sends the own slice
  *                               to rank + s and receives that of rank - s; nothing is waited for here
+ *   difb200_world_bind          collective: one zeroed device block of payload_bytes per rank for the
+ *                               gather buffers (the caller places them at offsets that are the same on
+ *                               every rank) and, unless DIFB200_EXCHANGE=nccl or a rank cannot export or
+ *                               map, the peers' blocks mapped into this rank; *direct tells which (the
+ *                               same on all ranks). difb200_world_unbind, collective too, frees it
+ *   difb200_world_push          direct form of difb200_world_exchange for a block with *direct = 1: this
+ *                               rank's slice of each buffer (offsets[i] in the block, slice_bytes[i] per
+ *                               rank) is copied into every peer's block by the copy engines, in ring
+ *                               order, each copy followed by the pass number in the peer's flag area;
+ *                               a push of pass n to a peer first waits until that peer's attention of
+ *                               pass n - 1 has read the slice it overwrites
  *   difb200_sharded_attention   this rank's queries q8 [Sq,H,128] / qs against the gather buffers k8
  *                               [size * slice_tokens, KV, 128], ks, v (slice_tokens a multiple of 128,
  *                               key_valid [size * slice_tokens] marks real tokens): a few launches of
  *                               difb200_attention_int8_chunk, the own slice first, each ordered behind
- *                               the ring steps it reads by CUDA events (DIFB200_ATTENTION_GROUPS="1,3,4"
- *                               sets how many steps each launch takes). world may be NULL (one rank)
+ *                               the ring steps it reads (DIFB200_ATTENTION_GROUPS="1,3,4" sets how many
+ *                               steps each launch takes): by CUDA events with binding NULL (NCCL), by a
+ *                               one-CTA kernel that waits for the pushed slices' flags with a direct
+ *                               binding. Those waits are bounded by DIFB200_WORLD_TIMEOUT_MS (worlds
+ *                               from the environment; 60 s otherwise): a slice that never arrives ends
+ *                               in status 5 at the next difb200_poll_status, not in a hang.
+ *                               world may be NULL (one rank)
+ *   difb200_world_selftest_flags  the flag kernels on one device: a wait for a flag that is set (set = 1,
+ *                               status 0) or that nothing sets (set = 0: gives up after limit_ns,
+ *                               status 5), leaving the context usable
  *   difb200_world_plan          the launch plan itself (host only): tile ranges, first ring step and
  *                               number of steps of every launch
- * A rank that is lost while an exchange is in flight is not detected here (NCCL has no deadline of
- * its own); hosts that need that put a heartbeat in front of every step.
+ * A rank that is lost while an NCCL exchange is in flight is not detected here (NCCL has no deadline
+ * of its own); hosts that need that put a heartbeat in front of every step.
  */
 DIFB200_EXPORT int difb200_world_unique_id(uint8_t *id128);
 DIFB200_EXPORT int difb200_world_rendezvous(const char *directory, int32_t rank, int32_t size, uint8_t *id128,
@@ -232,11 +253,17 @@ DIFB200_EXPORT int difb200_world_create(const uint8_t *id128, int32_t rank, int3
 DIFB200_EXPORT int difb200_world_destroy(void *world);
 DIFB200_EXPORT int difb200_world_exchange(void *world, int32_t which, void *const *buffers,
                                           const uint64_t *slice_bytes, int32_t count, void *producer_stream);
-DIFB200_EXPORT int difb200_sharded_attention(void *world, const int8_t *q8, const float *qs, const int8_t *k8,
-                                             const float *ks, const void *v, const uint8_t *key_valid,
-                                             uint64_t Sq, uint64_t slice_tokens, uint64_t H, uint64_t KV,
-                                             float scale, void *scratch, uint64_t scratch_bytes, void *state,
-                                             void *out, void *stream);
+DIFB200_EXPORT int difb200_world_bind(void *world, uint64_t payload_bytes, void *stream, void **binding, void **block,
+                                      int32_t *direct);
+DIFB200_EXPORT int difb200_world_unbind(void *world, void *binding);
+DIFB200_EXPORT int difb200_world_push(void *world, void *binding, int32_t which, const uint64_t *offsets,
+                                      const uint64_t *slice_bytes, int32_t count, void *producer_stream);
+DIFB200_EXPORT int difb200_world_selftest_flags(uint64_t limit_ns, int32_t set);
+DIFB200_EXPORT int difb200_sharded_attention(void *world, void *binding, const int8_t *q8, const float *qs,
+                                             const int8_t *k8, const float *ks, const void *v,
+                                             const uint8_t *key_valid, uint64_t Sq, uint64_t slice_tokens, uint64_t H,
+                                             uint64_t KV, float scale, void *scratch, uint64_t scratch_bytes,
+                                             void *state, void *out, void *stream);
 DIFB200_EXPORT int difb200_world_plan(int32_t rank, int32_t size, uint32_t tiles_per_slice,
                                       const int32_t *group_sizes, int32_t group_count, uint32_t *tile_ranges,
                                       int32_t *first_step, int32_t *step_count, int32_t capacity,
@@ -402,6 +429,13 @@ DIFB200_EXPORT int difb200_measure_i8_mma_peak(int32_t ctas_per_mma, uint32_t mm
  */
 DIFB200_EXPORT int difb200_executable_profile(void *executable, uint32_t *opcodes, double *milliseconds,
                                               uint64_t *steps, uint32_t capacity, uint32_t *count);
+
+/*
+ * How a token-sharded executable of the plugin moves its key / value slices: 0 = it is not sharded
+ * (one rank), 1 = NCCL send / receive (difb200_last_error() then holds why the direct form was not
+ * set up), 2 = direct pushes into peer-mapped gather blocks.
+ */
+DIFB200_EXPORT int difb200_executable_exchange(void *executable);
 
 #ifdef __cplusplus
 }

@@ -185,5 +185,10 @@ def test_attention_launch_plans_of_every_rank_match_the_single_launch(ops, size)
         parts = ops.attention_int8_chunked(*args, groups, t(valid))
         torch.cuda.synchronize()
         a, b = (ob.bf16_to_f32(from_torch_bf16(x)) for x in (parts, whole))
-        assert np.isfinite(a).all() and rel_l2(a, b) <= 1e-4, (size, rank, rel_l2(a, b))
+        # Another key order: the fp32 sums of the tensor cores round elsewhere, which moves about one
+        # bf16 output in a thousand by one step (rel-L2 near 1e-4). A slice read twice, skipped or taken
+        # from the wrong place would show as whole rows off by far more than one step.
+        assert np.isfinite(a).all() and rel_l2(a, b) <= 3e-4, (size, rank, rel_l2(a, b))
+        assert np.all(np.abs(a - b) <= 2.0 ** -7 * np.abs(b) + 1e-3 * np.abs(b).max()), (size, rank)
+        assert np.mean(a != b) <= 0.01, (size, rank, float(np.mean(a != b)))
     ops.poll_status()

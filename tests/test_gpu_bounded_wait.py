@@ -51,3 +51,21 @@ def test_gemm_wait_runs_out_is_reported_and_recovered(k_block):
     ops.poll_status()
     want = ob.orc().linear_int8_scaled(host[0], host[1], host[2], host[3])
     assert np.array_equal(got, want), "the call after a timed-out one is not bit-exact"
+
+
+def test_exchange_flag_wait_runs_out_is_reported_and_recovered():
+    """The one-CTA kernel that orders an attention launch behind the slices pushed by other ranks
+    (direct exchange): with the flag set beforehand it returns at once; with a flag that nothing
+    sets it gives up after its limit (10 ms here), which the status poll reports as status 5 with the
+    place (kernel 5), and the device goes on working."""
+    import torch
+    from diffusion_compiler_b200 import _lib, ops
+    lib = _lib.lib()
+    assert lib.difb200_world_selftest_flags(10_000_000, 1) == 0, lib.difb200_last_error().decode()
+    assert lib.difb200_world_selftest_flags(10_000_000, 0) == 5
+    text = lib.difb200_last_error().decode()
+    assert "bounded device-side wait ran out" in text and "kernel 5" in text
+    ops.poll_status()  # cleared by the failing poll
+    assert lib.difb200_world_selftest_flags(10_000_000, 1) == 0
+    x = torch.arange(8, device="cuda")
+    assert int(x.sum().item()) == 28
