@@ -407,6 +407,41 @@ __global__ void wait_flags_kernel(FlagList list, unsigned long long limit_ns, De
   __threadfence_system();
 }
 
+// Opens a pass of pushes: waits like wait_flags_kernel (the peers have read the slices of the
+// previous pass), then sets the word that the flag copies of this pass take their value from.
+__global__ void open_pass_kernel(FlagList list, uint32_t *stamp, uint32_t pass, unsigned long long limit_ns,
+                                 DeviceStatus *status) {
+  const int i = (int)threadIdx.x;
+  if (i < list.count) {
+    const uint32_t *flag = list.flag[i];
+    const uint32_t want = list.value[i];
+    unsigned long long start = 0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    for (;;) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+      if ((int32_t)(seen - want) >= 0)
+        break;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (now - start > limit_ns) {
+        if (atomicExch(&status->flag, 1u) == 0u) {
+          status->kernel = 6u;
+          status->role = (unsigned)i;
+          status->detail = seen;
+        }
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  if (i == 0) {
+    *stamp = pass;
+    __threadfence_system();
+  }
+}
+
 // One thread per flag: everything this stream did before is visible before the word is.
 __global__ void set_flags_kernel(FlagList list) {
   const int i = (int)threadIdx.x;
@@ -514,7 +549,6 @@ int world_bind(World *world, size_t payload_bytes, cudaStream_t stream, PeerBind
   const size_t granule = 2u << 20;
   b->block_bytes = (b->payload_bytes + sizeof(ExchangeFlags) + granule - 1) / granule * granule;
   b->peer.assign((size_t)world->size, nullptr);
-  b->checked.assign((size_t)world->size, 0u);
   int rc = check_cuda(cudaMalloc(&b->block, b->block_bytes), "cudaMalloc(gather block)");
   if (!rc)
     rc = check_cuda(cudaMemsetAsync(b->block, 0, b->block_bytes, stream), "cudaMemsetAsync(gather block)");
@@ -628,24 +662,33 @@ int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets,
     if (offsets[i] + (uint64_t)world->size * slice_bytes[i] > b->payload_bytes)
       return fail(kInvalidArgument, "world push: a buffer does not fit the gather block");
   cudaStream_t stream = world->comm_stream;
+  const uint32_t pass = ++b->pushes[which];
+  ExchangeFlags *own = b->flags(world->rank);
+  if (b->begun < pass) {
+    // first push of this pass: on the producer's stream (kernel after kernel), so that the
+    // communication stream carries nothing but copies
+    b->begun = pass;
+    FlagList list{};
+    if (pass > 1)
+      for (int r = 0; r < world->size; ++r)
+        if (r != world->rank) {
+          list.flag[list.count] = &own->consumed[r];
+          list.value[list.count] = pass - 1;
+          ++list.count;
+        }
+    DeviceStatus *status = device_status_words();
+    if (!status)
+      return fail(kInternalError, "device status words are unavailable");
+    open_pass_kernel<<<1, 2 * kMaxDirectWorld, 0, producer>>>(list, &own->stamp, pass, world->wait_ns, status);
+    if (int rc = launched(cudaGetLastError(), "open_pass_kernel"))
+      return rc;
+  }
   if (int rc = check_cuda(cudaEventRecord(world->ready, producer), "cudaEventRecord(slice ready)"))
     return rc;
   if (int rc = check_cuda(cudaStreamWaitEvent(stream, world->ready, 0), "cudaStreamWaitEvent(slice ready)"))
     return rc;
-  const uint32_t pass = ++b->pushes[which];
   for (int s = 1; s < world->size; ++s) {
     const int peer = ring_step(world->rank, world->size, s).send_to;
-    if (b->checked[(size_t)peer] < pass) {
-      b->checked[(size_t)peer] = pass;
-      if (pass > 1) { // the peer's attention of the previous pass has read what this push overwrites
-        FlagList list{};
-        list.flag[0] = &b->flags(world->rank)->consumed[peer];
-        list.value[0] = pass - 1;
-        list.count = 1;
-        if (int rc = wait_flags(list, world->wait_ns, stream))
-          return rc;
-      }
-    }
     for (int i = 0; i < count; ++i) {
       const uint64_t at = offsets[i] + (uint64_t)world->rank * slice_bytes[i];
       if (int rc = check_cuda(cudaMemcpyAsync(b->peer[(size_t)peer] + at, static_cast<char *>(b->block) + at,
@@ -653,11 +696,10 @@ int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets,
                               "cudaMemcpyAsync(slice to peer)"))
         return rc;
     }
-    FlagList list{};
-    list.flag[0] = &b->flags(peer)->arrived[which][world->rank];
-    list.value[0] = pass;
-    list.count = 1;
-    if (int rc = set_flags(list, stream))
+    // the pass number behind the data, by the same engine: in stream order, so it lands after them
+    if (int rc = check_cuda(cudaMemcpyAsync(&b->flags(peer)->arrived[which][world->rank], &own->stamp, sizeof(uint32_t),
+                                            cudaMemcpyDeviceToDevice, stream),
+                            "cudaMemcpyAsync(flag to peer)"))
       return rc;
   }
   return check_cuda(cudaEventRecord(b->pushed, stream), "cudaEventRecord(slices pushed)");

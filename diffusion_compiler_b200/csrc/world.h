@@ -16,11 +16,12 @@
 // Two ways to move the slices. (1) Direct (the default where it can be set up): the gather block
 // of every rank is mapped into every other rank (CUDA IPC over NVLink), and a rank PUSHES its
 // slice into the peers' blocks with copy-engine copies on its communication stream, each followed
-// by a one-word sequence number written into the peer's flag area; an attention launch is
-// preceded by a one-CTA kernel that waits (bounded, see World::wait_ns) until the flags of the
-// slices it reads carry the number of this pass. No SM and no rendezvous between the two sides is
-// involved in a transfer, so transfers neither compete with the attention and GEMM CTAs for SMs
-// nor couple the ranks' kernel schedules. (2) NCCL send / receive pairs, one grouped call per
+// by a four-byte copy of the pass number into the peer's flag area (the communication stream
+// carries copies only, so it never changes engines); an attention launch is preceded by a one-CTA
+// kernel that waits (bounded, see World::wait_ns) until the flags of the slices it reads carry the
+// number of this pass. No SM and no rendezvous between the two sides is involved in a transfer, so
+// transfers neither compete with the attention and GEMM CTAs for SMs nor couple the ranks' kernel
+// schedules. (2) NCCL send / receive pairs, one grouped call per
 // launch group, ordered by CUDA events; this is also what bootstraps (1).
 #pragma once
 
@@ -89,7 +90,8 @@ constexpr int kMaxDirectWorld = 16;
 struct ExchangeFlags {
   uint32_t arrived[2][kMaxDirectWorld]; // [class][source rank]: that rank's slice of pass n is here
   uint32_t consumed[kMaxDirectWorld];   // [reader rank]: that rank's attention of pass n has read MY slice there
-  uint32_t reserved[16];
+  uint32_t stamp;                       // the number of the pass being pushed: the source of the flag copies
+  uint32_t reserved[15];
 };
 // One gather block (the buffers of one sharded attention, at the same offsets on every rank).
 struct PeerBinding {
@@ -100,7 +102,7 @@ struct PeerBinding {
   std::vector<char *> peer;  // peer[r]: the block of rank r as mapped here ([rank] = block)
   uint32_t pushes[2] = {0, 0}; // exchanges enqueued so far, per class
   uint32_t passes = 0;         // attention passes enqueued so far
-  std::vector<uint32_t> checked; // [peer]: the pass up to which the communication stream has waited for `consumed`
+  uint32_t begun = 0;          // passes whose opening kernel (wait for `consumed`, set `stamp`) is enqueued
   cudaEvent_t pushed = nullptr;  // communication stream: every push enqueued so far has read the own slice
   ExchangeFlags *flags(int r) const { return reinterpret_cast<ExchangeFlags *>(peer[(size_t)r] + payload_bytes); }
 };
@@ -112,8 +114,9 @@ int world_bind(World *world, size_t payload_bytes, cudaStream_t stream, PeerBind
 int world_unbind(World *world, PeerBinding *binding);
 // Direct form of world_exchange_class: pushes this rank's slice of `count` buffers (at `offsets`
 // in the block, `slice_bytes` per rank) to every peer, in ring order, once `producer` has run what
-// is enqueued so far; before the first push of a pass to a peer the communication stream waits
-// until that peer's attention of the previous pass has read the slice it is about to overwrite.
+// is enqueued so far. The first push of a pass puts a one-CTA kernel on `producer` in front of
+// that: it waits (bounded) until every peer's attention of the previous pass has read the slices
+// about to be overwritten there, and sets the pass number the flag copies carry.
 int world_push(World *world, PeerBinding *binding, int which, const uint64_t *offsets, const uint64_t *slice_bytes,
                int count, cudaStream_t producer);
 // Test of the flag kernels on one device: a wait for a flag that is set beforehand (`set` true:
