@@ -819,7 +819,7 @@ def main():
                     "d2h_bytes_per_step": block["d2h"], "ms_per_step": block["e2e_ms"],
                     "path": "backend plugin C-ABI (dif_backend_get_v2 execute), one call per step and rank: x and the six "
                             "full-shape modulation tensors of the rank's token slice from pinned host memory, the block "
-                            "on the device (NCCL exchange inside the library), the output slice back to pinned host "
+                            "on the device (the exchange between the ranks inside the library), the output slice back to pinned host "
                             "memory; bytes are per rank"},
             "gpu_launches": block["launches"],
             "roofline": roofline,
@@ -830,6 +830,16 @@ def main():
             "clocks": block["clocks"],
             "plugin": {"operations": block["operations"], "resident_gb": block["resident_bytes"] / 1e9},
         }
+        pushes = {name: prof[op] for name, op in (("values", 0xF000), ("keys", 0xF001)) if op in prof}
+        if pushes:
+            slice_tokens = (max(block["plan"].local_tokens(r) for r in range(world)) + 127) // 128 * 128
+            sent = {"values": 256, "keys": 132}  # bytes per token and head that leave this rank for ONE peer
+            line["exchange_pushes"] = {
+                name: {"ms_per_push": ms_sum / n,
+                       "gb_per_s_out": (world - 1) * slice_tokens * VIDEO["heads"] * sent[name] / (ms_sum / n * 1e-3) / 1e9}
+                for name, (ms_sum, n) in pushes.items()}
+            line["exchange_pushes"]["note"] = ("rank 0's copy-engine pushes of its slice to the %d peers, CUDA events on the "
+                                               "communication stream (warm-up passes included)" % (world - 1))
         if block["parity"] is not None:
             line["parity"] = block["parity"]
         if block["sustained"] is not None:

@@ -153,6 +153,14 @@ struct EventPair { // two CUDA events that do not outlive their scope
   }
 };
 
+struct EventList { // CUDA events that do not outlive their scope
+  std::vector<cudaEvent_t> events;
+  ~EventList() {
+    for (cudaEvent_t e : events)
+      cudaEventDestroy(e);
+  }
+};
+
 void write_error(dif_backend_error *error, const std::string &text) {
   if (!error || !error->data || error->capacity == 0)
     return;
@@ -535,6 +543,7 @@ void allocate_world(Executable &exe) {
     sh.at_ks = sh.at_k8 + aligned(keys * KV * 128);
     require(world_bind(world, (size_t)(sh.at_ks + aligned(keys * KV * sizeof(float))), exe.ctx->stream, &sh.binding));
     exe.resident_bytes += sh.binding->block_bytes;
+    sh.binding->timed = exe.profile;
     char *block = static_cast<char *>(sh.binding->block);
     sh.v = block + sh.at_v;
     sh.k8 = reinterpret_cast<int8_t *>(block + sh.at_k8);
@@ -738,6 +747,8 @@ void profile_mark(Executable &exe, uint32_t opcode) {
 void profile_collect(Executable &exe) {
   for (size_t i = 0; i + 1 < exe.profile_opcodes.size(); ++i) {
     float ms = 0.0f;
+    if (exe.profile_opcodes[i] == 0)
+      continue; // the mark that closes a pass: what follows it belongs to no step
     if (cudaEventElapsedTime(&ms, exe.profile_events[i], exe.profile_events[i + 1]) == cudaSuccess) {
       auto &sum = exe.profile_sum[exe.profile_opcodes[i]];
       sum.first += ms;
@@ -1400,18 +1411,28 @@ dif_backend_status execute(dif_backend_executable executable, const dif_backend_
       }
       for (uint32_t w = 0; w < options->warmups; ++w)
         run_steps(*exe);
+      // The timed passes are enqueued back to back, an event between every two, and waited for
+      // once: the host stays ahead of the device, so no pass starts with an empty queue.
+      EventList marks;
+      for (uint32_t it = 0; it <= options->iterations; ++it) {
+        cudaEvent_t e = nullptr;
+        require_cuda(cudaEventCreate(&e), "cudaEventCreate");
+        marks.events.push_back(e);
+      }
+      require_cuda(cudaEventRecord(marks.events[0], ctx->stream), "cudaEventRecord");
       for (uint32_t it = 0; it < options->iterations; ++it) {
-        cudaEventRecord(e0, ctx->stream);
         exe->profile_pass = exe->profile;
         run_steps(*exe);
         if (exe->profile_pass)
           profile_mark(*exe, 0);
         exe->profile_pass = false;
-        cudaEventRecord(e1, ctx->stream);
-        require_cuda(cudaEventSynchronize(e1), "cudaEventSynchronize");
-        profile_collect(*exe);
+        require_cuda(cudaEventRecord(marks.events[(size_t)it + 1], ctx->stream), "cudaEventRecord");
+      }
+      require_cuda(cudaEventSynchronize(marks.events.back()), "cudaEventSynchronize");
+      profile_collect(*exe);
+      for (uint32_t it = 0; it < options->iterations; ++it) {
         float ms = 0.0f;
-        cudaEventElapsedTime(&ms, e0, e1);
+        cudaEventElapsedTime(&ms, marks.events[it], marks.events[(size_t)it + 1]);
         sum += ms;
         lo = ms < lo ? ms : lo;
         hi = ms > hi ? ms : hi;
@@ -1466,6 +1487,24 @@ extern "C" int difb200_executable_profile(void *executable, uint32_t *opcodes, d
     milliseconds[n] = entry.second.first;
     steps[n] = entry.second.second;
     ++n;
+  }
+  // token-sharded, direct exchange: the copies of the value / key pushes on the communication stream
+  for (int which = 0; which < 2; ++which) {
+    double ms = 0.0;
+    uint64_t pushes = 0;
+    for (const Sharded &sh : exe->sharded) {
+      double one = 0.0;
+      uint64_t k = 0;
+      world_push_times(sh.binding, which, &one, &k);
+      ms += one;
+      pushes += k;
+    }
+    if (pushes && n < capacity) {
+      opcodes[n] = 0xF000u + (uint32_t)which;
+      milliseconds[n] = ms;
+      steps[n] = pushes;
+      ++n;
+    }
   }
   *count = n;
   exe->profile_sum.clear();

@@ -646,6 +646,9 @@ int world_unbind(World *world, PeerBinding *b) {
       rc = rc ? rc : rc2;
     }
   }
+  for (auto &spans : b->spans)
+    for (cudaEvent_t e : spans)
+      cudaEventDestroy(e);
   if (b->pushed)
     cudaEventDestroy(b->pushed);
   if (b->block)
@@ -687,6 +690,15 @@ int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets,
     return rc;
   if (int rc = check_cuda(cudaStreamWaitEvent(stream, world->ready, 0), "cudaStreamWaitEvent(slice ready)"))
     return rc;
+  if (b->timed) {
+    for (int k = 0; k < 2; ++k) {
+      cudaEvent_t e = nullptr;
+      if (int rc = check_cuda(cudaEventCreate(&e), "cudaEventCreate(push span)"))
+        return rc;
+      b->spans[which].push_back(e);
+    }
+    cudaEventRecord(b->spans[which][b->spans[which].size() - 2], stream);
+  }
   for (int s = 1; s < world->size; ++s) {
     const int peer = ring_step(world->rank, world->size, s).send_to;
     for (int i = 0; i < count; ++i) {
@@ -702,7 +714,29 @@ int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets,
                             "cudaMemcpyAsync(flag to peer)"))
       return rc;
   }
+  if (b->timed)
+    cudaEventRecord(b->spans[which].back(), stream);
   return check_cuda(cudaEventRecord(b->pushed, stream), "cudaEventRecord(slices pushed)");
+}
+
+void world_push_times(PeerBinding *b, int which, double *milliseconds, uint64_t *pushes) {
+  *milliseconds = 0.0;
+  *pushes = 0;
+  if (!b || which < 0 || which > 1)
+    return;
+  auto &spans = b->spans[which];
+  for (size_t i = 0; i + 1 < spans.size(); i += 2) {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, spans[i], spans[i + 1]) == cudaSuccess) {
+      *milliseconds += ms;
+      *pushes += 1;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  for (cudaEvent_t e : spans)
+    cudaEventDestroy(e);
+  spans.clear();
 }
 
 int world_selftest_flags(unsigned long long limit_ns, bool set) {

@@ -104,6 +104,8 @@ struct PeerBinding {
   uint32_t passes = 0;         // attention passes enqueued so far
   uint32_t begun = 0;          // passes whose opening kernel (wait for `consumed`, set `stamp`) is enqueued
   cudaEvent_t pushed = nullptr;  // communication stream: every push enqueued so far has read the own slice
+  bool timed = false;            // record an event pair around the copies of every push (world_push_times)
+  std::vector<cudaEvent_t> spans[2]; // per class: begin, end, begin, end, ...
   ExchangeFlags *flags(int r) const { return reinterpret_cast<ExchangeFlags *>(peer[(size_t)r] + payload_bytes); }
 };
 // Collective: allocates a zeroed block of `payload_bytes` (+ flags) on every rank and, unless
@@ -119,6 +121,9 @@ int world_unbind(World *world, PeerBinding *binding);
 // about to be overwritten there, and sets the pass number the flag copies carry.
 int world_push(World *world, PeerBinding *binding, int which, const uint64_t *offsets, const uint64_t *slice_bytes,
                int count, cudaStream_t producer);
+// With binding->timed: the device time the copies of class `which` took on the communication stream,
+// summed over the pushes since the last call, and their number (call after the streams have drained).
+void world_push_times(PeerBinding *binding, int which, double *milliseconds, uint64_t *pushes);
 // Test of the flag kernels on one device: a wait for a flag that is set beforehand (`set` true:
 // returns kOk) or that nothing sets (`set` false: the wait gives up after `limit_ns` and the
 // status poll returns kExecutionError); the context stays usable either way.

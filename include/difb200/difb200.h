@@ -425,7 +425,10 @@ DIFB200_EXPORT int difb200_measure_i8_mma_peak(int32_t ctas_per_mma, uint32_t mm
  * stream in front of every step of its timed passes; this call returns, per DiffIR opcode, the
  * summed time between consecutive events and the number of steps, and clears the sums. It is how
  * the benchmark times the dominant kernel inside the timed region (the reference reports per-op
- * times from CUDA events the same way: src/runtime/cuda_executor.cpp:11139-11153).
+ * times from CUDA events the same way: src/runtime/cuda_executor.cpp:11139-11153). A token-sharded
+ * executable with the direct exchange adds two entries, opcodes 0xF000 (values) and 0xF001 (keys):
+ * the time the copies of its pushes took on the communication stream, and how many pushes
+ * (warm-up passes included) that sums.
  */
 DIFB200_EXPORT int difb200_executable_profile(void *executable, uint32_t *opcodes, double *milliseconds,
                                               uint64_t *steps, uint32_t capacity, uint32_t *count);
