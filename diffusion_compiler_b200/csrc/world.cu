@@ -179,6 +179,12 @@ World::~World() {
     for (cudaEvent_t e : events)
       if (e)
         cudaEventDestroy(e);
+  for (cudaEvent_t e : push_done)
+    cudaEventDestroy(e);
+  for (cudaStream_t st : push_streams)
+    cudaStreamDestroy(st);
+  if (push_fork)
+    cudaEventDestroy(push_fork);
   if (ready)
     cudaEventDestroy(ready);
   if (comm_stream)
@@ -657,6 +663,36 @@ int world_unbind(World *world, PeerBinding *b) {
   return rc;
 }
 
+namespace {
+// the push streams of a world, made on first use
+int push_streams_of(World *world) {
+  if (!world->push_streams.empty())
+    return kOk;
+  int lanes = 4;
+  if (const char *text = std::getenv("DIFB200_PUSH_STREAMS")) {
+    const int value = std::atoi(text);
+    if (value >= 1 && value <= kMaxDirectWorld)
+      lanes = value;
+  }
+  int least = 0, greatest = 0;
+  cudaDeviceGetStreamPriorityRange(&least, &greatest);
+  if (int rc = check_cuda(cudaEventCreateWithFlags(&world->push_fork, cudaEventDisableTiming), "cudaEventCreate"))
+    return rc;
+  for (int k = 0; k < lanes; ++k) {
+    cudaStream_t st = nullptr;
+    cudaEvent_t e = nullptr;
+    if (int rc = check_cuda(cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, greatest),
+                            "cudaStreamCreateWithPriority(push)"))
+      return rc;
+    world->push_streams.push_back(st);
+    if (int rc = check_cuda(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate"))
+      return rc;
+    world->push_done.push_back(e);
+  }
+  return kOk;
+}
+} // namespace
+
 int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets, const uint64_t *slice_bytes, int count,
                cudaStream_t producer) {
   if (!world || !b || !b->direct || which < 0 || which > 1 || count < 1 || !offsets || !slice_bytes)
@@ -699,19 +735,36 @@ int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets,
     }
     cudaEventRecord(b->spans[which][b->spans[which].size() - 2], stream);
   }
+  if (int rc = push_streams_of(world))
+    return rc;
+  const int lanes = (int)world->push_streams.size();
+  if (int rc = check_cuda(cudaEventRecord(world->push_fork, stream), "cudaEventRecord(push fork)"))
+    return rc;
+  for (int k = 0; k < lanes && k < world->size - 1; ++k)
+    if (int rc = check_cuda(cudaStreamWaitEvent(world->push_streams[(size_t)k], world->push_fork, 0),
+                            "cudaStreamWaitEvent(push fork)"))
+      return rc;
   for (int s = 1; s < world->size; ++s) {
     const int peer = ring_step(world->rank, world->size, s).send_to;
+    cudaStream_t lane = world->push_streams[(size_t)((s - 1) % lanes)]; // ring order within and across the lanes
     for (int i = 0; i < count; ++i) {
       const uint64_t at = offsets[i] + (uint64_t)world->rank * slice_bytes[i];
       if (int rc = check_cuda(cudaMemcpyAsync(b->peer[(size_t)peer] + at, static_cast<char *>(b->block) + at,
-                                              (size_t)slice_bytes[i], cudaMemcpyDeviceToDevice, stream),
+                                              (size_t)slice_bytes[i], cudaMemcpyDeviceToDevice, lane),
                               "cudaMemcpyAsync(slice to peer)"))
         return rc;
     }
     // the pass number behind the data, by the same engine: in stream order, so it lands after them
     if (int rc = check_cuda(cudaMemcpyAsync(&b->flags(peer)->arrived[which][world->rank], &own->stamp, sizeof(uint32_t),
-                                            cudaMemcpyDeviceToDevice, stream),
+                                            cudaMemcpyDeviceToDevice, lane),
                             "cudaMemcpyAsync(flag to peer)"))
+      return rc;
+  }
+  for (int k = 0; k < lanes && k < world->size - 1; ++k) {
+    if (int rc = check_cuda(cudaEventRecord(world->push_done[(size_t)k], world->push_streams[(size_t)k]),
+                            "cudaEventRecord(push lane)"))
+      return rc;
+    if (int rc = check_cuda(cudaStreamWaitEvent(stream, world->push_done[(size_t)k], 0), "cudaStreamWaitEvent(push lane)"))
       return rc;
   }
   if (b->timed)

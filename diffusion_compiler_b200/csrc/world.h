@@ -73,6 +73,11 @@ public:
   Transport *transport = nullptr;       // owned
   cudaStream_t comm_stream = nullptr;   // the exchange runs here, at the highest priority
   cudaEvent_t ready = nullptr;          // producer stream -> communication stream
+  // direct exchange: the pushes to different peers go out on several streams (DIFB200_PUSH_STREAMS,
+  // default 4), so that the set-up time of one copy hides behind the transfer of another
+  std::vector<cudaStream_t> push_streams;
+  std::vector<cudaEvent_t> push_done;   // one per push stream: its copies of the current push are enqueued
+  cudaEvent_t push_fork = nullptr;      // communication stream -> push streams
   // landed[c][s - 1]: slice of rank - s has arrived in the buffers of exchange class c
   // (0 = values, 1 = key codes and scales); recorded by world_exchange_class
   std::vector<cudaEvent_t> landed[2];
