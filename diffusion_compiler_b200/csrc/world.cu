@@ -668,13 +668,12 @@ namespace {
 int push_streams_of(World *world) {
   if (!world->push_streams.empty())
     return kOk;
-  int lanes = 2; // per class (values, keys)
+  int lanes = 4;
   if (const char *text = std::getenv("DIFB200_PUSH_STREAMS")) {
     const int value = std::atoi(text);
     if (value >= 1 && value <= kMaxDirectWorld)
       lanes = value;
   }
-  lanes *= 2;
   int least = 0, greatest = 0;
   cudaDeviceGetStreamPriorityRange(&least, &greatest);
   if (int rc = check_cuda(cudaEventCreateWithFlags(&world->push_fork, cudaEventDisableTiming), "cudaEventCreate"))
@@ -738,20 +737,16 @@ int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets,
   }
   if (int rc = push_streams_of(world))
     return rc;
-  // Each class has its own lanes and goes to the peers in ring order: the slice of the nearest
-  // ring step is complete first (values and keys of a step travel side by side), which is the
-  // order the attention launches take them in; the lanes of a class alternate between the steps
-  // so that the set-up of one copy hides behind the transfer of another.
-  const int lanes = (int)world->push_streams.size() / 2, first_lane = which * lanes;
+  const int lanes = (int)world->push_streams.size();
   if (int rc = check_cuda(cudaEventRecord(world->push_fork, stream), "cudaEventRecord(push fork)"))
     return rc;
-  for (int k = first_lane; k < first_lane + lanes; ++k)
+  for (int k = 0; k < lanes && k < world->size - 1; ++k)
     if (int rc = check_cuda(cudaStreamWaitEvent(world->push_streams[(size_t)k], world->push_fork, 0),
                             "cudaStreamWaitEvent(push fork)"))
       return rc;
   for (int s = 1; s < world->size; ++s) {
     const int peer = ring_step(world->rank, world->size, s).send_to;
-    cudaStream_t lane = world->push_streams[(size_t)(first_lane + (s - 1) % lanes)];
+    cudaStream_t lane = world->push_streams[(size_t)((s - 1) % lanes)]; // ring order within and across the lanes
     for (int i = 0; i < count; ++i) {
       const uint64_t at = offsets[i] + (uint64_t)world->rank * slice_bytes[i];
       if (int rc = check_cuda(cudaMemcpyAsync(b->peer[(size_t)peer] + at, static_cast<char *>(b->block) + at,
@@ -765,7 +760,7 @@ int world_push(World *world, PeerBinding *b, int which, const uint64_t *offsets,
                             "cudaMemcpyAsync(flag to peer)"))
       return rc;
   }
-  for (int k = first_lane; k < first_lane + lanes; ++k) {
+  for (int k = 0; k < lanes && k < world->size - 1; ++k) {
     if (int rc = check_cuda(cudaEventRecord(world->push_done[(size_t)k], world->push_streams[(size_t)k]),
                             "cudaEventRecord(push lane)"))
       return rc;

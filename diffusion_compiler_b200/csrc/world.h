@@ -73,8 +73,8 @@ public:
   Transport *transport = nullptr;       // owned
   cudaStream_t comm_stream = nullptr;   // the exchange runs here, at the highest priority
   cudaEvent_t ready = nullptr;          // producer stream -> communication stream
-  // direct exchange: the pushes go out on streams of their own, DIFB200_PUSH_STREAMS (default 2) per
-  // class; the first half serves the values, the second the keys
+  // direct exchange: the pushes to different peers go out on several streams (DIFB200_PUSH_STREAMS,
+  // default 4), so that the set-up time of one copy hides behind the transfer of another
   std::vector<cudaStream_t> push_streams;
   std::vector<cudaEvent_t> push_done;   // one per push stream: its copies of the current push are enqueued
   cudaEvent_t push_fork = nullptr;      // communication stream -> push streams
