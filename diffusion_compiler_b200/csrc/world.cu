@@ -24,18 +24,21 @@
 namespace difb200 {
 
 // ---- launch plan ------------------------------------------------------------------------------
-std::vector<int> default_groups(int size) {
+std::vector<int> default_groups(int size, bool direct) {
+  // Measured on 8 B200s (video block, 33272 tokens): every further launch costs more than the
+  // overlap it buys. NCCL: {1, 7} 2.49 ms, {1, 3, 4} 2.82 ms, {1, 1, 2, 4} 3.22 ms. Direct pushes
+  // arrive one after another, so one split of the remote slices pays: {1, 2, 5} 2.58 ms, {1, 7} 2.70 ms.
   std::vector<int> groups{1};
-  if (size > 1 && size <= 4) {
+  if (size > 1 && (size <= 4 || !direct)) {
     groups.push_back(size - 1);
   } else if (size > 4) {
-    groups.push_back((size - 1) / 2);
-    groups.push_back(size - 1 - (size - 1) / 2);
+    groups.push_back(2);
+    groups.push_back(size - 3);
   }
   return groups;
 }
 
-std::vector<int> launch_groups(int size) {
+std::vector<int> launch_groups(int size, bool direct) {
   // DIFB200_ATTENTION_GROUPS="1,3,4": how many ring steps (the own slice is step 0) each attention
   // launch covers; a list that is malformed or does not sum to the world size is ignored
   std::vector<int> groups;
@@ -61,7 +64,7 @@ std::vector<int> launch_groups(int size) {
     if (!ok || total != size)
       groups.clear();
   }
-  return groups.empty() ? default_groups(size) : groups;
+  return groups.empty() ? default_groups(size, direct) : groups;
 }
 
 bool plan_launches(int rank, int size, uint32_t tiles_per_slice, std::vector<int> group_sizes,
@@ -70,7 +73,7 @@ bool plan_launches(int rank, int size, uint32_t tiles_per_slice, std::vector<int
   if (size < 1 || rank < 0 || rank >= size)
     return false;
   if (group_sizes.empty())
-    group_sizes = default_groups(size);
+    group_sizes = default_groups(size, false);
   int total = 0;
   for (int g : group_sizes) {
     if (g <= 0)
@@ -329,7 +332,7 @@ int world_exchange(World *world, void *const *buffers, const uint64_t *slice_byt
   // The ring steps go out in the groups in which the attention launches consume them (one
   // grouped NCCL call per launch: its peers are served concurrently); all steps of a group share
   // the moment they are marked as landed.
-  const std::vector<int> groups = launch_groups(world->size);
+  const std::vector<int> groups = launch_groups(world->size, false);
   int first = 0;
   for (int g : groups) {
     const int begin = first == 0 ? 1 : first, end = first + g; // step 0 is the own slice
@@ -572,9 +575,13 @@ int world_bind(World *world, size_t payload_bytes, cudaStream_t stream, PeerBind
   *out = b;
   if (world->size == 1)
     return kOk;
+  // DIFB200_EXCHANGE=direct | nccl; unset: direct up to 4 ranks, NCCL beyond. Measured on B200s (video
+  // block, 33272 tokens, ms per pass direct / NCCL): 2 ranks 8.01 / 8.11, 4 ranks 4.27 / 4.39, 8 ranks
+  // 2.58 / 2.49 -- with 7 peers the copy engines reach about 420 GB/s per GPU in the all-to-all
+  // pattern where NCCL's SM copies reach more, and that outweighs the SMs NCCL takes.
   const char *mode = std::getenv("DIFB200_EXCHANGE");
-  const bool wanted = !(mode && std::strcmp(mode, "nccl") == 0) && world->size <= kMaxDirectWorld &&
-                      world->transport->on_device();
+  const bool chosen = mode && mode[0] ? std::strcmp(mode, "nccl") != 0 : world->size <= 4;
+  const bool wanted = chosen && world->size <= kMaxDirectWorld && world->transport->on_device();
   // round 1: every rank's handle; round 2: whether every rank could map every handle
   std::vector<BindRecord> records((size_t)world->size);
   BindRecord mine{};
@@ -821,7 +828,7 @@ int sharded_attention(World *world, PeerBinding *binding, const int8_t *q8, cons
   if (slice_tokens == 0 || slice_tokens % 128 != 0)
     return fail(kInvalidArgument, "sharded attention: the slice length must be a positive multiple of 128");
   std::vector<LaunchPlan> launches;
-  if (!plan_launches(rank, size, (uint32_t)(slice_tokens / 128), launch_groups(size), launches))
+  if (!plan_launches(rank, size, (uint32_t)(slice_tokens / 128), launch_groups(size, binding && binding->direct), launches))
     return fail(kInternalError, "sharded attention: no launch plan");
   if (launches.size() > 1 && !state)
     return fail(kInvalidArgument, "sharded attention: several launches need a state buffer");

@@ -13,7 +13,7 @@
 // arrived slices in a few launches that carry the softmax state (attention_int8 with an
 // AttentionChunk).
 //
-// Two ways to move the slices. (1) Direct (the default where it can be set up): the gather block
+// Two ways to move the slices. (1) Direct: the gather block
 // of every rank is mapped into every other rank (CUDA IPC over NVLink), and a rank PUSHES its
 // slice into the peers' blocks with copy-engine copies on its communication stream, each followed
 // by a four-byte copy of the pass number into the peer's flag area (the communication stream
@@ -21,8 +21,9 @@
 // kernel that waits (bounded, see World::wait_ns) until the flags of the slices it reads carry the
 // number of this pass. No SM and no rendezvous between the two sides is involved in a transfer, so
 // transfers neither compete with the attention and GEMM CTAs for SMs nor couple the ranks' kernel
-// schedules. (2) NCCL send / receive pairs, one grouped call per
-// launch group, ordered by CUDA events; this is also what bootstraps (1).
+// schedules. (2) NCCL send / receive pairs, one grouped call per launch group, ordered by CUDA
+// events; this is also what bootstraps (1). Which one a world uses by default follows the
+// measurements quoted in world_bind (direct up to 4 ranks, NCCL beyond).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -59,13 +60,14 @@ struct LaunchPlan {
   uint32_t tile_begin[2], tile_count[2];
 };
 // `group_sizes` partitions the steps 0 .. size - 1 in order (e.g. {1, 3, 4} at 8 ranks); an empty
-// vector selects the default (own slice first; the rest in one launch up to 4 ranks, in two from 5).
+// vector selects the default (own slice first, the rest in one launch; with the direct exchange and
+// more than 4 ranks the rest in two launches, the two nearest ring steps first).
 // Returns false when the sizes do not sum to `size` or contain a zero.
 bool plan_launches(int rank, int size, uint32_t tiles_per_slice, std::vector<int> group_sizes,
                    std::vector<LaunchPlan> &out);
-std::vector<int> default_groups(int size);
+std::vector<int> default_groups(int size, bool direct = false);
 // The grouping in force: DIFB200_ATTENTION_GROUPS when it is well-formed for `size`, else the default.
-std::vector<int> launch_groups(int size);
+std::vector<int> launch_groups(int size, bool direct = false);
 
 class World {
 public:

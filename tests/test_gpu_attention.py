@@ -151,8 +151,8 @@ def test_attention_chunked_launches_match_the_single_launch(ops, B, Sq, Sk, H, K
     assert np.array_equal(from_torch_bf16(same_order), from_torch_bf16(whole)) or rel_l2(c, b) <= 1e-5
 
 
-@pytest.mark.parametrize("size", [2, 4, 8])
-def test_attention_launch_plans_of_every_rank_match_the_single_launch(ops, size):
+@pytest.mark.parametrize("size,grouping", [(2, ()), (4, ()), (8, ()), (8, (1, 2, 5)), (8, (1, 3, 4))])
+def test_attention_launch_plans_of_every_rank_match_the_single_launch(ops, size, grouping):
     """The launch plan the token-sharded mode uses (difb200_world_plan: the own slice first, the other
     slices in the groups their ring steps arrive in, ranges that wrap around the end of the key
     axis) for every rank of a world of 2, 4 and 8, on one GPU: each rank's queries against the whole
@@ -176,7 +176,8 @@ def test_attention_launch_plans_of_every_rank_match_the_single_launch(ops, size)
         q8, qs = ob.orc().quantize_int8_rows([q.reshape(-1, 128)], 1)
         cap = 16
         ranges, first, count, n = (C.c_uint32 * (4 * cap))(), (C.c_int32 * cap)(), (C.c_int32 * cap)(), C.c_int32(0)
-        assert lib.difb200_world_plan(rank, size, slice_tokens // 128, (C.c_int32 * 1)(), 0, ranges, first, count, cap,
+        sizes = (C.c_int32 * max(1, len(grouping)))(*grouping)
+        assert lib.difb200_world_plan(rank, size, slice_tokens // 128, sizes, len(grouping), ranges, first, count, cap,
                                       C.byref(n)) == 0
         groups = [[(ranges[4 * i], ranges[4 * i + 1])] + ([(ranges[4 * i + 2], ranges[4 * i + 3])] if ranges[4 * i + 3] else [])
                   for i in range(n.value)]
