@@ -9,7 +9,8 @@ RoPE over 96 of the 128 head dimensions, every Linear W8A8 `int8-convrot`, INT8 
 DiffIR program through the backend plugin C-ABI. One step = one pass over the block. With N > 1
 the tokens are sharded over the N GPUs (strong scaling: the total work is fixed): every rank runs
 the same program on its slice through its own plugin context, and the plugin exchanges the INT8
-key codes, their scales and the bf16 values over NCCL inside the library. The metric is
+key codes, their scales and the bf16 values inside the library (copy-engine pushes into peer-mapped
+buffers up to 4 ranks, NCCL above; `config.exchange` says which). The metric is
 tokens per second of the whole job.
 
 `value`: device time of the timed passes of execute() (inputs already in HBM), max over ranks.
@@ -200,7 +201,7 @@ def pinned_output(torch, program, tid):
 
 
 def video_block_parity(torch, dist, device_index, rank, world, weights):
-    """Sharded against unsharded on real NCCL ranks: a reduced sequence (a 4 x 6 x 21 grid + 101 text
+    """Sharded against unsharded on real ranks: a reduced sequence (a 4 x 6 x 21 grid + 101 text
     tokens = 605 tokens, uneven over the ranks) at the block's true widths. Every rank runs its slice
     of ONE seeded input through its world context; rank 0 also runs the whole sequence through a
     single-GPU context and compares: the attention output (the only operator that sees other ranks'

@@ -18,10 +18,10 @@
 // rank then compiles and executes the SAME program on ITS slice of the tokens (the program's token
 // count is the slice length; weights are replicated as constants), and an Attention op attends from
 // the local queries to the keys and values of all ranks: K codes, K scales and V are produced
-// straight into this rank's slice of full-length gather buffers, exchanged in ring steps on a
-// communication stream as soon as their producers are enqueued (the steps in front of the attention
-// are reordered so that the V and K chains run before the Q chain), and attention runs as a few
-// launches, the own slice first, each behind the ring steps it reads. The reference has no such
+// straight into this rank's slice of a full-length gather block, pushed into the peers' blocks by
+// the copy engines or sent with NCCL (world.h) as soon as their producers are enqueued (the steps in
+// front of the attention are reordered so that the V and K chains run before the Q chain), and
+// attention runs as a few launches, the own slice first, each behind the slices it reads. The reference has no such
 // mode (one device per executor, include/dif/runtime/executor.hpp:683); a single-process host
 // drives one rank exactly as before.
 #include "difb200/abi.h"

@@ -582,7 +582,7 @@ int world_bind(World *world, size_t payload_bytes, cudaStream_t stream, PeerBind
   const char *mode = std::getenv("DIFB200_EXCHANGE");
   const bool chosen = mode && mode[0] ? std::strcmp(mode, "nccl") != 0 : world->size <= 4;
   const bool wanted = chosen && world->size <= kMaxDirectWorld && world->transport->on_device();
-  // round 1: every rank's handle; round 2: whether every rank could map every handle
+  // first gather: every rank's handle; second gather: whether every rank could map every handle
   std::vector<BindRecord> records((size_t)world->size);
   BindRecord mine{};
   {

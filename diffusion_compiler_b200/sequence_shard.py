@@ -4,8 +4,8 @@ The reference has no multi-GPU layer (one device per Executor, reference
 ``include/dif/runtime/executor.hpp:683``); the sequence-partitioned form of the block that
 ``blocks.video_block_program`` describes lives in the native library: with ``DIFB200_WORLD_SIZE``
 set, every rank's plugin context runs the block program on its token slice and exchanges the INT8
-key codes, their per-token-head scales and the bf16 values over its own NCCL communicator
-(``csrc/world.cu``, ``csrc/plugin.cu``). Rank r owns a contiguous slice of the tokens; weights,
+key codes, their per-token-head scales and the bf16 values with the other ranks (pushes into
+peer-mapped buffers or NCCL: ``csrc/world.cu``, ``csrc/plugin.cu``). Rank r owns a contiguous slice of the tokens; weights,
 norm weights and RoPE tables are replicated; everything except attention is row-local; queries
 stay local and each rank attends from its own queries to all keys; nothing is reduced afterwards.
 
