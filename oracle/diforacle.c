@@ -9,10 +9,10 @@
  * Two exceptions, both UNPINNED. orc_attention_int8: the reference has no CPU form of INT8
  * attention, so that function defines this repository's own numerical contract; its Q/K
  * codes and scales are the reference's (QuantizeInt8Rows, Direct) and it is additionally
- * compared, with a tolerance, against the reference's exact Attention. And the MSE scale
- * search of orc_quantize_weight_rows with orc_weight_equalization: they restate functions that
- * the reference keeps in a command-line tool's anonymous namespace, which no test of the
- * reference exercises and no library exports; without them that entry is the pinned quantiser.
+ * compared, with a tolerance, against the reference's exact Attention. And
+ * orc_weight_equalization: it restates a passage in the middle of a function of the reference's
+ * command-line packer that cannot be called on its own. (The MSE scale search of the same tool
+ * IS pinned: the Makefile builds a probe that includes the tool's source and calls its function.)
  *
  * Each function cites the reference file:line it follows (paths inside the reference
  * project). Build flags: -O3 without -march, so x86-64 never contracts a*b+c into an fma
@@ -128,8 +128,8 @@ typedef struct {
 
 /* tools/difflux2sample.cpp:1225-1259 (choose_mse_int8_weight_scale): seven clip factors, the
  * bf16-rounded scale of each, squared error over every fourth element in double, first best
- * wins. No test of the reference pins this function (it lives in a tool's anonymous namespace
- * and cannot be linked): parity of this one restatement is UNPINNED. */
+ * wins. Pinned bit for bit against the reference's own function (oracle/_ref/difpacker_scale,
+ * which includes the tool's source) and through the committed fixture made from it. */
 static float choose_mse_weight_scale(const float *values, uint64_t count) {
   static const float factors[7] = {1.0F, 0.96F, 0.92F, 0.88F, 0.84F, 0.80F, 0.76F};
   float maximum = 0.0F;
@@ -155,6 +155,13 @@ static float choose_mse_weight_scale(const float *values, uint64_t count) {
     }
   }
   return best_scale;
+}
+
+/* The search alone, on fp32 rows (what the packer hands it: the rotated weight row). */
+ORC_EXPORT void orc_choose_mse_weight_scale(const float *values, uint64_t rows, uint64_t columns,
+                                            float *scales) {
+  for (uint64_t r = 0; r < rows; ++r)
+    scales[r] = choose_mse_weight_scale(values + r * columns, columns);
 }
 
 static void quant_body(void *vctx, int64_t row_begin, int64_t row_end) {
@@ -291,7 +298,7 @@ ORC_EXPORT int orc_quantize_int8_rows(const uint16_t *const *parts,
 
 /* Input equalisation of the offline packer, tools/difflux2sample.cpp:2967-2990: per column the
  * absmax over the rows, their geometric mean as the centre, sqrt(max / centre) clamped to
- * [0.5, 2] and stored as bf16. Unpinned like the MSE search (same tool, same reason). */
+ * [0.5, 2] and stored as bf16. UNPINNED: the passage cannot be called on its own. */
 ORC_EXPORT void orc_weight_equalization(const uint16_t *weight, uint64_t rows,
                                         uint64_t columns, uint16_t *out) {
   float *maxima = (float *)calloc((size_t)columns, sizeof(float));

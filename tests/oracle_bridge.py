@@ -116,6 +116,16 @@ class _Orc:
             raise ValueError("illegal width or variant for weight packing")
         return codes, scales
 
+    def choose_mse_weight_scale(self, rows_f32: np.ndarray) -> np.ndarray:
+        """The packer's MSE row-scale search alone, on fp32 rows [rows, columns]."""
+        rows_f32 = np.ascontiguousarray(rows_f32, dtype=np.float32)
+        rows, columns = rows_f32.shape
+        scales = np.empty(rows, np.float32)
+        self.lib.orc_choose_mse_weight_scale.restype = None
+        self.lib.orc_choose_mse_weight_scale.argtypes = [_pf, C.c_uint64, C.c_uint64, _pf]
+        self.lib.orc_choose_mse_weight_scale(_ptr(rows_f32, _pf), rows, columns, _ptr(scales, _pf))
+        return scales
+
     def weight_equalization(self, weight: np.ndarray) -> np.ndarray:
         weight = np.ascontiguousarray(weight, dtype=np.uint16)
         rows, columns = weight.shape
@@ -302,6 +312,26 @@ def orc() -> _Orc:
     if _orc is None:
         _orc = _Orc()
     return _orc
+
+
+PACKER_PROBE = os.path.join(ORACLE_DIR, "_ref", "difpacker_scale")
+
+
+def packer_probe_available() -> bool:
+    return os.path.exists(PACKER_PROBE)
+
+
+def packer_mse_scales(rows_f32: np.ndarray) -> np.ndarray:
+    """choose_mse_int8_weight_scale of the reference's own packer (oracle/_ref/difpacker_scale, which
+    includes the reference tool's source) on fp32 rows [rows, columns]."""
+    import subprocess
+    import tempfile
+    rows_f32 = np.ascontiguousarray(rows_f32, dtype=np.float32)
+    with tempfile.NamedTemporaryFile(suffix=".f32") as f:
+        rows_f32.tofile(f.name)
+        out = subprocess.run([PACKER_PROBE, f.name, str(rows_f32.shape[0]), str(rows_f32.shape[1])],
+                             check=True, capture_output=True, text=True).stdout.split()
+    return np.array([int(h, 16) for h in out], np.uint32).view(np.float32)
 
 
 def ref_available() -> bool:

@@ -146,6 +146,37 @@ def test_weight_rows_without_mse_equal_the_pinned_quantiser():
         assert ((ratio > 0.75) & (ratio < 1.01)).all()
 
 
+def test_mse_scale_search_equals_the_reference_packer_fixture():
+    """orc_choose_mse_weight_scale against the scales the reference's own packer function chose for the
+    same rows (tests/golden/packer_mse_scale.npz, made by tests/golden/make_packer_golden.py from the
+    reference tool's source): bit-identical, edge rows included (all zero, one outlier, 1e-20, 1e20)."""
+    data = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "packer_mse_scale.npz"))
+    names = sorted({k.split("/")[0] for k in data.files})
+    assert names == ["w256", "w4096", "w768"]
+    for name in names:
+        rows, want = data[name + "/rows"], data[name + "/scale_bits"]
+        got = ob.orc().choose_mse_weight_scale(rows).view(np.uint32)
+        assert np.array_equal(got, want), name
+        assert got[1] == np.float32(1.0e-30).view(np.uint32)  # the all-zero channel
+
+
+@pytest.mark.skipif(not ob.packer_probe_available(), reason="reference packer probe (oracle/_ref) not present")
+def test_mse_scale_search_equals_the_reference_packer_live():
+    """The same comparison on fresh seeded rows, against the probe built from the reference tool's
+    source, and through the whole weight-row entry: rotate a bf16 weight with the pinned quantiser's
+    transform (F32 variant, whose codes expose the rotated row), search the scale with the reference
+    function, and find that scale in orc_quantize_weight_rows(mse=True)."""
+    rng = np.random.default_rng(23)
+    rows = (rng.standard_normal((64, 1024)) * rng.uniform(0.001, 10.0, (64, 1)).astype(np.float32)).astype(np.float32)
+    rows[::7, 3] *= 40.0
+    got = ob.orc().choose_mse_weight_scale(rows).view(np.uint32)
+    want = ob.packer_mse_scales(rows).view(np.uint32)
+    assert np.array_equal(got, want)
+    # the choice matters: for rows with an outlier the search leaves the absmax scale
+    absmax = np.abs(rows).max(axis=1) / np.float32(127.0)
+    assert (ob.orc().choose_mse_weight_scale(rows)[::7] < absmax[::7] * 0.99).any()
+
+
 @pytest.mark.skipif(not ob.ref_available(), reason="reference build (oracle/_ref) not present")
 def test_reference_block_amplifies_a_small_attention_difference():
     """Why a whole W8A8 block is not compared at the 2e-3 bar against an executor whose attention
