@@ -10,7 +10,7 @@ DiffIR program through the backend plugin C-ABI. One step = one pass over the bl
 the tokens are sharded over the N GPUs (strong scaling: the total work is fixed): every rank runs
 the same program on its slice through its own plugin context, and the plugin exchanges the INT8
 key codes, their scales and the bf16 values inside the library (copy-engine pushes into peer-mapped
-buffers up to 4 ranks, NCCL above; `config.exchange` says which). The metric is
+buffers up to 4 ranks, NCCL above; the line's `exchange` key says which). The metric is
 tokens per second of the whole job.
 
 `value`: device time of the timed passes of execute() (inputs already in HBM), max over ranks.
@@ -681,16 +681,16 @@ EXCHANGE_TEXT = {
     "nccl": "K codes / K scales / V exchanged over NCCL send / receive in ring steps"}
 
 
-def workload_config(world: int, exchange: str = "none"):
+def workload_config(world: int):
     v = VIDEO
     return {"workload": "video DiT block (benchmark configuration 4): %d tokens (21x30x52 latent + 512 text), hidden "
                         "%d, %d heads x %d, FFN %d SwiGLU, 3-axis RoPE over %d dims, W8A8 int8-convrot linears, INT8 "
                         "attention; one DiffIR program through the backend plugin"
                         % (v["tokens"], v["hidden"], v["heads"], v["dim"], v["ffn"], v["rotary"]),
             "tokens": v["tokens"],
-            "parallelism": "tokens sharded over %d GPU(s), weights replicated; %s; attention starts on the local "
-                           "slice" % (world, EXCHANGE_TEXT[exchange]),
-            "exchange": exchange,
+            "parallelism": "tokens sharded over %d GPU(s), weights replicated; K codes / K scales / V exchanged "
+                           "between the ranks inside the library (the line's `exchange` key says how); attention "
+                           "starts on the local slice" % world,
             "quantization": "H256ConvRot activations + per-channel INT8 weights; Q and K per token-head INT8, V bf16",
             "l2": "one pass streams ~6 GB of activations and weights per GPU at N=1 (0.9 GB at N=8), larger than the "
                   "126 MB L2; no flush"}
@@ -782,7 +782,6 @@ def main():
     block = run_video_block(torch, dist, args, rank, local_rank, world, device, barrier, reduce_max)
     ops.poll_status()
     S, ms = block["S"], block["ms_per_step"]
-    config = workload_config(max(world, 1), block["exchange"])
     line = None
     if rank == 0:
         prof = block["profile"]
@@ -823,6 +822,7 @@ def main():
                             "on the device (the exchange between the ranks inside the library), the output slice back to pinned host "
                             "memory; bytes are per rank"},
             "gpu_launches": block["launches"],
+            "exchange": {"kind": block["exchange"], "how": EXCHANGE_TEXT[block["exchange"]]},
             "roofline": roofline,
             "step_breakdown_ms": {"attention": attn_ms, "w8a8_gemms": gemm_ms, "convrot_quantisers": quant_ms,
                                   "gemm_tops": (gemm_ops / (gemm_ms * 1e-3) / 1e12) if gemm_ms else None,
