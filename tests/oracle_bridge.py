@@ -334,6 +334,23 @@ def packer_mse_scales(rows_f32: np.ndarray) -> np.ndarray:
     return np.array([int(h, 16) for h in out], np.uint32).view(np.float32)
 
 
+def packer_pack(weight_bf16: np.ndarray, implementation: int, equalise: bool, mse: bool, directory: str) -> str:
+    """The reference packer (rewrite_named_linear_w8a8 of tools/difflux2sample.cpp, through
+    oracle/_ref/difpacker_scale) on one bf16 weight matrix; returns the path of the cache file it wrote."""
+    import subprocess
+    weight_bf16 = np.ascontiguousarray(weight_bf16, dtype=np.uint16)
+    source = os.path.join(directory, "weight.bf16")
+    cache = os.path.join(directory, "cache")
+    os.makedirs(cache, exist_ok=True)
+    weight_bf16.tofile(source)
+    out = subprocess.run([PACKER_PROBE, "pack", source, str(weight_bf16.shape[0]), str(weight_bf16.shape[1]),
+                          str(int(implementation)), "1" if equalise else "0", "1" if mse else "0", cache],
+                         check=True, capture_output=True, text=True).stdout.split()
+    files = [f for f in out if f.endswith(".safetensors")]
+    assert len(files) == 1, out
+    return files[0]
+
+
 def ref_available() -> bool:
     return os.path.exists(REF_PATH)
 

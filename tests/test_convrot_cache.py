@@ -201,3 +201,44 @@ def test_cache_built_on_the_gpu_matches_the_cpu_packer_and_binds_as_plugin_const
     prepared.close()
     ex.close()
     assert np.array_equal(got[cur], want[cur])
+
+
+needs_packer = pytest.mark.skipif(not ob.packer_probe_available(),
+                                  reason="reference packer probe (oracle/_ref/difpacker_scale) not present")
+
+
+@needs_packer
+@pytest.mark.parametrize("impl,N,K", [(1, 40, 384), (2, 40, 768), (3, 40, 768), (5, 24, 512), (6, 24, 512),
+                                      (4, 8, 4096), (7, 8, 4096)])
+@pytest.mark.parametrize("equalise,mse", [(False, False), (True, False), (False, True), (True, True)])
+def test_reference_packer_output_equals_the_restatement_and_loads_here(tmp_path, impl, N, K, equalise, mse):
+    """The reference's OWN offline W8A8 packer (rewrite_named_linear_w8a8 of tools/difflux2sample.cpp,
+    run on a one-Linear program through oracle/_ref/difpacker_scale) writes its cache file for a seeded
+    bf16 weight; this library's reader loads that file, and the restatements the GPU weight quantiser
+    is tested against -- orc_weight_equalization, orc_quantize_weight_rows with and without the MSE
+    scale search -- reproduce its three tensors bit for bit, for every QuantizeInt8Rows variant."""
+    rng = np.random.default_rng(1000 * impl + 2 * int(equalise) + int(mse))
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    w[:, rng.integers(0, K, 6)] *= 12.0   # a few loud input channels: what equalisation is for
+    w[2] = 0.0                            # an all-zero output channel
+    w[3, 7] = 1.5                         # one outlier in a row: what the MSE search is for
+    w = ob.f32_to_bf16(w)
+    path = ob.packer_pack(w, impl, equalise, mse, str(tmp_path))
+    assert ("weight-equalized" in path) == equalise and ("mse-weight-scale" in path) == mse
+    with convrot_cache.Cache(path) as cache:
+        dt_w, codes = cache.tensor("weight")
+        dt_s, scales = cache.tensor("scale")
+        assert dt_w == int(diffir.DType.I8) and dt_s == int(diffir.DType.F32)
+        assert codes.shape == (N, K) and scales.shape == (N,)
+        eq = None
+        if equalise:
+            dt_e, eq = cache.tensor("input_scale")
+            assert dt_e == int(diffir.DType.BF16) and eq.shape == (K,)
+    if equalise:
+        want_eq = ob.orc().weight_equalization(w)
+        assert np.array_equal(eq.view(np.uint16).ravel(), want_eq.view(np.uint16).ravel())
+    if impl == 1:
+        return  # Direct weights are not a ConvRot variant of orc_quantize_weight_rows; the file loaded, the vector matched
+    want_codes, want_scales = ob.orc().quantize_weight_rows(w, impl, mse=mse, equalise=eq if equalise else None)
+    assert np.array_equal(scales.view(np.uint32), want_scales.view(np.uint32))
+    assert np.array_equal(codes.view(np.int8), want_codes)

@@ -190,3 +190,29 @@ def test_w8a8_linear_single_call_matches_two_calls(ops):
     torch.cuda.synchronize()
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     ops.poll_status()
+
+
+def test_weight_rows_equal_the_reference_packers_own_files(ops):
+    """The GPU weight quantiser against whole runs of the reference's own offline packer
+    (rewrite_named_linear_w8a8 of reference tools/difflux2sample.cpp; its cache tensors are the
+    committed fixture tests/golden/packer_mse_scale.npz): given the packer's input-equalisation
+    vector, the codes and scales are the packer's, bit for bit, with and without the MSE search."""
+    import os
+    import torch
+    data = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "packer_mse_scale.npz"))
+    keys = sorted({k.split("/")[0] for k in data.files if k.startswith("pack_")})
+    assert len(keys) == 6
+    for key in keys:
+        impl = int(key.split("_")[1][4:])
+        equalise, mse = key.split("_")[2] == "eq1", key.split("_")[3] == "mse1"
+        w = np.ascontiguousarray(data[key + "/weight"])
+        dw = torch.from_numpy(w.view(np.int16)).cuda().view(torch.bfloat16)
+        deq = None
+        if equalise:
+            eq = np.ascontiguousarray(data[key + "/input_scale"]).reshape(-1)
+            deq = torch.from_numpy(eq.view(np.int16)).cuda().view(torch.bfloat16)
+        codes, scales = ops.quantize_weight_rows(dw, impl, mse_scale=mse, input_scale=deq)
+        torch.cuda.synchronize()
+        assert np.array_equal(scales.cpu().numpy().view(np.uint32), data[key + "/scale_bits"]), key
+        assert np.array_equal(codes.cpu().numpy(), data[key + "/codes"]), key
+    ops.poll_status()

@@ -151,13 +151,33 @@ def test_mse_scale_search_equals_the_reference_packer_fixture():
     same rows (tests/golden/packer_mse_scale.npz, made by tests/golden/make_packer_golden.py from the
     reference tool's source): bit-identical, edge rows included (all zero, one outlier, 1e-20, 1e20)."""
     data = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "packer_mse_scale.npz"))
-    names = sorted({k.split("/")[0] for k in data.files})
+    names = sorted({k.split("/")[0] for k in data.files if k.startswith("w")})
     assert names == ["w256", "w4096", "w768"]
     for name in names:
         rows, want = data[name + "/rows"], data[name + "/scale_bits"]
         got = ob.orc().choose_mse_weight_scale(rows).view(np.uint32)
         assert np.array_equal(got, want), name
         assert got[1] == np.float32(1.0e-30).view(np.uint32)  # the all-zero channel
+
+
+def test_weight_packing_equals_the_reference_packer_fixture():
+    """orc_weight_equalization and orc_quantize_weight_rows against whole runs of the reference's own
+    packer (rewrite_named_linear_w8a8; the cache tensors are in tests/golden/packer_mse_scale.npz):
+    the input-equalisation vector, the scales and the codes, bit for bit, six variant / option mixes."""
+    data = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "packer_mse_scale.npz"))
+    keys = sorted({k.split("/")[0] for k in data.files if k.startswith("pack_")})
+    assert len(keys) == 6
+    for key in keys:
+        impl = int(key.split("_")[1][4:])
+        equalise, mse = key.split("_")[2] == "eq1", key.split("_")[3] == "mse1"
+        w = data[key + "/weight"]
+        eq = None
+        if equalise:
+            eq = ob.orc().weight_equalization(w)
+            assert np.array_equal(eq.view(np.uint16).ravel(), data[key + "/input_scale"].ravel()), key
+        codes, scales = ob.orc().quantize_weight_rows(w, impl, mse=mse, equalise=eq)
+        assert np.array_equal(scales.view(np.uint32), data[key + "/scale_bits"]), key
+        assert np.array_equal(codes, data[key + "/codes"]), key
 
 
 @pytest.mark.skipif(not ob.packer_probe_available(), reason="reference packer probe (oracle/_ref) not present")
