@@ -5,14 +5,13 @@
  *
  * Parity status: PINNED. Every function that restates a reference function is checked
  * bit-for-bit against the reference's own CPU executor (built from the reference sources
- * by the Makefile in this directory) through the committed fixtures under tests/golden/.
- * Two exceptions, both UNPINNED. orc_attention_int8: the reference has no CPU form of INT8
- * attention, so that function defines this repository's own numerical contract; its Q/K
- * codes and scales are the reference's (QuantizeInt8Rows, Direct) and it is additionally
- * compared, with a tolerance, against the reference's exact Attention. And
- * orc_weight_equalization: it restates a passage in the middle of a function of the reference's
- * command-line packer that cannot be called on its own. (The MSE scale search of the same tool
- * IS pinned: the Makefile builds a probe that includes the tool's source and calls its function.)
+ * by the Makefile in this directory) through the committed fixtures under tests/golden/; the
+ * weight packer's functions (equalisation vector, MSE scale search, row encoder) against runs of
+ * the reference's own packer, which the Makefile builds as a probe from the tool's source.
+ * One exception, UNPINNED: orc_attention_int8. The reference has no CPU form of INT8 attention,
+ * so that function defines this repository's own numerical contract; its Q/K codes and scales
+ * are the reference's (QuantizeInt8Rows, Direct) and it is additionally compared, with a
+ * tolerance, against the reference's exact Attention.
  *
  * Each function cites the reference file:line it follows (paths inside the reference
  * project). Build flags: -O3 without -march, so x86-64 never contracts a*b+c into an fma
@@ -298,7 +297,8 @@ ORC_EXPORT int orc_quantize_int8_rows(const uint16_t *const *parts,
 
 /* Input equalisation of the offline packer, tools/difflux2sample.cpp:2967-2990: per column the
  * absmax over the rows, their geometric mean as the centre, sqrt(max / centre) clamped to
- * [0.5, 2] and stored as bf16. UNPINNED: the passage cannot be called on its own. */
+ * [0.5, 2] and stored as bf16. Pinned through whole runs of the reference packer (its cache
+ * file's input_scale tensor). */
 ORC_EXPORT void orc_weight_equalization(const uint16_t *weight, uint64_t rows,
                                         uint64_t columns, uint16_t *out) {
   float *maxima = (float *)calloc((size_t)columns, sizeof(float));
