@@ -96,6 +96,8 @@ def lib() -> C.CDLL:
         L.difb200_executable_profile.restype = C.c_int
         L.difb200_executable_profile.argtypes = [vp, C.POINTER(u32), C.POINTER(C.c_double), C.POINTER(u64), u32,
                                                  C.POINTER(u32)]
+        L.difb200_program_check.restype = C.c_int
+        L.difb200_program_check.argtypes = [C.c_char_p, u64]
         L.difb200_executable_exchange.restype = C.c_int
         L.difb200_executable_exchange.argtypes = [vp]
         L.difb200_attention_scratch_bytes.restype = u64

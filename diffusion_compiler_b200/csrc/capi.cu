@@ -5,6 +5,7 @@
 #include "glue.h"
 #include "ops.h"
 #include "world.h"
+#include "diffir.h"
 
 #include <string>
 #include <thread>
@@ -93,6 +94,13 @@ int difb200_poll_status(void) {
 void difb200_set_wait_limit_ns(uint64_t nanoseconds) { set_wait_limit_ns(nanoseconds); }
 
 void difb200_test_withhold_gemm_load(uint32_t k_block) { withhold_next_gemm_load(k_block); }
+
+int difb200_program_check(const uint8_t *diffir, uint64_t size) {
+  ir::Program program;
+  std::string text;
+  const int rc = ir::decode(diffir, (size_t)size, program, text);
+  return rc ? fail(rc, "DiffIR: " + text) : kOk;
+}
 
 int difb200_selftest_host(void) {
   // per_device_once: one initialisation per (key, device ordinal), failures are not cached

@@ -281,9 +281,45 @@ void need(const Op &op, bool cond, const char *text) {
     bad(op, text);
 }
 
+// Attribute reads of the verifier: an attribute that is present must have the kind it is read as
+// (reference src/ir/codec.cpp:104-127, the accessors every rule below goes through).
+struct AttrReader {
+  const Op &op;
+  const Attr *kind(uint32_t key, uint32_t want, const char *name) const {
+    const Attr *a = op.find(key);
+    if (a && a->kind != want)
+      bad(op, std::string("attribute ") + std::to_string(key) + " must be " + name);
+    return a;
+  }
+  uint64_t u64(uint32_t key, uint64_t fallback) const {
+    const Attr *a = kind(key, 1, "u64");
+    return a ? a->bits : fallback;
+  }
+  double f64(uint32_t key, double fallback) const {
+    const Attr *a = kind(key, 3, "f64");
+    if (!a)
+      return fallback;
+    double v;
+    std::memcpy(&v, &a->bits, 8);
+    return v;
+  }
+  bool boolean(uint32_t key, bool fallback) const {
+    const Attr *a = kind(key, 4, "bool");
+    return a ? a->bits != 0 : fallback;
+  }
+  bool has(uint32_t key) const { return op.find(key) != nullptr; }
+};
+
+bool power_of_two_in(uint64_t v, uint64_t low, uint64_t high) { return v >= low && v <= high && (v & (v - 1)) == 0; }
+
+// Shape, dtype and attribute rules per operator, restated from the reference verifier (reference
+// src/ir/verify.cpp:89-1338, the cases of the operators this backend runs): what it rejects is
+// rejected here with status 1. A form it admits but this backend cannot run is status 2, given
+// here or by the planner.
 void verify_op(const Program &p, const Op &op) {
   auto in = [&](size_t i) -> const Tensor & { return T(p, op, op.in.at(i)); };
   auto out = [&](size_t i) -> const Tensor & { return T(p, op, op.out.at(i)); };
+  const AttrReader attr{op};
   switch (op.opcode) {
   case Add:
   case Multiply:
@@ -296,7 +332,8 @@ void verify_op(const Program &p, const Op &op) {
     counts(op, 1, 1);
     same(op, in(0), out(0));
     need(op, in(0).is_float(), "needs f32/bf16/f16");
-    const uint64_t a = op.u64(Approximation, 0);
+    need(op, attr.has(Approximation), "needs an explicit Approximation (1 = tanh, 2 = erf)");
+    const uint64_t a = attr.u64(Approximation, 0);
     need(op, a == 1 || a == 2, "needs an explicit Approximation (1 = tanh, 2 = erf)");
     return;
   }
@@ -322,20 +359,35 @@ void verify_op(const Program &p, const Op &op) {
     if (op.in.size() == 3)
       need(op, in(2).dtype == in(0).dtype && in(2).dims == in(1).dims, "bias must match the scale");
     return;
-  case RmsNorm:
+  case RmsNorm: {
     counts(op, 2, 1);
     same(op, in(0), out(0));
     need(op, in(0).is_float() && in(1).dtype == in(0).dtype && in(1).dims.size() == 1 &&
                  in(1).dims[0] == in(0).last(),
          "weight must be [last dim]");
+    need(op, attr.f64(Epsilon, 1.0e-5) > 0.0, "Epsilon must be positive");
+    (void)attr.f64(WeightOffset, 0.0); // finite like every f64 attribute
+    const uint64_t block = attr.u64(BlockSize, 256);
+    need(op, power_of_two_in(block, 32, 1024), "BlockSize must be a power of two in [32,1024]");
+    const uint64_t impl = attr.u64(Implementation, 1);
+    need(op, impl == 1 || impl == 2, "Implementation must be 1 or 2");
+    if (impl == 2)
+      need(op, in(0).dtype == BF16 && in(0).last() == 128 && block == 128,
+           "Implementation 2 needs bf16, width 128 and BlockSize 128");
+    const uint64_t tile = attr.u64(ReductionTileSize, 0);
+    need(op, tile == 0 || tile == 2048 || tile == 8192, "ReductionTileSize must be 0, 2048 or 8192");
+    if (tile != 0)
+      need(op, block == 512 && in(0).last() == 6144, "a reduction tile needs BlockSize 512 and width 6144");
     return;
+  }
   case Fill:
     counts(op, 0, 1);
     need(op, out(0).is_float(), "needs a float output");
     return;
   case Cast:
     counts(op, 1, 1);
-    need(op, in(0).is_float() && out(0).is_float() && in(0).dims == out(0).dims, "needs equal-shaped float tensors");
+    need(op, in(0).is_float() && out(0).is_float() && in(0).dtype != out(0).dtype && in(0).dims == out(0).dims,
+         "needs equal-shaped tensors of two different float dtypes");
     return;
   case Reshape:
     counts(op, 1, 1);
@@ -354,27 +406,34 @@ void verify_op(const Program &p, const Op &op) {
   case Slice: {
     counts(op, 1, 1);
     const Tensor &a = in(0), &o = out(0);
-    const uint64_t axis = op.u64(Axis, 0), start = op.u64(Start, 0);
-    need(op, a.is_float() && a.dtype == o.dtype && a.dims.size() == o.dims.size() && axis < a.dims.size(),
-         "rank/dtype/axis mismatch");
+    need(op, a.is_float() && a.dtype == o.dtype && a.dims.size() == o.dims.size() && attr.has(Axis) && attr.has(Start),
+         "needs equal-rank float tensors and Axis / Start");
+    const uint64_t axis = attr.u64(Axis, 0), start = attr.u64(Start, 0);
+    need(op, axis < a.dims.size() && start <= a.dims[axis] && o.dims[axis] <= a.dims[axis] - start,
+         "axis or window is outside the input");
     for (size_t i = 0; i < a.dims.size(); ++i)
-      need(op, i == axis ? start + o.dims[i] <= a.dims[i] : o.dims[i] == a.dims[i], "window is outside the input");
+      need(op, i == axis || o.dims[i] == a.dims[i], "only the sliced axis may change");
     return;
   }
   case Concat: {
-    need(op, !op.in.empty() && op.out.size() == 1, "expects at least one input");
-    const Tensor &o = out(0);
-    const uint64_t axis = op.u64(Axis, 0);
-    need(op, axis < o.dims.size() && o.is_float(), "axis/dtype mismatch");
+    need(op, op.in.size() >= 2 && op.out.size() == 1, "expects at least two inputs and one output");
+    const Tensor &first = in(0), &o = out(0);
+    need(op, attr.has(Axis), "needs an Axis");
+    const uint64_t axis = attr.u64(Axis, 0);
+    need(op, axis < first.dims.size() && first.is_float() && o.dtype == first.dtype &&
+                 o.dims.size() == first.dims.size(),
+         "axis/dtype/rank mismatch");
     uint64_t total = 0;
     for (size_t k = 0; k < op.in.size(); ++k) {
       const Tensor &a = in(k);
-      need(op, a.dtype == o.dtype && a.dims.size() == o.dims.size(), "inputs must share rank and dtype");
+      need(op, a.dtype == first.dtype && a.dims.size() == first.dims.size(), "inputs must share rank and dtype");
       for (size_t i = 0; i < a.dims.size(); ++i)
-        need(op, i == axis || a.dims[i] == o.dims[i], "inputs must agree off the axis");
+        need(op, i == axis || a.dims[i] == first.dims[i], "inputs must agree off the axis");
+      need(op, total <= UINT64_MAX - a.dims[axis], "axis extent overflows");
       total += a.dims[axis];
     }
-    need(op, total == o.dims[axis], "axis extents do not add up");
+    for (size_t i = 0; i < first.dims.size(); ++i)
+      need(op, o.dims[i] == (i == axis ? total : first.dims[i]), "output shape is not the joined inputs");
     return;
   }
   case RotaryFrequency: {
@@ -388,6 +447,7 @@ void verify_op(const Program &p, const Op &op) {
       need(op, out(k).dtype == F32 && out(k).dims.size() == 3 && out(k).dims[0] == pos.dims[0] &&
                    out(k).dims[1] == pos.dims[1] && out(k).dims[2] == axes.dims[0],
            "tables must be F32 [B,L,P]");
+    need(op, attr.f64(Theta, 10000.0) > 0.0 && attr.f64(Ntk, 1.0) > 0.0, "Theta and Ntk must be positive");
     return;
   }
   case RotaryApply: {
@@ -395,19 +455,20 @@ void verify_op(const Program &p, const Op &op) {
     const Tensor &x = in(0), &c = in(1), &s = in(2);
     same(op, x, out(0));
     need(op, x.is_float() && x.dims.size() == 4 && c.dtype == F32 && c.dims.size() == 3 && s.dims == c.dims &&
-                 s.dtype == F32 && c.dims[0] == x.dims[0] && c.dims[1] == x.dims[1] && 2 * c.dims[2] <= x.dims[3],
+                 s.dtype == F32 && c.dims[0] == x.dims[0] && c.dims[1] == x.dims[1] && c.dims[2] <= x.dims[3] / 2,
          "input [B,S,H,D] with F32 [B,S,P] tables expected");
-    need(op, op.u64(RotaryLayout, 1) == 1, "only the interleaved layout exists for this op");
+    need(op, attr.u64(RotaryLayout, 0) == 1, "needs an explicit interleaved RotaryLayout");
     return;
   }
   case BooleanMaskToBias: {
     counts(op, 1, 1);
     const Tensor &m = in(0), &o = out(0);
     need(op, m.dtype == Bool && o.is_float() && o.dims.size() == 4 && o.dims[1] == 1 && o.dims[2] == o.dims[3] &&
-                 o.dims[0] == m.dims[0] &&
+                 (m.dims.size() == 2 || m.dims.size() == 3) && o.dims[0] == m.dims[0] &&
                  ((m.dims.size() == 2 && m.dims[1] == o.dims[2]) ||
                   (m.dims.size() == 3 && m.dims[1] == o.dims[2] && m.dims[2] == o.dims[2])),
          "Bool [B,L] or [B,L,L] -> float [B,1,L,L] expected");
+    (void)attr.boolean(MaskQueries, true);
     return;
   }
   case QkNormPartialRope: {
@@ -415,39 +476,58 @@ void verify_op(const Program &p, const Op &op) {
     const Tensor &x = in(0), &w = in(1), &c = in(2), &s = in(3);
     same(op, x, out(0));
     need(op, x.is_float() && (x.dims.size() == 3 || x.dims.size() == 4), "input [S,H,D] or [B,S,H,D] expected");
-    const uint64_t D = x.last(), rotary = op.u64(RotaryDim, D);
-    need(op, w.dims.size() == 1 && w.dims[0] == D && w.dtype == x.dtype, "weight must be [D]");
-    need(op, c.dims == s.dims && c.dtype == s.dtype && (c.dtype == x.dtype || c.dtype == F32) &&
-                 (c.dims.size() == 2 || c.dims.size() == 3),
-         "cos/sin tables must match each other");
-    need(op, rotary <= D && rotary % 2 == 0 && (c.last() == rotary || c.last() == rotary / 2),
-         "table width must be the rotary dimension or its half");
-    const uint64_t in_seq = x.dims.size() == 4 ? x.dims[1] : x.dims[0];
-    const uint64_t tab_seq = c.dims.size() == 3 ? c.dims[1] : c.dims[0];
-    need(op, op.u64(Start, 0) + in_seq <= tab_seq, "table window is outside the tables");
-    if (c.dims.size() == 3)
-      need(op, x.dims.size() == 4 && c.dims[0] == x.dims[0], "batched tables need a batched input");
+    const bool table_rank_fits = x.dims.size() == 4 ? c.dims.size() == 3
+                                                    : (c.dims.size() == 2 || (c.dims.size() == 3 && c.dims[0] == 1));
+    need(op, w.dtype == x.dtype && w.dims.size() == 1 && (c.dtype == x.dtype || c.dtype == F32) &&
+                 s.dtype == c.dtype && c.dims == s.dims && table_rank_fits,
+         "weight [D] and matching cos/sin tables expected");
+    const size_t head_axis = x.dims.size() - 2;
+    const uint64_t D = x.last(), width = c.last();
+    const uint64_t heads = attr.u64(Heads, x.dims[head_axis]), head_dim = attr.u64(HeadDim, D);
+    need(op, width <= UINT64_MAX / 2, "table width overflows");
+    const uint64_t rotary = attr.u64(RotaryDim, width * 2);
+    const uint64_t in_batch = x.dims.size() == 4 ? x.dims[0] : 1, in_seq = x.dims.size() == 4 ? x.dims[1] : x.dims[0];
+    const uint64_t tab_batch = c.dims.size() == 3 ? c.dims[0] : 1, tab_seq = c.dims.size() == 3 ? c.dims[1] : c.dims[0];
+    const uint64_t start = attr.u64(Start, 0);
+    need(op, heads == x.dims[head_axis] && head_dim == D && w.dims[0] == D && tab_batch == in_batch &&
+                 start <= tab_seq && in_seq <= tab_seq - start && rotary != 0 && rotary <= D && rotary % 2 == 0 &&
+                 (width == rotary || width * 2 == rotary),
+         "Heads / HeadDim / RotaryDim / Start do not fit the shapes");
+    need(op, power_of_two_in(attr.u64(BlockSize, 256), 32, 1024), "BlockSize must be a power of two in [32,1024]");
     return;
   }
   case RmsNormModulate: {
-    const uint64_t layout = op.u64(ModulationLayout, 1);
-    need(op, op.out.size() == 1 && in(0).dims.size() == 2 && in(0).is_float(), "rank-2 float input expected");
-    same(op, in(0), out(0));
-    const uint64_t cols = in(0).dims[1];
+    need(op, (op.in.size() == 3 || op.in.size() == 4) && op.out.size() == 1, "expects x, [weight], scale, shift");
+    const Tensor &x = in(0);
+    const uint64_t layout = attr.u64(ModulationLayout, 1);
     if (layout == 2) {
       counts(op, 4, 1);
-      need(op, in(1).dims.size() == 1 && in(1).dims[0] == cols && in(2).dims.size() == 2 &&
-                   in(2).dims[1] == cols && in(2).dims[0] > 0 && in(0).dims[0] % in(2).dims[0] == 0 &&
-                   in(3).dims.size() == 2 && in(3).dims[0] == 2 && in(3).dims[1] == cols,
+      same(op, x, out(0));
+      need(op, x.is_float() && x.dims.size() == 2, "rank-2 float input expected");
+      const uint64_t cols = x.dims[1];
+      need(op, in(1).dtype == x.dtype && in(1).dims.size() == 1 && in(1).dims[0] == cols &&
+                   in(2).dtype == x.dtype && in(2).dims.size() == 2 && in(2).dims[1] == cols && in(2).dims[0] > 0 &&
+                   x.dims[0] % in(2).dims[0] == 0 && in(3).dtype == x.dtype && in(3).dims.size() == 2 &&
+                   in(3).dims[0] == 2 && in(3).dims[1] == cols,
            "weight [H], vector [V,H], delta [2,H] expected");
-    } else {
-      need(op, op.in.size() == 3 || op.in.size() == 4, "expects x, [weight], scale, shift");
-      const bool weighted = op.in.size() == 4;
-      if (weighted)
-        need(op, in(1).dims.size() == 1 && in(1).dims[0] == cols, "weight must be [H]");
-      same(op, in(0), in(weighted ? 2 : 1));
-      same(op, in(0), in(weighted ? 3 : 2));
+      need(op, attr.f64(Epsilon, 1.0e-5) > 0.0, "Epsilon must be positive");
+      (void)attr.f64(WeightOffset, 0.0);
+      const uint64_t block = attr.u64(BlockSize, 256), tile = attr.u64(ReductionTileSize, 0);
+      need(op, power_of_two_in(block, 32, 1024) && (tile == 0 || tile == 2048 || tile == 8192) &&
+                   (tile == 0 || (block == 512 && cols == 6144)),
+           "BlockSize / ReductionTileSize do not fit");
+      return;
     }
+    need(op, layout == 1, "unknown ModulationLayout");
+    const bool weighted = op.in.size() == 4;
+    same(op, x, in(weighted ? 2 : 1));
+    same(op, x, in(weighted ? 3 : 2));
+    same(op, x, out(0));
+    need(op, x.is_float() && x.dims.size() == 2, "rank-2 float input expected");
+    if (weighted)
+      need(op, in(1).dtype == x.dtype && in(1).dims.size() == 1 && in(1).dims[0] == x.dims[1], "weight must be [H]");
+    need(op, attr.f64(Epsilon, 1.0e-5) > 0.0, "Epsilon must be positive");
+    need(op, power_of_two_in(attr.u64(BlockSize, 256), 32, 1024), "BlockSize must be a power of two in [32,1024]");
     return;
   }
   case LayerNormModulate: {
@@ -459,6 +539,8 @@ void verify_op(const Program &p, const Op &op) {
                  in(1).dtype == x.dtype && in(2).dtype == x.dtype && in(3).dtype == x.dtype && in(4).dtype == x.dtype,
          "[hidden] weight/bias and compatible scale/shift rows expected");
     need(op, in(3).rows() > 0 && x.rows() % in(3).rows() == 0, "scale/shift rows must divide the input rows");
+    need(op, power_of_two_in(attr.u64(BlockSize, 256), 32, 1024) && attr.f64(Epsilon, 1.0e-5) > 0.0,
+         "BlockSize must be a power of two in [32,1024] and Epsilon positive");
     return;
   }
   case ResidualGate: {
@@ -476,7 +558,10 @@ void verify_op(const Program &p, const Op &op) {
     need(op, x.is_float() && o.dtype == x.dtype && x.dims.size() == o.dims.size(), "compatible float tensors expected");
     for (size_t i = 0; i + 1 < x.dims.size(); ++i)
       need(op, x.dims[i] == o.dims[i], "prefix dimensions must match");
-    need(op, op.u64(Start, 0) + 2 * o.last() <= x.last(), "packed window is outside the input");
+    const uint64_t start = attr.u64(Start, 0);
+    need(op, o.last() <= (UINT64_MAX - start) / 2 && start + 2 * o.last() <= x.last(),
+         "packed window is outside the input");
+    (void)attr.boolean(GateFirst, false);
     return;
   }
   case Linear: {
@@ -484,40 +569,49 @@ void verify_op(const Program &p, const Op &op) {
     const Tensor &x = in(0), &w = in(1), &o = out(0);
     need(op, x.is_float() && w.dtype == x.dtype && o.dtype == x.dtype && w.dims.size() == 2, "uniform float dtype, rank-2 weight");
     const uint64_t rows = x.dims[0];
-    need(op, rows > 0 && x.elements() / rows == w.dims[1] && o.dims[0] == rows && o.elements() / rows == w.dims[0],
+    need(op, x.elements() / rows == w.dims[1] && o.dims[0] == rows && o.elements() / o.dims[0] == w.dims[0],
          "shapes must flatten as [M,K] x [N,K] -> [M,N]");
     if (op.in.size() == 3)
       need(op, in(2).dtype == x.dtype && in(2).dims.size() == 1 && in(2).dims[0] == w.dims[0], "bias must be [N]");
+    const uint64_t bias_mode = attr.u64(LinearBiasMode, 1);
+    need(op, bias_mode == 1 || (bias_mode == 2 && op.in.size() == 3), "LinearBiasMode must be 1, or 2 with a bias");
+    if (attr.has(WorkspaceLimitBytes))
+      need(op, attr.u64(WorkspaceLimitBytes, 0) != 0, "WorkspaceLimitBytes must be positive");
+    const uint64_t impl = attr.u64(Implementation, 1);
+    need(op, impl >= 1 && impl <= 3 && (impl != 2 || x.dtype == F32), "Implementation must be 1..3 (2 needs f32)");
     return;
   }
   case QuantizeInt8Rows: {
     need(op, !op.in.empty() && (op.out.size() == 2 || op.out.size() == 4), "expects BF16 inputs and 2 or 4 outputs");
     const bool dynamic = in(op.in.size() - 1).dtype == F32;
     const size_t n_data = op.in.size() - (dynamic ? 1 : 0);
-    need(op, n_data >= 1 && n_data <= 8, "1..8 data inputs are supported");
+    need(op, n_data >= 1, "needs at least one data input in front of the clip");
     if (dynamic)
       need(op, in(op.in.size() - 1).dims == std::vector<uint64_t>{1}, "dynamic clip must be F32[1]");
     const uint64_t rows = in(0).rows();
     uint64_t width = 0;
     for (size_t k = 0; k < n_data; ++k) {
       need(op, in(k).dtype == BF16 && in(k).rows() == rows, "data inputs must be BF16 with equal row counts");
+      need(op, width <= UINT64_MAX - in(k).last(), "combined width overflows");
       width += in(k).last();
     }
-    need(op, out(0).dtype == I8 && out(0).last() == width && out(0).rows() == rows && out(1).dtype == F32 &&
-                 out(1).dims == std::vector<uint64_t>{rows},
+    need(op, out(0).dtype == I8 && out(0).last() == width && out(0).elements() / width == rows &&
+                 out(1).dtype == F32 && out(1).dims == std::vector<uint64_t>{rows},
          "outputs must be I8 [.., width] and F32 [rows]");
     if (op.out.size() == 4)
       need(op, out(2).dtype == I8 && out(2).dims == out(0).dims && out(3).dtype == F32 && out(3).dims == out(1).dims,
            "residual outputs must mirror the primary ones");
-    need(op, op.u64(BlockSize, 256) == 256, "BlockSize must be 256");
-    const double clip = op.f64(Scale, 1.0);
+    need(op, attr.u64(BlockSize, 256) == 256, "BlockSize must be 256");
+    const double clip = attr.f64(Scale, 1.0);
     need(op, clip > 0.0 && clip <= 1.0, "Scale must be in (0,1]");
-    const uint64_t impl = op.u64(Implementation, 1);
+    const uint64_t impl = attr.u64(Implementation, 1);
     need(op, impl >= 1 && impl <= 7, "unknown Implementation");
     if (impl == 4 || impl == 7)
       need(op, width % 4096 == 0, "H4096 variants need a width divisible by 4096");
     else if (impl != 1)
       need(op, width % 256 == 0, "H256 variants need a width divisible by 256");
+    if (n_data > 8)
+      bad(op, "more than 8 concatenated data inputs are not implemented", 2);
     return;
   }
   case LinearInt8Scaled: {
@@ -528,7 +622,8 @@ void verify_op(const Program &p, const Op &op) {
          "I8 input/weight, F32 scales, BF16 output expected");
     const uint64_t rows = x.rows();
     need(op, w.dims[1] == x.last() && rs.dims == std::vector<uint64_t>{rows} &&
-                 cs.dims == std::vector<uint64_t>{w.dims[0]} && o.elements() == rows * w.dims[0] && o.last() == w.dims[0],
+                 cs.dims == std::vector<uint64_t>{w.dims[0]} && w.dims[0] <= UINT64_MAX / rows &&
+                 o.elements() == rows * w.dims[0] && o.last() == w.dims[0],
          "shapes must flatten as [M,K] x [N,K] with row [M], column [N], BF16 [M,N]");
     need(op, w.has(Constant) && cs.has(Constant), "weight and column scales must be constants");
     return;
@@ -539,20 +634,37 @@ void verify_op(const Program &p, const Op &op) {
     same(op, k, v);
     same(op, q, out(0));
     need(op, q.is_float() && (q.dims.size() == 3 || q.dims.size() == 4), "float [S,H,D] or [B,S,H,D] expected");
-    const size_t ha = q.dims.size() - 2;
-    const uint64_t kv = op.u64(KvHeads, q.dims[ha]);
-    need(op, kv != 0 && q.dims[ha] % kv == 0, "KvHeads must divide the head count");
+    const size_t ha = q.dims.size() - 2, sa = q.dims.size() - 3;
+    const uint64_t H = q.dims[ha], S = q.dims[sa];
+    const uint64_t kv = attr.u64(KvHeads, H);
+    need(op, kv != 0 && H % kv == 0, "KvHeads must divide the head count");
     auto expect = q.dims;
     expect[ha] = kv;
     need(op, k.dtype == q.dtype && k.dims == expect, "k/v must carry KvHeads heads");
-    if (op.in.size() == 4) {
+    const bool biased = op.in.size() == 4, batched = q.dims.size() == 4;
+    if (biased) {
       const Tensor &b = in(3);
-      const uint64_t S = q.dims[q.dims.size() - 3];
-      need(op, q.dims.size() == 4 && b.dtype == q.dtype && b.dims == std::vector<uint64_t>{q.dims[0], 1, S, S},
+      need(op, batched && b.dtype == q.dtype && b.dims == std::vector<uint64_t>{q.dims[0], 1, S, S},
            "bias must be [B,1,S,S] in the query dtype");
     }
-    const uint64_t impl = op.u64(Implementation, 1);
+    const uint64_t impl = attr.u64(Implementation, 1);
     need(op, impl >= 1 && impl <= 5, "Implementation must be 1..5");
+    // what each implementation admits (reference src/ir/verify.cpp:1293-1320)
+    if (impl == 2)
+      need(op, q.dtype == BF16 || q.dtype == F16, "Implementation 2 needs bf16 or f16");
+    if (impl == 1)
+      need(op, !batched && !biased && S <= 4096, "Implementation 1 is unbatched, unbiased and S <= 4096");
+    const bool causal = (impl >= 3) ? attr.boolean(Causal, false) : false;
+    if (impl == 3)
+      need(op, q.dtype == F32 && !batched && H == 1 && kv == 1 && !biased && !causal,
+           "Implementation 3 is noncausal unbatched f32 [S,1,D] without bias");
+    if (impl == 4)
+      need(op, q.dtype == BF16 && q.last() == 128 && !biased && !causal,
+           "Implementation 4 is noncausal bf16 head dimension 128 without bias");
+    if (impl == 5)
+      need(op, q.dtype == BF16 && q.last() == 128 && kv == H && !biased && !causal,
+           "Implementation 5 is noncausal bf16 head dimension 128, full heads, no bias");
+    need(op, power_of_two_in(attr.u64(BlockSize, 64), 32, 256), "BlockSize must be a power of two in [32,256]");
     return;
   }
   default:
@@ -576,12 +688,19 @@ int verify(const Program &program, std::string &error) {
         throw Fail{1, "tensor rank must be 1..8"};
       if ((t.roles & ~63u) != 0 || (t.has(Streamed) && !t.has(Constant)))
         throw Fail{1, "invalid tensor role mask"};
+      // training roles (reference src/ir/verify.cpp:2073-2085): parameters and optimizer state are
+      // inputs or outputs and never constants
+      const bool trained = t.has(Parameter) || t.has(OptimizerState);
+      if (trained && ((!t.has(Input) && !t.has(Output)) || t.has(Constant)))
+        throw Fail{1, "a parameter or optimizer state must be an input or output and not a constant"};
       uint64_t n = 1;
       for (auto d : t.dims) {
-        if (d != 0 && n > (1ull << 46) / d)
-          throw Fail{1, "tensor is too large"};
+        if (d == 0 || n > UINT64_MAX / d)
+          throw Fail{1, "tensor has a zero dimension or its element count overflows"};
         n *= d;
       }
+      if (n > UINT64_MAX / dtype_size(t.dtype))
+        throw Fail{1, "tensor byte count overflows"};
     }
     std::set<uint32_t> available, written, op_ids;
     for (const auto &t : program.tensors)
@@ -620,7 +739,7 @@ int verify(const Program &program, std::string &error) {
         available.insert(id);
     }
     for (const auto &t : program.tensors)
-      if (t.has(Output) && !written.count(t.id))
+      if (t.has(Output) && !available.count(t.id))
         throw Fail{1, "output tensor " + std::to_string(t.id) + " is never produced"};
   } catch (const Fail &f) {
     error = f.text;

@@ -25,9 +25,10 @@ enum Opcode : uint32_t {
 };
 
 enum AttrKey : uint32_t {
-  Epsilon = 1, BlockSize = 2, RotaryDim = 5, AttentionScale = 6, Causal = 7, Implementation = 9,
-  GateFirst = 13, Value = 15, Scale = 18, KvHeads = 39, Approximation = 40, Axis = 41, Start = 42,
-  Theta = 43, Ntk = 44, WeightOffset = 45, RotaryLayout = 46, ModulationLayout = 57, MaskQueries = 73,
+  Epsilon = 1, BlockSize = 2, Heads = 3, HeadDim = 4, RotaryDim = 5, AttentionScale = 6, Causal = 7,
+  Implementation = 9, GateFirst = 13, Value = 15, Scale = 18, KvHeads = 39, Approximation = 40, Axis = 41,
+  Start = 42, Theta = 43, Ntk = 44, WeightOffset = 45, RotaryLayout = 46, LinearBiasMode = 55,
+  ReductionTileSize = 56, ModulationLayout = 57, WorkspaceLimitBytes = 58, MaskQueries = 73,
   kFirstAttr = 1, kLastAttr = 74,
 };
 

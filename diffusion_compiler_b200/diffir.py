@@ -103,7 +103,10 @@ class AttrKey(IntEnum):
     Ntk = 44
     WeightOffset = 45
     RotaryLayout = 46
+    LinearBiasMode = 55
+    ReductionTileSize = 56
     ModulationLayout = 57
+    WorkspaceLimitBytes = 58
     MaskQueries = 73
 
 

@@ -65,6 +65,16 @@ DIFB200_EXPORT void difb200_test_withhold_gemm_load(uint32_t k_block);
 DIFB200_EXPORT int difb200_selftest_host(void);
 
 /*
+ * Decodes and verifies DIFIR bytes on the host exactly as the plugin's compile does (container:
+ * magic, version, trailing SHA-256, counts; program rules: unique ids, operands defined before use,
+ * roles; per-operator shape and attribute rules of the operators this backend runs; reference
+ * src/ir/codec.cpp:370-476, src/ir/verify.cpp). 0 = compile would accept the program's form,
+ * 1 = malformed or invalid, 2 = well-formed but uses an operator or form this backend does not
+ * implement; text for difb200_last_error(). Needs no GPU.
+ */
+DIFB200_EXPORT int difb200_program_check(const uint8_t *diffir, uint64_t size);
+
+/*
  * Opcode QuantizeInt8Rows (67). Replaces the reference CPU op
  * src/runtime/cpu_executor.cpp:124-307 and its generated CUDA kernel
  * src/compiler/compiler.cpp:635-845 (semantics: include/dif/ir/ir.hpp:123-134,285-293;
