@@ -242,3 +242,51 @@ def test_reference_packer_output_equals_the_restatement_and_loads_here(tmp_path,
     want_codes, want_scales = ob.orc().quantize_weight_rows(w, impl, mse=mse, equalise=eq if equalise else None)
     assert np.array_equal(scales.view(np.uint32), want_scales.view(np.uint32))
     assert np.array_equal(codes.view(np.int8), want_codes)
+
+
+def test_mutated_cache_files_are_refused_or_read_never_crashed_on(tmp_path):
+    """Seeded mutations of a valid file (header bytes flipped, truncation, a wrong length word, junk
+    inserted into the JSON, tokens replaced, 2000 levels of nesting): the reader either opens the file
+    and serves or refuses each tensor, or refuses the file with an error -- it never faults."""
+    import random
+    import struct
+    from diffusion_compiler_b200 import _lib
+    rng = random.Random(5)
+    good = str(tmp_path / "good.safetensors")
+    convrot_cache.write(good, {"weight": (int(diffir.DType.I8), np.arange(64, dtype=np.int8).reshape(4, 16)),
+                               "scale": (int(diffir.DType.F32), np.ones(4, np.float32))})
+    raw = open(good, "rb").read()
+    opened = refused = 0
+    for _ in range(600):
+        b = bytearray(raw)
+        mode = rng.randrange(6)
+        if mode == 0:
+            for _ in range(rng.randrange(1, 6)):
+                b[rng.randrange(0, min(len(b), 208))] = rng.randrange(256)
+        elif mode == 1:
+            b = b[:rng.randrange(0, len(b))]
+        elif mode == 2:
+            b[0:8] = struct.pack("<Q", rng.choice([0, 1, 7, 2 ** 63, 2 ** 64 - 1, len(b), 2 * len(b), rng.randrange(2 ** 40)]))
+        elif mode == 3:
+            at = rng.randrange(8, min(len(b), 200))
+            b[at:at] = bytes(rng.randrange(256) for _ in range(rng.randrange(1, 40)))
+        elif mode == 4:
+            body = bytes(b[8:])
+            token = rng.choice([b'"data_offsets"', b'"shape"', b'"dtype"', b"[", b"]", b"{", b"}", b":", b",", b'"I8"'])
+            b = b[:8] + body.replace(token, rng.choice([b"", b'"x"', b"[[", b"-1", b"1e999", b"9" * 30, b"null", b'"\\']), 1)
+        else:
+            b = bytearray(struct.pack("<Q", 4000) + b"[" * 2000 + b"]" * 2000)
+        path = str(tmp_path / "mutated.safetensors")
+        with open(path, "wb") as f:
+            f.write(bytes(b))
+        try:
+            with convrot_cache.Cache(path) as cache:
+                for name in ("weight", "scale", "absent"):
+                    try:
+                        cache.tensor(name)
+                    except (_lib.Difb200Error, KeyError, ValueError):
+                        pass
+            opened += 1
+        except (_lib.Difb200Error, ValueError):
+            refused += 1
+    assert opened + refused == 600 and refused > 300
